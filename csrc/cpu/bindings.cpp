@@ -1,0 +1,407 @@
+// Python bindings of the CPU oracle (module sketchml_b200._oracle).
+#include <pybind11/numpy.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include "oracle.h"
+
+namespace py = pybind11;
+using namespace skml;
+
+typedef py::array_t<int32_t, py::array::c_style | py::array::forcecast> I32Array;
+typedef py::array_t<double, py::array::c_style | py::array::forcecast> F64Array;
+typedef py::array_t<float, py::array::c_style | py::array::forcecast> F32Array;
+typedef py::array_t<uint64_t, py::array::c_style | py::array::forcecast> U64Array;
+
+template <class T>
+static py::array_t<T> to_array(const std::vector<T>& v) {
+    py::array_t<T> a(v.size());
+    if (!v.empty()) std::memcpy(a.mutable_data(), v.data(), v.size() * sizeof(T));
+    return a;
+}
+
+static py::bytes to_bytes(const std::vector<uint8_t>& b) {
+    return py::bytes(reinterpret_cast<const char*>(b.data()), b.size());
+}
+
+static bool is_f32(const py::array& a) { return a.dtype().is(py::dtype::of<float>()); }
+
+static SketchOptions options_from(const py::dict& d) {
+    SketchOptions o;
+    auto geti = [&](const char* k, auto& dst) {
+        if (d.contains(k)) dst = d[k].cast<std::decay_t<decltype(dst)>>();
+    };
+    geti("bin_num", o.bin_num);
+    geti("group_num", o.group_num);
+    geti("row_num", o.row_num);
+    geti("col_ratio", o.col_ratio);
+    geti("key_encoder", o.key_encoder);
+    geti("cell_bits", o.cell_bits);
+    geti("sketch_k", o.sketch_k);
+    geti("seed", o.seed);
+    geti("step", o.step);
+    geti("rank", o.rank);
+    geti("world", o.world);
+    geti("offset_mode", o.offset_mode);
+    geti("tie_mode", o.tie_mode);
+    geti("java_compat_max", o.java_compat_max);
+    geti("restart", o.restart);
+    if (d.contains("loss_partials")) {
+        auto lp = d["loss_partials"].cast<std::vector<double>>();
+        for (size_t i = 0; i < lp.size() && i < 4; ++i) o.loss_partials[i] = lp[i];
+    }
+    return o;
+}
+
+template <class T>
+static py::dict quantizer_dict(const Quantizer<T>& q) {
+    py::dict r;
+    r["bin_num"] = q.bin_num;
+    r["zero_idx"] = q.zero_idx;
+    r["min"] = (double)q.min;
+    r["max"] = (double)q.max;
+    r["splits"] = to_array(q.splits);
+    r["bins"] = to_array(q.bins);
+    r["values"] = to_array(q.values());
+    return r;
+}
+
+static py::dict encoded_dict(const EncodedKeys& e) {
+    py::dict r;
+    r["size"] = e.size;
+    r["num_intervals"] = e.num_intervals;
+    r["flag_kind"] = e.flag_kind;
+    r["flag_words"] = to_array(e.flags.words);
+    r["delta_words"] = to_array(e.deltas.words);
+    r["flag_bits"] = e.flag_bits;
+    r["delta_bits"] = e.delta_bits;
+    return r;
+}
+
+static EncodedKeys encoded_from(const py::dict& d) {
+    EncodedKeys e;
+    e.size = d["size"].cast<uint32_t>();
+    e.num_intervals = d["num_intervals"].cast<uint32_t>();
+    e.flag_kind = d["flag_kind"].cast<uint32_t>();
+    e.flags.words = d["flag_words"].cast<std::vector<uint64_t>>();
+    e.deltas.words = d["delta_words"].cast<std::vector<uint64_t>>();
+    return e;
+}
+
+template <class T>
+struct PySketch {
+    QuantileSketch<T> s;
+    PySketch(int k, uint64_t seed, int offset_mode, bool jmax) : s(k, seed, offset_mode, jmax) {}
+};
+
+template <class T>
+static py::dict parse_payload(const std::string& buf) {
+    SketchGradient<T> g = skml_parse<T>(reinterpret_cast<const uint8_t*>(buf.data()), buf.size());
+    py::dict r;
+    const SkmlHeader& h = g.h;
+    r["kind"] = h.kind;
+    r["dtype"] = h.dtype;
+    r["step"] = h.step;
+    r["rank"] = h.rank;
+    r["world"] = h.world;
+    r["dim"] = h.dim;
+    r["nnz"] = h.nnz;
+    r["bin_num"] = h.bin_num;
+    r["zero_idx"] = h.zero_idx;
+    r["group_num"] = h.group_num;
+    r["row_num"] = h.row_num;
+    r["col_ratio"] = h.col_ratio;
+    r["key_encoder"] = h.key_encoder;
+    r["cell_bits"] = h.cell_bits;
+    r["seed"] = h.seed;
+    r["min_value"] = h.min_value;
+    r["max_value"] = h.max_value;
+    r["restart_interval"] = h.restart_interval;
+    r["total_bytes"] = h.total_bytes;
+    r["loss_partials"] = std::vector<double>(h.loss_partials, h.loss_partials + 4);
+    py::dict offs;
+    offs["bucket_values"] = h.off_bucket_values;
+    offs["group_table"] = h.off_group_table;
+    offs["tables"] = h.off_tables;
+    offs["key_flags"] = h.off_key_flags;
+    offs["key_deltas"] = h.off_key_deltas;
+    offs["restart"] = h.off_restart;
+    offs["dense_codes"] = h.off_dense_codes;
+    r["offsets"] = offs;
+    r["bucket_values"] = to_array(g.bucket_values);
+    if (h.kind == SKML_KIND_DENSE) {
+        r["dense_codes"] = to_array(g.dense_codes);
+    } else if (h.kind == SKML_KIND_SPARSE) {
+        py::list groups;
+        std::vector<SkmlGroupEntry> ent(h.group_num);
+        std::memcpy(ent.data(), buf.data() + h.off_group_table, h.group_num * sizeof(SkmlGroupEntry));
+        for (uint32_t i = 0; i < h.group_num; ++i) {
+            py::dict gd;
+            const MinMaxSketch& m = g.sketch.sketches[i];
+            gd["n"] = ent[i].n;
+            gd["col_num"] = ent[i].col_num;
+            gd["hash_ids"] = std::vector<int>(ent[i].hash_ids, ent[i].hash_ids + 8);
+            gd["table_off"] = ent[i].table_off;
+            gd["flag_off"] = ent[i].flag_off;
+            gd["delta_off"] = ent[i].delta_off;
+            gd["restart_off"] = ent[i].restart_off;
+            gd["n_flag_words"] = ent[i].n_flag_words;
+            gd["n_delta_words"] = ent[i].n_delta_words;
+            gd["table"] = to_array(m.table);
+            gd["keys"] = encoded_dict(g.sketch.keys[i]);
+            if (ent[i].n && ent[i].restart_off) {
+                size_t cnt = (ent[i].n + h.restart_interval - 1) / h.restart_interval;
+                std::vector<uint64_t> raw(cnt * 2);
+                std::memcpy(raw.data(), buf.data() + ent[i].restart_off, cnt * 16);
+                gd["restart_raw"] = to_array(raw);
+            }
+            groups.append(gd);
+        }
+        r["groups"] = groups;
+        r["edges"] = g.sketch.edges;
+    }
+    return r;
+}
+
+PYBIND11_MODULE(_oracle, m) {
+    m.doc() = "CPU oracle of the SketchML compression algorithms";
+    py::register_exception<Error>(m, "SketchMLError");
+
+    m.def("hash", [](int id, I32Array keys, int32_t size) {
+        if (id < 0 || id > 7) throw Error("hash id out of range [0, 8)");
+        if (size <= 0) throw Error("hash range must be positive");
+        std::vector<int32_t> out(keys.size());
+        for (ssize_t i = 0; i < keys.size(); ++i) out[i] = skml_hash(id, keys.data()[i], size);
+        return to_array(out);
+    });
+    m.def("pick_hashes", [](uint64_t seed, uint64_t step, uint32_t rank, uint32_t group, int rows) {
+        if (rows > 8 || rows < 1) throw Error("Currently only 8 hash functions are available");
+        uint8_t ids[8];
+        skml_pick_hashes(seed, step, rank, group, rows, ids);
+        return std::vector<int>(ids, ids + rows);
+    });
+    m.def("group_edges", [](int zero, int bins, int groups) {
+        std::vector<int> e(groups);
+        skml_group_edges(zero, bins, groups, e.data());
+        return e;
+    });
+    m.def("rand64", [](uint64_t seed, uint64_t a, uint64_t b, uint64_t c) { return skml_rand(seed, a, b, c); });
+
+    py::class_<PySketch<double>>(m, "QuantileSketch")
+        .def(py::init<int, uint64_t, int, bool>(), py::arg("k") = 128, py::arg("seed") = 0,
+             py::arg("offset_mode") = 2, py::arg("java_compat_max") = false)
+        .def("update", [](PySketch<double>& s, F64Array v) {
+            for (ssize_t i = 0; i < v.size(); ++i) s.s.update(v.data()[i]);
+        })
+        .def("merge", [](PySketch<double>& s, const PySketch<double>& o) { s.s.merge(o.s); })
+        .def("quantiles", [](PySketch<double>& s, int q) { return to_array(s.s.quantiles(q)); })
+        .def("summary", [](PySketch<double>& s) {
+            std::vector<double> a;
+            std::vector<uint64_t> c;
+            s.s.summary(a, c);
+            return py::make_tuple(to_array(a), to_array(c));
+        })
+        .def("reset", [](PySketch<double>& s) { s.s.reset(); })
+        .def_property_readonly("n", [](PySketch<double>& s) { return s.s.n(); })
+        .def_property_readonly("min", [](PySketch<double>& s) { return s.s.min_value(); })
+        .def_property_readonly("max", [](PySketch<double>& s) { return s.s.max_value(); })
+        .def_property_readonly("k", [](PySketch<double>& s) { return s.s.k(); })
+        .def_property_readonly("retained", [](PySketch<double>& s) { return s.s.retained(); });
+
+    m.def("quantile_quantize",
+          [](py::array v, int bins, int k, uint64_t seed, int offset_mode, bool jmax) -> py::dict {
+              if (is_f32(v)) {
+                  F32Array a(v);
+                  return quantizer_dict(quantile_quantize<float>(a.data(), a.size(), bins, k, seed, offset_mode, jmax));
+              }
+              F64Array a(v);
+              return quantizer_dict(quantile_quantize<double>(a.data(), a.size(), bins, k, seed, offset_mode, jmax));
+          },
+          py::arg("values"), py::arg("bin_num") = 256, py::arg("k") = 128, py::arg("seed") = 0,
+          py::arg("offset_mode") = 2, py::arg("java_compat_max") = false);
+    m.def("uniform_quantize", [](F64Array v, int bins) {
+        return quantizer_dict(uniform_quantize<double>(v.data(), v.size(), bins));
+    });
+    m.def("zipml_quantize", [](F64Array v, int bins) {
+        return quantizer_dict(zipml_quantize<double>(v.data(), v.size(), bins));
+    });
+    m.def("quantizer_from_splits", [](py::array splits, double mn, double mx, py::array v) -> py::dict {
+        if (is_f32(v)) {
+            F32Array s(splits), a(v);
+            std::vector<float> sv(s.data(), s.data() + s.size());
+            return quantizer_dict(quantizer_from_splits<float>(sv, (float)mn, (float)mx, a.data(), a.size()));
+        }
+        F64Array s(splits), a(v);
+        std::vector<double> sv(s.data(), s.data() + s.size());
+        return quantizer_dict(quantizer_from_splits<double>(sv, mn, mx, a.data(), a.size()));
+    });
+    m.def("export_java_quantizer", [](F64Array splits, double mn, double mx, F64Array v) {
+        std::vector<double> sv(splits.data(), splits.data() + splits.size());
+        return to_bytes(export_java_quantizer(quantizer_from_splits<double>(sv, mn, mx, v.data(), v.size())));
+    });
+
+    m.def("delta_binary_encode", [](I32Array k) { return encoded_dict(delta_binary_encode(k.data(), k.size())); });
+    m.def("delta_binary_decode", [](py::dict d) { return to_array(delta_binary_decode(encoded_from(d))); });
+    m.def("delta_adaptive_encode", [](I32Array k) { return encoded_dict(delta_adaptive_encode(k.data(), k.size())); });
+    m.def("delta_adaptive_decode", [](py::dict d) { return to_array(delta_adaptive_decode(encoded_from(d))); });
+    m.def("set_bits", [](std::vector<uint64_t> words, uint64_t off, uint32_t value, int nbits) {
+        BitStream b;
+        b.words = words;
+        b.put(off, value, nbits);
+        return b.words;
+    });
+    m.def("get_bits", [](std::vector<uint64_t> words, uint64_t off, int nbits) {
+        BitStream b;
+        b.words = words;
+        return b.take(off, nbits);
+    });
+
+    m.def("huffman_encode", [](I32Array v) {
+        HuffmanCode h = huffman_encode(v.data(), v.size());
+        py::dict r;
+        py::list items;
+        for (auto& it : h.items) items.append(py::make_tuple(it.value, it.bits, it.num_bits));
+        r["items"] = items;
+        r["words"] = to_array(h.bits.words);
+        r["nbits"] = h.nbits;
+        r["size"] = h.size;
+        return r;
+    });
+    m.def("huffman_decode", [](py::dict d) {
+        HuffmanCode h;
+        h.size = d["size"].cast<uint32_t>();
+        for (auto it : d["items"].cast<py::list>()) {
+            auto t = it.cast<py::tuple>();
+            h.items.push_back({t[0].cast<int32_t>(), t[1].cast<uint32_t>(), t[2].cast<int32_t>()});
+        }
+        h.bits.words = d["words"].cast<std::vector<uint64_t>>();
+        return to_array(huffman_decode(h));
+    });
+
+    py::class_<MinMaxSketch>(m, "MinMaxSketch")
+        .def(py::init([](int rows, int cols, int zero, std::vector<int> ids, int tie_mode) {
+                 if (rows > 8) throw Error("Currently only 8 hash functions are available");
+                 uint8_t h[8] = {0};
+                 for (size_t i = 0; i < ids.size() && i < 8; ++i) h[i] = (uint8_t)ids[i];
+                 return MinMaxSketch(rows, cols, zero, h, tie_mode);
+             }),
+             py::arg("rows"), py::arg("cols"), py::arg("zero"), py::arg("hash_ids"), py::arg("tie_mode") = 0)
+        .def("insert", [](MinMaxSketch& s, I32Array k, I32Array b) {
+            for (ssize_t i = 0; i < k.size(); ++i) s.insert(k.data()[i], b.data()[i]);
+        })
+        .def("query", [](MinMaxSketch& s, I32Array k) {
+            std::vector<int32_t> r(k.size());
+            for (ssize_t i = 0; i < k.size(); ++i) r[i] = s.query(k.data()[i]);
+            return to_array(r);
+        })
+        .def_property_readonly("table", [](MinMaxSketch& s) { return to_array(s.table); });
+
+    m.def("compress_sparse",
+          [](I32Array keys, py::array vals, uint64_t dim, py::dict opts, py::object splits, double mn, double mx) {
+              SketchOptions o = options_from(opts);
+              if (keys.size() != vals.size()) throw Error("Lengths of key array and value array do not match");
+              if (is_f32(vals)) {
+                  F32Array a(vals);
+                  if (splits.is_none()) return to_bytes(compress_sparse<float>(keys.data(), a.data(), a.size(), dim, o));
+                  F32Array s(splits);
+                  std::vector<float> sv(s.data(), s.data() + s.size());
+                  return to_bytes(compress_sparse<float>(keys.data(), a.data(), a.size(), dim, o, &sv, (float)mn, (float)mx));
+              }
+              F64Array a(vals);
+              if (splits.is_none()) return to_bytes(compress_sparse<double>(keys.data(), a.data(), a.size(), dim, o));
+              F64Array s(splits);
+              std::vector<double> sv(s.data(), s.data() + s.size());
+              return to_bytes(compress_sparse<double>(keys.data(), a.data(), a.size(), dim, o, &sv, mn, mx));
+          },
+          py::arg("keys"), py::arg("values"), py::arg("dim"), py::arg("options"), py::arg("splits") = py::none(),
+          py::arg("min") = 0.0, py::arg("max") = 0.0);
+    m.def("compress_dense",
+          [](py::array vals, py::dict opts, py::object splits, double mn, double mx) {
+              SketchOptions o = options_from(opts);
+              if (is_f32(vals)) {
+                  F32Array a(vals);
+                  if (splits.is_none()) return to_bytes(compress_dense<float>(a.data(), a.size(), o));
+                  F32Array s(splits);
+                  std::vector<float> sv(s.data(), s.data() + s.size());
+                  return to_bytes(compress_dense<float>(a.data(), a.size(), o, &sv, (float)mn, (float)mx));
+              }
+              F64Array a(vals);
+              if (splits.is_none()) return to_bytes(compress_dense<double>(a.data(), a.size(), o));
+              F64Array s(splits);
+              std::vector<double> sv(s.data(), s.data() + s.size());
+              return to_bytes(compress_dense<double>(a.data(), a.size(), o, &sv, mn, mx));
+          },
+          py::arg("values"), py::arg("options"), py::arg("splits") = py::none(), py::arg("min") = 0.0,
+          py::arg("max") = 0.0);
+    m.def("payload_dtype", [](const std::string& b) {
+        SkmlHeader h;
+        skml_validate(reinterpret_cast<const uint8_t*>(b.data()), b.size(), h);
+        return (int)h.dtype;
+    });
+    m.def("decompress", [](const std::string& b) {
+        SkmlHeader h;
+        const uint8_t* p = reinterpret_cast<const uint8_t*>(b.data());
+        skml_validate(p, b.size(), h);
+        std::vector<int32_t> keys;
+        if (h.dtype == SKML_F32) {
+            std::vector<float> v;
+            decompress<float>(p, b.size(), keys, v);
+            return py::make_tuple((int)h.kind, to_array(keys), py::array(to_array(v)));
+        }
+        std::vector<double> v;
+        decompress<double>(p, b.size(), keys, v);
+        return py::make_tuple((int)h.kind, to_array(keys), py::array(to_array(v)));
+    });
+    m.def("parse", [](const std::string& b) -> py::dict {
+        SkmlHeader h;
+        skml_validate(reinterpret_cast<const uint8_t*>(b.data()), b.size(), h);
+        return h.dtype == SKML_F32 ? parse_payload<float>(b) : parse_payload<double>(b);
+    });
+    m.def("payload_times_by", [](const std::string& b, double x) {
+        std::vector<uint8_t> c(b.begin(), b.end());
+        payload_times_by(c.data(), c.size(), x);
+        return to_bytes(c);
+    });
+    m.def("export_java_fields", [](const std::string& b) {
+        SkmlHeader h;
+        const uint8_t* p = reinterpret_cast<const uint8_t*>(b.data());
+        skml_validate(p, b.size(), h);
+        return to_bytes(h.dtype == SKML_F32 ? export_java_fields<float>(p, b.size())
+                                            : export_java_fields<double>(p, b.size()));
+    });
+
+    m.def("fixed_point_encode", [](F64Array v, int bits, uint64_t seed) {
+        FixedPointCode c = fixed_point_encode<double>(v.data(), v.size(), bits, seed);
+        py::dict r;
+        r["size"] = c.size;
+        r["num_bits"] = c.num_bits;
+        r["norm"] = c.norm;
+        r["words"] = to_array(c.bits.words);
+        return r;
+    });
+    m.def("fixed_point_decode", [](py::dict d) {
+        FixedPointCode c;
+        c.size = d["size"].cast<uint32_t>();
+        c.num_bits = d["num_bits"].cast<int>();
+        c.norm = d["norm"].cast<double>();
+        c.bits.words = d["words"].cast<std::vector<uint64_t>>();
+        return to_array(fixed_point_decode<double>(c));
+    });
+
+    m.def("quick_select", [](F64Array a, size_t k) {
+        return quick_select(std::vector<double>(a.data(), a.data() + a.size()), k);
+    });
+    m.def("select_kth_largest", [](F64Array a, size_t k) {
+        return select_kth_largest(std::vector<double>(a.data(), a.data() + a.size()), k);
+    });
+    m.def("kway_merge", [](std::vector<std::vector<int32_t>> ks, std::vector<std::vector<int32_t>> ys) {
+        std::vector<int32_t> k, y;
+        kway_merge(ks, ys, k, y);
+        return py::make_tuple(to_array(k), to_array(y));
+    });
+    m.def("unique_sorted", [](F64Array a) {
+        return to_array(unique_sorted(std::vector<double>(a.data(), a.data() + a.size())));
+    });
+    m.attr("HEADER_BYTES") = SKML_HEADER_BYTES;
+    m.attr("RESTART_INTERVAL") = SKML_RESTART_INTERVAL;
+}
