@@ -1,0 +1,1162 @@
+// Fused SketchML compress + publish for sm_100a.
+//
+// One persistent cooperative kernel (one block per SM, 1024 threads) runs the whole
+// sender side of the gradient exchange:
+//   S1  mergeable quantile summary of the values (sorted shared-memory tiles, k = 128
+//       samples per run, pairwise merge + keep-every-second carry chain), min / max
+//   S2  weighted-rank query of the merged summaries -> q-1 raw split points
+//   S3  dedupe splits, zero bucket, bucket midpoints, group edges; bucketize every
+//       value; per-block per-group counts / key-delta byte sums
+//   S4  payload layout; grouped MinMaxSketch insert (atomicMin on packed cells);
+//       delta-binary key code (2 flag bits + 1/2/4 bytes), restart points; header
+//   S5  narrow the sketch tables to 8/16-bit bucket codes and store the finished payload
+//       into every peer's receive slot with 16-byte peer stores, then release the
+//       arrival flags (system scope). There is no separate all-gather.
+// Grid-wide dependencies are bounded software barriers (cooperative launch guarantees
+// co-residency). With `fused = 0` the same stage functions run as separate launches.
+//
+// Reference behaviour restated (paths inside the reference project, module `sketch`):
+//   quantization/QuantileQuantizer.java:27-50, sketch/quantile/HeapQuantileSketch.java:73-143,
+//   293-323, sketch/quantile/QSketchUtils.java:45-82, base/Quantizer.java:39-92,
+//   sketch/frequency/FSketchUtils.java:9-47, MinMaxSketch.java:27-55,
+//   GroupedMinMaxSketch.java:103-121, binary/DeltaBinaryEncoder.java:26-39, and
+//   ml/gradient/SketchGradient.scala:24-48.
+#include <cooperative_groups.h>
+#include <stdio.h>
+
+#include "skml_api.h"
+#include "skml_device.cuh"
+
+#define MAX_GRID 192
+#define SK_K 128            // samples per run
+#define TILE 2048           // values sorted at once
+#define TILE_W 16           // TILE / SK_K: weight of a sample taken from a full tile
+#define MAX_LEVELS 24
+#define FP_SHIFT 20         // fixed-point fraction bits of sample weights
+#define MIN_TILES_PER_BLOCK 4
+
+struct CtaStat {
+    unsigned int count;
+    int first_key;
+    int last_key;
+    unsigned int pad;
+    unsigned long long bytes;  // delta bytes of this block's keys except the first of the group
+    unsigned long long pad2;
+};
+
+struct CP {
+    const int* keys;
+    const float* vals;
+    const long long* meta;
+    long long n_max, dim;
+    int q, G, rows;
+    double col_ratio;
+    unsigned long long seed, step;
+    unsigned int rank, world;
+    const double* loss_partials;
+    unsigned char* payload;
+    long long slot_capacity;
+    unsigned char* peer_payload[SKML_MAX_PEERS];
+    unsigned long long* peer_flag[SKML_MAX_PEERS];
+    unsigned int* ctrl;
+    unsigned int* run_vals;
+    unsigned int* run_cnt;
+    unsigned long long* run_w;
+    unsigned int* splits_raw;
+    CtaStat* stats;
+    unsigned short* bins;
+    unsigned int* tables;
+    long long tables_cap;
+    unsigned int* status;
+    long long budget;
+    const float* given_splits;
+    int n_given;
+    float given_min, given_max;
+};
+
+struct QInfo {
+    int nsplits, bin_num, zero_idx, cell_bits;
+    float minv, maxv;
+    int edges[SKML_MAX_GROUPS];
+};
+
+struct Layout {
+    unsigned int n_g[SKML_MAX_GROUPS];
+    unsigned int col[SKML_MAX_GROUPS];
+    unsigned long long bytes_g[SKML_MAX_GROUPS];
+    unsigned long long table_off[SKML_MAX_GROUPS], flag_off[SKML_MAX_GROUPS], delta_off[SKML_MAX_GROUPS],
+        restart_off[SKML_MAX_GROUPS], tab32_off[SKML_MAX_GROUPS];
+    unsigned int base_rank[SKML_MAX_GROUPS];
+    unsigned long long base_bytes[SKML_MAX_GROUPS];
+    int base_prev[SKML_MAX_GROUPS];
+    unsigned char hash_ids[SKML_MAX_GROUPS][8];
+    unsigned long long off_bv, off_gt, off_flags, off_restart, off_tables, off_deltas, total_bytes;
+    int overflow;
+};
+
+struct WsLayout {
+    long long ctrl, run_vals, run_cnt, run_w, splits_raw, stats, bins, tables, total;
+    long long tables_cap;
+};
+
+static inline long long al256(long long x) { return (x + 255) & ~255ll; }
+
+static WsLayout ws_layout(long long n_max, long long q, long long G, long long rows, double col_ratio, long long grid) {
+    WsLayout L;
+    long long o = 0;
+    L.ctrl = o; o += 256;
+    L.run_vals = o; o += al256(grid * SK_K * 4);
+    L.run_cnt = o; o += al256(grid * 4);
+    L.run_w = o; o += al256(grid * 8);
+    L.splits_raw = o; o += al256(q * 4);
+    L.stats = o; o += al256(grid * SKML_MAX_GROUPS * (long long)sizeof(CtaStat));
+    L.bins = o; o += al256(n_max * 2);
+    L.tables_cap = rows * ((long long)(col_ratio * (double)n_max) + 2 + G) + 64;
+    L.tables = o; o += al256(L.tables_cap * 4);
+    L.total = o;
+    return L;
+}
+
+extern "C" long long skml_compress_workspace_bytes(long long n_max, long long bin_num, long long group_num,
+                                                   long long row_num, double col_ratio, long long grid) {
+    if (grid <= 0 || grid > MAX_GRID) grid = MAX_GRID;
+    return ws_layout(n_max, bin_num, group_num, row_num, col_ratio, grid).total;
+}
+
+// Upper bound of the payload size for n_max non-zeros (sparse kind) or dim codes (dense kind).
+extern "C" long long skml_payload_capacity(long long n_max, long long dim, long long bin_num, long long group_num,
+                                           long long row_num, double col_ratio) {
+    long long G = group_num, R = SKML_RESTART_INTERVAL;
+    long long head = SKML_HEADER_BYTES + skml_align16(4 * bin_num) + SKML_GROUP_ENTRY_BYTES * G;
+    long long flags = n_max / 4 + 24 * G + 16;
+    long long restart = 16 * (n_max / R + G) + 16 * G;
+    long long tables = 2 * row_num * ((long long)(col_ratio * (double)n_max) + 2) + 32 * G;
+    long long deltas = 4 * n_max + 24 * G;
+    long long sparse = head + flags + restart + tables + deltas + 64;
+    long long dense = head + 2 * dim + 64;
+    long long cap = sparse > dense ? sparse : dense;
+    return (cap + 255) & ~255ll;
+}
+
+// ---------------------------------------------------------------------------
+// shared memory carve-up (dynamic, one block per SM)
+// ---------------------------------------------------------------------------
+struct Smem {
+    // stage S1
+    unsigned int tile[TILE];
+    unsigned int levels[MAX_LEVELS][SK_K];
+    unsigned int run[SK_K];
+    unsigned int merge[2 * SK_K];
+    unsigned int tail[SK_K];
+    unsigned long long e_acc[SK_K];
+    // stage S2 (all blocks' runs)
+    unsigned int runs_all[MAX_GRID * SK_K];
+    unsigned int runs_cnt[MAX_GRID];
+    unsigned long long runs_w[MAX_GRID];
+    // stages S3..S5
+    float splits[SKML_GPU_MAX_BINS];
+    QInfo qi;
+    Layout lay;
+    int wlast[SKML_WARPS][SKML_MAX_GROUPS];
+    unsigned int wcnt[SKML_WARPS][SKML_MAX_GROUPS];
+    unsigned int wbytes[SKML_WARPS][SKML_MAX_GROUPS];
+    int cin[SKML_WARPS][SKML_MAX_GROUPS];
+    int carry_key[SKML_MAX_GROUPS];
+    int first_key[SKML_MAX_GROUPS];
+    unsigned int cnt[SKML_MAX_GROUPS];
+    unsigned long long bytes[SKML_MAX_GROUPS];
+    unsigned int tile_rank[SKML_MAX_GROUPS];
+    unsigned long long tile_bytes[SKML_MAX_GROUPS];
+    unsigned long long unit_prefix[SKML_MAX_GROUPS + 1];
+    int flag;
+};
+
+__device__ __forceinline__ unsigned int lanemask_lt() {
+    unsigned int m;
+    asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
+    return m;
+}
+
+// ---------------------------------------------------------------------------
+// S1: quantile summary
+// ---------------------------------------------------------------------------
+// Merge the sorted runs a[128] and b[128] into s.merge (ascending) with a bitonic merge.
+__device__ __forceinline__ void merge_runs(Smem& s, const unsigned int* a, const unsigned int* b) {
+    for (int t = threadIdx.x; t < SK_K; t += blockDim.x) {
+        s.merge[t] = a[t];
+        s.merge[2 * SK_K - 1 - t] = b[t];
+    }
+    __syncthreads();
+    for (int j = SK_K; j > 0; j >>= 1) {
+        for (int t = threadIdx.x; t < SK_K; t += blockDim.x) {
+            int i = ((t & ~(j - 1)) << 1) | (t & (j - 1));
+            unsigned int x = s.merge[i], y = s.merge[i | j];
+            if (x > y) {
+                s.merge[i] = y;
+                s.merge[i | j] = x;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// Carry s.run (weight TILE_W << level0) up the level chain.
+__device__ __forceinline__ void carry_run(Smem& s, unsigned int& occupied, int level, const CP& p, unsigned long long salt) {
+    while (true) {
+        if (!(occupied & (1u << level))) {
+            for (int t = threadIdx.x; t < SK_K; t += blockDim.x) s.levels[level][t] = s.run[t];
+            occupied |= 1u << level;
+            __syncthreads();
+            return;
+        }
+        merge_runs(s, s.levels[level], s.run);
+        unsigned int off = (unsigned int)(skml_rand(p.seed, p.step, ((unsigned long long)p.rank << 32) | blockIdx.x,
+                                                    salt * 64 + level) & 1u);
+        for (int t = threadIdx.x; t < SK_K; t += blockDim.x) s.run[t] = s.merge[2 * t + off];
+        occupied &= ~(1u << level);
+        __syncthreads();
+        ++level;
+        if (level >= MAX_LEVELS) return;  // unreachable for n < 2^31
+    }
+}
+
+__device__ void stage_summary(const CP& p, Smem& s, const float* __restrict__ vals, long long n) {
+    const long long ntiles = (n + TILE - 1) / TILE;
+    long long CA = (ntiles + MIN_TILES_PER_BLOCK - 1) / MIN_TILES_PER_BLOCK;
+    if (CA > gridDim.x) CA = gridDim.x;
+    if (CA < 1) CA = 1;
+    const long long tpc = (ntiles + CA - 1) / CA;
+    long long t0 = (long long)blockIdx.x * tpc, t1 = t0 + tpc;
+    if (t1 > ntiles) t1 = ntiles;
+    if ((long long)blockIdx.x >= CA || t0 >= t1 || n <= 0) {
+        if (threadIdx.x == 0) {
+            p.run_cnt[blockIdx.x] = 0;
+            p.run_w[blockIdx.x] = 0;
+        }
+        return;
+    }
+    unsigned int occupied = 0;
+    int tail_cnt = 0;
+    unsigned long long tail_w = 0;
+    unsigned int kmin = 0xFFFFFFFFu, kmax = 0u;
+    unsigned long long n_c = 0;
+    for (long long tile = t0; tile < t1; ++tile) {
+        long long base = tile * TILE;
+        int m = (int)((n - base) < TILE ? (n - base) : TILE);
+        for (int t = threadIdx.x; t < TILE; t += blockDim.x) {
+            unsigned int k = 0xFFFFFFFFu;
+            if (t < m) {
+                k = f2ord(vals[base + t]);
+                kmin = min(kmin, k);
+                kmax = max(kmax, k);
+            }
+            s.tile[t] = k;
+        }
+        __syncthreads();
+        block_bitonic_sort<TILE>(s.tile);
+        n_c += (unsigned long long)m;
+        if (m == TILE) {
+            unsigned int off = (unsigned int)(skml_rand(p.seed, p.step, ((unsigned long long)p.rank << 32) | blockIdx.x,
+                                                        0x7000u + (unsigned long long)(tile - t0)) & (TILE_W - 1));
+            for (int t = threadIdx.x; t < SK_K; t += blockDim.x) s.run[t] = s.tile[t * TILE_W + off];
+            __syncthreads();
+            carry_run(s, occupied, 0, p, (unsigned long long)(tile - t0) + 1);
+        } else {
+            int stride = 1;
+            while ((m + stride - 1) / stride > SK_K) stride <<= 1;
+            tail_cnt = (m + stride - 1) / stride;
+            unsigned int off = stride > 1 ? (unsigned int)(skml_rand(p.seed, p.step, p.rank, 0x7100u) % stride) : 0u;
+            for (int t = threadIdx.x; t < tail_cnt; t += blockDim.x) {
+                int idx = t * stride + (int)off;
+                if (idx > m - 1) idx = m - 1;
+                s.tail[t] = s.tile[idx];
+            }
+            tail_w = (((unsigned long long)m) << FP_SHIFT) / (unsigned long long)tail_cnt;
+            __syncthreads();
+        }
+    }
+    // block min / max -> global (stored so that an all-zero word means "nothing yet")
+    {
+        unsigned int a = kmin, b = kmax;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            a = min(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+            b = max(b, __shfl_xor_sync(0xFFFFFFFFu, b, o));
+        }
+        if ((threadIdx.x & 31) == 0) {
+            atomicMax(&p.ctrl[4], ~a);
+            atomicMax(&p.ctrl[5], b);
+        }
+    }
+    // collapse the levels (+ tail) into one published run
+    int nruns = __popc(occupied) + (tail_cnt > 0 ? 1 : 0);
+    unsigned int* out = p.run_vals + (long long)blockIdx.x * SK_K;
+    if (nruns == 1) {
+        const unsigned int* src;
+        int cnt;
+        unsigned long long w;
+        if (tail_cnt > 0) {
+            src = s.tail; cnt = tail_cnt; w = tail_w;
+        } else {
+            int lv = __ffs(occupied) - 1;
+            src = s.levels[lv]; cnt = SK_K; w = ((unsigned long long)TILE_W << lv) << FP_SHIFT;
+        }
+        for (int t = threadIdx.x; t < cnt; t += blockDim.x) out[t] = src[t];
+        if (threadIdx.x == 0) {
+            p.run_cnt[blockIdx.x] = (unsigned int)cnt;
+            p.run_w[blockIdx.x] = w;
+        }
+        return;
+    }
+    // several runs: exclusive cumulative weight of every sample, then 128 mid-rank samples
+    unsigned long long Wc = 0;
+    for (int lv = 0; lv < MAX_LEVELS; ++lv)
+        if (occupied & (1u << lv)) Wc += (unsigned long long)SK_K * (((unsigned long long)TILE_W << lv) << FP_SHIFT);
+    Wc += (unsigned long long)tail_cnt * tail_w;
+    const int total_samples = __popc(occupied) * SK_K + tail_cnt;
+    for (int sidx = threadIdx.x; sidx < total_samples; sidx += blockDim.x) {
+        // locate (run a, index i): occupied levels in ascending order, then the tail
+        int a = -1, i = sidx, seen = 0;
+        for (int lv = 0; lv < MAX_LEVELS; ++lv) {
+            if (!(occupied & (1u << lv))) continue;
+            if (i < SK_K) { a = lv; break; }
+            i -= SK_K;
+            ++seen;
+        }
+        const unsigned int value = a >= 0 ? s.levels[a][i] : s.tail[i];
+        const unsigned long long wa = a >= 0 ? (((unsigned long long)TILE_W << a) << FP_SHIFT) : tail_w;
+        unsigned long long e = (unsigned long long)i * wa;
+        for (int lv = 0; lv < MAX_LEVELS; ++lv) {
+            if (!(occupied & (1u << lv)) || lv == a) continue;
+            unsigned long long wl = ((unsigned long long)TILE_W << lv) << FP_SHIFT;
+            bool before = a < 0 || lv < a;  // runs earlier in the order win ties
+            int c = before ? upper_bound_u(s.levels[lv], SK_K, value) : lower_bound_u(s.levels[lv], SK_K, value);
+            e += (unsigned long long)c * wl;
+        }
+        if (tail_cnt > 0 && a >= 0) e += (unsigned long long)lower_bound_u(s.tail, tail_cnt, value) * tail_w;
+        // targets t_j = (2j+1) * Wc / 256, j = 0..127, covered iff e <= t_j < e + wa
+        long long j = (long long)((e << 7) / Wc) - 1;
+        if (j < 0) j = 0;
+        for (; j < SK_K; ++j) {
+            unsigned long long tj = ((unsigned long long)(2 * j + 1) * (Wc >> 8));
+            if (tj < e) continue;
+            if (tj >= e + wa) break;
+            out[j] = value;
+        }
+        (void)seen;
+    }
+    if (threadIdx.x == 0) {
+        p.run_cnt[blockIdx.x] = SK_K;
+        p.run_w[blockIdx.x] = Wc / SK_K;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// S2: weighted-rank query over all published runs -> splits_raw[q-1] (ordered keys)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ unsigned long long rank_target(long long n, int t, double inv_q) {
+    unsigned long long r = (unsigned long long)((double)n * ((double)(t + 1) * inv_q));
+    if (r > (unsigned long long)(n - 1)) r = (unsigned long long)(n - 1);
+    return r << FP_SHIFT;
+}
+
+__device__ void stage_query(const CP& p, Smem& s, long long n) {
+    if (n <= 0) return;
+    const int nb = gridDim.x;
+    for (int t = threadIdx.x; t < nb; t += blockDim.x) {
+        s.runs_cnt[t] = p.run_cnt[t];
+        s.runs_w[t] = p.run_w[t];
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < nb * SK_K; t += blockDim.x) {
+        int c = t / SK_K, i = t % SK_K;
+        s.runs_all[t] = i < (int)s.runs_cnt[c] ? __ldcg(p.run_vals + t) : 0xFFFFFFFFu;
+    }
+    __syncthreads();
+    unsigned long long Wtot = 0;
+    for (int c = 0; c < nb; ++c) Wtot += (unsigned long long)s.runs_cnt[c] * s.runs_w[c];
+    const double inv_q = 1.0 / (double)p.q;
+    const int i = threadIdx.x & (SK_K - 1), part = threadIdx.x / SK_K, parts = blockDim.x / SK_K;
+    for (int c = blockIdx.x; c < nb; c += gridDim.x) {
+        const int cnt = (int)s.runs_cnt[c];
+        if (cnt == 0) continue;  // uniform over the block
+        if (threadIdx.x < SK_K) s.e_acc[threadIdx.x] = 0ull;
+        __syncthreads();
+        if (i < cnt) {
+            const unsigned int value = s.runs_all[c * SK_K + i];
+            unsigned long long e = 0;
+            for (int c2 = part; c2 < nb; c2 += parts) {
+                int cnt2 = (int)s.runs_cnt[c2];
+                if (cnt2 == 0) continue;
+                int k;
+                if (c2 == c) k = i;
+                else if (c2 < c) k = upper_bound_u(s.runs_all + c2 * SK_K, cnt2, value);
+                else k = lower_bound_u(s.runs_all + c2 * SK_K, cnt2, value);
+                e += (unsigned long long)k * s.runs_w[c2];
+            }
+            atomicAdd(&s.e_acc[i], e);
+        }
+        __syncthreads();
+        if (threadIdx.x < cnt) {
+            const unsigned int value = s.runs_all[c * SK_K + threadIdx.x];
+            const unsigned long long e = s.e_acc[threadIdx.x], w = s.runs_w[c];
+            const bool last = e + w >= Wtot;
+            // smallest t with target >= e
+            int lo = 0, hi = p.q - 1;
+            while (lo < hi) {
+                int mid = (lo + hi) >> 1;
+                if (rank_target(n, mid, inv_q) >= e) hi = mid;
+                else lo = mid + 1;
+            }
+            for (int t = lo; t < p.q - 1; ++t) {
+                unsigned long long r = rank_target(n, t, inv_q);
+                if (!last && r >= e + w) break;
+                p.splits_raw[t] = value;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------
+// S3 prelude: unique splits, zero bucket, group edges (every block, in shared memory)
+// ---------------------------------------------------------------------------
+__device__ void load_quantizer(const CP& p, Smem& s) {
+    const bool given = p.given_splits != nullptr;
+    const int nraw = given ? p.n_given : p.q - 1;
+    __shared__ int s_base;
+    if (threadIdx.x == 0) s_base = 0;
+    __syncthreads();
+    for (int b = 0; b < nraw; b += blockDim.x) {
+        int i = b + threadIdx.x;
+        float v = 0.f, prev = 0.f;
+        bool keep = false;
+        if (i < nraw) {
+            v = given ? p.given_splits[i] : ord2f(__ldcg(p.splits_raw + i));
+            if (i > 0) prev = given ? p.given_splits[i - 1] : ord2f(__ldcg(p.splits_raw + i - 1));
+            keep = i == 0 || v != prev;
+        }
+        unsigned int total;
+        unsigned int pos = block_exclusive_scan<unsigned int>(keep ? 1u : 0u, &total);
+        int base = s_base;
+        if (keep) s.splits[base + pos] = v;
+        __syncthreads();
+        if (threadIdx.x == 0) s_base = base + (int)total;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        QInfo& q = s.qi;
+        q.nsplits = s_base;
+        q.bin_num = s_base + 1;
+        q.cell_bits = q.bin_num <= 256 ? 8 : 16;
+        if (given) {
+            q.minv = p.given_min;
+            q.maxv = p.given_max;
+        } else {
+            q.minv = ord2f(~__ldcg(p.ctrl + 4));
+            q.maxv = ord2f(__ldcg(p.ctrl + 5));
+        }
+        int z;
+        if (q.minv > 0.f) z = 0;
+        else if (q.maxv < 0.f) z = q.bin_num - 1;
+        else {
+            z = 0;
+            while (z < q.bin_num - 1 && s.splits[z] < 0.f) ++z;
+        }
+        q.zero_idx = z;
+        skml_group_edges(z, q.bin_num, p.G, q.edges);
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ float bucket_value(const Smem& s, int b) {
+    const QInfo& q = s.qi;
+    if (q.bin_num == 1) return 0.5f * (q.minv + q.maxv);
+    if (b == 0) return 0.5f * (q.minv + s.splits[0]);
+    if (b == q.bin_num - 1) return 0.5f * (s.splits[q.nsplits - 1] + q.maxv);
+    return 0.5f * (s.splits[b - 1] + s.splits[b]);
+}
+
+// ---------------------------------------------------------------------------
+// Element passes. PACK = false: bucketize + per-block statistics (S3).
+// PACK = true: ranks, byte offsets, flag / delta / restart writes, sketch insert (S4).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ long long chunk_size(long long n) {
+    long long c = (n + gridDim.x - 1) / gridDim.x;
+    return (c + SKML_BLOCK - 1) / SKML_BLOCK * SKML_BLOCK;
+}
+
+template <bool PACK>
+__device__ void element_pass(const CP& p, Smem& s, long long n) {
+    const int G = p.G;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long chunk = chunk_size(n);
+    long long lo = (long long)blockIdx.x * chunk, hi = lo + chunk;
+    if (hi > n) hi = n;
+    if (threadIdx.x < SKML_MAX_GROUPS) {
+        s.carry_key[threadIdx.x] = -1;
+        s.first_key[threadIdx.x] = -1;
+        s.cnt[threadIdx.x] = 0;
+        s.bytes[threadIdx.x] = 0;
+        s.tile_rank[threadIdx.x] = 0;
+        s.tile_bytes[threadIdx.x] = 0;
+    }
+    __syncthreads();
+    const int wg_g = threadIdx.x % G, wg_w = threadIdx.x / G;  // (warp, group) role of this thread
+    const bool wg_on = threadIdx.x < SKML_WARPS * G;
+    const Layout& L = s.lay;
+    const int zero = s.qi.zero_idx;
+    const bool overflow = PACK && L.overflow;
+
+    for (long long tlo = lo; tlo < hi; tlo += SKML_BLOCK) {
+        const long long i = tlo + threadIdx.x;
+        const bool valid = i < hi;
+        int key = 0, bin = 0, g = 63;
+        if (valid) {
+            key = p.keys[i];
+            if (PACK) {
+                bin = p.bins[i];
+            } else {
+                bin = upper_bound_f(s.splits, s.qi.nsplits, p.vals[i]);
+                p.bins[i] = (unsigned short)bin;
+            }
+            g = skml_group_of(bin, s.qi.edges, G);
+        }
+        if (wg_on) {
+            s.wlast[wg_w][wg_g] = -1;
+            s.wcnt[wg_w][wg_g] = 0;
+            s.wbytes[wg_w][wg_g] = 0;
+        }
+        __syncthreads();
+        const unsigned int peers = __match_any_sync(0xFFFFFFFFu, g);
+        const unsigned int lower = peers & lanemask_lt();
+        const int prev_lane = lower ? 31 - __clz(lower) : 0;
+        const int prev_in_warp = __shfl_sync(0xFFFFFFFFu, key, prev_lane);
+        const bool last_in_warp = valid && (peers >> lane) == 1u;
+        if (last_in_warp) s.wlast[warp][g] = key;
+        __syncthreads();
+        if (wg_on) {
+            int c = s.carry_key[wg_g];
+            for (int w2 = 0; w2 < wg_w; ++w2) {
+                int k2 = s.wlast[w2][wg_g];
+                if (k2 >= 0) c = k2;
+            }
+            s.cin[wg_w][wg_g] = c;
+        }
+        __syncthreads();
+        int prev = -1;
+        if (valid) prev = lower ? prev_in_warp : s.cin[warp][g];
+        // widths
+        int w = 0;
+        unsigned int delta = 0;
+        if (valid) {
+            if (PACK) {
+                int pk = prev >= 0 ? prev : L.base_prev[g];
+                delta = (unsigned int)(key - pk);
+                w = skml_delta_bytes(delta);
+            } else if (prev >= 0) {
+                w = skml_delta_bytes((unsigned int)(key - prev));
+            }
+        }
+        const unsigned int b1 = __ballot_sync(0xFFFFFFFFu, w == 1);
+        const unsigned int b2 = __ballot_sync(0xFFFFFFFFu, w == 2);
+        const unsigned int b4 = __ballot_sync(0xFFFFFFFFu, w == 4);
+        if (!PACK) {
+            if (valid) {
+                if (prev < 0) s.first_key[g] = key;
+                if (lower == 0) {  // first lane of its group in this warp adds the warp's share
+                    atomicAdd(&s.cnt[g], (unsigned int)__popc(peers));
+                    unsigned long long by = __popc(peers & b1) + 2 * __popc(peers & b2) + 4 * __popc(peers & b4);
+                    if (by) atomicAdd(&s.bytes[g], by);
+                }
+            }
+            __syncthreads();
+            if (threadIdx.x < G) {  // carry the last key of every group into the next tile
+                int c = s.carry_key[threadIdx.x];
+                for (int w2 = 0; w2 < SKML_WARPS; ++w2) {
+                    int k2 = s.wlast[w2][threadIdx.x];
+                    if (k2 >= 0) c = k2;
+                }
+                s.carry_key[threadIdx.x] = c;
+            }
+            __syncthreads();
+            continue;
+        }
+        // ---- PACK ----
+        const unsigned int r_w = __popc(lower);
+        const unsigned int bw = __popc(lower & b1) + 2 * __popc(lower & b2) + 4 * __popc(lower & b4);
+        if (last_in_warp) {
+            s.wcnt[warp][g] = r_w + 1;
+            s.wbytes[warp][g] = bw + (unsigned int)w;
+        }
+        __syncthreads();
+        unsigned int ex_cnt = 0, ex_bytes = 0;
+        if (valid) {
+            for (int w2 = 0; w2 < warp; ++w2) {
+                ex_cnt += s.wcnt[w2][g];
+                ex_bytes += s.wbytes[w2][g];
+            }
+        }
+        if (valid && !overflow) {
+            const unsigned long long prank = (unsigned long long)L.base_rank[g] + s.tile_rank[g] + ex_cnt + r_w;
+            const unsigned long long boff = L.base_bytes[g] + s.tile_bytes[g] + ex_bytes + bw;
+            // flags: (w - 1) most significant bit first at stream bits 2p, 2p+1
+            const unsigned int fv = (unsigned int)(w - 1);
+            if (fv) {
+                const unsigned int bits = ((fv >> 1) & 1u) | ((fv & 1u) << 1);
+                unsigned int* fw = reinterpret_cast<unsigned int*>(p.payload + L.flag_off[g]) + ((2 * prank) >> 5);
+                atomicOr(fw, bits << ((2 * prank) & 31));
+            }
+            unsigned char* dst = p.payload + L.delta_off[g] + boff;
+            for (int j = 0; j < w; ++j) dst[j] = skml_delta_stream_byte(delta, w, j);
+            if ((prank % SKML_RESTART_INTERVAL) == 0) {
+                SkmlRestart r;
+                r.prev_key = (unsigned int)key - delta;
+                r.flag_bit_off = (unsigned int)(2 * prank);
+                r.delta_bit_off = 8ull * boff;
+                *reinterpret_cast<SkmlRestart*>(p.payload + L.restart_off[g] +
+                                                (prank / SKML_RESTART_INTERVAL) * sizeof(SkmlRestart)) = r;
+            }
+            const unsigned int cell = skml_pack_cell(bin, zero);
+            const int col = (int)L.col[g];
+            unsigned int* tab = p.tables + L.tab32_off[g];
+            for (int r = 0; r < p.rows; ++r)
+                atomicMin(tab + (long long)r * col + skml_hash(L.hash_ids[g][r], key, col), cell);
+        }
+        __syncthreads();
+        if (threadIdx.x < G) {
+            int c = s.carry_key[threadIdx.x];
+            unsigned int tc = 0, tb = 0;
+            for (int w2 = 0; w2 < SKML_WARPS; ++w2) {
+                int k2 = s.wlast[w2][threadIdx.x];
+                if (k2 >= 0) c = k2;
+                tc += s.wcnt[w2][threadIdx.x];
+                tb += s.wbytes[w2][threadIdx.x];
+            }
+            s.carry_key[threadIdx.x] = c;
+            s.tile_rank[threadIdx.x] += tc;
+            s.tile_bytes[threadIdx.x] += tb;
+        }
+        __syncthreads();
+    }
+    if (!PACK) {
+        __syncthreads();
+        if (threadIdx.x < G) {
+            CtaStat st;
+            st.count = s.cnt[threadIdx.x];
+            st.first_key = s.first_key[threadIdx.x];
+            st.last_key = s.carry_key[threadIdx.x];
+            st.pad = 0;
+            st.bytes = s.bytes[threadIdx.x];
+            st.pad2 = 0;
+            p.stats[(long long)blockIdx.x * SKML_MAX_GROUPS + threadIdx.x] = st;
+        }
+    }
+}
+
+// Fill helpers run inside S1 (they do not depend on the summary).
+__device__ void stage_prepare(const CP& p, long long n) {
+    // working sketch cells start "empty"
+    long long cells = (long long)p.rows * ((long long)(p.col_ratio * (double)n) + 2 + p.G);
+    if (cells > p.tables_cap - 4) cells = p.tables_cap - 4;
+    const long long gsz = (long long)gridDim.x * blockDim.x, gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    uint4 ones = make_uint4(~0u, ~0u, ~0u, ~0u);
+    uint4* t4 = reinterpret_cast<uint4*>(p.tables);
+    for (long long i = gid; i < (cells + 3) / 4; i += gsz) t4[i] = ones;
+    // the flag region is written with atomicOr and must start at zero
+    const long long off_flags = SKML_HEADER_BYTES + (long long)skml_align16(4ull * p.q) + SKML_GROUP_ENTRY_BYTES * p.G;
+    long long flag_bytes = (long long)skml_align16((unsigned long long)(n / 4 + 24 * p.G + 16));
+    if (off_flags + flag_bytes > p.slot_capacity) flag_bytes = p.slot_capacity > off_flags ? ((p.slot_capacity - off_flags) & ~15ll) : 0;
+    uint4 z = make_uint4(0, 0, 0, 0);
+    uint4* f4 = reinterpret_cast<uint4*>(p.payload + off_flags);
+    for (long long i = gid; i < flag_bytes / 16; i += gsz) f4[i] = z;
+}
+
+// ---------------------------------------------------------------------------
+// S4 prelude: payload layout from the per-block statistics (every block)
+// ---------------------------------------------------------------------------
+__device__ void compute_layout(const CP& p, Smem& s, long long n) {
+    const int G = p.G, nb = gridDim.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    Layout& L = s.lay;
+    if (warp < G) {
+        const int g = warp;
+        unsigned int run_cnt = 0;
+        unsigned long long run_bytes = 0;
+        int carry_last = -1;
+        unsigned int my_rank = 0;
+        unsigned long long my_bytes = 0;
+        int my_prev = 0;
+        for (int base = 0; base < nb; base += 32) {
+            const int c = base + lane;
+            CtaStat st;
+            st.count = 0; st.first_key = -1; st.last_key = -1; st.bytes = 0;
+            if (c < nb) st = p.stats[(long long)c * SKML_MAX_GROUPS + g];
+            const unsigned int nonempty = __ballot_sync(0xFFFFFFFFu, st.count > 0);
+            const unsigned int lowm = nonempty & lanemask_lt();
+            const int src = lowm ? 31 - __clz(lowm) : 0;
+            const int prev_last_lane = __shfl_sync(0xFFFFFFFFu, st.last_key, src);
+            const int before = lowm ? prev_last_lane : carry_last;  // last key of the group before block c
+            unsigned long long full = st.bytes;
+            if (st.count > 0) full += (unsigned long long)skml_delta_bytes((unsigned int)(st.first_key - (before >= 0 ? before : 0)));
+            // inclusive scans over the 32 blocks of this chunk
+            unsigned int ic = st.count;
+            unsigned long long ib = full;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                unsigned int tc = __shfl_up_sync(0xFFFFFFFFu, ic, o);
+                unsigned long long tb = __shfl_up_sync(0xFFFFFFFFu, ib, o);
+                if (lane >= o) { ic += tc; ib += tb; }
+            }
+            if (c == (int)blockIdx.x) {
+                my_rank = run_cnt + ic - st.count;
+                my_bytes = run_bytes + ib - full;
+                my_prev = before >= 0 ? before : 0;
+                L.base_rank[g] = my_rank;
+                L.base_bytes[g] = my_bytes;
+                L.base_prev[g] = my_prev;
+            }
+            run_cnt += __shfl_sync(0xFFFFFFFFu, ic, 31);
+            run_bytes += __shfl_sync(0xFFFFFFFFu, ib, 31);
+            if (nonempty) {
+                const int hl = 31 - __clz(nonempty);
+                carry_last = __shfl_sync(0xFFFFFFFFu, st.last_key, hl);
+            }
+        }
+        if (lane == 0) {
+            L.n_g[g] = run_cnt;
+            L.bytes_g[g] = run_bytes;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int cb = s.qi.cell_bits;
+        L.off_bv = SKML_HEADER_BYTES;
+        L.off_gt = L.off_bv + skml_align16(4ull * p.q);
+        L.off_flags = L.off_gt + (unsigned long long)SKML_GROUP_ENTRY_BYTES * G;
+        unsigned long long o = L.off_flags;
+        for (int g = 0; g < G; ++g) {
+            L.flag_off[g] = o;
+            if (L.n_g[g]) o += skml_align16(8ull * ((2ull * L.n_g[g] + 63) / 64));
+        }
+        L.off_restart = o;
+        for (int g = 0; g < G; ++g) {
+            L.restart_off[g] = o;
+            if (L.n_g[g]) o += 16ull * ((L.n_g[g] + SKML_RESTART_INTERVAL - 1) / SKML_RESTART_INTERVAL);
+        }
+        L.off_tables = o;
+        unsigned long long t32 = 0;
+        for (int g = 0; g < G; ++g) {
+            unsigned int col = 0;
+            if (L.n_g[g]) {
+                col = (unsigned int)ceil((double)L.n_g[g] * p.col_ratio);
+                if (col < 1) col = 1;
+            }
+            L.col[g] = col;
+            L.table_off[g] = o;
+            L.tab32_off[g] = t32;
+            o += skml_align16((unsigned long long)p.rows * col * (cb / 8));
+            t32 += (unsigned long long)p.rows * col;
+            skml_pick_hashes(p.seed, p.step, p.rank, (unsigned int)g, p.rows, L.hash_ids[g]);
+        }
+        L.off_deltas = o;
+        for (int g = 0; g < G; ++g) {
+            L.delta_off[g] = o;
+            if (L.n_g[g]) o += skml_align16(8ull * ((L.bytes_g[g] + 7) / 8));
+        }
+        L.total_bytes = o;
+        L.overflow = (o > (unsigned long long)p.slot_capacity) || (t32 + 4 > (unsigned long long)p.tables_cap);
+        if (L.overflow) skml_set_status(p.status, SKML_CAPACITY, 0x30u);
+    }
+    __syncthreads();
+    (void)n;
+}
+
+// Header, bucket values, group table and zero padding of the delta sections (block 0).
+__device__ void write_header(const CP& p, Smem& s, long long n, int kind) {
+    if (blockIdx.x != 0) return;
+    const Layout& L = s.lay;
+    const QInfo& q = s.qi;
+    const bool sparse = kind == SKML_KIND_SPARSE && !L.overflow;
+    if (kind != SKML_KIND_EMPTY && (kind == SKML_KIND_DENSE || sparse)) {
+        float* bv = reinterpret_cast<float*>(p.payload + SKML_HEADER_BYTES);
+        const int padded = (int)(skml_align16(4ull * p.q) / 4);
+        for (int b = threadIdx.x; b < padded; b += blockDim.x) bv[b] = b < q.bin_num ? bucket_value(s, b) : 0.f;
+    }
+    if (sparse) {
+        if (threadIdx.x < p.G) {
+            const int g = threadIdx.x;
+            SkmlGroupEntry e;
+            e.n = L.n_g[g];
+            e.col_num = L.col[g];
+            for (int i = 0; i < 8; ++i) e.hash_ids[i] = L.n_g[g] ? L.hash_ids[g][i] : 0;
+            e.table_off = L.n_g[g] ? L.table_off[g] : 0;
+            e.flag_off = L.n_g[g] ? L.flag_off[g] : 0;
+            e.n_flag_words = (unsigned int)((2ull * L.n_g[g] + 63) / 64);
+            e.num_intervals = 4;
+            e.delta_off = L.n_g[g] ? L.delta_off[g] : 0;
+            e.n_delta_words = (unsigned int)((L.bytes_g[g] + 7) / 8);
+            e.flag_kind = 0;
+            e.restart_off = L.n_g[g] ? L.restart_off[g] : 0;
+            *reinterpret_cast<SkmlGroupEntry*>(p.payload + L.off_gt + (unsigned long long)g * sizeof(SkmlGroupEntry)) = e;
+            // zero the padding after the last delta byte of the group
+            unsigned long long endb = L.delta_off[g] + L.bytes_g[g];
+            unsigned long long endp = L.delta_off[g] + (L.n_g[g] ? skml_align16(8ull * ((L.bytes_g[g] + 7) / 8)) : 0);
+            for (unsigned long long a = endb; a < endp; ++a) p.payload[a] = 0;
+        }
+    }
+    if (threadIdx.x == 0) {
+        SkmlHeader h;
+        unsigned char* hb = reinterpret_cast<unsigned char*>(&h);
+        for (int i = 0; i < SKML_HEADER_BYTES; ++i) hb[i] = 0;
+        h.magic = SKML_MAGIC;
+        h.version = SKML_VERSION;
+        h.kind = (kind == SKML_KIND_SPARSE && L.overflow) ? SKML_KIND_EMPTY : (unsigned int)kind;
+        h.dtype = SKML_F32;
+        h.step = p.step;
+        h.rank = p.rank;
+        h.world = p.world;
+        h.dim = (unsigned long long)p.dim;
+        h.seed = p.seed;
+        if (p.loss_partials)
+            for (int i = 0; i < 4; ++i) h.loss_partials[i] = p.loss_partials[i];
+        h.total_bytes = SKML_HEADER_BYTES;
+        if (h.kind != SKML_KIND_EMPTY) {
+            h.nnz = (unsigned long long)n;
+            h.bin_num = (unsigned int)q.bin_num;
+            h.zero_idx = (unsigned int)q.zero_idx;
+            h.cell_bits = (unsigned int)q.cell_bits;
+            h.min_value = (double)q.minv;
+            h.max_value = (double)q.maxv;
+            h.off_bucket_values = SKML_HEADER_BYTES;
+        }
+        if (h.kind == SKML_KIND_SPARSE) {
+            h.group_num = (unsigned int)p.G;
+            h.row_num = (unsigned int)p.rows;
+            h.col_ratio = p.col_ratio;
+            h.key_encoder = SKML_KEYS_DELTA_BINARY;
+            h.restart_interval = SKML_RESTART_INTERVAL;
+            h.off_group_table = L.off_gt;
+            h.off_key_flags = L.off_flags;
+            h.off_restart = L.off_restart;
+            h.off_tables = L.off_tables;
+            h.off_key_deltas = L.off_deltas;
+            h.total_bytes = L.total_bytes;
+        } else if (h.kind == SKML_KIND_DENSE) {
+            h.off_dense_codes = SKML_HEADER_BYTES + skml_align16(4ull * p.q);
+            h.total_bytes = skml_align16(h.off_dense_codes + (unsigned long long)p.dim * (q.cell_bits / 8));
+        }
+        h.header_checksum = skml_header_checksum(&h);
+        const uint4* src = reinterpret_cast<const uint4*>(&h);
+        uint4* dst = reinterpret_cast<uint4*>(p.payload);
+        for (int i = 0; i < SKML_HEADER_BYTES / 16; ++i) dst[i] = src[i];
+    }
+}
+
+// ---------------------------------------------------------------------------
+// S5: narrow tables, store everything into the peers' slots, release the flags
+// ---------------------------------------------------------------------------
+__device__ void copy_range_to_peers(const CP& p, unsigned long long lo, unsigned long long hi) {
+    if (p.world <= 1 || hi <= lo) return;
+    const long long gsz = (long long)gridDim.x * blockDim.x, gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long units = (long long)((hi - lo) / 16);
+    const uint4* src = reinterpret_cast<const uint4*>(p.payload + lo);
+    for (long long i = gid; i < units; i += gsz) {
+        uint4 v = ld_cg_v4(src + i);
+        for (unsigned int r = 0; r < p.world; ++r)
+            if (r != p.rank) st_v4(reinterpret_cast<uint4*>(p.peer_payload[r] + lo) + i, v);
+    }
+}
+
+__device__ void finish_publish(const CP& p) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned int prev = atomicAdd(&p.ctrl[2], 1u);
+        if (prev == gridDim.x - 1) {
+            p.ctrl[2] = 0;
+            p.ctrl[4] = 0;  // the summary's min / max words go back to "nothing yet"
+            p.ctrl[5] = 0;
+            __threadfence_system();
+            for (unsigned int r = 0; r < p.world; ++r)
+                if (p.peer_flag[r]) st_release_sys(p.peer_flag[r], p.step + 1);
+        }
+    }
+}
+
+__device__ void stage_push_sparse(const CP& p, Smem& s) {
+    const Layout& L = s.lay;
+    const int G = p.G, cb = s.qi.cell_bits, per = 16 / (cb / 8);  // cells per 16-byte unit
+    if (!L.overflow) {
+        if (threadIdx.x == 0) {
+            unsigned long long u = 0;
+            for (int g = 0; g < G; ++g) {
+                s.unit_prefix[g] = u;
+                u += skml_align16((unsigned long long)p.rows * L.col[g] * (cb / 8)) / 16;
+            }
+            s.unit_prefix[G] = u;
+        }
+        __syncthreads();
+        const long long gsz = (long long)gridDim.x * blockDim.x, gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+        const long long units = (long long)s.unit_prefix[G];
+        const unsigned int zero = (unsigned int)s.qi.zero_idx;
+        for (long long u = gid; u < units; u += gsz) {
+            int g = 0;
+            while (g + 1 < G && (unsigned long long)u >= s.unit_prefix[g + 1]) ++g;
+            const long long j = u - (long long)s.unit_prefix[g];
+            const long long cells = (long long)p.rows * L.col[g];
+            const unsigned int* tab = p.tables + L.tab32_off[g];
+            unsigned int words[4] = {0, 0, 0, 0};
+            for (int t = 0; t < per; ++t) {
+                long long c = j * per + t;
+                unsigned int code = 0;
+                if (c < cells) {
+                    unsigned int cell = __ldcg(tab + c);
+                    code = cell == SKML_EMPTY_CELL ? zero : (cell & 0xFFFFu);
+                }
+                if (cb == 8) words[t >> 2] |= (code & 0xFFu) << (8 * (t & 3));
+                else words[t >> 1] |= (code & 0xFFFFu) << (16 * (t & 1));
+            }
+            uint4 v = make_uint4(words[0], words[1], words[2], words[3]);
+            const unsigned long long off = L.table_off[g] + 16ull * j;
+            st_v4(reinterpret_cast<uint4*>(p.payload + off), v);
+            for (unsigned int r = 0; r < p.world; ++r)
+                if (r != p.rank) st_v4(reinterpret_cast<uint4*>(p.peer_payload[r] + off), v);
+        }
+        copy_range_to_peers(p, 0, L.off_tables);
+        copy_range_to_peers(p, L.off_deltas, L.total_bytes);
+    } else {
+        copy_range_to_peers(p, 0, SKML_HEADER_BYTES);
+    }
+    finish_publish(p);
+}
+
+// ---------------------------------------------------------------------------
+// Kernels
+// ---------------------------------------------------------------------------
+#define STAGE_BARRIER(stage_id)                                                           \
+    if (FUSED) {                                                                          \
+        if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, stage_id)) return; \
+    }
+
+// STAGE < 0: all stages in one cooperative launch; otherwise only that stage.
+template <bool FUSED>
+__global__ void __launch_bounds__(SKML_BLOCK, 1) compress_sparse_kernel(CP p, int stage) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    Smem& s = *reinterpret_cast<Smem*>(smem_raw);
+    const long long kind = p.meta[1];
+    if (kind == SKML_KIND_DENSE) return;  // handled by the dense kernel
+    long long n = p.meta[0];
+    if (n > p.n_max) {
+        if (threadIdx.x == 0) skml_set_status(p.status, SKML_CAPACITY, 0x31u);
+        n = 0;
+    }
+    if (n <= 0) {  // empty gradient: header-only payload
+        if (FUSED || stage == 4) {
+            if (threadIdx.x == 0) {
+                s.lay.overflow = 0;
+                s.qi.bin_num = 0;
+            }
+            __syncthreads();
+            write_header(p, s, 0, SKML_KIND_EMPTY);
+        }
+        if (FUSED) {
+            if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, 9)) return;
+        }
+        if (FUSED || stage == 5) {
+            copy_range_to_peers(p, 0, SKML_HEADER_BYTES);
+            finish_publish(p);
+        }
+        return;
+    }
+    const bool given = p.given_splits != nullptr;
+    if (FUSED || stage == 1) {
+        stage_prepare(p, n);
+        if (!given) stage_summary(p, s, p.vals, n);
+    }
+    STAGE_BARRIER(1)
+    if ((FUSED || stage == 2) && !given) stage_query(p, s, n);
+    STAGE_BARRIER(2)
+    if (FUSED || stage == 3) {
+        load_quantizer(p, s);
+        if (s.qi.bin_num > SKML_GPU_MAX_BINS) {
+            if (threadIdx.x == 0) skml_set_status(p.status, SKML_BAD_INPUT, 0x32u);
+            return;
+        }
+        element_pass<false>(p, s, n);
+    }
+    STAGE_BARRIER(3)
+    if (FUSED || stage == 4) {
+        if (!FUSED) load_quantizer(p, s);
+        compute_layout(p, s, n);
+        write_header(p, s, n, SKML_KIND_SPARSE);
+        element_pass<true>(p, s, n);
+    }
+    STAGE_BARRIER(4)
+    if (FUSED || stage == 5) {
+        if (!FUSED) {
+            load_quantizer(p, s);
+            compute_layout(p, s, n);
+        }
+        stage_push_sparse(p, s);
+    }
+}
+
+// Dense kind: one narrow bucket code per coordinate, written straight into the local
+// payload and every peer's slot.
+template <bool FUSED>
+__global__ void __launch_bounds__(SKML_BLOCK, 1) compress_dense_kernel(CP p, int stage) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    Smem& s = *reinterpret_cast<Smem*>(smem_raw);
+    if (p.meta[1] != SKML_KIND_DENSE) return;
+    const long long n = p.dim;
+    const bool given = p.given_splits != nullptr;
+    if ((FUSED || stage == 1) && !given) stage_summary(p, s, p.vals, n);
+    STAGE_BARRIER(1)
+    if ((FUSED || stage == 2) && !given) stage_query(p, s, n);
+    STAGE_BARRIER(2)
+    if (FUSED || stage == 3) {
+        load_quantizer(p, s);
+        if (s.qi.bin_num > SKML_GPU_MAX_BINS) {
+            if (threadIdx.x == 0) skml_set_status(p.status, SKML_BAD_INPUT, 0x33u);
+            return;
+        }
+        if (threadIdx.x == 0) s.lay.overflow = 0;
+        __syncthreads();
+        const int cb = s.qi.cell_bits, per = 16 / (cb / 8);
+        const unsigned long long off_codes = SKML_HEADER_BYTES + skml_align16(4ull * p.q);
+        const unsigned long long total = skml_align16(off_codes + (unsigned long long)n * (cb / 8));
+        if (total > (unsigned long long)p.slot_capacity) {
+            if (threadIdx.x == 0) skml_set_status(p.status, SKML_CAPACITY, 0x34u);
+            return;
+        }
+        write_header(p, s, n, SKML_KIND_DENSE);
+        const long long units = (n + per - 1) / per;
+        const long long gsz = (long long)gridDim.x * blockDim.x, gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+        for (long long u = gid; u < units; u += gsz) {
+            unsigned int words[4] = {0, 0, 0, 0};
+            for (int t = 0; t < per; ++t) {
+                long long i = u * per + t;
+                unsigned int code = 0;
+                if (i < n) code = (unsigned int)upper_bound_f(s.splits, s.qi.nsplits, p.vals[i]);
+                if (cb == 8) words[t >> 2] |= (code & 0xFFu) << (8 * (t & 3));
+                else words[t >> 1] |= (code & 0xFFFFu) << (16 * (t & 1));
+            }
+            uint4 v = make_uint4(words[0], words[1], words[2], words[3]);
+            st_v4(reinterpret_cast<uint4*>(p.payload + off_codes) + u, v);
+            for (unsigned int r = 0; r < p.world; ++r)
+                if (r != p.rank) st_v4(reinterpret_cast<uint4*>(p.peer_payload[r] + off_codes) + u, v);
+        }
+    }
+    STAGE_BARRIER(3)
+    if (FUSED || stage == 4) {
+        copy_range_to_peers(p, 0, SKML_HEADER_BYTES + skml_align16(4ull * p.q));
+        finish_publish(p);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host launchers
+// ---------------------------------------------------------------------------
+static int device_sms() {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return sms > 0 ? sms : 148;
+}
+
+static int fill_params(const SkmlCompressArgs* a, CP& p, int& grid) {
+    if (!a || !a->meta || !a->payload || !a->workspace || !a->status) return (int)cudaErrorInvalidValue;
+    if (a->bin_num < 2 || a->bin_num > SKML_GPU_MAX_BINS) return (int)cudaErrorInvalidValue;
+    if (a->group_num < 1 || a->group_num > SKML_MAX_GROUPS) return (int)cudaErrorInvalidValue;
+    if (a->row_num < 1 || a->row_num > SKML_MAX_ROWS) return (int)cudaErrorInvalidValue;
+    if (a->world < 1 || a->world > SKML_MAX_PEERS || a->rank < 0 || a->rank >= a->world) return (int)cudaErrorInvalidValue;
+    if (a->n_max >= (1ll << 31) || a->dim >= (1ll << 31)) return (int)cudaErrorInvalidValue;
+    grid = a->grid > 0 ? (int)a->grid : device_sms();
+    if (grid > MAX_GRID) grid = MAX_GRID;
+    WsLayout L = ws_layout(a->n_max, a->bin_num, a->group_num, a->row_num, a->col_ratio, grid);
+    if (L.total > a->workspace_bytes) return (int)cudaErrorInvalidValue;
+    p.keys = a->keys;
+    p.vals = a->vals;
+    p.meta = a->meta;
+    p.n_max = a->n_max;
+    p.dim = a->dim;
+    p.q = (int)a->bin_num;
+    p.G = (int)a->group_num;
+    p.rows = (int)a->row_num;
+    p.col_ratio = a->col_ratio;
+    p.seed = a->seed;
+    p.step = a->step;
+    p.rank = (unsigned int)a->rank;
+    p.world = (unsigned int)a->world;
+    p.loss_partials = a->loss_partials;
+    p.payload = a->payload;
+    p.slot_capacity = a->slot_capacity;
+    for (int i = 0; i < SKML_MAX_PEERS; ++i) {
+        p.peer_payload[i] = a->peer_payload[i];
+        p.peer_flag[i] = a->peer_flag[i];
+    }
+    unsigned char* ws = a->workspace;
+    p.ctrl = reinterpret_cast<unsigned int*>(ws + L.ctrl);
+    p.run_vals = reinterpret_cast<unsigned int*>(ws + L.run_vals);
+    p.run_cnt = reinterpret_cast<unsigned int*>(ws + L.run_cnt);
+    p.run_w = reinterpret_cast<unsigned long long*>(ws + L.run_w);
+    p.splits_raw = reinterpret_cast<unsigned int*>(ws + L.splits_raw);
+    p.stats = reinterpret_cast<CtaStat*>(ws + L.stats);
+    p.bins = reinterpret_cast<unsigned short*>(ws + L.bins);
+    p.tables = reinterpret_cast<unsigned int*>(ws + L.tables);
+    p.tables_cap = L.tables_cap;
+    p.status = a->status;
+    p.budget = a->budget_cycles > 0 ? a->budget_cycles : 2000000000ll;
+    p.given_splits = a->given_splits;
+    p.n_given = (int)a->n_given;
+    p.given_min = (float)a->given_min;
+    p.given_max = (float)a->given_max;
+    return 0;
+}
+
+template <class K>
+static int launch_stages(K fused_kernel, K staged_kernel, CP& p, int grid, bool fused, int nstages, cudaStream_t stream) {
+    static bool attr_done = false;
+    (void)attr_done;
+    cudaError_t e;
+    e = cudaFuncSetAttribute(fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem));
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem));
+    if (e != cudaSuccess) return (int)e;
+    if (fused) {
+        int per_sm = 0;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_kernel, SKML_BLOCK, sizeof(Smem));
+        if (per_sm < 1) return (int)cudaErrorLaunchOutOfResources;
+        int max_grid = per_sm * device_sms();
+        if (grid > max_grid) grid = max_grid;
+        int stage = -1;
+        void* args[] = {&p, &stage};
+        e = cudaLaunchCooperativeKernel((const void*)fused_kernel, dim3(grid), dim3(SKML_BLOCK), args, sizeof(Smem), stream);
+        return (int)e;
+    }
+    for (int st = 1; st <= nstages; ++st) {
+        staged_kernel<<<grid, SKML_BLOCK, sizeof(Smem), stream>>>(p, st);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
+}
+
+extern "C" int skml_compress_sparse(const SkmlCompressArgs* a, void* stream) {
+    CP p;
+    int grid = 0;
+    int rc = fill_params(a, p, grid);
+    if (rc) return rc;
+    return launch_stages(compress_sparse_kernel<true>, compress_sparse_kernel<false>, p, grid, a->fused != 0, 5,
+                         (cudaStream_t)stream);
+}
+
+extern "C" int skml_compress_dense(const SkmlCompressArgs* a, void* stream) {
+    CP p;
+    int grid = 0;
+    int rc = fill_params(a, p, grid);
+    if (rc) return rc;
+    return launch_stages(compress_dense_kernel<true>, compress_dense_kernel<false>, p, grid, a->fused != 0, 4,
+                         (cudaStream_t)stream);
+}

@@ -1,0 +1,379 @@
+// Fused decode + aggregate + update for sm_100a: the receiving side of the gradient
+// exchange in one persistent cooperative kernel.
+//   D0  bounded wait for the arrival flags of all ranks' payloads (written by the peers'
+//       compress kernels straight into this GPU's memory), header validation
+//   D1  per 1024-key chunk (restart points make chunks independent): flag bits -> delta
+//       widths -> scan -> gather -> prefix sum = keys; grouped MinMaxSketch query
+//       (furthest-from-zero over the rows); dequantize; add value / world into 64-bit
+//       fixed-point accumulators (integer adds commute, so every replica gets bit-identical
+//       sums whatever the arrival order)
+//   D2  each touched coordinate is claimed once (atomic exchange with zero) and updated:
+//       SGD, or the reference's lazy Adam with per-epoch beta powers
+//
+// Reference behaviour restated (paths inside the reference project):
+//   sketch/.../binary/DeltaBinaryEncoder.java:42-53 (key decode),
+//   sketch/.../sketch/frequency/MinMaxSketch.java:64-73, GroupedMinMaxSketch.java:123-146,
+//   ml/.../gradient/SketchGradient.scala:57-68, Gradient.scala:44-49 (sum over workers),
+//   ml/.../algorithm/GeneralizedLinearModel.scala:150 (1/workerNum),
+//   ml/.../objective/GradientDescent.scala:89-117, Adam.scala:27-77 (updates).
+#include <math.h>
+
+#include "skml_api.h"
+#include "skml_device.cuh"
+
+#define DEC_MAX_ITEMS (SKML_MAX_PEERS * SKML_MAX_GROUPS)
+
+struct DP {
+    const unsigned char* payload[SKML_MAX_PEERS];
+    const unsigned long long* flag[SKML_MAX_PEERS];
+    int world;
+    long long slot_capacity;
+    unsigned long long step;
+    long long dim;
+    float* w;
+    float* adam_m;
+    float* adam_v;
+    float lr, adam_scale;
+    long long* acc;
+    int* key_scratch;
+    long long key_capacity;
+    double* loss_out;
+    float* out_sum;
+    unsigned int* ctrl;
+    unsigned int* status;
+    long long budget;
+};
+
+struct DecItem {  // one (rank, group) key stream
+    const unsigned char* base;
+    SkmlGroupEntry e;
+    unsigned long long chunk_prefix, key_prefix;
+    unsigned int zero, cell_bits, rows;
+    unsigned long long off_bv;
+};
+
+struct DecSmem {
+    SkmlHeader hdr[SKML_MAX_PEERS];
+    DecItem items[DEC_MAX_ITEMS];
+    int nitems;
+    unsigned long long total_chunks, total_keys;
+    int any_dense;
+    int shift;       // fixed-point: accumulator = value * 2^shift
+    double inv_world;
+    int ok;
+};
+
+__device__ __forceinline__ long long to_fixed(double v, int shift) { return __double2ll_rn(ldexp(v, shift)); }
+__device__ __forceinline__ double from_fixed(long long a, int shift) { return ldexp((double)a, -shift); }
+
+__device__ __forceinline__ void apply_one(const DP& p, long long k, float g) {
+    if (p.out_sum) {
+        p.out_sum[k] = g;
+    } else if (!p.adam_v) {
+        p.w[k] -= p.lr * g;
+    } else {
+        float mt = 0.9f * p.adam_m[k] + 0.1f * g;
+        float vt = 0.999f * p.adam_v[k] + 0.001f * g * g;
+        p.w[k] -= p.lr * p.adam_scale * mt / (sqrtf(vt) + 1e-8f);
+        p.adam_m[k] = mt;
+        p.adam_v[k] = vt;
+    }
+}
+
+// D0: wait, validate, build the work table (identically in every block).
+__device__ bool decode_prepare(const DP& p, DecSmem& s) {
+    if (threadIdx.x == 0) {
+        s.ok = 1;
+        for (int r = 0; r < p.world; ++r)
+            if (p.flag[r] && !skml_wait_flag(p.flag[r], p.step + 1, p.status, p.budget, (unsigned int)r)) {
+                s.ok = 0;
+                break;
+            }
+    }
+    __syncthreads();
+    if (!s.ok) return false;
+    // headers -> shared memory (L2 loads: the bytes were written by other GPUs)
+    for (int t = threadIdx.x; t < p.world * (SKML_HEADER_BYTES / 16); t += blockDim.x) {
+        int r = t / (SKML_HEADER_BYTES / 16), i = t % (SKML_HEADER_BYTES / 16);
+        reinterpret_cast<uint4*>(&s.hdr[r])[i] = ld_cg_v4(reinterpret_cast<const uint4*>(p.payload[r]) + i);
+    }
+    __syncthreads();
+    if (threadIdx.x < p.world) {
+        const SkmlHeader& h = s.hdr[threadIdx.x];
+        bool good = h.magic == SKML_MAGIC && h.version == SKML_VERSION && h.header_checksum == skml_header_checksum(&h) &&
+                    h.step == p.step && h.rank == (unsigned int)threadIdx.x && h.dim == (unsigned long long)p.dim &&
+                    h.total_bytes <= (unsigned long long)p.slot_capacity && h.dtype == SKML_F32 &&
+                    h.group_num <= SKML_MAX_GROUPS && h.row_num <= SKML_MAX_ROWS && h.kind <= SKML_KIND_DENSE &&
+                    (h.kind == SKML_KIND_EMPTY || (h.bin_num >= 1 && h.bin_num <= SKML_GPU_MAX_BINS && h.zero_idx < h.bin_num)) &&
+                    (h.kind != SKML_KIND_SPARSE || (h.key_encoder == SKML_KEYS_DELTA_BINARY &&
+                                                    h.restart_interval == SKML_RESTART_INTERVAL &&
+                                                    (h.cell_bits == 8 || h.cell_bits == 16)));
+        if (!good) {
+            skml_set_status(p.status, SKML_BAD_HEADER, (unsigned int)threadIdx.x);
+            s.ok = 0;
+        }
+    }
+    __syncthreads();
+    if (!s.ok) return false;
+    if (threadIdx.x == 0) {
+        int ni = 0;
+        unsigned long long chunks = 0, keys = 0;
+        int dense = 0;
+        double mx = 0.0;
+        for (int r = 0; r < p.world; ++r) {
+            const SkmlHeader& h = s.hdr[r];
+            if (h.kind == SKML_KIND_EMPTY) continue;
+            mx = fmax(mx, fmax(fabs(h.min_value), fabs(h.max_value)));
+            if (h.kind == SKML_KIND_DENSE) {
+                dense = 1;
+                continue;
+            }
+            for (unsigned int g = 0; g < h.group_num; ++g) {
+                DecItem& it = s.items[ni];
+                it.base = p.payload[r];
+                it.e = *reinterpret_cast<const SkmlGroupEntry*>(p.payload[r] + h.off_group_table + g * sizeof(SkmlGroupEntry));
+                if (it.e.n == 0) continue;
+                const unsigned long long lim = h.total_bytes;
+                bool good = it.e.col_num > 0 && it.e.table_off + (unsigned long long)h.row_num * it.e.col_num * (h.cell_bits / 8) <= lim &&
+                            it.e.flag_off + 8ull * it.e.n_flag_words <= lim && it.e.delta_off + 8ull * it.e.n_delta_words <= lim &&
+                            it.e.restart_off + 16ull * ((it.e.n + SKML_RESTART_INTERVAL - 1) / SKML_RESTART_INTERVAL) <= lim &&
+                            2ull * it.e.n <= 64ull * it.e.n_flag_words;
+                if (!good) {
+                    skml_set_status(p.status, SKML_BAD_HEADER, 0x100u | (unsigned int)r);
+                    s.ok = 0;
+                    break;
+                }
+                it.chunk_prefix = chunks;
+                it.key_prefix = keys;
+                it.zero = h.zero_idx;
+                it.cell_bits = h.cell_bits;
+                it.rows = h.row_num;
+                it.off_bv = h.off_bucket_values;
+                chunks += (it.e.n + SKML_RESTART_INTERVAL - 1) / SKML_RESTART_INTERVAL;
+                keys += it.e.n;
+                ++ni;
+            }
+        }
+        if (keys > (unsigned long long)p.key_capacity) {
+            skml_set_status(p.status, SKML_CAPACITY, 0x40u);
+            s.ok = 0;
+        }
+        s.nitems = ni;
+        s.total_chunks = chunks;
+        s.total_keys = keys;
+        s.any_dense = dense;
+        int e = 0;
+        if (mx > 0.0 && isfinite(mx)) frexp(mx, &e);
+        s.shift = 60 - e;
+        s.inv_world = 1.0 / (double)p.world;
+    }
+    __syncthreads();
+    return s.ok != 0;
+}
+
+// D1 for sparse payloads: chunk loop.
+__device__ void decode_accumulate(const DP& p, DecSmem& s) {
+    for (unsigned long long ch = blockIdx.x; ch < s.total_chunks; ch += gridDim.x) {
+        int it_i = 0;
+        while (it_i + 1 < s.nitems && ch >= s.items[it_i + 1].chunk_prefix) ++it_i;
+        const DecItem& it = s.items[it_i];
+        const unsigned int j = (unsigned int)(ch - it.chunk_prefix);
+        const unsigned int first = j * SKML_RESTART_INTERVAL;
+        const unsigned int cnt = min((unsigned int)SKML_RESTART_INTERVAL, it.e.n - first);
+        const SkmlRestart rs = *reinterpret_cast<const SkmlRestart*>(it.base + it.e.restart_off + 16ull * j);
+        const unsigned int i = threadIdx.x;
+        unsigned int w = 0;
+        if (i < cnt) {
+            const unsigned long long fb = (unsigned long long)rs.flag_bit_off + 2ull * i;
+            const unsigned int word = __ldcg(reinterpret_cast<const unsigned int*>(it.base + it.e.flag_off) + (fb >> 5));
+            const unsigned int b = (word >> (fb & 31)) & 3u;
+            w = (((b & 1u) << 1) | (b >> 1)) + 1u;  // stream order is most significant bit first
+            if (w == 3) w = 4;                      // flag value 2 is never written
+        }
+        unsigned int total_w;
+        const unsigned int boff = block_exclusive_scan<unsigned int>(w, &total_w);
+        unsigned int delta = 0;
+        if (i < cnt) {
+            const unsigned long long byte0 = (rs.delta_bit_off >> 3) + boff;
+            if (byte0 + w <= 8ull * it.e.n_delta_words) {
+                const unsigned char* src = it.base + it.e.delta_off + byte0;
+                for (unsigned int t = 0; t < w; ++t) delta = (delta << 8) | skml_brev8(__ldcg(src + t));
+            }
+        }
+        unsigned int total_d;
+        const unsigned int dex = block_exclusive_scan<unsigned int>(delta, &total_d);
+        if (i < cnt) {
+            const unsigned int key = rs.prev_key + dex + delta;
+            p.key_scratch[it.key_prefix + first + i] = (int)key;
+            if (key < (unsigned long long)p.dim) {
+                const int col = (int)it.e.col_num;
+                const int zero = (int)it.zero;
+                int res = zero, best = 0;
+                for (unsigned int r = 0; r < it.rows; ++r) {
+                    const unsigned long long c = (unsigned long long)r * col + (unsigned int)skml_hash(it.e.hash_ids[r], (int)key, col);
+                    int cell;
+                    if (it.cell_bits == 8) cell = __ldcg(it.base + it.e.table_off + c);
+                    else cell = __ldcg(reinterpret_cast<const unsigned short*>(it.base + it.e.table_off) + c);
+                    int d = cell - zero;
+                    if (d < 0) d = -d;
+                    if (d > best) {
+                        best = d;
+                        res = cell;
+                    }
+                }
+                const float bv = __ldcg(reinterpret_cast<const float*>(it.base + it.off_bv) + res);
+                const long long fx = to_fixed((double)bv * s.inv_world, s.shift);
+                if (fx) atomicAdd(reinterpret_cast<unsigned long long*>(p.acc + key), (unsigned long long)fx);
+            } else {
+                skml_set_status(p.status, SKML_BAD_HEADER, 0x200u);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// D1 for dense payloads: every coordinate carries a bucket code.
+__device__ void decode_accumulate_dense(const DP& p, DecSmem& s) {
+    const long long gsz = (long long)gridDim.x * blockDim.x, gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    for (int r = 0; r < p.world; ++r) {
+        const SkmlHeader& h = s.hdr[r];
+        if (h.kind != SKML_KIND_DENSE) continue;
+        const unsigned char* codes = p.payload[r] + h.off_dense_codes;
+        const float* bv = reinterpret_cast<const float*>(p.payload[r] + h.off_bucket_values);
+        for (long long i = gid; i < p.dim; i += gsz) {
+            unsigned int code = h.cell_bits == 8 ? __ldcg(codes + i) : __ldcg(reinterpret_cast<const unsigned short*>(codes) + i);
+            if (code >= h.bin_num) code = h.zero_idx;
+            const long long fx = to_fixed((double)__ldcg(bv + code) * s.inv_world, s.shift);
+            if (fx) atomicAdd(reinterpret_cast<unsigned long long*>(p.acc + i), (unsigned long long)fx);
+        }
+    }
+}
+
+// D2: claim and update.
+__device__ void decode_update(const DP& p, DecSmem& s) {
+    const long long gsz = (long long)gridDim.x * blockDim.x, gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (s.any_dense) {
+        for (long long i = gid; i < p.dim; i += gsz) {
+            long long a = p.acc[i];
+            if (a) {
+                p.acc[i] = 0;
+                apply_one(p, i, (float)from_fixed(a, s.shift));
+            }
+        }
+    } else {
+        for (long long t = gid; t < (long long)s.total_keys; t += gsz) {
+            const long long k = (unsigned int)p.key_scratch[t];
+            if (k >= p.dim) continue;
+            const long long a = (long long)atomicExch(reinterpret_cast<unsigned long long*>(p.acc + k), 0ull);
+            if (a) apply_one(p, k, (float)from_fixed(a, s.shift));
+        }
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0 && p.loss_out) {
+        double l[4] = {0, 0, 0, 0};
+        for (int r = 0; r < p.world; ++r)
+            for (int i = 0; i < 4; ++i) l[i] += s.hdr[r].loss_partials[i];
+        for (int i = 0; i < 4; ++i) p.loss_out[i] = l[i];
+    }
+}
+
+template <bool FUSED>
+__global__ void __launch_bounds__(SKML_BLOCK, 1) decode_update_kernel(DP p, int stage) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    DecSmem& s = *reinterpret_cast<DecSmem*>(smem_raw);
+    if (!decode_prepare(p, s)) return;
+    if (FUSED || stage == 1) {
+        decode_accumulate(p, s);
+        if (s.any_dense) decode_accumulate_dense(p, s);
+    }
+    if (FUSED) {
+        if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, 0x21u)) return;
+    }
+    if (FUSED || stage == 2) decode_update(p, s);
+}
+
+extern "C" long long skml_decode_workspace_bytes(long long world, long long group_num) {
+    (void)world;
+    (void)group_num;
+    return 256;
+}
+
+extern "C" int skml_decode_update(const SkmlDecodeArgs* a, void* stream_) {
+    if (!a || !a->acc || !a->key_scratch || !a->workspace || !a->status) return (int)cudaErrorInvalidValue;
+    if (a->world < 1 || a->world > SKML_MAX_PEERS) return (int)cudaErrorInvalidValue;
+    if (!a->out_sum && !a->w) return (int)cudaErrorInvalidValue;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    DP p;
+    for (int i = 0; i < SKML_MAX_PEERS; ++i) {
+        p.payload[i] = a->payload[i];
+        p.flag[i] = a->flag[i];
+    }
+    p.world = (int)a->world;
+    p.slot_capacity = a->slot_capacity;
+    p.step = a->step;
+    p.dim = a->dim;
+    p.w = a->w;
+    p.adam_m = a->adam_m;
+    p.adam_v = a->adam_v;
+    p.lr = (float)a->lr;
+    p.adam_scale = (float)a->adam_scale;
+    p.acc = a->acc;
+    p.key_scratch = a->key_scratch;
+    p.key_capacity = a->key_capacity;
+    p.loss_out = a->loss_out;
+    p.out_sum = a->out_sum;
+    p.ctrl = reinterpret_cast<unsigned int*>(a->workspace);
+    p.status = a->status;
+    p.budget = a->budget_cycles > 0 ? a->budget_cycles : 2000000000ll;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int grid = a->grid > 0 ? (int)a->grid : (sms > 0 ? sms : 148);
+    cudaError_t e = cudaFuncSetAttribute(decode_update_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DecSmem));
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(decode_update_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DecSmem));
+    if (e != cudaSuccess) return (int)e;
+    if (a->fused) {
+        int per_sm = 0;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_update_kernel<true>, SKML_BLOCK, sizeof(DecSmem));
+        if (per_sm < 1) return (int)cudaErrorLaunchOutOfResources;
+        if (grid > per_sm * sms) grid = per_sm * sms;
+        int stage = -1;
+        void* args[] = {&p, &stage};
+        return (int)cudaLaunchCooperativeKernel((const void*)decode_update_kernel<true>, dim3(grid), dim3(SKML_BLOCK), args,
+                                                sizeof(DecSmem), stream);
+    }
+    for (int st = 1; st <= 2; ++st) {
+        decode_update_kernel<false><<<grid, SKML_BLOCK, sizeof(DecSmem), stream>>>(p, st);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Peer memory helpers (one process per GPU, same node).
+// ---------------------------------------------------------------------------
+extern "C" int skml_ipc_get_handle(void* dev_ptr, unsigned char* handle64) {
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, dev_ptr);
+    if (e != cudaSuccess) return (int)e;
+    memcpy(handle64, &h, sizeof(h));
+    return 0;
+}
+
+extern "C" int skml_ipc_open_handle(const unsigned char* handle64, void** dev_ptr) {
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    return (int)cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess);
+}
+
+extern "C" int skml_ipc_close(void* dev_ptr) { return (int)cudaIpcCloseMemHandle(dev_ptr); }
+
+extern "C" int skml_enable_peer_access(int peer_device) {
+    cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        cudaGetLastError();
+        return 0;
+    }
+    return (int)e;
+}

@@ -1,0 +1,600 @@
+// Sparse generalized-linear-model numerics for sm_100a:
+//   * skml_glm_grad      : per-row margin, loss and coefficient, fused with the scatter of
+//                          coefficient * feature into the dense gradient accumulator
+//                          (row tiles staged into shared memory by 1-D bulk TMA copies,
+//                          one warp per row, shuffle reductions, hot columns kept in
+//                          shared memory, touched-coordinate bitmap)
+//   * skml_compact_*     : touched bitmap -> sorted (key, value) list with L2 term and
+//                          the |v| > 1e-8 filter; decides sparse vs dense kind
+//   * skml_glm_validate  : margin, loss and confusion counts over a validation shard
+//   * skml_update_*      : SGD / lazy-Adam updates used by the uncompressed baselines
+//
+// Reference behaviour restated (paths inside the reference project, module `ml`):
+//   objective/GradientDescent.scala:23-51,70-87 (minibatch gradient, 1/batch, L2 on the
+//   gradient's own coordinates), objective/Loss.scala:82-137 (log / hinge / square loss and
+//   their negative derivatives, +-18 cut-offs), gradient/DenseDoubleGradient.scala:51-95
+//   (scatter-add, countNNZ with |v| > 1e-8, toSparse, dense iff nnz > 2/3 dim),
+//   util/ValidationUtil.scala:12-41, objective/Adam.scala:27-77,
+//   objective/GradientDescent.scala:89-132.
+#include <math.h>
+
+#include "skml_api.h"
+#include "skml_device.cuh"
+
+#define GRAD_THREADS 512
+#define GRAD_WARPS (GRAD_THREADS / 32)
+#define GRAD_TILE_CAP 4096  // elements of one staged tile (cols and values each)
+#define SKML_EPS 1e-8f
+
+__device__ __forceinline__ float glm_loss(int loss_id, float pre, float y) {
+    if (loss_id == 0) {
+        float z = pre * y;
+        if (z > 18.f) return __expf(-z);
+        if (z < -18.f) return -z;
+        return log1pf(__expf(-z));
+    } else if (loss_id == 1) {
+        float z = pre * y;
+        return z < 1.f ? 1.f - z : 0.f;
+    }
+    float d = pre - y;
+    return 0.5f * d * d;
+}
+
+// negative derivative of the loss with respect to the prediction
+__device__ __forceinline__ float glm_grad(int loss_id, float pre, float y) {
+    if (loss_id == 0) {
+        float z = pre * y;
+        if (z > 18.f) return y * __expf(-z);
+        if (z < -18.f) return y;
+        return y / (1.f + __expf(z));
+    } else if (loss_id == 1) {
+        return pre * y <= 1.f ? y : 0.f;
+    }
+    return y - pre;
+}
+
+__device__ __forceinline__ void red_add_f32(float* p, float v) {
+    asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+
+struct GradSmem {
+    uint64_t bar[2];
+};
+
+// MODE 0: training (scatter), MODE 1: validation (loss + confusion counts only)
+template <int MODE>
+__global__ void __launch_bounds__(GRAD_THREADS)
+glm_rows_kernel(const long long* __restrict__ rowptr, const int* __restrict__ cols, const float* __restrict__ vals,
+                const float* __restrict__ labels, long long row_lo, long long row_cnt, int rows_per_tile,
+                long long nnz_padded, const float* __restrict__ w, float* __restrict__ g,
+                unsigned int* __restrict__ bitmap, int loss_id, float inv_batch, int hot, double* __restrict__ acc,
+                float* __restrict__ margins, unsigned int* status, long long budget) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    // layout: [2 stages x cols][2 stages x vals][hot floats]; barriers in static smem
+    __shared__ GradSmem sb;
+    int* s_cols = reinterpret_cast<int*>(smem_raw);
+    float* s_vals = reinterpret_cast<float*>(smem_raw + 2 * GRAD_TILE_CAP * sizeof(int));
+    float* s_hot = reinterpret_cast<float*>(smem_raw + 4 * GRAD_TILE_CAP * sizeof(int));
+    const bool has_vals = vals != nullptr;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    if (MODE == 0)
+        for (int i = threadIdx.x; i < hot; i += blockDim.x) s_hot[i] = 0.f;
+    if (threadIdx.x == 0) {
+        mbar_init(&sb.bar[0], 1);
+        mbar_init(&sb.bar[1], 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    const long long ntiles = (row_cnt + rows_per_tile - 1) / rows_per_tile;
+    double loss_sum = 0.0;
+    unsigned int tp = 0, tn = 0, fp = 0, fn = 0;
+    unsigned int phase[2] = {0, 0};
+
+    // Issues the bulk copies of one tile into `stage`; returns false when the tile does
+    // not fit the staging buffer (it is then read with plain loads).
+    auto tile_span = [&](long long tile, long long& a0, long long& a1) -> bool {
+        long long r0 = row_lo + tile * rows_per_tile;
+        long long r1 = r0 + rows_per_tile;
+        if (r1 > row_lo + row_cnt) r1 = row_lo + row_cnt;
+        long long e0 = rowptr[r0], e1 = rowptr[r1];
+        a0 = e0 & ~3ll;
+        a1 = (e1 + 3ll) & ~3ll;
+        if (a1 > nnz_padded) a1 = nnz_padded;
+        return (a1 - a0) <= GRAD_TILE_CAP && a1 > a0;
+    };
+    auto issue = [&](long long tile, int stage) {
+        long long a0, a1;
+        if (!tile_span(tile, a0, a1)) return;
+        unsigned int bytes = (unsigned int)(a1 - a0) * 4u;
+        mbar_expect_tx(&sb.bar[stage], has_vals ? 2 * bytes : bytes);
+        bulk_g2s(s_cols + stage * GRAD_TILE_CAP, cols + a0, bytes, &sb.bar[stage]);
+        if (has_vals) bulk_g2s(s_vals + stage * GRAD_TILE_CAP, vals + a0, bytes, &sb.bar[stage]);
+    };
+
+    long long tile = blockIdx.x;
+    if (tile < ntiles && threadIdx.x == 0) issue(tile, 0);
+    int stage = 0;
+    for (; tile < ntiles; tile += gridDim.x, stage ^= 1) {
+        long long next = tile + gridDim.x;
+        if (next < ntiles && threadIdx.x == 0) issue(next, stage ^ 1);
+        long long a0, a1;
+        bool staged = tile_span(tile, a0, a1);
+        if (staged) {
+            if (!mbar_wait(&sb.bar[stage], phase[stage], budget)) {
+                staged = false;  // never expected; read from global memory instead
+                if (threadIdx.x == 0) skml_set_status(status, SKML_TIMEOUT_BARRIER, 0x10u);
+            }
+            phase[stage] ^= 1;
+        }
+        const int* tc = s_cols + stage * GRAD_TILE_CAP;
+        const float* tv = s_vals + stage * GRAD_TILE_CAP;
+        long long r0 = row_lo + tile * rows_per_tile;
+        long long r1 = r0 + rows_per_tile;
+        if (r1 > row_lo + row_cnt) r1 = row_lo + row_cnt;
+        for (long long r = r0 + warp; r < r1; r += GRAD_WARPS) {
+            long long e0 = rowptr[r], e1 = rowptr[r + 1];
+            float sum = 0.f;
+            for (long long e = e0 + lane; e < e1; e += 32) {
+                int c = staged ? tc[e - a0] : cols[e];
+                float v = has_vals ? (staged ? tv[e - a0] : vals[e]) : 1.f;
+                sum = fmaf(__ldg(w + c), v, sum);
+            }
+            float pre = warp_sum(sum);
+            float y = labels[r];
+            if (MODE == 0) {
+                float coef = -glm_grad(loss_id, pre, y) * inv_batch;
+                if (lane == 0) loss_sum += (double)glm_loss(loss_id, pre, y);
+                if (coef != 0.f) {
+                    for (long long e = e0 + lane; e < e1; e += 32) {
+                        int c = staged ? tc[e - a0] : cols[e];
+                        float v = has_vals ? (staged ? tv[e - a0] : vals[e]) : 1.f;
+                        float contrib = coef * v;
+                        if (c < hot) {
+                            atomicAdd(&s_hot[c], contrib);
+                        } else {
+                            red_add_f32(g + c, contrib);
+                            unsigned int bit = 1u << (c & 31);
+                            unsigned int* word = bitmap + (c >> 5);
+                            if (!(*(volatile unsigned int*)word & bit)) atomicOr(word, bit);
+                        }
+                    }
+                }
+            } else {
+                if (lane == 0) {
+                    loss_sum += (double)glm_loss(loss_id, pre, y);
+                    float z = pre * y;
+                    if (z > 0.f) {
+                        if (pre > 0.f) ++tp; else ++tn;
+                    } else if (z < 0.f) {
+                        if (pre > 0.f) ++fp; else ++fn;
+                    }
+                    if (margins) margins[r - row_lo] = pre;
+                }
+            }
+        }
+        __syncthreads();  // everyone is done with `stage` before it is refilled
+    }
+
+    if (MODE == 0) {
+        // flush the hot columns: one red.add per non-zero entry, one atomicOr per 32 columns
+        for (int base = warp * 32; base < hot; base += GRAD_WARPS * 32) {
+            int i = base + lane;
+            float v = i < hot ? s_hot[i] : 0.f;
+            unsigned int m = __ballot_sync(0xFFFFFFFFu, v != 0.f);
+            if (v != 0.f) red_add_f32(g + i, v);
+            if (lane == 0 && m) atomicOr(bitmap + (base >> 5), m);
+        }
+    }
+    double tot = block_sum_double(loss_sum);
+    if (threadIdx.x == 0 && tot != 0.0) atomicAdd(&acc[0], tot);
+    if (MODE == 1) {
+        double c0 = block_sum_double((double)tp), c1 = block_sum_double((double)tn);
+        double c2 = block_sum_double((double)fp), c3 = block_sum_double((double)fn);
+        if (threadIdx.x == 0) {
+            if (c0 != 0.0) atomicAdd(&acc[1], c0);
+            if (c1 != 0.0) atomicAdd(&acc[2], c1);
+            if (c2 != 0.0) atomicAdd(&acc[3], c2);
+            if (c3 != 0.0) atomicAdd(&acc[4], c3);
+        }
+    }
+}
+
+static int g_sm_count = 0;
+static int sm_count() {
+    if (g_sm_count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (g_sm_count <= 0) g_sm_count = 148;
+    }
+    return g_sm_count;
+}
+
+static int grad_launch(int mode, const long long* rowptr, const int* cols, const float* vals, const float* labels,
+                       long long row_lo, long long row_cnt, long long nnz_padded, double avg_nnz, const float* w,
+                       float* g, unsigned int* bitmap, int loss_id, float inv_batch, int hot, double* acc,
+                       float* margins, unsigned int* status, long long budget, cudaStream_t stream) {
+    if (row_cnt <= 0) return 0;
+    if (hot < 0) hot = 0;
+    if (hot > 16384) hot = 16384;
+    hot &= ~31;
+    if (mode != 0) hot = 0;
+    int rpt = (int)(GRAD_TILE_CAP * 0.8 / (avg_nnz > 1.0 ? avg_nnz : 1.0));
+    if (rpt < 1) rpt = 1;
+    if (rpt > 256) rpt = 256;
+    long long ntiles = (row_cnt + rpt - 1) / rpt;
+    size_t smem = 4 * GRAD_TILE_CAP * sizeof(int) + (size_t)hot * sizeof(float);
+    int per_sm = smem > 100 * 1024 ? 1 : 2;
+    long long grid = (long long)sm_count() * per_sm;
+    if (grid > ntiles) grid = ntiles;
+    static bool attr_set[2] = {false, false};
+    if (!attr_set[mode]) {
+        cudaFuncSetAttribute(glm_rows_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(glm_rows_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr_set[0] = attr_set[1] = true;
+    }
+    if (mode == 0)
+        glm_rows_kernel<0><<<(unsigned)grid, GRAD_THREADS, smem, stream>>>(
+            rowptr, cols, vals, labels, row_lo, row_cnt, rpt, nnz_padded, w, g, bitmap, loss_id, inv_batch, hot, acc,
+            margins, status, budget);
+    else
+        glm_rows_kernel<1><<<(unsigned)grid, GRAD_THREADS, smem, stream>>>(
+            rowptr, cols, vals, labels, row_lo, row_cnt, rpt, nnz_padded, w, g, bitmap, loss_id, inv_batch, hot, acc,
+            margins, status, budget);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int skml_glm_grad(const long long* rowptr, const int* cols, const float* vals, const float* labels,
+                             long long row_lo, long long row_cnt, long long nnz_padded, double avg_nnz,
+                             const float* w, float* g, unsigned int* bitmap, int loss_id, float inv_batch, int hot,
+                             double* loss_acc, unsigned int* status, long long budget, void* stream) {
+    return grad_launch(0, rowptr, cols, vals, labels, row_lo, row_cnt, nnz_padded, avg_nnz, w, g, bitmap, loss_id,
+                       inv_batch, hot, loss_acc, nullptr, status, budget, (cudaStream_t)stream);
+}
+
+extern "C" int skml_glm_validate(const long long* rowptr, const int* cols, const float* vals, const float* labels,
+                                 long long row_lo, long long row_cnt, long long nnz_padded, double avg_nnz,
+                                 const float* w, int loss_id, double* acc5, float* margins, unsigned int* status,
+                                 long long budget, void* stream) {
+    return grad_launch(1, rowptr, cols, vals, labels, row_lo, row_cnt, nnz_padded, avg_nnz, w, nullptr, nullptr,
+                       loss_id, 1.f, 0, acc5, margins, status, budget, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------
+// Compaction of the touched bitmap into a sorted sparse gradient.
+// Each block owns COMPACT_WORDS consecutive bitmap words (4 per thread).
+// meta[0] = nnz, meta[1] = kind (1 sparse, 2 dense, 0 empty), meta[2] = touched before filter
+// ---------------------------------------------------------------------------
+#define COMPACT_WPT 4
+#define COMPACT_WORDS (SKML_BLOCK * COMPACT_WPT)
+
+__global__ void __launch_bounds__(SKML_BLOCK)
+compact_count_kernel(float* __restrict__ g, const float* __restrict__ w, unsigned int* __restrict__ bitmap,
+                     long long nwords, int dim, float lambda, unsigned int* __restrict__ block_counts) {
+    long long base = ((long long)blockIdx.x * SKML_BLOCK + threadIdx.x) * COMPACT_WPT;
+    unsigned int cnt = 0;
+#pragma unroll
+    for (int j = 0; j < COMPACT_WPT; ++j) {
+        long long wi = base + j;
+        if (wi >= nwords) break;
+        unsigned int bits = bitmap[wi];
+        if (!bits) continue;
+        unsigned int keep = 0;
+        unsigned int b = bits;
+        while (b) {
+            int t = __ffs(b) - 1;
+            b &= b - 1;
+            long long k = wi * 32 + t;
+            if (k < dim) {
+                float v = g[k] + lambda * w[k];
+                if (fabsf(v) > SKML_EPS) keep |= 1u << t;
+                else g[k] = 0.f;
+            }
+        }
+        if (keep != bits) bitmap[wi] = keep;
+        cnt += __popc(keep);
+    }
+    unsigned int total;
+    block_exclusive_scan<unsigned int>(cnt, &total);
+    if (threadIdx.x == 0) block_counts[blockIdx.x] = total;
+}
+
+__global__ void __launch_bounds__(SKML_BLOCK)
+compact_scan_kernel(unsigned int* __restrict__ block_counts, int nblocks, int dim, int allow_dense,
+                    long long* __restrict__ meta) {
+    __shared__ unsigned int carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (int base = 0; base < nblocks; base += SKML_BLOCK) {
+        int i = base + threadIdx.x;
+        unsigned int v = i < nblocks ? block_counts[i] : 0u;
+        unsigned int total;
+        unsigned int ex = block_exclusive_scan<unsigned int>(v, &total);
+        unsigned int c = carry;
+        if (i < nblocks) block_counts[i] = c + ex;
+        __syncthreads();
+        if (threadIdx.x == 0) carry = c + total;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        long long nnz = carry;
+        meta[0] = nnz;
+        long long thr = (long long)dim * 2 / 3;
+        meta[1] = nnz == 0 ? 0 : ((allow_dense && nnz > thr) ? 2 : 1);
+    }
+}
+
+__global__ void __launch_bounds__(SKML_BLOCK)
+compact_write_kernel(float* __restrict__ g, const float* __restrict__ w, unsigned int* __restrict__ bitmap,
+                     long long nwords, int dim, float lambda, const unsigned int* __restrict__ block_offsets,
+                     const long long* __restrict__ meta, int* __restrict__ keys, float* __restrict__ vals,
+                     float* __restrict__ dense_vals, long long capacity, unsigned int* status) {
+    const int kind = (int)meta[1];
+    long long base = ((long long)blockIdx.x * SKML_BLOCK + threadIdx.x) * COMPACT_WPT;
+    if (kind == 2 && dense_vals != nullptr) {
+        // dense kind: every coordinate is shipped, so write g + lambda*w for all of them
+#pragma unroll
+        for (int j = 0; j < COMPACT_WPT; ++j) {
+            long long wi = base + j;
+            if (wi >= nwords) break;
+            bitmap[wi] = 0;
+            for (int t = 0; t < 32; ++t) {
+                long long k = wi * 32 + t;
+                if (k < dim) {
+                    dense_vals[k] = g[k] + lambda * w[k];
+                    g[k] = 0.f;
+                }
+            }
+        }
+        return;
+    }
+    unsigned int words[COMPACT_WPT];
+    unsigned int cnt = 0;
+#pragma unroll
+    for (int j = 0; j < COMPACT_WPT; ++j) {
+        long long wi = base + j;
+        words[j] = wi < nwords ? bitmap[wi] : 0u;
+        cnt += __popc(words[j]);
+    }
+    unsigned int ex = block_exclusive_scan<unsigned int>(cnt, nullptr);
+    long long out = (long long)block_offsets[blockIdx.x] + ex;
+#pragma unroll
+    for (int j = 0; j < COMPACT_WPT; ++j) {
+        unsigned int b = words[j];
+        if (!b) continue;
+        long long wi = base + j;
+        bitmap[wi] = 0;
+        while (b) {
+            int t = __ffs(b) - 1;
+            b &= b - 1;
+            long long k = wi * 32 + t;
+            float v = g[k] + lambda * w[k];
+            g[k] = 0.f;
+            if (out < capacity) {
+                keys[out] = (int)k;
+                vals[out] = v;
+            } else {
+                skml_set_status(status, SKML_CAPACITY, 0x20u);
+            }
+            ++out;
+        }
+    }
+}
+
+extern "C" int skml_compact(float* g, const float* w, unsigned int* bitmap, int dim, float lambda,
+                            unsigned int* block_counts, long long* meta, int* keys, float* vals, float* dense_vals,
+                            long long capacity, unsigned int* status, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    long long nwords = ((long long)dim + 31) / 32;
+    int nblocks = (int)((nwords + COMPACT_WORDS - 1) / COMPACT_WORDS);
+    compact_count_kernel<<<nblocks, SKML_BLOCK, 0, stream>>>(g, w, bitmap, nwords, dim, lambda, block_counts);
+    compact_scan_kernel<<<1, SKML_BLOCK, 0, stream>>>(block_counts, nblocks, dim, dense_vals != nullptr, meta);
+    compact_write_kernel<<<nblocks, SKML_BLOCK, 0, stream>>>(g, w, bitmap, nwords, dim, lambda, block_counts, meta,
+                                                            keys, vals, dense_vals, capacity, status);
+    return (int)cudaGetLastError();
+}
+
+extern "C" long long skml_compact_blocks(int dim) {
+    long long nwords = ((long long)dim + 31) / 32;
+    return (nwords + COMPACT_WORDS - 1) / COMPACT_WORDS;
+}
+
+// ---------------------------------------------------------------------------
+// Updates for the uncompressed baselines (the compressed path updates inside the
+// fused decode kernel).
+// opt[0] = lr, opt[1] = sqrt(1 - beta2^t) / (1 - beta1^t) for Adam.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void apply_update(float* w, float* m, float* v, long long k, float gval, int adam,
+                                             float lr, float adam_scale) {
+    if (!adam) {
+        w[k] -= lr * gval;
+    } else {
+        float mt = 0.9f * m[k] + 0.1f * gval;
+        float vt = 0.999f * v[k] + 0.001f * gval * gval;
+        w[k] -= lr * adam_scale * mt / (sqrtf(vt) + 1e-8f);
+        m[k] = mt;
+        v[k] = vt;
+    }
+}
+
+__global__ void update_dense_kernel(float* w, float* m, float* v, const float* g, long long dim, float scale,
+                                    int adam, float lr, float adam_scale, int sparse_only) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < dim; i += (long long)gridDim.x * blockDim.x) {
+        float gv = g[i] * scale;
+        if (sparse_only && gv == 0.f) continue;
+        apply_update(w, m, v, i, gv, adam, lr, adam_scale);
+    }
+}
+
+__global__ void update_sparse_kernel(float* w, float* m, float* v, const int* keys, const float* vals,
+                                     const long long* n_ptr, long long n_max, float scale, int adam, float lr,
+                                     float adam_scale) {
+    long long n = n_ptr ? *n_ptr : n_max;
+    if (n > n_max) n = n_max;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        apply_update(w, m, v, keys[i], vals[i] * scale, adam, lr, adam_scale);
+}
+
+extern "C" int skml_update_dense(float* w, float* m, float* v, const float* g, long long dim, float scale, int adam,
+                                 float lr, float adam_scale, int sparse_only, void* stream) {
+    int grid = sm_count() * 8;
+    update_dense_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(w, m, v, g, dim, scale, adam, lr, adam_scale,
+                                                                sparse_only);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int skml_update_sparse(float* w, float* m, float* v, const int* keys, const float* vals,
+                                  const long long* n_ptr, long long n_max, float scale, int adam, float lr,
+                                  float adam_scale, void* stream) {
+    int grid = sm_count() * 8;
+    update_sparse_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(w, m, v, keys, vals, n_ptr, n_max, scale, adam, lr,
+                                                                 adam_scale);
+    return (int)cudaGetLastError();
+}
+
+// Scatter-add of (key, value) lists into a dense accumulator (raw key/value all-gather
+// baseline: local sum of the gathered lists).
+__global__ void scatter_kv_kernel(float* acc, const int* keys, const float* vals, const long long* counts,
+                                  long long stride, int lists) {
+    for (int l = 0; l < lists; ++l) {
+        long long n = counts[l];
+        if (n > stride) n = stride;
+        const int* k = keys + (long long)l * stride;
+        const float* v = vals + (long long)l * stride;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+             i += (long long)gridDim.x * blockDim.x)
+            atomicAdd(acc + k[i], v[i]);
+    }
+}
+
+extern "C" int skml_scatter_kv(float* acc, const int* keys, const float* vals, const long long* counts,
+                               long long stride, int lists, void* stream) {
+    scatter_kv_kernel<<<sm_count() * 8, 256, 0, (cudaStream_t)stream>>>(acc, keys, vals, counts, stride, lists);
+    return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// Synthetic data generation on the device.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ double u01(uint64_t h) { return (double)(h >> 11) * (1.0 / 9007199254740992.0); }
+
+__device__ __forceinline__ float normal_from(uint64_t h1, uint64_t h2) {
+    double a = u01(h1), b = u01(h2);
+    if (a < 1e-300) a = 1e-300;
+    return (float)(sqrt(-2.0 * log(a)) * cospi(2.0 * b));
+}
+
+__global__ void gen_wstar_kernel(float* w, long long dim, double density, uint64_t seed) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < dim; i += (long long)gridDim.x * blockDim.x) {
+        bool on = density >= 1.0 || u01(skml_rand(seed, 0xA1u, (uint64_t)i, 0)) < density;
+        w[i] = on ? normal_from(skml_rand(seed, 0xA2u, (uint64_t)i, 0), skml_rand(seed, 0xA3u, (uint64_t)i, 0)) : 0.f;
+    }
+}
+
+extern "C" int skml_gen_wstar(float* w, long long dim, double density, unsigned long long seed, void* stream) {
+    gen_wstar_kernel<<<sm_count() * 8, 256, 0, (cudaStream_t)stream>>>(w, dim, density, seed);
+    return (int)cudaGetLastError();
+}
+
+// 0-based Zipf(s) rank from a uniform draw: the density x^-s on [1, dim+1) inverted in
+// closed form (s == 0: uniform).
+__device__ __forceinline__ int zipf_rank(double u, int dim, double s, double top_pow, double inv_a, double log_top) {
+    double x;
+    if (s == 0.0) x = 1.0 + u * dim;
+    else if (inv_a == 0.0) x = exp(u * log_top);
+    else x = pow(1.0 + u * (top_pow - 1.0), inv_a);
+    long long r = (long long)x - 1;
+    if (r < 0) r = 0;
+    if (r >= dim) r = dim - 1;
+    return (int)r;
+}
+
+#define GEN_WARPS 8
+#define GEN_MAX_K 256
+// One warp per row. Candidates are drawn in rounds of 32; a candidate is kept if it is
+// new to the row (compared with the kept list and with lower lanes of the round).
+__global__ void __launch_bounds__(GEN_WARPS * 32)
+gen_rows_kernel(int* __restrict__ cols, float* __restrict__ vals, float* __restrict__ labels, long long row_offset,
+                long long rows, int dim, int k, double s, int value_kind, int task, float noise,
+                const float* __restrict__ wstar, uint64_t seed) {
+    __shared__ int s_cols[GEN_WARPS][GEN_MAX_K];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const double a = 1.0 - s;
+    const bool is_one = fabs(a) < 1e-9;
+    const double inv_a = is_one ? 0.0 : 1.0 / a;
+    const double top_pow = is_one ? 0.0 : pow((double)dim + 1.0, a);
+    const double log_top = log((double)dim + 1.0);
+    for (long long r = (long long)blockIdx.x * GEN_WARPS + warp; r < rows; r += (long long)gridDim.x * GEN_WARPS) {
+        const uint64_t gid = (uint64_t)(row_offset + r);
+        int have = 0;
+        unsigned int round = 0;
+        while (have < k && round < 4096) {
+            uint64_t h = skml_rand(seed, gid, (uint64_t)round * 32 + lane, 0xC0u);
+            int c = zipf_rank(u01(h), dim, s, top_pow, inv_a, log_top);
+            bool fresh = true;
+            for (int j = 0; j < have; ++j)
+                if (s_cols[warp][j] == c) fresh = false;
+            unsigned int same = __match_any_sync(0xFFFFFFFFu, c);
+            if ((same & ((1u << lane) - 1u)) != 0) fresh = false;  // a lower lane drew the same column
+            unsigned int m = __ballot_sync(0xFFFFFFFFu, fresh);
+            int pos = have + __popc(m & ((1u << lane) - 1u));
+            if (fresh && pos < k) s_cols[warp][pos] = c;
+            have += __popc(m);
+            if (have > k) have = k;
+            ++round;
+            __syncwarp();
+        }
+        // values, margin, label
+        float sq = 0.f;
+        for (int j = lane; j < k; j += 32) {
+            float v = 1.f;
+            if (value_kind == 1) v = (float)u01(skml_rand(seed, gid, j, 0xC1u)) + 1e-12f;
+            else if (value_kind == 2) v = normal_from(skml_rand(seed, gid, j, 0xC2u), skml_rand(seed, gid, j, 0xC3u));
+            sq += v * v;
+        }
+        sq = warp_sum(sq);
+        float scale = value_kind == 1 ? rsqrtf(sq) : 1.f;
+        float margin = 0.f;
+        for (int j = lane; j < k; j += 32) {
+            float v = 1.f;
+            if (value_kind == 1) v = ((float)u01(skml_rand(seed, gid, j, 0xC1u)) + 1e-12f) * scale;
+            else if (value_kind == 2) v = normal_from(skml_rand(seed, gid, j, 0xC2u), skml_rand(seed, gid, j, 0xC3u));
+            int c = j < have ? s_cols[warp][j] : 0;
+            cols[r * k + j] = c;
+            if (vals) vals[r * k + j] = v;
+            margin += wstar[c] * v;
+        }
+        margin = warp_sum(margin);
+        if (lane == 0) {
+            float y;
+            float nz = noise != 0.f ? noise * normal_from(skml_rand(seed, gid, 1, 0xC4u), skml_rand(seed, gid, 2, 0xC4u)) : 0.f;
+            if (task == 0) {
+                float p = 1.f / (1.f + __expf(-margin));
+                y = u01(skml_rand(seed, gid, 0, 0xC5u)) < (double)p ? 1.f : -1.f;
+            } else if (task == 1) {
+                y = margin + nz >= 0.f ? 1.f : -1.f;
+            } else {
+                y = margin + nz;
+            }
+            labels[r] = y;
+        }
+        __syncwarp();
+    }
+}
+
+extern "C" int skml_gen_rows(int* cols, float* vals, float* labels, long long row_offset, long long rows, int dim,
+                             int k, double s, int value_kind, int task, float noise, const float* wstar,
+                             unsigned long long seed, void* stream) {
+    if (k > GEN_MAX_K || k > dim || k < 1) return -1;
+    long long blocks = (rows + GEN_WARPS - 1) / GEN_WARPS;
+    long long cap = (long long)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    gen_rows_kernel<<<(unsigned)blocks, GEN_WARPS * 32, 0, (cudaStream_t)stream>>>(
+        cols, vals, labels, row_offset, rows, dim, k, s, value_kind, task, noise, wstar, seed);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int skml_sm_count() { return sm_count(); }

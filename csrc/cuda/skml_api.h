@@ -1,0 +1,108 @@
+// C ABI of libskml_cuda.so (loaded from Python with ctypes). Every function
+// returns a cudaError_t value as int (0 = success) unless stated otherwise and
+// launches on the given stream without synchronising.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SKML_MAX_PEERS 16
+#define SKML_GPU_MAX_BINS 4096
+
+// Arguments of the fused compress kernels. Only 8-byte fields, so the ctypes mirror
+// in sketchml_b200/ops/lib.py cannot disagree about padding.
+typedef struct SkmlCompressArgs {
+    const int* keys;            // sorted keys (sparse kind)
+    const float* vals;          // values: nnz of them (sparse) or dim of them (dense)
+    const long long* meta;      // device: meta[0] = nnz, meta[1] = kind (0 empty, 1 sparse, 2 dense)
+    long long n_max;            // capacity of keys / vals
+    long long dim;
+    long long bin_num, group_num, row_num;
+    double col_ratio;
+    unsigned long long seed, step;
+    long long rank, world;
+    const double* loss_partials;   // device, 4 doubles, may be null
+    unsigned char* payload;        // this rank's slot in its own receive region
+    long long slot_capacity;
+    unsigned char* peer_payload[SKML_MAX_PEERS];       // this rank's slot in every rank's region (self included)
+    unsigned long long* peer_flag[SKML_MAX_PEERS];     // arrival flag of that slot
+    unsigned char* workspace;      // skml_compress_workspace_bytes() bytes, zero-filled once by the caller
+    long long workspace_bytes;
+    unsigned int* status;
+    long long budget_cycles;
+    const float* given_splits;     // test hook: use these split points instead of the sketch
+    long long n_given;
+    double given_min, given_max;
+    long long fused;               // 1 = one cooperative launch, 0 = one launch per stage
+    long long grid;                // 0 = one block per SM
+} SkmlCompressArgs;
+
+long long skml_compress_workspace_bytes(long long n_max, long long bin_num, long long group_num, long long row_num,
+                                        double col_ratio, long long grid);
+long long skml_payload_capacity(long long n_max, long long dim, long long bin_num, long long group_num,
+                                long long row_num, double col_ratio);
+int skml_compress_sparse(const SkmlCompressArgs* args, void* stream);
+int skml_compress_dense(const SkmlCompressArgs* args, void* stream);
+
+// Arguments of the fused decode + aggregate + update kernel.
+typedef struct SkmlDecodeArgs {
+    const unsigned char* payload[SKML_MAX_PEERS];     // the slots of this rank's receive region
+    const unsigned long long* flag[SKML_MAX_PEERS];   // their arrival flags (null = do not wait)
+    long long world;
+    long long slot_capacity;
+    unsigned long long step;
+    long long dim;
+    float* w;
+    float* adam_m;
+    float* adam_v;             // null for SGD
+    double lr, adam_scale;     // Adam: scale = sqrt(1 - beta2^t) / (1 - beta1^t)
+    long long* acc;            // dim fixed-point accumulators, all zero between calls
+    int* key_scratch;          // decoded keys, capacity key_capacity
+    long long key_capacity;
+    double* loss_out;          // device, 4 doubles: sum over ranks of the payloads' loss partials
+    float* out_sum;            // optional dense fp32 [dim]: receives the averaged decoded sum instead of updating w
+    unsigned char* workspace;  // skml_decode_workspace_bytes()
+    unsigned int* status;
+    long long budget_cycles;
+    long long fused;
+    long long grid;
+} SkmlDecodeArgs;
+
+long long skml_decode_workspace_bytes(long long world, long long group_num);
+int skml_decode_update(const SkmlDecodeArgs* args, void* stream);
+
+// GLM numerics
+int skml_glm_grad(const long long* rowptr, const int* cols, const float* vals, const float* labels, long long row_lo,
+                  long long row_cnt, long long nnz_padded, double avg_nnz, const float* w, float* g,
+                  unsigned int* bitmap, int loss_id, float inv_batch, int hot, double* loss_acc, unsigned int* status,
+                  long long budget, void* stream);
+int skml_glm_validate(const long long* rowptr, const int* cols, const float* vals, const float* labels,
+                      long long row_lo, long long row_cnt, long long nnz_padded, double avg_nnz, const float* w,
+                      int loss_id, double* acc5, float* margins, unsigned int* status, long long budget, void* stream);
+int skml_compact(float* g, const float* w, unsigned int* bitmap, int dim, float lambda, unsigned int* block_counts,
+                 long long* meta, int* keys, float* vals, float* dense_vals, long long capacity, unsigned int* status,
+                 void* stream);
+long long skml_compact_blocks(int dim);
+int skml_update_dense(float* w, float* m, float* v, const float* g, long long dim, float scale, int adam, float lr,
+                      float adam_scale, int sparse_only, void* stream);
+int skml_update_sparse(float* w, float* m, float* v, const int* keys, const float* vals, const long long* n_ptr,
+                       long long n_max, float scale, int adam, float lr, float adam_scale, void* stream);
+int skml_scatter_kv(float* acc, const int* keys, const float* vals, const long long* counts, long long stride,
+                    int lists, void* stream);
+int skml_gen_wstar(float* w, long long dim, double density, unsigned long long seed, void* stream);
+int skml_gen_rows(int* cols, float* vals, float* labels, long long row_offset, long long rows, int dim, int k,
+                  double s, int value_kind, int task, float noise, const float* wstar, unsigned long long seed,
+                  void* stream);
+int skml_sm_count();
+
+// Peer memory (one process per GPU): CUDA IPC handles of a cudaMalloc'ed region.
+int skml_ipc_get_handle(void* dev_ptr, unsigned char* handle64);
+int skml_ipc_open_handle(const unsigned char* handle64, void** dev_ptr);
+int skml_ipc_close(void* dev_ptr);
+int skml_enable_peer_access(int peer_device);
+
+#ifdef __cplusplus
+}
+#endif

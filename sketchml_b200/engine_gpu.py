@@ -1,0 +1,241 @@
+"""Device engine of the training driver: every per-step phase is a kernel launch on the
+rank's B200 and nothing in the step synchronises with the host.
+
+Step = gradient kernel (margin + coefficient + scatter) -> compaction -> fused compress +
+publish into all peers' receive slots -> fused decode + aggregate + update. Loss partials
+travel inside the payload headers and are summed by the decode kernel into a per-step ring
+that the host reads once per epoch. The uncompressed NCCL baselines (``compressor=None``:
+dense all-reduce; ``compressor=Float``: raw key/value all-gather) share the gradient and
+compaction kernels.
+
+Reference: ml/algorithm/GeneralizedLinearModel.scala:116-177 (the same phases, run as Spark
+actions with a driver round-trip each).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import config as C
+from .data import CSRMatrix, DataSet, SyntheticSpec
+from .ops import lib as L
+from .ops.codec import GpuCompressor, GpuDecoder, read_status
+from .ops.datagen import generate_gpu
+from .ops.glm import DeviceCSR, GlmState, compact_gradient, glm_grad, glm_validate, update_dense, update_sparse
+from .parallel.failure import check_status
+
+
+class _BatchHandle:
+    def __init__(self, rows: int, index: int):
+        self.rows, self.index = rows, index
+
+
+class GpuEngine:
+    name = "gpu"
+
+    def __init__(self, trainer):
+        self.t = trainer
+        self.conf = trainer.conf
+        self.device = trainer.device
+        L.lib()  # fail now if the CUDA library is missing
+        self.csr: Optional[DeviceCSR] = None
+        self.valid_csr: Optional[DeviceCSR] = None
+        self.read_index = 0
+        self.last_payload_bytes = 0
+        self.last_raw_nnz = 0
+        self.mode = {C.COMPRESSOR_SKETCH: "sketch", C.COMPRESSOR_NONE: "nccl_dense",
+                     C.COMPRESSOR_FLOAT: "nccl_kv"}.get(self.conf.compressor)
+        if self.mode is None:
+            raise ValueError(f"the GPU engine supports the Sketch, None and Float compressors; "
+                             f"{self.conf.compressor} runs on the host engine")
+        if self.conf.dtype != "float32":
+            raise ValueError("the GPU engine computes in float32")
+
+    # ------------------------------------------------------------------ data
+    def generate(self, spec: SyntheticSpec, lo: int, rows: int):
+        csr, w = generate_gpu(spec, lo, rows, self.device)
+        return csr.to_matrix(), w
+
+    def attach_data(self) -> None:
+        t, conf = self.t, self.conf
+        self.csr = DeviceCSR(t.train_data.matrix, self.device)
+        self.valid_csr = DeviceCSR(t.valid_data.matrix, self.device) if t.valid_data.size else None
+        self._setup_buffers()
+
+    def attach_device_csr(self, csr: DeviceCSR, valid: Optional[DeviceCSR] = None) -> None:
+        """Used by benchmarks: adopt an existing device shard without a host round trip."""
+        self.csr, self.valid_csr = csr, valid
+        self._setup_buffers()
+
+    def _setup_buffers(self) -> None:
+        conf, comm = self.conf, self.t.comm
+        dim = conf.feature_num
+        self.batch_rows = int(self.csr.rows * conf.batch_sample_ratio)
+        bound = min(dim, max(1, self.batch_rows * max(1, self.csr.max_row_nnz)))
+        # every rank must size its slots alike: take the maximum over ranks
+        if comm.world > 1:
+            tt = torch.tensor([bound], dtype=torch.int64, device=self.device)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            bound = int(tt.item())
+        self.n_max = bound
+        allow_dense = bound > dim * 2 // 3
+        if allow_dense and self.mode == "nccl_kv":
+            self.mode = "nccl_dense"  # near-dense gradients: the raw key/value list is no smaller
+        self.st = GlmState.create(dim, bound, self.device, allow_dense)
+        self.loss_ring = torch.zeros((max(conf.batch_num, 1), 4), dtype=torch.float64, device=self.device)
+        self.partials_template = torch.tensor([float(self.batch_rows), 0.0, 0.0, 0.0], dtype=torch.float64,
+                                              device=self.device)
+        self.batch_index = 0
+        m = self.t.model
+        self.adam = conf.optimizer == "adam"
+        if self.mode == "sketch":
+            self.comp = GpuCompressor(dim, bound, conf.quant_bin_num, conf.sketch_group_num, conf.sketch_row_num,
+                                      conf.sketch_col_ratio, conf.seed, self.device,
+                                      fused=bool(conf.extras.get("fused", True)), budget_s=conf.step_timeout_s)
+            self.dec = GpuDecoder(dim, bound * comm.world, self.device, fused=bool(conf.extras.get("fused", True)),
+                                  budget_s=conf.step_timeout_s)
+            from .parallel.exchange import PeerExchange
+            self.xchg = PeerExchange(comm, self.comp.capacity, self.device)
+        elif self.mode == "nccl_kv":
+            self.kv_keys = torch.zeros((comm.world, bound), dtype=torch.int32, device=self.device)
+            self.kv_vals = torch.zeros((comm.world, bound), dtype=torch.float32, device=self.device)
+            self.kv_counts = torch.zeros(comm.world, dtype=torch.int64, device=self.device)
+            self.kv_acc = torch.zeros(dim, dtype=torch.float32, device=self.device)
+        else:
+            self.dense_sum = torch.zeros(dim, dtype=torch.float32, device=self.device)
+
+    # ----------------------------------------------------------------- steps
+    def _segments(self, count: int):
+        segs, n, left = [], self.csr.rows, count
+        while left > 0 and n > 0:
+            take = min(left, n - self.read_index)
+            segs.append((self.read_index, self.read_index + take))
+            self.read_index = (self.read_index + take) % n
+            left -= take
+        return segs
+
+    def compute_gradient(self, csr: Optional[DeviceCSR] = None, segments=None, batch_rows: Optional[int] = None):
+        m, st = self.t.model, self.st
+        csr = csr or self.csr
+        rows = self.batch_rows if batch_rows is None else batch_rows
+        segs = self._segments(rows) if segments is None else segments
+        if rows != self.batch_rows:
+            self.partials_template[0] = float(rows)
+        st.partials.copy_(self.partials_template)
+        glm_grad(csr, segs, m.weights, st, m.loss.loss_id, rows, self.conf.hot_columns, self.conf.step_timeout_s)
+        lam = m.loss.get_reg_param() if m.loss.is_l2_reg else 0.0
+        compact_gradient(st, m.weights, lam)
+        m.optimizer.advance()
+        h = _BatchHandle(rows, self.batch_index)
+        return h, None, None
+
+    def _lr_and_scale(self):
+        opt = self.t.model.optimizer
+        if self.adam:
+            opt.advance_betas()
+            return opt.lr_0, opt.step_scale()
+        return opt.learning_rate(), 1.0
+
+    def aggregate_and_update(self, step: int, partials) -> None:
+        m, st, comm = self.t.model, self.st, self.t.comm
+        lr, adam_scale = self._lr_and_scale()
+        opt = m.optimizer
+        am, av = (opt.m, opt.v) if self.adam else (None, None)
+        ring = self.loss_ring[self.batch_index % self.loss_ring.shape[0]]
+        if self.mode == "sketch":
+            send_p, send_f = self.xchg.send_ptrs(step)
+            recv_p, recv_f = self.xchg.recv_ptrs(step)
+            skip = self.t.injector is not None and step in self.t.injector.skip_publish_steps
+            if not skip:
+                self.comp.compress(st.keys, st.vals, st.meta, step, comm.rank, comm.world, send_p[comm.rank],
+                                   self.xchg.slot_capacity, send_p, send_f, st.status, st.partials, st.dense_vals)
+            self.dec.decode_update(recv_p, recv_f, self.xchg.slot_capacity, step, st.status, m.weights, lr, am, av,
+                                   adam_scale, ring)
+            if self.conf.extras.get("check_status_every_step", comm.world > 1 and bool(self.t.injector)):
+                self.check()
+        elif self.mode == "nccl_dense":
+            # baseline: all-reduce of the dense fp32 gradient, then update of every coordinate
+            self._densify()
+            if comm.world > 1:
+                dist.all_reduce(self.dense_sum)
+                dist.all_reduce(st.partials)
+            ring.copy_(st.partials)
+            update_dense(m.weights, self.dense_sum, 1.0 / comm.world, lr, am, av, adam_scale, sparse_only=True)
+        else:
+            # baseline: all-gather of raw (key, value) pairs padded to the slot size, local sum
+            if comm.world > 1:
+                dist.all_gather_into_tensor(self.kv_keys.view(-1), st.keys)
+                dist.all_gather_into_tensor(self.kv_vals.view(-1), st.vals)
+                dist.all_gather_into_tensor(self.kv_counts, st.meta[:1])
+                dist.all_reduce(st.partials)
+                L.check(L.lib().skml_scatter_kv(L.ptr(self.kv_acc), L.ptr(self.kv_keys), L.ptr(self.kv_vals),
+                                                L.ptr(self.kv_counts), self.n_max, comm.world, L.stream()), "scatter_kv")
+                update_dense(m.weights, self.kv_acc, 1.0 / comm.world, lr, am, av, adam_scale, sparse_only=True)
+                self.kv_acc.zero_()
+            else:
+                update_sparse(m.weights, st.keys, st.vals, st.meta, self.n_max, 1.0, lr, am, av, adam_scale)
+            ring.copy_(st.partials)
+        self.batch_index += 1
+
+    def _densify(self) -> None:
+        st = self.st
+        self.dense_sum.zero_()
+        L.check(L.lib().skml_scatter_kv(L.ptr(self.dense_sum), L.ptr(st.keys), L.ptr(st.vals), L.ptr(st.meta), st.n_max,
+                                        1, L.stream()), "scatter_kv")
+        if st.dense_vals is not None:  # dense kind: the compaction wrote every coordinate instead of a list
+            self.dense_sum.copy_(torch.where(st.meta[1] == 2, st.dense_vals, self.dense_sum))
+
+    def check(self) -> None:
+        """Reads the status word (synchronises) and raises on a kernel-reported error."""
+        s = read_status(self.st.status)
+        if s:
+            if self.mode == "sketch":
+                self.comp.reset()
+                self.dec.reset()
+            check_status(s, f"at step {self.t.step} on rank {self.t.comm.rank}")
+
+    def resolve_losses(self, handles) -> List[float]:
+        """One device->host read per epoch: batch loss = sum obj / sum batch + reg / world."""
+        self.check()
+        ring = self.loss_ring.cpu()
+        world = self.t.comm.world
+        out = []
+        for h in handles:
+            r = ring[h.index % ring.shape[0]]
+            out.append(float(r[1] / max(float(r[0]), 1.0) + r[2] / world))
+        return out
+
+    def validate(self):
+        m = self.t.model
+        if self.valid_csr is None or self.valid_csr.rows == 0:
+            return [0.0, 0, 0, 0, 0, 0]
+        acc = glm_validate(self.valid_csr, m.weights, m.loss.loss_id, self.st.status, budget_s=self.conf.step_timeout_s)
+        return acc.cpu().tolist()
+
+    def payload_stats(self, step: int):
+        """(nnz, payload bytes) of this rank's last payload (synchronises)."""
+        if self.mode != "sketch":
+            n = int(self.st.meta[0])
+            return n, 8 * n
+        buf = self.xchg.local_slot(step, self.t.comm.rank)
+        head = buf[:256].cpu().numpy()
+        import numpy as np
+        total = int(np.frombuffer(head.tobytes(), dtype=np.uint64, count=1, offset=144)[0])
+        return int(self.st.meta[0]), total
+
+    def sync(self) -> None:
+        torch.cuda.synchronize(self.device)
+
+    def cursor(self) -> int:
+        return self.read_index
+
+    def set_cursor(self, c: int) -> None:
+        self.read_index = c
+
+    def close(self) -> None:
+        if getattr(self, "xchg", None) is not None:
+            self.sync()
+            self.xchg.close()

@@ -240,6 +240,27 @@ class Trainer:
         self.step += 1
         return batch_loss
 
+    def train_streamed(self, feeder, steps: int, first: int = 0, loss_host: Optional[torch.Tensor] = None):
+        """Runs ``steps`` iterations on minibatches that live in pinned host memory: every step
+        copies its batch host->device (overlapped with the previous step through the feeder's
+        side stream) and copies the step's loss partials device->host into ``loss_host``
+        (pinned, shape [steps, 4]). Returns ``loss_host``; synchronise before reading it."""
+        eng = self.engine
+        if loss_host is None:
+            loss_host = torch.zeros((steps, 4), dtype=torch.float64).pin_memory()
+        feeder.prefetch(first)
+        for k in range(steps):
+            i = first + k
+            if k + 1 < steps:
+                feeder.prefetch(i + 1)
+            csr, rows = feeder.get(i)
+            h, _, _ = eng.compute_gradient(csr=csr, segments=[(0, rows)], batch_rows=rows)
+            feeder.release(i)
+            eng.aggregate_and_update(self.step, None)
+            loss_host[k].copy_(eng.loss_ring[h.index % eng.loss_ring.shape[0]], non_blocking=True)
+            self.step += 1
+        return loss_host
+
     def compute_gradient(self, epoch: int, batch: int):
         """GeneralizedLinearModel.scala:125-141: batch loss = objLoss/batchSize + regLoss/workerNum."""
         with self.timer.phase("gradient"):

@@ -1,0 +1,217 @@
+"""GPU compress / decode kernels against the C++ CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _sparse_grad(n, dim, seed, scale=1e-3, positive_only=False):
+    rng = np.random.default_rng(seed)
+    if dim <= 4 * n or dim < 10_000_000:
+        keys = np.sort(rng.choice(dim, n, replace=False)).astype(np.int32)
+    else:
+        keys = np.unique(rng.integers(0, dim, size=2 * n + 16))
+        keys = np.sort(rng.permutation(keys)[:n]).astype(np.int32)
+    vals = rng.laplace(0, scale, n).astype(np.float32)
+    if positive_only:
+        vals = np.abs(vals) + 1e-6
+    vals[vals == 0] = 1e-6
+    return keys, vals
+
+
+def _sections(p):
+    out = []
+    for g in p["groups"]:
+        out.append((g["n"], g["col_num"], tuple(g["hash_ids"]), g["table"].tolist() if g["n"] else None,
+                    g["keys"]["flag_words"].tolist() if g["n"] else None,
+                    g["keys"]["delta_words"].tolist() if g["n"] else None,
+                    g.get("restart_raw").tolist() if g["n"] else None))
+    return out
+
+
+@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("n,dim,q,G,rows,ratio", [
+    (5000, 200000, 256, 8, 2, 0.3), (1, 1000, 64, 8, 3, 0.2), (2049, 100000000, 128, 1, 3, 0.2),
+    (70000, 80000, 256, 8, 2, 0.3), (3000, 2 ** 31 - 2, 300, 4, 1, 0.5), (40000, 5000000, 64, 2, 8, 0.1)])
+def test_payload_bit_exact_with_given_splits(fused, n, dim, q, G, rows, ratio):
+    from sketchml_b200.compress import oracle
+    from sketchml_b200.ops import GpuCompressor
+    keys, vals = _sparse_grad(n, dim, seed=n)
+    qz = oracle.quantile_quantize(vals, q, 128, 1, 2, False)
+    splits = qz["splits"].astype(np.float32)
+    opts = dict(bin_num=q, group_num=G, row_num=rows, col_ratio=ratio, seed=11, step=7, rank=2, world=4, tie_mode=1)
+    ref = oracle.compress_sparse(keys, vals, dim, opts, splits, float(qz["min"]), float(qz["max"]))
+    comp = GpuCompressor(dim, n, q, G, rows, ratio, seed=11, fused=fused)
+    buf = comp.compress_local(torch.from_numpy(keys).cuda(), torch.from_numpy(vals).cuda(), step=7, rank=2, world=4,
+                              given=(torch.from_numpy(splits).cuda(), qz["min"], qz["max"]))
+    got = comp.payload_bytes(buf)
+    pg, pr = oracle.parse(got), oracle.parse(ref)
+    for k in ("kind", "step", "rank", "world", "dim", "nnz", "bin_num", "zero_idx", "group_num", "row_num", "col_ratio",
+              "key_encoder", "cell_bits", "seed", "restart_interval"):
+        assert pg[k] == pr[k], k
+    assert np.array_equal(pg["bucket_values"], pr["bucket_values"])
+    sg, sr = _sections(pg), _sections(pr)
+    for gi, (a, b) in enumerate(zip(sg, sr)):
+        for fi, (x, y) in enumerate(zip(a, b)):
+            assert x == y, f"group {gi} field {fi} differs"
+    kind, k2, v2 = oracle.decompress(got)
+    _, k3, v3 = oracle.decompress(ref)
+    assert np.array_equal(k2, keys) and np.array_equal(v2, v3)
+
+
+@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("n", [100, 255, 256, 257, 2047, 2048, 2049, 30000, 1000003])
+def test_quantile_splits_rank_error(fused, n):
+    from sketchml_b200.compress import oracle
+    from sketchml_b200.ops import GpuCompressor
+    dim = max(4 * n, 1000)
+    keys, vals = _sparse_grad(n, dim, seed=n + 1)
+    q = 256
+    comp = GpuCompressor(dim, n, q, 8, 2, 0.3, seed=3, fused=fused)
+    buf = comp.compress_local(torch.from_numpy(keys).cuda(), torch.from_numpy(vals).cuda())
+    p = oracle.parse(comp.payload_bytes(buf))
+    bv = p["bucket_values"]
+    assert p["nnz"] == n and 2 <= p["bin_num"] <= q
+    assert abs(p["min_value"] - vals.min()) < 1e-12 and abs(p["max_value"] - vals.max()) < 1e-12
+    assert np.all(np.diff(bv) > 0)
+    # recover the splits from the midpoints and measure their rank error
+    splits = np.empty(p["bin_num"] - 1)
+    prev = p["min_value"]
+    for i in range(p["bin_num"] - 1):
+        splits[i] = 2 * float(bv[i]) - prev
+        prev = splits[i]
+    s = np.sort(vals.astype(np.float64))
+    ranks = np.searchsorted(s, splits, side="left") / n
+    if n <= 128:
+        assert p["bin_num"] >= min(q, n) // 2
+    # every split is an order statistic near an even quantile: gaps between consecutive
+    # split ranks stay within the k = 128 sketch's error band
+    err = np.abs(np.diff(np.concatenate([[0.0], ranks, [1.0]]))).max()
+    assert err < 1.0 / q + 0.03, err
+    kind, k2, v2 = oracle.decompress(comp.payload_bytes(buf))
+    assert np.array_equal(k2, keys)
+    assert np.all(np.sign(v2) == np.sign(vals)) or (np.sign(v2) != np.sign(vals)).mean() < 0.02
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_decode_sum_matches_oracle(fused):
+    from sketchml_b200.compress import oracle
+    from sketchml_b200.ops import GpuCompressor, GpuDecoder
+    dim, world = 300000, 3
+    comp = GpuCompressor(dim, 20000, 128, 8, 3, 0.2, seed=5, fused=fused)
+    bufs, ref = [], np.zeros(dim)
+    for r in range(world):
+        keys, vals = _sparse_grad(15000 + 1000 * r, dim, seed=100 + r)
+        b = comp.compress_local(torch.from_numpy(keys).cuda(), torch.from_numpy(vals).cuda(), step=4, rank=r, world=world)
+        bufs.append(b.clone())
+        _, k, v = oracle.decompress(comp.payload_bytes(b))
+        ref[k] += v.astype(np.float64) / world
+    dec = GpuDecoder(dim, 20000 * world, fused=fused)
+    out = dec.decode_sum(bufs, step=4).cpu().numpy().astype(np.float64)
+    assert np.abs(out - ref).max() <= 1e-6 * np.abs(ref).max()
+    assert int(dec.acc.abs().max()) == 0
+    # a second call gives the same bits (accumulators were left clean, sums are order independent)
+    out2 = dec.decode_sum(bufs, step=4).cpu().numpy()
+    assert np.array_equal(out2.astype(np.float64), out)
+
+
+def test_dense_kind_roundtrip_and_mixed_decode():
+    from sketchml_b200.compress import oracle
+    from sketchml_b200.ops import GpuCompressor, GpuDecoder
+    dim = 50000
+    rng = np.random.default_rng(1)
+    dense = rng.normal(0, 1e-2, dim).astype(np.float32)
+    comp = GpuCompressor(dim, dim, 256, 8, 2, 0.3, seed=1)
+    qz = oracle.quantile_quantize(dense, 256, 128, 1, 2, False)
+    splits = torch.from_numpy(qz["splits"].astype(np.float32)).cuda()
+    b0 = comp.compress_local(None, torch.from_numpy(dense).cuda(), step=2, rank=0, world=2, dense=True,
+                             given=(splits, qz["min"], qz["max"])).clone()
+    ref0 = oracle.compress_dense(dense, dict(bin_num=256, step=2, rank=0, world=2, seed=1), qz["splits"].astype(np.float32),
+                                 float(qz["min"]), float(qz["max"]))
+    k0, kk, v0 = oracle.decompress(comp.payload_bytes(b0))
+    _, _, vr = oracle.decompress(ref0)
+    assert k0 == 2 and np.array_equal(v0, vr)
+    # sketch-built splits (no given): decode error bounded by bucket width
+    b0s = comp.compress_local(None, torch.from_numpy(dense).cuda(), step=2, rank=0, world=2, dense=True).clone()
+    _, _, v0s = oracle.decompress(comp.payload_bytes(b0s))
+    assert np.abs(v0s - dense).mean() < 2e-3
+    keys, vals = _sparse_grad(4000, dim, seed=8)
+    b1 = comp.compress_local(torch.from_numpy(keys).cuda(), torch.from_numpy(vals).cuda(), step=2, rank=1, world=2).clone()
+    _, k1, v1 = oracle.decompress(comp.payload_bytes(b1))
+    ref = v0s.astype(np.float64) / 2
+    ref[k1] += v1.astype(np.float64) / 2
+    out = GpuDecoder(dim, dim).decode_sum([b0s, b1], step=2).cpu().numpy()
+    assert np.abs(out - ref).max() <= 1e-6 * np.abs(ref).max()
+
+
+def test_empty_gradient_and_updates():
+    from sketchml_b200.compress import oracle
+    from sketchml_b200.ops import GpuCompressor, GpuDecoder
+    dim = 10000
+    comp = GpuCompressor(dim, 1000, 64, 8, 2, 0.3, seed=2)
+    e = comp.compress_local(torch.zeros(0, dtype=torch.int32, device="cuda"), torch.zeros(0, device="cuda"), step=1,
+                            rank=0, world=2).clone()
+    assert oracle.parse(comp.payload_bytes(e))["kind"] == 0
+    keys, vals = _sparse_grad(900, dim, seed=4, scale=1e-1)
+    b = comp.compress_local(torch.from_numpy(keys).cuda(), torch.from_numpy(vals).cuda(), step=1, rank=1, world=2).clone()
+    _, k, v = oracle.decompress(comp.payload_bytes(b))
+    g = np.zeros(dim)
+    g[k] = v.astype(np.float64) / 2
+    dec = GpuDecoder(dim, 2000)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    cap = min(e.numel(), b.numel())
+    # SGD
+    w = torch.ones(dim, device="cuda")
+    dec.decode_update([e.data_ptr(), b.data_ptr()], [None, None], cap, 1, status, w=w, lr=0.5)
+    assert int(status.item()) == 0
+    assert np.abs(w.cpu().numpy() - (1 - 0.5 * g)).max() < 1e-6
+    # lazy Adam: only touched coordinates move
+    w = torch.ones(dim, device="cuda")
+    m = torch.zeros(dim, device="cuda")
+    vv = torch.zeros(dim, device="cuda")
+    scale = np.sqrt(1 - 0.999) / (1 - 0.9)
+    dec.decode_update([e.data_ptr(), b.data_ptr()], [None, None], cap, 1, status, w=w, lr=0.1, adam_m=m, adam_v=vv,
+                      adam_scale=scale)
+    mt, vt = 0.1 * g, 0.001 * g * g
+    ref = 1 - 0.1 * scale * mt / (np.sqrt(vt) + 1e-8)
+    assert np.abs(w.cpu().numpy() - ref).max() < 1e-4
+    assert np.abs(m.cpu().numpy() - mt).max() < 1e-7
+    untouched = np.ones(dim, bool)
+    untouched[k] = False
+    assert (w.cpu().numpy()[untouched] == 1).all()
+
+
+def test_bad_header_and_timeout_are_reported_not_fatal():
+    from sketchml_b200.ops import GpuCompressor, GpuDecoder
+    from sketchml_b200.parallel.failure import PayloadError, StepTimeout, check_status
+    dim = 10000
+    comp = GpuCompressor(dim, 1000, 64, 8, 2, 0.3, seed=2)
+    keys, vals = _sparse_grad(500, dim, seed=4)
+    b = comp.compress_local(torch.from_numpy(keys).cuda(), torch.from_numpy(vals).cuda(), step=3).clone()
+    dec = GpuDecoder(dim, 1000, budget_s=0.05)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    w = torch.zeros(dim, device="cuda")
+    # stale step: the header says 3, the decoder expects 4
+    dec.decode_update([b.data_ptr()], [None], b.numel(), 4, status, w=w, lr=1.0)
+    with pytest.raises(PayloadError):
+        check_status(int(status.item()))
+    status.zero_()
+    # corrupted header byte -> checksum mismatch
+    bad = b.clone()
+    bad[40] ^= 0x11
+    dec.decode_update([bad.data_ptr()], [None], bad.numel(), 3, status, w=w, lr=1.0)
+    with pytest.raises(PayloadError):
+        check_status(int(status.item()))
+    status.zero_()
+    # an arrival flag that nothing sets: the bounded wait gives up and the context stays usable
+    flag = torch.zeros(4, dtype=torch.int64, device="cuda")
+    dec.decode_update([b.data_ptr()], [flag.data_ptr()], b.numel(), 3, status, w=w, lr=1.0)
+    with pytest.raises(StepTimeout):
+        check_status(int(status.item()))
+    status.zero_()
+    dec.reset()
+    assert float(w.abs().max()) == 0.0
+    flag[0] = 4  # step + 1
+    dec.decode_update([b.data_ptr()], [flag.data_ptr()], b.numel(), 3, status, w=w, lr=1.0)
+    assert int(status.item()) == 0 and float(w.abs().max()) > 0

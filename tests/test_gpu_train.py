@@ -1,0 +1,68 @@
+"""End-to-end training on one GPU: fused sketch path vs the uncompressed baselines and the
+host engine."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _conf(**kw):
+    from sketchml_b200.config import MLConf
+    base = dict(algo="lr", format="synthetic", feature_num=50000, syn_rows=40000, syn_nnz_per_row=20, epoch_num=3,
+                learn_rate=0.5, l2_reg=1e-4, valid_ratio=0.1, batch_sample_ratio=0.1, quant_bin_num=128,
+                sketch_row_num=3, sketch_col_ratio=0.2, device="cuda", seed=1)
+    base.update(kw)
+    return MLConf(**base)
+
+
+def _train(conf, matrix=None):
+    from sketchml_b200.trainer import Trainer
+    t = Trainer(conf)
+    t.load_data(matrix)
+    h = t.train()
+    w = t.model.weights.detach().cpu().clone()
+    t.close()
+    return h, w, t
+
+
+@pytest.mark.parametrize("algo,opt", [("lr", "sgd"), ("svm", "sgd"), ("lr", "adam"), ("linreg", "sgd")])
+def test_sketch_training_tracks_uncompressed(algo, opt):
+    kw = dict(algo=algo, optimizer=opt)
+    if opt == "adam":
+        kw["learn_rate"] = 0.01
+    if algo == "linreg":
+        kw.update(learn_rate=0.05, syn_values="normal", syn_wstar_density=1.0, syn_noise=0.1, feature_num=2000,
+                  syn_nnz_per_row=50, syn_zipf_s=0.0)
+    h_s, w_s, t_s = _train(_conf(compressor="Sketch", **kw))
+    h_n, w_n, _ = _train(_conf(compressor="None", **kw))
+    assert all(np.isfinite(h_s["train_loss"])) and all(np.isfinite(h_n["train_loss"]))
+    assert h_n["train_loss"][-1] < h_n["train_loss"][0]
+    assert h_s["train_loss"][-1] < h_s["train_loss"][0]
+    # the sketch underestimates magnitudes, so it trails the exact gradient a little
+    gap = abs(h_s["valid_loss"][-1] - h_n["valid_loss"][-1]) / abs(h_n["valid_loss"][-1])
+    assert gap < 0.05, (h_s, h_n)
+
+
+def test_gpu_uncompressed_matches_host_engine():
+    from sketchml_b200.data import SyntheticSpec, generate_cpu
+    spec = SyntheticSpec(6000, 8000, 15, 1.1, "binary", "logistic", 0.1, 0.0, 3)
+    m, _ = generate_cpu(spec)
+    kw = dict(feature_num=8000, epoch_num=2, valid_ratio=0.2, compressor="None", l2_reg=1e-3)
+    h_g, w_g, _ = _train(_conf(**kw), m)
+    h_c, w_c, _ = _train(_conf(device="cpu", dtype="float64", **kw), m)
+    assert np.allclose(h_g["train_loss"], h_c["train_loss"], rtol=2e-4)
+    assert np.allclose(h_g["valid_loss"], h_c["valid_loss"], rtol=2e-4)
+    assert float((w_g.double() - w_c.double()).abs().max()) < 1e-4
+
+
+def test_kv_baseline_and_checkpoint_resume(tmp_path):
+    h1, w1, _ = _train(_conf(compressor="Float", epoch_num=2))
+    h2, w2, _ = _train(_conf(compressor="None", epoch_num=2))
+    assert float((w1 - w2).abs().max()) < 1e-5
+    ck = tmp_path / "ck"
+    _train(_conf(compressor="Sketch", epoch_num=1, checkpoint_dir=str(ck), checkpoint_every=1))
+    h3, w3, _ = _train(_conf(compressor="Sketch", epoch_num=2, resume=str(ck / "epoch_0001.ckpt")))
+    h4, w4, _ = _train(_conf(compressor="Sketch", epoch_num=2))
+    assert len(h3["train_loss"]) == 1
+    assert float((w3 - w4).abs().mean()) < 1e-5 and float((w3 - w4).abs().max()) < 1e-2
