@@ -864,7 +864,7 @@ __device__ void copy_range_to_peers(const CP& p, unsigned long long lo, unsigned
     for (long long i = gid; i < units; i += gsz) {
         uint4 v = ld_cg_v4(src + i);
         for (unsigned int r = 0; r < p.world; ++r)
-            if (r != p.rank) st_v4(reinterpret_cast<uint4*>(p.peer_payload[r] + lo) + i, v);
+            if (r != p.rank && p.peer_payload[r]) st_v4(reinterpret_cast<uint4*>(p.peer_payload[r] + lo) + i, v);
     }
 }
 
@@ -921,7 +921,7 @@ __device__ void stage_push_sparse(const CP& p, Smem& s) {
             const unsigned long long off = L.table_off[g] + 16ull * j;
             st_v4(reinterpret_cast<uint4*>(p.payload + off), v);
             for (unsigned int r = 0; r < p.world; ++r)
-                if (r != p.rank) st_v4(reinterpret_cast<uint4*>(p.peer_payload[r] + off), v);
+                if (r != p.rank && p.peer_payload[r]) st_v4(reinterpret_cast<uint4*>(p.peer_payload[r] + off), v);
         }
         copy_range_to_peers(p, 0, L.off_tables);
         copy_range_to_peers(p, L.off_deltas, L.total_bytes);
@@ -1045,7 +1045,7 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_dense_kernel(CP p, int
             uint4 v = make_uint4(words[0], words[1], words[2], words[3]);
             st_v4(reinterpret_cast<uint4*>(p.payload + off_codes) + u, v);
             for (unsigned int r = 0; r < p.world; ++r)
-                if (r != p.rank) st_v4(reinterpret_cast<uint4*>(p.peer_payload[r] + off_codes) + u, v);
+                if (r != p.rank && p.peer_payload[r]) st_v4(reinterpret_cast<uint4*>(p.peer_payload[r] + off_codes) + u, v);
         }
     }
     STAGE_BARRIER(3)

@@ -90,6 +90,7 @@ class GpuEngine:
                                               device=self.device)
         self.batch_index = 0
         m = self.t.model
+        self.reg_every_step = bool(conf.extras.get("reg_loss_every_step", dim <= (1 << 22)))
         self.adam = conf.optimizer == "adam"
         if self.mode == "sketch":
             self.comp = GpuCompressor(dim, bound, conf.quant_bin_num, conf.sketch_group_num, conf.sketch_row_num,
@@ -124,6 +125,10 @@ class GpuEngine:
         segs = self._segments(rows) if segments is None else segments
         if rows != self.batch_rows:
             self.partials_template[0] = float(rows)
+        if self.reg_every_step and m.loss.is_l2_reg:
+            # reg loss = lambda * ||w||_2 (un-squared, ml/objective/Loss.scala:48-53); an O(dim) pass,
+            # so large models refresh it once per epoch instead
+            self.partials_template[2:3].copy_(torch.linalg.vector_norm(m.weights).double() * m.loss.lam)
         st.partials.copy_(self.partials_template)
         glm_grad(csr, segs, m.weights, st, m.loss.loss_id, rows, self.conf.hot_columns, self.conf.step_timeout_s)
         lam = m.loss.get_reg_param() if m.loss.is_l2_reg else 0.0
@@ -200,6 +205,9 @@ class GpuEngine:
     def resolve_losses(self, handles) -> List[float]:
         """One device->host read per epoch: batch loss = sum obj / sum batch + reg / world."""
         self.check()
+        m = self.t.model
+        if not self.reg_every_step and m.loss.is_l2_reg:
+            self.loss_ring[:, 2] = torch.linalg.vector_norm(m.weights).double() * m.loss.lam * self.t.comm.world
         ring = self.loss_ring.cpu()
         world = self.t.comm.world
         out = []
