@@ -598,3 +598,68 @@ extern "C" int skml_gen_rows(int* cols, float* vals, float* labels, long long ro
 }
 
 extern "C" int skml_sm_count() { return sm_count(); }
+
+// ---------------------------------------------------------------------------
+// skml_compact_noalloc: the compaction above for callers that must not allocate.
+// (Declared and documented in skml_noalloc.h; it has no counterpart in the reference.)
+//
+// The only scratch memory of the compaction is the per-block count / offset array. Here
+// it lives in a file-scope device array instead of a caller-supplied buffer, so the call
+// needs no cudaMalloc, no cudaFree and no allocating library routine.
+// ---------------------------------------------------------------------------
+#include <stdio.h>
+
+#include <mutex>
+
+#include "skml_noalloc.h"
+
+static __device__ __align__(256) unsigned int g_noalloc_block_counts[SKML_NOALLOC_MAX_BLOCKS + 64];
+
+#define NOALLOC_MAX_DEVICES 64
+static unsigned int* g_noalloc_scratch_ptr[NOALLOC_MAX_DEVICES];  // device address of the array, per device
+static std::mutex g_noalloc_mutex;
+
+// In host code the array's name is only a handle of the symbol, not a device address:
+// the address is asked for once per device, with that device current.
+static int noalloc_scratch(unsigned int** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return (int)cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_scratch_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_block_counts);
+        if (e != cudaSuccess) return (int)e;
+        g_noalloc_scratch_ptr[dev] = static_cast<unsigned int*>(p);
+    }
+    *out = g_noalloc_scratch_ptr[dev];
+    return 0;
+}
+
+extern "C" int skml_compact_noalloc(float* g, const float* w, unsigned int* bitmap, int dim, float lambda,
+                                    long long* meta, int* keys, float* vals, long long capacity,
+                                    unsigned int* status, void* stream_) {
+    if (dim <= 0 || !g || !w || !bitmap || !meta || !keys || !vals || !status) {
+        fprintf(stderr, "skml_compact_noalloc: null pointer or non-positive dim\n");
+        return SKML_NOALLOC_BAD_ARGUMENT;
+    }
+    if ((long long)dim > SKML_NOALLOC_MAX_DIM) {
+        fprintf(stderr, "skml_compact_noalloc: dim %d exceeds the built-in scratch (at most %lld coordinates); "
+                        "use skml_compact with a caller-owned block_counts buffer\n", dim, (long long)SKML_NOALLOC_MAX_DIM);
+        return SKML_NOALLOC_TOO_LARGE;
+    }
+    unsigned int* scratch = nullptr;
+    int rc = noalloc_scratch(&scratch);
+    if (rc) return rc;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    long long nwords = ((long long)dim + 31) / 32;
+    int nblocks = (int)((nwords + COMPACT_WORDS - 1) / COMPACT_WORDS);
+    // every entry of the scratch that is read (the first nblocks) is rewritten by the count
+    // kernel of this call, so nothing of an earlier call has to be cleared
+    compact_count_kernel<<<nblocks, SKML_BLOCK, 0, stream>>>(g, w, bitmap, nwords, dim, lambda, scratch);
+    compact_scan_kernel<<<1, SKML_BLOCK, 0, stream>>>(scratch, nblocks, dim, 0, meta);
+    compact_write_kernel<<<nblocks, SKML_BLOCK, 0, stream>>>(g, w, bitmap, nwords, dim, lambda, scratch, meta, keys,
+                                                            vals, nullptr, capacity, status);
+    return (int)cudaGetLastError();
+}
