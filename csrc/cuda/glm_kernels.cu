@@ -264,34 +264,61 @@ extern "C" int skml_glm_validate(const long long* rowptr, const int* cols, const
 
 // ---------------------------------------------------------------------------
 // Compaction of the touched bitmap into a sorted sparse gradient.
-// Each block owns COMPACT_WORDS consecutive bitmap words (4 per thread).
+// Each block owns COMPACT_WORDS consecutive bitmap words (each warp 4 groups of 32 words).
 // meta[0] = nnz, meta[1] = kind (1 sparse, 2 dense, 0 empty), meta[2] = touched before filter
 // ---------------------------------------------------------------------------
 #define COMPACT_WPT 4
 #define COMPACT_WORDS (SKML_BLOCK * COMPACT_WPT)
+#define COMPACT_SPARSE_BITS 4  // words with at most this many bits are walked by one lane
 
 __global__ void __launch_bounds__(SKML_BLOCK)
 compact_count_kernel(float* __restrict__ g, const float* __restrict__ w, unsigned int* __restrict__ bitmap,
                      long long nwords, int dim, float lambda, unsigned int* __restrict__ block_counts) {
-    long long base = ((long long)blockIdx.x * SKML_BLOCK + threadIdx.x) * COMPACT_WPT;
+    // A warp owns COMPACT_WPT groups of 32 consecutive bitmap words. Words with few bits are
+    // walked by their own lane; words with many bits are walked by the whole warp, one bit
+    // per lane, so that the g / w accesses of dense regions are coalesced. The filtered value
+    // g + lambda * w is stored back into g so that the write pass reads one array only.
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long wbase = (long long)blockIdx.x * COMPACT_WORDS + (long long)warp * (32 * COMPACT_WPT);
     unsigned int cnt = 0;
 #pragma unroll
-    for (int j = 0; j < COMPACT_WPT; ++j) {
-        long long wi = base + j;
-        if (wi >= nwords) break;
-        unsigned int bits = bitmap[wi];
-        if (!bits) continue;
-        unsigned int keep = 0;
-        unsigned int b = bits;
-        while (b) {
-            int t = __ffs(b) - 1;
-            b &= b - 1;
-            long long k = wi * 32 + t;
-            if (k < dim) {
-                float v = g[k] + lambda * w[k];
-                if (fabsf(v) > SKML_EPS) keep |= 1u << t;
-                else g[k] = 0.f;
+    for (int grp = 0; grp < COMPACT_WPT; ++grp) {
+        const long long gbase = wbase + grp * 32;
+        const long long wi = gbase + lane;
+        const unsigned int bits = wi < nwords ? bitmap[wi] : 0u;
+        unsigned int keep = bits;
+        const int pc = __popc(bits);
+        if (pc > 0 && pc <= COMPACT_SPARSE_BITS) {
+            unsigned int b = bits;
+            while (b) {
+                const int t = __ffs(b) - 1;
+                b &= b - 1;
+                const long long k = wi * 32 + t;
+                float v = 0.f;
+                if (k < dim) v = g[k] + lambda * w[k];
+                if (fabsf(v) > SKML_EPS) {
+                    g[k] = v;
+                } else {
+                    keep &= ~(1u << t);
+                    if (k < dim) g[k] = 0.f;
+                }
             }
+        }
+        unsigned int dense = __ballot_sync(0xFFFFFFFFu, pc > COMPACT_SPARSE_BITS);
+        while (dense) {
+            const int j = __ffs(dense) - 1;
+            dense &= dense - 1;
+            const unsigned int wb = __shfl_sync(0xFFFFFFFFu, bits, j);
+            const long long k = (gbase + j) * 32 + lane;
+            const bool active = (wb >> lane) & 1u;
+            bool ok = false;
+            if (active && k < dim) {
+                const float v = g[k] + lambda * w[k];
+                ok = fabsf(v) > SKML_EPS;
+                g[k] = ok ? v : 0.f;
+            }
+            const unsigned int kb = __ballot_sync(0xFFFFFFFFu, ok);
+            if (lane == j) keep = kb;
         }
         if (keep != bits) bitmap[wi] = keep;
         cnt += __popc(keep);
@@ -331,19 +358,23 @@ compact_write_kernel(float* __restrict__ g, const float* __restrict__ w, unsigne
                      long long nwords, int dim, float lambda, const unsigned int* __restrict__ block_offsets,
                      const long long* __restrict__ meta, int* __restrict__ keys, float* __restrict__ vals,
                      float* __restrict__ dense_vals, long long capacity, unsigned int* status) {
+    __shared__ unsigned int s_warp_off[SKML_WARPS];
     const int kind = (int)meta[1];
-    long long base = ((long long)blockIdx.x * SKML_BLOCK + threadIdx.x) * COMPACT_WPT;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long wbase = (long long)blockIdx.x * COMPACT_WORDS + (long long)warp * (32 * COMPACT_WPT);
     if (kind == 2 && dense_vals != nullptr) {
-        // dense kind: every coordinate is shipped, so write g + lambda*w for all of them
-#pragma unroll
-        for (int j = 0; j < COMPACT_WPT; ++j) {
-            long long wi = base + j;
-            if (wi >= nwords) break;
-            bitmap[wi] = 0;
-            for (int t = 0; t < 32; ++t) {
-                long long k = wi * 32 + t;
+        // dense kind: every coordinate is shipped. Kept coordinates already hold g + lambda*w
+        // (count pass); all others contribute lambda * w alone.
+        for (int grp = 0; grp < COMPACT_WPT; ++grp) {
+            const long long gbase = wbase + grp * 32;
+            const long long wi = gbase + lane;
+            const unsigned int bits = wi < nwords ? bitmap[wi] : 0u;
+            if (wi < nwords) bitmap[wi] = 0;
+            for (int j = 0; j < 32; ++j) {
+                const unsigned int wb = __shfl_sync(0xFFFFFFFFu, bits, j);
+                const long long k = (gbase + j) * 32 + lane;
                 if (k < dim) {
-                    dense_vals[k] = g[k] + lambda * w[k];
+                    dense_vals[k] = ((wb >> lane) & 1u) ? g[k] : lambda * w[k];
                     g[k] = 0.f;
                 }
             }
@@ -353,34 +384,79 @@ compact_write_kernel(float* __restrict__ g, const float* __restrict__ w, unsigne
     unsigned int words[COMPACT_WPT];
     unsigned int cnt = 0;
 #pragma unroll
-    for (int j = 0; j < COMPACT_WPT; ++j) {
-        long long wi = base + j;
-        words[j] = wi < nwords ? bitmap[wi] : 0u;
-        cnt += __popc(words[j]);
+    for (int grp = 0; grp < COMPACT_WPT; ++grp) {
+        const long long wi = wbase + grp * 32 + lane;
+        words[grp] = wi < nwords ? bitmap[wi] : 0u;
+        cnt += __popc(words[grp]);
     }
-    unsigned int ex = block_exclusive_scan<unsigned int>(cnt, nullptr);
-    long long out = (long long)block_offsets[blockIdx.x] + ex;
+    const unsigned int warp_total = warp_sum(cnt);
+    if (lane == 0) s_warp_off[warp] = warp_total;
+    __syncthreads();
+    if (warp == 0) {
+        unsigned int v = s_warp_off[lane], inc = v;
 #pragma unroll
-    for (int j = 0; j < COMPACT_WPT; ++j) {
-        unsigned int b = words[j];
-        if (!b) continue;
-        long long wi = base + j;
-        bitmap[wi] = 0;
-        while (b) {
-            int t = __ffs(b) - 1;
-            b &= b - 1;
-            long long k = wi * 32 + t;
-            float v = g[k] + lambda * w[k];
-            g[k] = 0.f;
-            if (out < capacity) {
-                keys[out] = (int)k;
-                vals[out] = v;
-            } else {
-                skml_set_status(status, SKML_CAPACITY, 0x20u);
-            }
-            ++out;
+        for (int o = 1; o < 32; o <<= 1) {
+            unsigned int t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+            if (lane >= o) inc += t;
         }
+        s_warp_off[lane] = inc - v;
     }
+    __syncthreads();
+    long long out = (long long)block_offsets[blockIdx.x] + s_warp_off[warp];
+    bool overflow = false;
+#pragma unroll
+    for (int grp = 0; grp < COMPACT_WPT; ++grp) {
+        const long long gbase = wbase + grp * 32;
+        const long long wi = gbase + lane;
+        const unsigned int bits = words[grp];
+        const int pc = __popc(bits);
+        unsigned int inc = (unsigned int)pc;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            unsigned int t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+            if (lane >= o) inc += t;
+        }
+        const unsigned int ex = inc - (unsigned int)pc;
+        const unsigned int grp_total = __shfl_sync(0xFFFFFFFFu, inc, 31);
+        if (pc > 0 && pc <= COMPACT_SPARSE_BITS) {
+            unsigned int b = bits;
+            long long pos = out + ex;
+            while (b) {
+                const int t = __ffs(b) - 1;
+                b &= b - 1;
+                const long long k = wi * 32 + t;
+                if (pos < capacity) {
+                    keys[pos] = (int)k;
+                    vals[pos] = g[k];
+                } else {
+                    overflow = true;
+                }
+                g[k] = 0.f;
+                ++pos;
+            }
+        }
+        unsigned int dense = __ballot_sync(0xFFFFFFFFu, pc > COMPACT_SPARSE_BITS);
+        while (dense) {
+            const int j = __ffs(dense) - 1;
+            dense &= dense - 1;
+            const unsigned int wb = __shfl_sync(0xFFFFFFFFu, bits, j);
+            const unsigned int exj = __shfl_sync(0xFFFFFFFFu, ex, j);
+            if ((wb >> lane) & 1u) {
+                const long long k = (gbase + j) * 32 + lane;
+                const long long pos = out + exj + __popc(wb & ((1u << lane) - 1u));
+                if (pos < capacity) {
+                    keys[pos] = (int)k;
+                    vals[pos] = g[k];
+                } else {
+                    overflow = true;
+                }
+                g[k] = 0.f;
+            }
+        }
+        if (bits) bitmap[wi] = 0;
+        out += grp_total;
+    }
+    if (overflow) skml_set_status(status, SKML_CAPACITY, 0x20u);
 }
 
 extern "C" int skml_compact(float* g, const float* w, unsigned int* bitmap, int dim, float lambda,
