@@ -934,9 +934,20 @@ __device__ void stage_push_sparse(const CP& p, Smem& s) {
 // ---------------------------------------------------------------------------
 // Kernels
 // ---------------------------------------------------------------------------
+// Block 0 leaves a nanosecond time stamp per stage in the control words (u64 at ctrl[16 + 2 i]);
+// skml tools read them to show where a fused launch spends its time.
+__device__ __forceinline__ void stage_stamp(unsigned int* ctrl, int i) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        reinterpret_cast<unsigned long long*>(ctrl)[8 + i] = t;
+    }
+}
+
 #define STAGE_BARRIER(stage_id)                                                           \
     if (FUSED) {                                                                          \
         if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, stage_id)) return; \
+        stage_stamp(p.ctrl, stage_id);                                                    \
     }
 
 // STAGE < 0: all stages in one cooperative launch; otherwise only that stage.
@@ -970,6 +981,7 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_sparse_kernel(CP p, in
         return;
     }
     const bool given = p.given_splits != nullptr;
+    if (FUSED) stage_stamp(p.ctrl, 0);
     if (FUSED || stage == 1) {
         stage_prepare(p, n);
         if (!given) stage_summary(p, s, p.vals, n);
@@ -999,6 +1011,7 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_sparse_kernel(CP p, in
             compute_layout(p, s, n);
         }
         stage_push_sparse(p, s);
+        if (FUSED) stage_stamp(p.ctrl, 5);
     }
 }
 

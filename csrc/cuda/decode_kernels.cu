@@ -280,7 +280,17 @@ template <bool FUSED>
 __global__ void __launch_bounds__(SKML_BLOCK, 1) decode_update_kernel(DP p, int stage) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     DecSmem& s = *reinterpret_cast<DecSmem*>(smem_raw);
+    if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        reinterpret_cast<unsigned long long*>(p.ctrl)[8] = t;
+    }
     if (!decode_prepare(p, s)) return;
+    if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        reinterpret_cast<unsigned long long*>(p.ctrl)[9] = t;
+    }
     if (FUSED || stage == 1) {
         decode_accumulate(p, s);
         if (s.any_dense) decode_accumulate_dense(p, s);
@@ -288,7 +298,17 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) decode_update_kernel(DP p, int 
     if (FUSED) {
         if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, 0x21u)) return;
     }
+    if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        reinterpret_cast<unsigned long long*>(p.ctrl)[10] = t;
+    }
     if (FUSED || stage == 2) decode_update(p, s);
+    if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        reinterpret_cast<unsigned long long*>(p.ctrl)[11] = t;
+    }
 }
 
 extern "C" long long skml_decode_workspace_bytes(long long world, long long group_num) {

@@ -25,6 +25,8 @@
 #define GRAD_WARPS (GRAD_THREADS / 32)
 #define GRAD_TILE_CAP 4096  // elements of one staged tile (cols and values each)
 #define SKML_EPS 1e-8f
+#define GRAD_MAX_RPT 256   // rows of one tile at most
+#define GRAD_RPI 4         // rows per warp and iteration
 
 __device__ __forceinline__ float glm_loss(int loss_id, float pre, float y) {
     if (loss_id == 0) {
@@ -72,6 +74,8 @@ glm_rows_kernel(const long long* __restrict__ rowptr, const int* __restrict__ co
     extern __shared__ __align__(128) unsigned char smem_raw[];
     // layout: [2 stages x cols][2 stages x vals][hot floats]; barriers in static smem
     __shared__ GradSmem sb;
+    __shared__ long long s_rp[GRAD_MAX_RPT + 1];
+    __shared__ float s_lab[GRAD_MAX_RPT];
     int* s_cols = reinterpret_cast<int*>(smem_raw);
     float* s_vals = reinterpret_cast<float*>(smem_raw + 2 * GRAD_TILE_CAP * sizeof(int));
     float* s_hot = reinterpret_cast<float*>(smem_raw + 4 * GRAD_TILE_CAP * sizeof(int));
@@ -128,53 +132,74 @@ glm_rows_kernel(const long long* __restrict__ rowptr, const int* __restrict__ co
             }
             phase[stage] ^= 1;
         }
-        const int* tc = s_cols + stage * GRAD_TILE_CAP;
-        const float* tv = s_vals + stage * GRAD_TILE_CAP;
+        const int* cp = staged ? (s_cols + stage * GRAD_TILE_CAP) - a0 : cols;
+        const float* vp = has_vals ? (staged ? (s_vals + stage * GRAD_TILE_CAP) - a0 : vals) : nullptr;
         long long r0 = row_lo + tile * rows_per_tile;
         long long r1 = r0 + rows_per_tile;
         if (r1 > row_lo + row_cnt) r1 = row_lo + row_cnt;
-        for (long long r = r0 + warp; r < r1; r += GRAD_WARPS) {
-            long long e0 = rowptr[r], e1 = rowptr[r + 1];
-            float sum = 0.f;
-            for (long long e = e0 + lane; e < e1; e += 32) {
-                int c = staged ? tc[e - a0] : cols[e];
-                float v = has_vals ? (staged ? tv[e - a0] : vals[e]) : 1.f;
-                sum = fmaf(__ldg(w + c), v, sum);
+        const int nrows = (int)(r1 - r0);
+        for (int t = threadIdx.x; t <= nrows; t += blockDim.x) s_rp[t] = rowptr[r0 + t];
+        for (int t = threadIdx.x; t < nrows; t += blockDim.x) s_lab[t] = labels[r0 + t];
+        __syncthreads();
+        // GRAD_RPI rows per warp and iteration: their gathers of w are independent, so several
+        // L2 round trips overlap instead of one per row.
+        for (int rb = warp * GRAD_RPI; rb < nrows; rb += GRAD_WARPS * GRAD_RPI) {
+            long long e0[GRAD_RPI], e1[GRAD_RPI];
+            float sum[GRAD_RPI];
+#pragma unroll
+            for (int u = 0; u < GRAD_RPI; ++u) {
+                const int rr = rb + u < nrows ? rb + u : nrows - 1;
+                e0[u] = s_rp[rr];
+                e1[u] = rb + u < nrows ? s_rp[rr + 1] : e0[u];
+                sum[u] = 0.f;
             }
-            float pre = warp_sum(sum);
-            float y = labels[r];
-            if (MODE == 0) {
-                float coef = -glm_grad(loss_id, pre, y) * inv_batch;
-                if (lane == 0) loss_sum += (double)glm_loss(loss_id, pre, y);
-                if (coef != 0.f) {
-                    for (long long e = e0 + lane; e < e1; e += 32) {
-                        int c = staged ? tc[e - a0] : cols[e];
-                        float v = has_vals ? (staged ? tv[e - a0] : vals[e]) : 1.f;
-                        float contrib = coef * v;
-                        if (c < hot) {
-                            atomicAdd(&s_hot[c], contrib);
-                        } else {
-                            red_add_f32(g + c, contrib);
-                            unsigned int bit = 1u << (c & 31);
-                            unsigned int* word = bitmap + (c >> 5);
-                            if (!(*(volatile unsigned int*)word & bit)) atomicOr(word, bit);
+#pragma unroll
+            for (int u = 0; u < GRAD_RPI; ++u) {
+                for (long long e = e0[u] + lane; e < e1[u]; e += 32) {
+                    const float v = vp ? vp[e] : 1.f;
+                    sum[u] = fmaf(__ldg(w + cp[e]), v, sum[u]);
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+                for (int u = 0; u < GRAD_RPI; ++u) sum[u] += __shfl_xor_sync(0xFFFFFFFFu, sum[u], o);
+            }
+#pragma unroll
+            for (int u = 0; u < GRAD_RPI; ++u) {
+                if (rb + u >= nrows) break;
+                const float pre = sum[u];
+                const float y = s_lab[rb + u];
+                if (MODE == 0) {
+                    const float coef = -glm_grad(loss_id, pre, y) * inv_batch;
+                    if (lane == 0) loss_sum += (double)glm_loss(loss_id, pre, y);
+                    if (coef != 0.f) {
+                        for (long long e = e0[u] + lane; e < e1[u]; e += 32) {
+                            const int c = cp[e];
+                            const float contrib = coef * (vp ? vp[e] : 1.f);
+                            if (c < hot) {
+                                atomicAdd(&s_hot[c], contrib);
+                            } else {
+                                red_add_f32(g + c, contrib);
+                                const unsigned int bit = 1u << (c & 31);
+                                unsigned int* word = bitmap + (c >> 5);
+                                if (!(*(volatile unsigned int*)word & bit)) atomicOr(word, bit);
+                            }
                         }
                     }
-                }
-            } else {
-                if (lane == 0) {
+                } else if (lane == 0) {
                     loss_sum += (double)glm_loss(loss_id, pre, y);
-                    float z = pre * y;
+                    const float z = pre * y;
                     if (z > 0.f) {
                         if (pre > 0.f) ++tp; else ++tn;
                     } else if (z < 0.f) {
                         if (pre > 0.f) ++fp; else ++fn;
                     }
-                    if (margins) margins[r - row_lo] = pre;
+                    if (margins) margins[r0 - row_lo + rb + u] = pre;
                 }
             }
         }
-        __syncthreads();  // everyone is done with `stage` before it is refilled
+        __syncthreads();  // everyone is done with `stage` (and s_rp / s_lab) before it is refilled
     }
 
     if (MODE == 0) {
@@ -223,7 +248,7 @@ static int grad_launch(int mode, const long long* rowptr, const int* cols, const
     if (mode != 0) hot = 0;
     int rpt = (int)(GRAD_TILE_CAP * 0.8 / (avg_nnz > 1.0 ? avg_nnz : 1.0));
     if (rpt < 1) rpt = 1;
-    if (rpt > 256) rpt = 256;
+    if (rpt > GRAD_MAX_RPT) rpt = GRAD_MAX_RPT;
     long long ntiles = (row_cnt + rpt - 1) / rpt;
     size_t smem = 4 * GRAD_TILE_CAP * sizeof(int) + (size_t)hot * sizeof(float);
     int per_sm = smem > 100 * 1024 ? 1 : 2;
