@@ -169,6 +169,56 @@ SKML_HD int32_t skml_hash(int id, int32_t key, int32_t size) {
     return skml_mod_size(c, size);
 }
 
+// Division-free variants for the kernels' inner loops. They return exactly what
+// skml_hash returns for non-negative keys (checked against it on the CPU):
+// * the decimal digits of a key are extracted once and shared by the BKDR members;
+// * `x % size` uses a precomputed magic number (Lemire's fastmod: for 32-bit x and size,
+//   x mod size = mulhi64(magic * x, size) with magic = floor((2^64 - 1) / size) + 1).
+struct SkmlKeyDigits {
+    uint64_t packed;  // digit i (least significant first) in bits [4i, 4i + 4)
+    int count;
+};
+
+SKML_HD void skml_key_digits(int32_t key, SkmlKeyDigits& kd) {
+    uint32_t k = key < 0 ? 0u : (uint32_t)key;
+    kd.packed = 0;
+    kd.count = 0;
+    while (k != 0) {
+        uint32_t q = k / 10u;
+        kd.packed |= (uint64_t)(k - q * 10u) << (4 * kd.count);
+        ++kd.count;
+        k = q;
+    }
+}
+
+SKML_HD uint64_t skml_fastmod_magic(uint32_t size) { return 0xFFFFFFFFFFFFFFFFull / size + 1ull; }
+
+SKML_HD uint32_t skml_fastmod(uint32_t x, uint64_t magic, uint32_t size) {
+    uint64_t low = magic * (uint64_t)x;
+#if defined(__CUDA_ARCH__)
+    return (uint32_t)__umul64hi(low, (uint64_t)size);
+#else
+    return (uint32_t)(((unsigned __int128)low * size) >> 64);
+#endif
+}
+
+SKML_HD int32_t skml_hash_fast(int id, int32_t key, const SkmlKeyDigits& kd, int32_t size, uint64_t magic) {
+    if (key < 0) return skml_hash(id, key, size);
+    uint32_t c;
+    if (id == 0) c = skml_mix_bj((uint32_t)key);
+    else if (id == 1) c = skml_mix_64((uint32_t)key);
+    else if (id == 2) c = skml_mix_tw((uint32_t)key);
+    else {
+        const uint32_t seed = id == 3 ? 31u : (id == 4 ? 131u : (id == 5 ? 267u : (id == 6 ? 1313u : 13131u)));
+        c = 0;
+        for (int i = 0; i < kd.count; ++i) c = seed * c + (uint32_t)((kd.packed >> (4 * i)) & 15u);
+    }
+    const int32_t sc = (int32_t)c;
+    if (sc >= 0) return (int32_t)skml_fastmod(c, magic, (uint32_t)size);
+    const uint32_t m = skml_fastmod((uint32_t)(-(int64_t)sc), magic, (uint32_t)size);  // Java: remainder keeps the sign
+    return m ? size - (int32_t)m : 0;
+}
+
 // ---------------------------------------------------------------------------
 // Counter-based random numbers (splitmix64): every rank derives the same value
 // from (seed, step, rank, group, slot) without any shared state.

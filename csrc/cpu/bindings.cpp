@@ -174,6 +174,17 @@ PYBIND11_MODULE(_oracle, m) {
         for (ssize_t i = 0; i < keys.size(); ++i) out[i] = skml_hash(id, keys.data()[i], size);
         return to_array(out);
     });
+    m.def("hash_fast", [](int id, I32Array keys, int32_t size) {
+        if (id < 0 || id > 7 || size <= 0) throw Error("hash id or range out of bounds");
+        std::vector<int32_t> out(keys.size());
+        uint64_t magic = skml_fastmod_magic((uint32_t)size);
+        for (ssize_t i = 0; i < keys.size(); ++i) {
+            SkmlKeyDigits kd;
+            skml_key_digits(keys.data()[i], kd);
+            out[i] = skml_hash_fast(id, keys.data()[i], kd, size, magic);
+        }
+        return to_array(out);
+    });
     m.def("pick_hashes", [](uint64_t seed, uint64_t step, uint32_t rank, uint32_t group, int rows) {
         if (rows > 8 || rows < 1) throw Error("Currently only 8 hash functions are available");
         uint8_t ids[8];

@@ -90,6 +90,7 @@ struct Layout {
     unsigned long long base_bytes[SKML_MAX_GROUPS];
     int base_prev[SKML_MAX_GROUPS];
     unsigned char hash_ids[SKML_MAX_GROUPS][8];
+    unsigned long long col_magic[SKML_MAX_GROUPS];  // ceil(2^64 / col) for the division-free modulo
     unsigned long long off_bv, off_gt, off_flags, off_restart, off_tables, off_deltas, total_bytes;
     int overflow;
 };
@@ -161,6 +162,8 @@ struct Smem {
     unsigned int wcnt[SKML_WARPS][SKML_MAX_GROUPS];
     unsigned int wbytes[SKML_WARPS][SKML_MAX_GROUPS];
     int cin[SKML_WARPS][SKML_MAX_GROUPS];
+    unsigned int wexc[SKML_WARPS][SKML_MAX_GROUPS];
+    unsigned int wexb[SKML_WARPS][SKML_MAX_GROUPS];
     int carry_key[SKML_MAX_GROUPS];
     int first_key[SKML_MAX_GROUPS];
     unsigned int cnt[SKML_MAX_GROUPS];
@@ -253,7 +256,7 @@ __device__ void stage_summary(const CP& p, Smem& s, const float* __restrict__ va
             s.tile[t] = k;
         }
         __syncthreads();
-        block_bitonic_sort<TILE>(s.tile);
+        block_sort_2048(s.tile);
         n_c += (unsigned long long)m;
         if (m == TILE) {
             unsigned int off = (unsigned int)(skml_rand(p.seed, p.step, ((unsigned long long)p.rank << 32) | blockIdx.x,
@@ -502,7 +505,8 @@ __device__ void element_pass(const CP& p, Smem& s, long long n) {
         s.tile_bytes[threadIdx.x] = 0;
     }
     __syncthreads();
-    const int wg_g = threadIdx.x % G, wg_w = threadIdx.x / G;  // (warp, group) role of this thread
+    // (warp, group) role of the first 32 * G threads: cross-warp prefixes of one group
+    const int wg_g = threadIdx.x % G, wg_w = threadIdx.x / G;
     const bool wg_on = threadIdx.x < SKML_WARPS * G;
     const Layout& L = s.lay;
     const int zero = s.qi.zero_idx;
@@ -535,23 +539,23 @@ __device__ void element_pass(const CP& p, Smem& s, long long n) {
         const bool last_in_warp = valid && (peers >> lane) == 1u;
         if (last_in_warp) s.wlast[warp][g] = key;
         __syncthreads();
+        int role_carry = -1;  // last key of group wg_g before warp wg_w (role threads)
         if (wg_on) {
-            int c = s.carry_key[wg_g];
+            role_carry = s.carry_key[wg_g];
             for (int w2 = 0; w2 < wg_w; ++w2) {
-                int k2 = s.wlast[w2][wg_g];
-                if (k2 >= 0) c = k2;
+                const int k2 = s.wlast[w2][wg_g];
+                if (k2 >= 0) role_carry = k2;
             }
-            s.cin[wg_w][wg_g] = c;
+            s.cin[wg_w][wg_g] = role_carry;
         }
         __syncthreads();
         int prev = -1;
         if (valid) prev = lower ? prev_in_warp : s.cin[warp][g];
-        // widths
         int w = 0;
         unsigned int delta = 0;
         if (valid) {
             if (PACK) {
-                int pk = prev >= 0 ? prev : L.base_prev[g];
+                const int pk = prev >= 0 ? prev : L.base_prev[g];
                 delta = (unsigned int)(key - pk);
                 w = skml_delta_bytes(delta);
             } else if (prev >= 0) {
@@ -566,20 +570,16 @@ __device__ void element_pass(const CP& p, Smem& s, long long n) {
                 if (prev < 0) s.first_key[g] = key;
                 if (lower == 0) {  // first lane of its group in this warp adds the warp's share
                     atomicAdd(&s.cnt[g], (unsigned int)__popc(peers));
-                    unsigned long long by = __popc(peers & b1) + 2 * __popc(peers & b2) + 4 * __popc(peers & b4);
+                    const unsigned long long by = __popc(peers & b1) + 2 * __popc(peers & b2) + 4 * __popc(peers & b4);
                     if (by) atomicAdd(&s.bytes[g], by);
                 }
             }
-            __syncthreads();
-            if (threadIdx.x < G) {  // carry the last key of every group into the next tile
-                int c = s.carry_key[threadIdx.x];
-                for (int w2 = 0; w2 < SKML_WARPS; ++w2) {
-                    int k2 = s.wlast[w2][threadIdx.x];
-                    if (k2 >= 0) c = k2;
-                }
-                s.carry_key[threadIdx.x] = c;
+            // the last key of every group is carried into the next tile (the next tile's first
+            // barrier orders this write against its readers)
+            if (wg_on && wg_w == SKML_WARPS - 1) {
+                const int k2 = s.wlast[wg_w][wg_g];
+                s.carry_key[wg_g] = k2 >= 0 ? k2 : role_carry;
             }
-            __syncthreads();
             continue;
         }
         // ---- PACK ----
@@ -590,16 +590,19 @@ __device__ void element_pass(const CP& p, Smem& s, long long n) {
             s.wbytes[warp][g] = bw + (unsigned int)w;
         }
         __syncthreads();
-        unsigned int ex_cnt = 0, ex_bytes = 0;
-        if (valid) {
-            for (int w2 = 0; w2 < warp; ++w2) {
-                ex_cnt += s.wcnt[w2][g];
-                ex_bytes += s.wbytes[w2][g];
+        unsigned int role_cnt = 0, role_bytes = 0;
+        if (wg_on) {  // exclusive prefix over the warps, once per (warp, group)
+            for (int w2 = 0; w2 < wg_w; ++w2) {
+                role_cnt += s.wcnt[w2][wg_g];
+                role_bytes += s.wbytes[w2][wg_g];
             }
+            s.wexc[wg_w][wg_g] = role_cnt;
+            s.wexb[wg_w][wg_g] = role_bytes;
         }
+        __syncthreads();
         if (valid && !overflow) {
-            const unsigned long long prank = (unsigned long long)L.base_rank[g] + s.tile_rank[g] + ex_cnt + r_w;
-            const unsigned long long boff = L.base_bytes[g] + s.tile_bytes[g] + ex_bytes + bw;
+            const unsigned long long prank = (unsigned long long)L.base_rank[g] + s.tile_rank[g] + s.wexc[warp][g] + r_w;
+            const unsigned long long boff = L.base_bytes[g] + s.tile_bytes[g] + s.wexb[warp][g] + bw;
             // flags: (w - 1) most significant bit first at stream bits 2p, 2p+1
             const unsigned int fv = (unsigned int)(w - 1);
             if (fv) {
@@ -620,24 +623,18 @@ __device__ void element_pass(const CP& p, Smem& s, long long n) {
             const unsigned int cell = skml_pack_cell(bin, zero);
             const int col = (int)L.col[g];
             unsigned int* tab = p.tables + L.tab32_off[g];
+            SkmlKeyDigits kd;
+            skml_key_digits(key, kd);
             for (int r = 0; r < p.rows; ++r)
-                atomicMin(tab + (long long)r * col + skml_hash(L.hash_ids[g][r], key, col), cell);
+                atomicMin(tab + (long long)r * col + skml_hash_fast(L.hash_ids[g][r], key, kd, col, L.col_magic[g]), cell);
         }
-        __syncthreads();
-        if (threadIdx.x < G) {
-            int c = s.carry_key[threadIdx.x];
-            unsigned int tc = 0, tb = 0;
-            for (int w2 = 0; w2 < SKML_WARPS; ++w2) {
-                int k2 = s.wlast[w2][threadIdx.x];
-                if (k2 >= 0) c = k2;
-                tc += s.wcnt[w2][threadIdx.x];
-                tb += s.wbytes[w2][threadIdx.x];
-            }
-            s.carry_key[threadIdx.x] = c;
-            s.tile_rank[threadIdx.x] += tc;
-            s.tile_bytes[threadIdx.x] += tb;
+        __syncthreads();  // all readers of tile_rank / tile_bytes are done
+        if (wg_on && wg_w == SKML_WARPS - 1) {
+            const int k2 = s.wlast[wg_w][wg_g];
+            s.carry_key[wg_g] = k2 >= 0 ? k2 : role_carry;
+            s.tile_rank[wg_g] += role_cnt + s.wcnt[wg_w][wg_g];
+            s.tile_bytes[wg_g] += role_bytes + s.wbytes[wg_w][wg_g];
         }
-        __syncthreads();
     }
     if (!PACK) {
         __syncthreads();
@@ -753,6 +750,7 @@ __device__ void compute_layout(const CP& p, Smem& s, long long n) {
                 if (col < 1) col = 1;
             }
             L.col[g] = col;
+            L.col_magic[g] = col ? skml_fastmod_magic(col) : 0ull;
             L.table_off[g] = o;
             L.tab32_off[g] = t32;
             o += skml_align16((unsigned long long)p.rows * col * (cb / 8));

@@ -22,6 +22,7 @@
 #include "skml_device.cuh"
 
 #define DEC_MAX_ITEMS (SKML_MAX_PEERS * SKML_MAX_GROUPS)
+#define DEC_THREADS 512  // two keys of a 1024-key chunk per thread
 
 struct DP {
     const unsigned char* payload[SKML_MAX_PEERS];
@@ -50,6 +51,7 @@ struct DecItem {  // one (rank, group) key stream
     unsigned long long chunk_prefix, key_prefix;
     unsigned int zero, cell_bits, rows;
     unsigned long long off_bv;
+    unsigned long long col_magic;
 };
 
 struct DecSmem {
@@ -58,6 +60,7 @@ struct DecSmem {
     int nitems;
     unsigned long long total_chunks, total_keys;
     int any_dense;
+    int direct;      // world == 1 and no dense payload: D1 applies the update, D2 has nothing to do
     int shift;       // fixed-point: accumulator = value * 2^shift
     double inv_world;
     int ok;
@@ -149,6 +152,7 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
                 it.cell_bits = h.cell_bits;
                 it.rows = h.row_num;
                 it.off_bv = h.off_bucket_values;
+                it.col_magic = skml_fastmod_magic(it.e.col_num);
                 chunks += (it.e.n + SKML_RESTART_INTERVAL - 1) / SKML_RESTART_INTERVAL;
                 keys += it.e.n;
                 ++ni;
@@ -162,6 +166,7 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
         s.total_chunks = chunks;
         s.total_keys = keys;
         s.any_dense = dense;
+        s.direct = (p.world == 1 && !dense) ? 1 : 0;
         int e = 0;
         if (mx > 0.0 && isfinite(mx)) frexp(mx, &e);
         s.shift = 60 - e;
@@ -171,7 +176,48 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
     return s.ok != 0;
 }
 
-// D1 for sparse payloads: chunk loop.
+// Query of one key in its group's sketch and accumulation of the dequantized value.
+__device__ __forceinline__ void decode_one(const DP& p, const DecSmem& s, const DecItem& it, unsigned int key) {
+    if (key >= (unsigned long long)p.dim) {
+        skml_set_status(p.status, SKML_BAD_HEADER, 0x200u);
+        return;
+    }
+    const int col = (int)it.e.col_num;
+    const int zero = (int)it.zero;
+    SkmlKeyDigits kd;
+    skml_key_digits((int)key, kd);
+    int cells[SKML_MAX_ROWS];
+#pragma unroll
+    for (int r = 0; r < SKML_MAX_ROWS; ++r) {  // independent loads first
+        cells[r] = zero;
+        if (r < (int)it.rows) {
+            const unsigned long long c = (unsigned long long)r * col +
+                                         (unsigned int)skml_hash_fast(it.e.hash_ids[r], (int)key, kd, col, it.col_magic);
+            if (it.cell_bits == 8) cells[r] = __ldcg(it.base + it.e.table_off + c);
+            else cells[r] = __ldcg(reinterpret_cast<const unsigned short*>(it.base + it.e.table_off) + c);
+        }
+    }
+    int res = zero, best = 0;
+#pragma unroll
+    for (int r = 0; r < SKML_MAX_ROWS; ++r) {
+        int d = cells[r] - zero;
+        if (d < 0) d = -d;
+        if (d > best) {
+            best = d;
+            res = cells[r];
+        }
+    }
+    const float bv = __ldcg(reinterpret_cast<const float*>(it.base + it.off_bv) + res);
+    if (s.direct) {  // one rank, sparse payload: nothing to sum, update in place (keys are unique)
+        apply_one(p, key, bv);
+        return;
+    }
+    const long long fx = to_fixed((double)bv * s.inv_world, s.shift);
+    if (fx) atomicAdd(reinterpret_cast<unsigned long long*>(p.acc + key), (unsigned long long)fx);
+}
+
+// D1 for sparse payloads: one 1024-key chunk per block iteration, two adjacent keys per thread
+// (512 threads), so that every thread has two independent load chains in flight.
 __device__ void decode_accumulate(const DP& p, DecSmem& s) {
     for (unsigned long long ch = blockIdx.x; ch < s.total_chunks; ch += gridDim.x) {
         int it_i = 0;
@@ -181,52 +227,48 @@ __device__ void decode_accumulate(const DP& p, DecSmem& s) {
         const unsigned int first = j * SKML_RESTART_INTERVAL;
         const unsigned int cnt = min((unsigned int)SKML_RESTART_INTERVAL, it.e.n - first);
         const SkmlRestart rs = *reinterpret_cast<const SkmlRestart*>(it.base + it.e.restart_off + 16ull * j);
-        const unsigned int i = threadIdx.x;
-        unsigned int w = 0;
-        if (i < cnt) {
-            const unsigned long long fb = (unsigned long long)rs.flag_bit_off + 2ull * i;
+        const unsigned int i0 = 2 * threadIdx.x, i1 = i0 + 1;
+        unsigned int w0 = 0, w1 = 0;
+        if (i0 < cnt) {
+            // the flags of keys 2t and 2t+1 are 4 adjacent bits of one 32-bit word
+            const unsigned long long fb = (unsigned long long)rs.flag_bit_off + 2ull * i0;
             const unsigned int word = __ldcg(reinterpret_cast<const unsigned int*>(it.base + it.e.flag_off) + (fb >> 5));
-            const unsigned int b = (word >> (fb & 31)) & 3u;
-            w = (((b & 1u) << 1) | (b >> 1)) + 1u;  // stream order is most significant bit first
-            if (w == 3) w = 4;                      // flag value 2 is never written
+            const unsigned int b = (word >> (fb & 31)) & 15u;
+            w0 = (((b & 1u) << 1) | ((b >> 1) & 1u)) + 1u;  // stream order is most significant bit first
+            if (w0 == 3) w0 = 4;                             // flag value 2 is never written
+            if (i1 < cnt) {
+                const unsigned int b2 = b >> 2;
+                w1 = (((b2 & 1u) << 1) | (b2 >> 1)) + 1u;
+                if (w1 == 3) w1 = 4;
+            }
         }
         unsigned int total_w;
-        const unsigned int boff = block_exclusive_scan<unsigned int>(w, &total_w);
-        unsigned int delta = 0;
-        if (i < cnt) {
+        const unsigned int boff = block_exclusive_scan<unsigned int>(w0 + w1, &total_w);
+        unsigned int d0 = 0, d1 = 0;
+        if (i0 < cnt) {
             const unsigned long long byte0 = (rs.delta_bit_off >> 3) + boff;
-            if (byte0 + w <= 8ull * it.e.n_delta_words) {
+            if (byte0 + w0 + w1 <= 8ull * it.e.n_delta_words) {
                 const unsigned char* src = it.base + it.e.delta_off + byte0;
-                for (unsigned int t = 0; t < w; ++t) delta = (delta << 8) | skml_brev8(__ldcg(src + t));
+                unsigned char raw[8];
+#pragma unroll
+                for (unsigned int t = 0; t < 8; ++t) raw[t] = t < w0 + w1 ? __ldcg(src + t) : 0;
+#pragma unroll
+                for (unsigned int t = 0; t < 8; ++t) {
+                    if (t < w0) d0 = (d0 << 8) | skml_brev8(raw[t]);
+                    else if (t < w0 + w1) d1 = (d1 << 8) | skml_brev8(raw[t]);
+                }
             }
         }
         unsigned int total_d;
-        const unsigned int dex = block_exclusive_scan<unsigned int>(delta, &total_d);
-        if (i < cnt) {
-            const unsigned int key = rs.prev_key + dex + delta;
-            p.key_scratch[it.key_prefix + first + i] = (int)key;
-            if (key < (unsigned long long)p.dim) {
-                const int col = (int)it.e.col_num;
-                const int zero = (int)it.zero;
-                int res = zero, best = 0;
-                for (unsigned int r = 0; r < it.rows; ++r) {
-                    const unsigned long long c = (unsigned long long)r * col + (unsigned int)skml_hash(it.e.hash_ids[r], (int)key, col);
-                    int cell;
-                    if (it.cell_bits == 8) cell = __ldcg(it.base + it.e.table_off + c);
-                    else cell = __ldcg(reinterpret_cast<const unsigned short*>(it.base + it.e.table_off) + c);
-                    int d = cell - zero;
-                    if (d < 0) d = -d;
-                    if (d > best) {
-                        best = d;
-                        res = cell;
-                    }
-                }
-                const float bv = __ldcg(reinterpret_cast<const float*>(it.base + it.off_bv) + res);
-                const long long fx = to_fixed((double)bv * s.inv_world, s.shift);
-                if (fx) atomicAdd(reinterpret_cast<unsigned long long*>(p.acc + key), (unsigned long long)fx);
-            } else {
-                skml_set_status(p.status, SKML_BAD_HEADER, 0x200u);
-            }
+        const unsigned int dex = block_exclusive_scan<unsigned int>(d0 + d1, &total_d);
+        if (i0 < cnt) {
+            const unsigned int key0 = rs.prev_key + dex + d0;
+            const unsigned int key1 = key0 + d1;
+            int* ks = p.key_scratch + it.key_prefix + first;
+            ks[i0] = (int)key0;
+            if (i1 < cnt) ks[i1] = (int)key1;
+            decode_one(p, s, it, key0);
+            if (i1 < cnt) decode_one(p, s, it, key1);
         }
         __syncthreads();
     }
@@ -252,7 +294,9 @@ __device__ void decode_accumulate_dense(const DP& p, DecSmem& s) {
 // D2: claim and update.
 __device__ void decode_update(const DP& p, DecSmem& s) {
     const long long gsz = (long long)gridDim.x * blockDim.x, gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (s.any_dense) {
+    if (s.direct) {
+        // already applied in D1
+    } else if (s.any_dense) {
         for (long long i = gid; i < p.dim; i += gsz) {
             long long a = p.acc[i];
             if (a) {
@@ -261,11 +305,20 @@ __device__ void decode_update(const DP& p, DecSmem& s) {
             }
         }
     } else {
-        for (long long t = gid; t < (long long)s.total_keys; t += gsz) {
-            const long long k = (unsigned int)p.key_scratch[t];
-            if (k >= p.dim) continue;
-            const long long a = (long long)atomicExch(reinterpret_cast<unsigned long long*>(p.acc + k), 0ull);
-            if (a) apply_one(p, k, (float)from_fixed(a, s.shift));
+        // four independent claims per thread and iteration: their round trips overlap
+        for (long long t = gid; t < (long long)s.total_keys; t += 4 * gsz) {
+            long long k[4], a[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const long long tt = t + u * gsz;
+                k[u] = tt < (long long)s.total_keys ? (long long)(unsigned int)p.key_scratch[tt] : p.dim;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                a[u] = k[u] < p.dim ? (long long)atomicExch(reinterpret_cast<unsigned long long*>(p.acc + k[u]), 0ull) : 0ll;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (a[u]) apply_one(p, k[u], (float)from_fixed(a[u], s.shift));
         }
     }
     if (blockIdx.x == 0 && threadIdx.x == 0 && p.loss_out) {
@@ -277,7 +330,7 @@ __device__ void decode_update(const DP& p, DecSmem& s) {
 }
 
 template <bool FUSED>
-__global__ void __launch_bounds__(SKML_BLOCK, 1) decode_update_kernel(DP p, int stage) {
+__global__ void __launch_bounds__(DEC_THREADS, 2) decode_update_kernel(DP p, int stage) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     DecSmem& s = *reinterpret_cast<DecSmem*>(smem_raw);
     if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) {
@@ -295,7 +348,7 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) decode_update_kernel(DP p, int 
         decode_accumulate(p, s);
         if (s.any_dense) decode_accumulate_dense(p, s);
     }
-    if (FUSED) {
+    if (FUSED && !s.direct) {
         if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, 0x21u)) return;
     }
     if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) {
@@ -347,23 +400,23 @@ extern "C" int skml_decode_update(const SkmlDecodeArgs* a, void* stream_) {
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int grid = a->grid > 0 ? (int)a->grid : (sms > 0 ? sms : 148);
+    int grid = a->grid > 0 ? (int)a->grid : 2 * (sms > 0 ? sms : 148);  // two 512-thread blocks per SM
     cudaError_t e = cudaFuncSetAttribute(decode_update_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DecSmem));
     if (e != cudaSuccess) return (int)e;
     e = cudaFuncSetAttribute(decode_update_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DecSmem));
     if (e != cudaSuccess) return (int)e;
     if (a->fused) {
         int per_sm = 0;
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_update_kernel<true>, SKML_BLOCK, sizeof(DecSmem));
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_update_kernel<true>, DEC_THREADS, sizeof(DecSmem));
         if (per_sm < 1) return (int)cudaErrorLaunchOutOfResources;
         if (grid > per_sm * sms) grid = per_sm * sms;
         int stage = -1;
         void* args[] = {&p, &stage};
-        return (int)cudaLaunchCooperativeKernel((const void*)decode_update_kernel<true>, dim3(grid), dim3(SKML_BLOCK), args,
+        return (int)cudaLaunchCooperativeKernel((const void*)decode_update_kernel<true>, dim3(grid), dim3(DEC_THREADS), args,
                                                 sizeof(DecSmem), stream);
     }
     for (int st = 1; st <= 2; ++st) {
-        decode_update_kernel<false><<<grid, SKML_BLOCK, sizeof(DecSmem), stream>>>(p, st);
+        decode_update_kernel<false><<<grid, DEC_THREADS, sizeof(DecSmem), stream>>>(p, st);
         e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;
     }

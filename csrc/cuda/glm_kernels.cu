@@ -27,6 +27,7 @@
 #define SKML_EPS 1e-8f
 #define GRAD_MAX_RPT 256   // rows of one tile at most
 #define GRAD_RPI 4         // rows per warp and iteration
+#define GRAD_PRIV 256      // hottest columns kept once per warp
 
 __device__ __forceinline__ float glm_loss(int loss_id, float pre, float y) {
     if (loss_id == 0) {
@@ -59,6 +60,10 @@ __device__ __forceinline__ void red_add_f32(float* p, float v) {
     asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
 }
 
+__device__ __forceinline__ void red_or_u32(unsigned int* p, unsigned int v) {
+    asm volatile("red.global.or.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 struct GradSmem {
     uint64_t bar[2];
 };
@@ -72,18 +77,22 @@ glm_rows_kernel(const long long* __restrict__ rowptr, const int* __restrict__ co
                 unsigned int* __restrict__ bitmap, int loss_id, float inv_batch, int hot, double* __restrict__ acc,
                 float* __restrict__ margins, unsigned int* status, long long budget) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    // layout: [2 stages x cols][2 stages x vals][hot floats]; barriers in static smem
+    // layout: [2 stages x cols][2 stages x vals, only if the shard stores values][hot floats]
     __shared__ GradSmem sb;
     __shared__ long long s_rp[GRAD_MAX_RPT + 1];
     __shared__ float s_lab[GRAD_MAX_RPT];
     int* s_cols = reinterpret_cast<int*>(smem_raw);
     float* s_vals = reinterpret_cast<float*>(smem_raw + 2 * GRAD_TILE_CAP * sizeof(int));
-    float* s_hot = reinterpret_cast<float*>(smem_raw + 4 * GRAD_TILE_CAP * sizeof(int));
     const bool has_vals = vals != nullptr;
+    float* s_hot = reinterpret_cast<float*>(smem_raw + (has_vals ? 4 : 2) * GRAD_TILE_CAP * sizeof(int));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int priv = hot < GRAD_PRIV ? hot : GRAD_PRIV;  // columns [0, priv): per-warp private sums
+    float* s_priv = s_hot + hot;
 
-    if (MODE == 0)
+    if (MODE == 0) {
         for (int i = threadIdx.x; i < hot; i += blockDim.x) s_hot[i] = 0.f;
+        for (int i = threadIdx.x; i < priv * GRAD_WARPS; i += blockDim.x) s_priv[i] = 0.f;
+    }
     if (threadIdx.x == 0) {
         mbar_init(&sb.bar[0], 1);
         mbar_init(&sb.bar[1], 1);
@@ -141,53 +150,52 @@ glm_rows_kernel(const long long* __restrict__ rowptr, const int* __restrict__ co
         for (int t = threadIdx.x; t <= nrows; t += blockDim.x) s_rp[t] = rowptr[r0 + t];
         for (int t = threadIdx.x; t < nrows; t += blockDim.x) s_lab[t] = labels[r0 + t];
         __syncthreads();
-        // GRAD_RPI rows per warp and iteration: their gathers of w are independent, so several
-        // L2 round trips overlap instead of one per row.
+        // GRAD_RPI rows per warp and iteration. All loads of one 32-element slice of the
+        // GRAD_RPI rows are issued before any of them is consumed, so their L2 round trips overlap.
         for (int rb = warp * GRAD_RPI; rb < nrows; rb += GRAD_WARPS * GRAD_RPI) {
-            long long e0[GRAD_RPI], e1[GRAD_RPI];
+            long long e0[GRAD_RPI];
+            int len[GRAD_RPI];
             float sum[GRAD_RPI];
+            int maxlen = 0;
 #pragma unroll
             for (int u = 0; u < GRAD_RPI; ++u) {
                 const int rr = rb + u < nrows ? rb + u : nrows - 1;
                 e0[u] = s_rp[rr];
-                e1[u] = rb + u < nrows ? s_rp[rr + 1] : e0[u];
+                len[u] = rb + u < nrows ? (int)(s_rp[rr + 1] - e0[u]) : 0;
+                maxlen = max(maxlen, len[u]);
                 sum[u] = 0.f;
             }
+            for (int off = lane; off < maxlen + lane; off += 32) {
+                if (off - lane >= maxlen) break;
+                int c[GRAD_RPI];
+                float wv[GRAD_RPI], xv[GRAD_RPI];
 #pragma unroll
-            for (int u = 0; u < GRAD_RPI; ++u) {
-                for (long long e = e0[u] + lane; e < e1[u]; e += 32) {
-                    const float v = vp ? vp[e] : 1.f;
-                    sum[u] = fmaf(__ldg(w + cp[e]), v, sum[u]);
+                for (int u = 0; u < GRAD_RPI; ++u) {
+                    const bool ok = off < len[u];
+                    c[u] = ok ? cp[e0[u] + off] : -1;
+                    xv[u] = (ok && vp) ? vp[e0[u] + off] : 1.f;
                 }
+#pragma unroll
+                for (int u = 0; u < GRAD_RPI; ++u) wv[u] = c[u] >= 0 ? __ldg(w + c[u]) : 0.f;
+#pragma unroll
+                for (int u = 0; u < GRAD_RPI; ++u) sum[u] = fmaf(wv[u], xv[u], sum[u]);
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
 #pragma unroll
                 for (int u = 0; u < GRAD_RPI; ++u) sum[u] += __shfl_xor_sync(0xFFFFFFFFu, sum[u], o);
             }
+            float coef[GRAD_RPI];
 #pragma unroll
             for (int u = 0; u < GRAD_RPI; ++u) {
-                if (rb + u >= nrows) break;
+                coef[u] = 0.f;
+                if (rb + u >= nrows) continue;
                 const float pre = sum[u];
                 const float y = s_lab[rb + u];
                 if (MODE == 0) {
-                    const float coef = -glm_grad(loss_id, pre, y) * inv_batch;
-                    if (lane == 0) loss_sum += (double)glm_loss(loss_id, pre, y);
-                    if (coef != 0.f) {
-                        for (long long e = e0[u] + lane; e < e1[u]; e += 32) {
-                            const int c = cp[e];
-                            const float contrib = coef * (vp ? vp[e] : 1.f);
-                            if (c < hot) {
-                                atomicAdd(&s_hot[c], contrib);
-                            } else {
-                                red_add_f32(g + c, contrib);
-                                const unsigned int bit = 1u << (c & 31);
-                                unsigned int* word = bitmap + (c >> 5);
-                                if (!(*(volatile unsigned int*)word & bit)) atomicOr(word, bit);
-                            }
-                        }
-                    }
-                } else if (lane == 0) {
+                    coef[u] = -glm_grad(loss_id, pre, y) * inv_batch;
+                    if (lane == u) loss_sum += (double)glm_loss(loss_id, pre, y);
+                } else if (lane == u) {
                     loss_sum += (double)glm_loss(loss_id, pre, y);
                     const float z = pre * y;
                     if (z > 0.f) {
@@ -198,11 +206,52 @@ glm_rows_kernel(const long long* __restrict__ rowptr, const int* __restrict__ co
                     if (margins) margins[r0 - row_lo + rb + u] = pre;
                 }
             }
+            if (MODE == 0) {
+                for (int off = lane; off - lane < maxlen; off += 32) {
+                    int c[GRAD_RPI];
+                    float contrib[GRAD_RPI];
+                    unsigned int seen[GRAD_RPI];
+#pragma unroll
+                    for (int u = 0; u < GRAD_RPI; ++u) {
+                        const bool ok = off < len[u] && coef[u] != 0.f;
+                        c[u] = ok ? cp[e0[u] + off] : -1;
+                        contrib[u] = ok ? coef[u] * (vp ? vp[e0[u] + off] : 1.f) : 0.f;
+                    }
+                    // cold columns: read the bitmap words first (independent L2 loads), so that
+                    // the atomicOr is only issued for bits that are not set yet
+#pragma unroll
+                    for (int u = 0; u < GRAD_RPI; ++u)
+                        seen[u] = c[u] >= hot ? *(volatile unsigned int*)(bitmap + (c[u] >> 5)) : ~0u;
+#pragma unroll
+                    for (int u = 0; u < GRAD_RPI; ++u) {
+                        if (c[u] < 0) continue;
+                        if (c[u] < priv) {
+                            // the hottest columns: one private copy per warp. The lanes of a row hold
+                            // distinct columns and a warp's shared-memory accesses are ordered, so a
+                            // plain read-modify-write is exact and free of atomics.
+                            s_priv[warp * priv + c[u]] += contrib[u];
+                        } else if (c[u] < hot) {
+                            atomicAdd(&s_hot[c[u]], contrib[u]);
+                        } else {
+                            red_add_f32(g + c[u], contrib[u]);
+                            const unsigned int bit = 1u << (c[u] & 31);
+                            if (!(seen[u] & bit)) atomicOr(bitmap + (c[u] >> 5), bit);
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
         }
         __syncthreads();  // everyone is done with `stage` (and s_rp / s_lab) before it is refilled
     }
 
     if (MODE == 0) {
+        for (int i = threadIdx.x; i < priv; i += blockDim.x) {
+            float t = s_hot[i];
+            for (int w2 = 0; w2 < GRAD_WARPS; ++w2) t += s_priv[w2 * priv + i];
+            s_hot[i] = t;
+        }
+        __syncthreads();
         // flush the hot columns: one red.add per non-zero entry, one atomicOr per 32 columns
         for (int base = warp * 32; base < hot; base += GRAD_WARPS * 32) {
             int i = base + lane;
@@ -250,8 +299,9 @@ static int grad_launch(int mode, const long long* rowptr, const int* cols, const
     if (rpt < 1) rpt = 1;
     if (rpt > GRAD_MAX_RPT) rpt = GRAD_MAX_RPT;
     long long ntiles = (row_cnt + rpt - 1) / rpt;
-    size_t smem = 4 * GRAD_TILE_CAP * sizeof(int) + (size_t)hot * sizeof(float);
-    int per_sm = smem > 100 * 1024 ? 1 : 2;
+    size_t smem = (vals ? 4 : 2) * GRAD_TILE_CAP * sizeof(int) + (size_t)hot * sizeof(float) +
+                  (size_t)(hot < GRAD_PRIV ? hot : GRAD_PRIV) * GRAD_WARPS * sizeof(float);
+    int per_sm = smem > 100 * 1024 ? 1 : (smem > 70 * 1024 ? 2 : 3);
     long long grid = (long long)sm_count() * per_sm;
     if (grid > ntiles) grid = ntiles;
     static bool attr_set[2] = {false, false};

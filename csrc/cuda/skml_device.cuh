@@ -239,6 +239,57 @@ __device__ __forceinline__ void block_bitonic_sort(unsigned int* s) {
     }
 }
 
+// Ascending sort of 2048 unsigned keys in shared memory by a block of 1024 threads.
+// Every warp keeps 64 consecutive elements in registers (two per lane), so the bitonic steps
+// with partner distance <= 32 are register / shuffle exchanges without a block barrier; only
+// the steps with distance >= 64 go through shared memory (20 barriers instead of 66).
+__device__ __forceinline__ void block_sort_2048(unsigned int* s) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int i0 = warp * 64 + lane, i1 = i0 + 32;
+    unsigned int a = s[i0], b = s[i1];
+    for (int k = 2; k <= 2048; k <<= 1) {
+        if (k >= 128) {
+            s[i0] = a;
+            s[i1] = b;
+            __syncthreads();
+            for (int j = k >> 1; j >= 64; j >>= 1) {
+                const int t = threadIdx.x;
+                const int i = ((t & ~(j - 1)) << 1) | (t & (j - 1));
+                const int p = i | j;
+                const bool up = (i & k) == 0;
+                const unsigned int x = s[i], y = s[p];
+                if ((x > y) == up) {
+                    s[i] = y;
+                    s[p] = x;
+                }
+                __syncthreads();
+            }
+            a = s[i0];
+            b = s[i1];
+        }
+        if (k >= 64) {  // distance 32: both elements live in this thread
+            const bool up = (i0 & k) == 0;
+            if ((a > b) == up) {
+                const unsigned int t = a;
+                a = b;
+                b = t;
+            }
+        }
+        for (int j = (k >> 1) < 16 ? (k >> 1) : 16; j > 0; j >>= 1) {
+            const unsigned int pa = __shfl_xor_sync(0xFFFFFFFFu, a, j);
+            const unsigned int pb = __shfl_xor_sync(0xFFFFFFFFu, b, j);
+            const bool low = (lane & j) == 0;
+            const bool up0 = (i0 & k) == 0, up1 = (i1 & k) == 0;
+            a = (low == up0) ? min(a, pa) : max(a, pa);
+            b = (low == up1) ? min(b, pb) : max(b, pb);
+        }
+        __syncwarp();
+    }
+    s[i0] = a;
+    s[i1] = b;
+    __syncthreads();
+}
+
 // Number of elements of the ascending array a[0..n) that are <= x (upper bound).
 __device__ __forceinline__ int upper_bound_f(const float* a, int n, float x) {
     int lo = 0, hi = n;

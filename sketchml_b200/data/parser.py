@@ -69,6 +69,7 @@ def parse_lines(lines: Iterable[str], fmt: str, max_dim: int, neg_y: bool = True
     parse = _PARSERS[fmt]
     rowptr, cols, vals, labels = [0], [], [], []
     implicit = fmt == "dummy"
+    dup_rows = 0
     for line in lines:
         if not line.strip():
             continue
@@ -79,14 +80,25 @@ def parse_lines(lines: Iterable[str], fmt: str, max_dim: int, neg_y: bool = True
         if idx and (min(idx) < 0 or max(idx) >= max_dim):
             raise ValueError(f"feature index out of range [0, {max_dim}) in line: {line[:80]!r}")
         order = np.argsort(np.asarray(idx, dtype=np.int64), kind="stable") if idx else []
-        cols.extend(int(idx[i]) for i in order)
-        if not implicit:
-            vals.extend(float(val[i]) for i in order)
+        # a feature listed twice in one row is merged (values add up): the kernels rely on
+        # distinct columns inside a row
+        last = None
+        for i in order:
+            c = int(idx[i])
+            x = 1.0 if val is None else float(val[i])
+            if c == last:
+                dup_rows += 1
+                vals[-1] += x
+            else:
+                cols.append(c)
+                vals.append(x)
+                last = c
         labels.append(y)
         rowptr.append(len(cols))
     return CSRMatrix(
         torch.tensor(rowptr, dtype=torch.int64), torch.tensor(cols, dtype=torch.int32),
-        None if implicit else torch.tensor(vals, dtype=dtype), torch.tensor(labels, dtype=dtype), max_dim)
+        None if (implicit and dup_rows == 0) else torch.tensor(vals, dtype=dtype), torch.tensor(labels, dtype=dtype),
+        max_dim)
 
 
 def load_data(path: str, fmt: str, max_dim: int, rank: int = 0, world: int = 1, neg_y: bool = True,

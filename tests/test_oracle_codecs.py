@@ -75,6 +75,14 @@ def test_hashes_follow_java_int_semantics(hid, fn):
         assert got.min() >= 0 and got.max() < size
 
 
+def test_division_free_hash_equals_exact_hash():
+    rng = np.random.default_rng(0)
+    keys = np.concatenate([rng.integers(0, 2 ** 31 - 1, 50000), [0, 1, 9, 10, 2147483647]]).astype(np.int32)
+    for size in (1, 2, 7, 1000, 65537, 300001, 2147483647):
+        for hid in range(8):
+            assert np.array_equal(o.hash(hid, keys, size), o.hash_fast(hid, keys, size))
+
+
 def test_pick_hashes_distinct_and_deterministic():
     for rows in range(1, 9):
         a = o.pick_hashes(5, 7, 1, 3, rows)
