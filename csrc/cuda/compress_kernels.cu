@@ -34,6 +34,7 @@
 #define MAX_LEVELS 24
 #define FP_SHIFT 20         // fixed-point fraction bits of sample weights
 #define MIN_TILES_PER_BLOCK 4
+#define SUPER_TILES 4       // tiles folded into one sort by the bottom-level sampler
 
 struct CtaStat {
     unsigned int count;
@@ -180,6 +181,16 @@ __device__ __forceinline__ unsigned int lanemask_lt() {
     return m;
 }
 
+// Block 0 leaves a nanosecond time stamp per stage in the control words (u64 at ctrl[16 + 2 i]);
+// skml tools read them to show where a fused launch spends its time.
+__device__ __forceinline__ void stage_stamp(unsigned int* ctrl, int i) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        reinterpret_cast<unsigned long long*>(ctrl)[8 + i] = t;
+    }
+}
+
 // ---------------------------------------------------------------------------
 // S1: quantile summary
 // ---------------------------------------------------------------------------
@@ -245,6 +256,31 @@ __device__ void stage_summary(const CP& p, Smem& s, const float* __restrict__ va
     unsigned long long n_c = 0;
     for (long long tile = t0; tile < t1; ++tile) {
         long long base = tile * TILE;
+        if (t1 - tile >= SUPER_TILES && base + (long long)SUPER_TILES * TILE <= n) {
+            // Bottom-level sampler (as in KLL sketches): of every 4 consecutive values one is kept
+            // at random with weight 4, so 8192 values cost one 2048-sort and enter the level chain
+            // as one run of weight 64. Min and max still see every value.
+            const float4* v4 = reinterpret_cast<const float4*>(vals + base);
+            for (int t = threadIdx.x; t < TILE; t += blockDim.x) {
+                const float4 q = v4[t];
+                const unsigned int k0 = f2ord(q.x), k1 = f2ord(q.y), k2 = f2ord(q.z), k3 = f2ord(q.w);
+                kmin = min(min(kmin, k0), min(min(k1, k2), k3));
+                kmax = max(max(kmax, k0), max(max(k1, k2), k3));
+                const unsigned int r = (unsigned int)(skml_splitmix64(p.seed ^ (p.step * 0x9E3779B97F4A7C15ull) ^
+                                                                      ((unsigned long long)p.rank << 40) ^ (unsigned long long)(base + t)) >> 62);
+                s.tile[t] = r == 0 ? k0 : (r == 1 ? k1 : (r == 2 ? k2 : k3));
+            }
+            __syncthreads();
+            block_sort_2048(s.tile);
+            n_c += (unsigned long long)SUPER_TILES * TILE;
+            const unsigned int off = (unsigned int)(skml_rand(p.seed, p.step, ((unsigned long long)p.rank << 32) | blockIdx.x,
+                                                              0x7200u + (unsigned long long)(tile - t0)) & (TILE_W - 1));
+            for (int t = threadIdx.x; t < SK_K; t += blockDim.x) s.run[t] = s.tile[t * TILE_W + off];
+            __syncthreads();
+            carry_run(s, occupied, 2, p, (unsigned long long)(tile - t0) + 1);
+            tile += SUPER_TILES - 1;
+            continue;
+        }
         int m = (int)((n - base) < TILE ? (n - base) : TILE);
         for (int t = threadIdx.x; t < TILE; t += blockDim.x) {
             unsigned int k = 0xFFFFFFFFu;
@@ -505,9 +541,10 @@ __device__ void element_pass(const CP& p, Smem& s, long long n) {
         s.tile_bytes[threadIdx.x] = 0;
     }
     __syncthreads();
-    // (warp, group) role of the first 32 * G threads: cross-warp prefixes of one group
-    const int wg_g = threadIdx.x % G, wg_w = threadIdx.x / G;
-    const bool wg_on = threadIdx.x < SKML_WARPS * G;
+    // role of the first G warps: warp g owns group g, its lane w stands for warp w of the block,
+    // so cross-warp prefixes of one group are warp shuffles
+    const int wg_g = warp, wg_w = lane;
+    const bool wg_on = warp < G;
     const Layout& L = s.lay;
     const int zero = s.qi.zero_idx;
     const bool overflow = PACK && L.overflow;
@@ -541,11 +578,11 @@ __device__ void element_pass(const CP& p, Smem& s, long long n) {
         __syncthreads();
         int role_carry = -1;  // last key of group wg_g before warp wg_w (role threads)
         if (wg_on) {
-            role_carry = s.carry_key[wg_g];
-            for (int w2 = 0; w2 < wg_w; ++w2) {
-                const int k2 = s.wlast[w2][wg_g];
-                if (k2 >= 0) role_carry = k2;
-            }
+            const int mine = s.wlast[wg_w][wg_g];
+            const unsigned int has = __ballot_sync(0xFFFFFFFFu, mine >= 0) & lanemask_lt();
+            const int src = has ? 31 - __clz(has) : 0;
+            const int from = __shfl_sync(0xFFFFFFFFu, mine, src);
+            role_carry = has ? from : s.carry_key[wg_g];
             s.cin[wg_w][wg_g] = role_carry;
         }
         __syncthreads();
@@ -592,10 +629,19 @@ __device__ void element_pass(const CP& p, Smem& s, long long n) {
         __syncthreads();
         unsigned int role_cnt = 0, role_bytes = 0;
         if (wg_on) {  // exclusive prefix over the warps, once per (warp, group)
-            for (int w2 = 0; w2 < wg_w; ++w2) {
-                role_cnt += s.wcnt[w2][wg_g];
-                role_bytes += s.wbytes[w2][wg_g];
+            const unsigned int c0 = s.wcnt[wg_w][wg_g], y0 = s.wbytes[wg_w][wg_g];
+            unsigned int ci = c0, yi = y0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned int tc = __shfl_up_sync(0xFFFFFFFFu, ci, o);
+                const unsigned int ty = __shfl_up_sync(0xFFFFFFFFu, yi, o);
+                if (lane >= o) {
+                    ci += tc;
+                    yi += ty;
+                }
             }
+            role_cnt = ci - c0;
+            role_bytes = yi - y0;
             s.wexc[wg_w][wg_g] = role_cnt;
             s.wexb[wg_w][wg_g] = role_bytes;
         }
@@ -625,8 +671,20 @@ __device__ void element_pass(const CP& p, Smem& s, long long n) {
             unsigned int* tab = p.tables + L.tab32_off[g];
             SkmlKeyDigits kd;
             skml_key_digits(key, kd);
-            for (int r = 0; r < p.rows; ++r)
-                atomicMin(tab + (long long)r * col + skml_hash_fast(L.hash_ids[g][r], key, kd, col, L.col_magic[g]), cell);
+            unsigned int* slot[SKML_MAX_ROWS];
+            unsigned int cur[SKML_MAX_ROWS];
+#pragma unroll
+            for (int r = 0; r < SKML_MAX_ROWS; ++r) {
+                slot[r] = nullptr;
+                cur[r] = 0;
+                if (r < p.rows) {
+                    slot[r] = tab + (long long)r * col + skml_hash_fast(L.hash_ids[g][r], key, kd, col, L.col_magic[g]);
+                    cur[r] = __ldcg(slot[r]);  // cells only decrease: a stale value only costs a redundant atomic
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < SKML_MAX_ROWS; ++r)
+                if (r < p.rows && cell < cur[r]) atomicMin(slot[r], cell);
         }
         __syncthreads();  // all readers of tile_rank / tile_bytes are done
         if (wg_on && wg_w == SKML_WARPS - 1) {
@@ -932,16 +990,6 @@ __device__ void stage_push_sparse(const CP& p, Smem& s) {
 // ---------------------------------------------------------------------------
 // Kernels
 // ---------------------------------------------------------------------------
-// Block 0 leaves a nanosecond time stamp per stage in the control words (u64 at ctrl[16 + 2 i]);
-// skml tools read them to show where a fused launch spends its time.
-__device__ __forceinline__ void stage_stamp(unsigned int* ctrl, int i) {
-    if (blockIdx.x == 0 && threadIdx.x == 0) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        reinterpret_cast<unsigned long long*>(ctrl)[8 + i] = t;
-    }
-}
-
 #define STAGE_BARRIER(stage_id)                                                           \
     if (FUSED) {                                                                          \
         if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, stage_id)) return; \
@@ -982,7 +1030,9 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_sparse_kernel(CP p, in
     if (FUSED) stage_stamp(p.ctrl, 0);
     if (FUSED || stage == 1) {
         stage_prepare(p, n);
+        stage_stamp(p.ctrl, 8);
         if (!given) stage_summary(p, s, p.vals, n);
+        stage_stamp(p.ctrl, 9);
     }
     STAGE_BARRIER(1)
     if ((FUSED || stage == 2) && !given) stage_query(p, s, n);
@@ -1070,10 +1120,14 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_dense_kernel(CP p, int
 // Host launchers
 // ---------------------------------------------------------------------------
 static int device_sms() {
-    int dev = 0, sms = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    return sms > 0 ? sms : 148;
+    static int cached = 0;
+    if (cached == 0) {
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cached = sms > 0 ? sms : 148;
+    }
+    return cached;
 }
 
 static int fill_params(const SkmlCompressArgs* a, CP& p, int& grid) {
@@ -1126,21 +1180,30 @@ static int fill_params(const SkmlCompressArgs* a, CP& p, int& grid) {
     return 0;
 }
 
+// Function attributes and the co-residency limit are looked up once per kernel (one process
+// drives one GPU), so a steady-state launch makes a single runtime call.
+struct LaunchCache {
+    bool ready = false;
+    int max_grid = 0;
+};
+
 template <class K>
-static int launch_stages(K fused_kernel, K staged_kernel, CP& p, int grid, bool fused, int nstages, cudaStream_t stream) {
-    static bool attr_done = false;
-    (void)attr_done;
+static int launch_stages(K fused_kernel, K staged_kernel, LaunchCache& cache, CP& p, int grid, bool fused, int nstages,
+                         cudaStream_t stream) {
     cudaError_t e;
-    e = cudaFuncSetAttribute(fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem));
-    if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem));
-    if (e != cudaSuccess) return (int)e;
-    if (fused) {
+    if (!cache.ready) {
+        e = cudaFuncSetAttribute(fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem));
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem));
+        if (e != cudaSuccess) return (int)e;
         int per_sm = 0;
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_kernel, SKML_BLOCK, sizeof(Smem));
         if (per_sm < 1) return (int)cudaErrorLaunchOutOfResources;
-        int max_grid = per_sm * device_sms();
-        if (grid > max_grid) grid = max_grid;
+        cache.max_grid = per_sm * device_sms();
+        cache.ready = true;
+    }
+    if (fused) {
+        if (grid > cache.max_grid) grid = cache.max_grid;
         int stage = -1;
         void* args[] = {&p, &stage};
         e = cudaLaunchCooperativeKernel((const void*)fused_kernel, dim3(grid), dim3(SKML_BLOCK), args, sizeof(Smem), stream);
@@ -1159,7 +1222,8 @@ extern "C" int skml_compress_sparse(const SkmlCompressArgs* a, void* stream) {
     int grid = 0;
     int rc = fill_params(a, p, grid);
     if (rc) return rc;
-    return launch_stages(compress_sparse_kernel<true>, compress_sparse_kernel<false>, p, grid, a->fused != 0, 5,
+    static LaunchCache cache;
+    return launch_stages(compress_sparse_kernel<true>, compress_sparse_kernel<false>, cache, p, grid, a->fused != 0, 5,
                          (cudaStream_t)stream);
 }
 
@@ -1168,6 +1232,7 @@ extern "C" int skml_compress_dense(const SkmlCompressArgs* a, void* stream) {
     int grid = 0;
     int rc = fill_params(a, p, grid);
     if (rc) return rc;
-    return launch_stages(compress_dense_kernel<true>, compress_dense_kernel<false>, p, grid, a->fused != 0, 4,
+    static LaunchCache cache;
+    return launch_stages(compress_dense_kernel<true>, compress_dense_kernel<false>, cache, p, grid, a->fused != 0, 4,
                          (cudaStream_t)stream);
 }

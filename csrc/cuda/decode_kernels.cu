@@ -397,19 +397,28 @@ extern "C" int skml_decode_update(const SkmlDecodeArgs* a, void* stream_) {
     p.ctrl = reinterpret_cast<unsigned int*>(a->workspace);
     p.status = a->status;
     p.budget = a->budget_cycles > 0 ? a->budget_cycles : 2000000000ll;
-    int dev = 0, sms = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int grid = a->grid > 0 ? (int)a->grid : 2 * (sms > 0 ? sms : 148);  // two 512-thread blocks per SM
-    cudaError_t e = cudaFuncSetAttribute(decode_update_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DecSmem));
-    if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(decode_update_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DecSmem));
-    if (e != cudaSuccess) return (int)e;
-    if (a->fused) {
+    static int sms = 0, max_grid = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+        cudaError_t e0 = cudaFuncSetAttribute(decode_update_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DecSmem));
+        if (e0 == cudaSuccess)
+            e0 = cudaFuncSetAttribute(decode_update_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DecSmem));
+        if (e0 != cudaSuccess) {
+            sms = 0;
+            return (int)e0;
+        }
         int per_sm = 0;
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_update_kernel<true>, DEC_THREADS, sizeof(DecSmem));
-        if (per_sm < 1) return (int)cudaErrorLaunchOutOfResources;
-        if (grid > per_sm * sms) grid = per_sm * sms;
+        max_grid = per_sm * sms;
+    }
+    int grid = a->grid > 0 ? (int)a->grid : 2 * sms;  // two 512-thread blocks per SM
+    cudaError_t e;
+    if (a->fused) {
+        if (max_grid < 1) return (int)cudaErrorLaunchOutOfResources;
+        if (grid > max_grid) grid = max_grid;
         int stage = -1;
         void* args[] = {&p, &stage};
         return (int)cudaLaunchCooperativeKernel((const void*)decode_update_kernel<true>, dim3(grid), dim3(DEC_THREADS), args,
