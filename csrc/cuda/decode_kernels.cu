@@ -4,11 +4,15 @@
 //       compress kernels straight into this GPU's memory), header validation
 //   D1  per 1024-key chunk (restart points make chunks independent): flag bits -> delta
 //       widths -> scan -> gather -> prefix sum = keys; grouped MinMaxSketch query
-//       (furthest-from-zero over the rows); dequantize; add value / world into 64-bit
-//       fixed-point accumulators (integer adds commute, so every replica gets bit-identical
-//       sums whatever the arrival order)
-//   D2  each touched coordinate is claimed once (atomic exchange with zero) and updated:
-//       SGD, or the reference's lazy Adam with per-epoch beta powers
+//       (furthest-from-zero over the rows); dequantize
+//   SGD (linear update): the payloads are applied one rank after the other with a grid
+//       barrier in between. Keys are unique inside a payload, so each pass is a plain
+//       read-modify-write of w without atomics, and the fixed rank order makes every
+//       replica bit-identical. One random access per key, no scratch.
+//   Adam (needs the cross-rank sum first): value / world is added into 64-bit fixed-point
+//       accumulators (integer adds commute, so every replica gets the same sums whatever
+//       the arrival order); D2 claims each touched coordinate once (atomic exchange with
+//       zero) and applies the reference's lazy Adam with per-epoch beta powers
 //
 // Reference behaviour restated (paths inside the reference project):
 //   sketch/.../binary/DeltaBinaryEncoder.java:42-53 (key decode),
@@ -60,7 +64,8 @@ struct DecSmem {
     int nitems;
     unsigned long long total_chunks, total_keys;
     int any_dense;
-    int direct;      // world == 1 and no dense payload: D1 applies the update, D2 has nothing to do
+    int direct;      // linear update (SGD / plain sum): payloads applied in rank order, no accumulators
+    unsigned long long rank_chunk_begin[SKML_MAX_PEERS + 1];
     int shift;       // fixed-point: accumulator = value * 2^shift
     double inv_world;
     int ok;
@@ -81,6 +86,12 @@ __device__ __forceinline__ void apply_one(const DP& p, long long k, float g) {
         p.adam_m[k] = mt;
         p.adam_v[k] = vt;
     }
+}
+
+// Linear modes: SGD step on w, or accumulation of the plain mean into out_sum.
+__device__ __forceinline__ void apply_direct(const DP& p, long long k, float g) {
+    if (p.out_sum) p.out_sum[k] += g;
+    else p.w[k] -= p.lr * g;
 }
 
 // D0: wait, validate, build the work table (identically in every block).
@@ -125,6 +136,7 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
         double mx = 0.0;
         for (int r = 0; r < p.world; ++r) {
             const SkmlHeader& h = s.hdr[r];
+            s.rank_chunk_begin[r] = chunks;
             if (h.kind == SKML_KIND_EMPTY) continue;
             mx = fmax(mx, fmax(fabs(h.min_value), fabs(h.max_value)));
             if (h.kind == SKML_KIND_DENSE) {
@@ -162,11 +174,12 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
             skml_set_status(p.status, SKML_CAPACITY, 0x40u);
             s.ok = 0;
         }
+        for (int r = p.world; r <= SKML_MAX_PEERS; ++r) s.rank_chunk_begin[r] = chunks;
         s.nitems = ni;
         s.total_chunks = chunks;
         s.total_keys = keys;
         s.any_dense = dense;
-        s.direct = (p.world == 1 && !dense) ? 1 : 0;
+        s.direct = (p.adam_v == nullptr) ? 1 : 0;
         int e = 0;
         if (mx > 0.0 && isfinite(mx)) frexp(mx, &e);
         s.shift = 60 - e;
@@ -208,8 +221,8 @@ __device__ __forceinline__ void decode_one(const DP& p, const DecSmem& s, const 
         }
     }
     const float bv = __ldcg(reinterpret_cast<const float*>(it.base + it.off_bv) + res);
-    if (s.direct) {  // one rank, sparse payload: nothing to sum, update in place (keys are unique)
-        apply_one(p, key, bv);
+    if (s.direct) {  // rank-ordered pass: keys are unique inside a payload, plain read-modify-write
+        apply_direct(p, key, bv * (float)s.inv_world);
         return;
     }
     const long long fx = to_fixed((double)bv * s.inv_world, s.shift);
@@ -218,8 +231,8 @@ __device__ __forceinline__ void decode_one(const DP& p, const DecSmem& s, const 
 
 // D1 for sparse payloads: one 1024-key chunk per block iteration, two adjacent keys per thread
 // (512 threads), so that every thread has two independent load chains in flight.
-__device__ void decode_accumulate(const DP& p, DecSmem& s) {
-    for (unsigned long long ch = blockIdx.x; ch < s.total_chunks; ch += gridDim.x) {
+__device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch_begin, unsigned long long ch_end) {
+    for (unsigned long long ch = ch_begin + blockIdx.x; ch < ch_end; ch += gridDim.x) {
         int it_i = 0;
         while (it_i + 1 < s.nitems && ch >= s.items[it_i + 1].chunk_prefix) ++it_i;
         const DecItem& it = s.items[it_i];
@@ -265,8 +278,10 @@ __device__ void decode_accumulate(const DP& p, DecSmem& s) {
             const unsigned int key0 = rs.prev_key + dex + d0;
             const unsigned int key1 = key0 + d1;
             int* ks = p.key_scratch + it.key_prefix + first;
-            ks[i0] = (int)key0;
-            if (i1 < cnt) ks[i1] = (int)key1;
+            if (!s.direct) {
+                ks[i0] = (int)key0;
+                if (i1 < cnt) ks[i1] = (int)key1;
+            }
             decode_one(p, s, it, key0);
             if (i1 < cnt) decode_one(p, s, it, key1);
         }
@@ -275,9 +290,9 @@ __device__ void decode_accumulate(const DP& p, DecSmem& s) {
 }
 
 // D1 for dense payloads: every coordinate carries a bucket code.
-__device__ void decode_accumulate_dense(const DP& p, DecSmem& s) {
+__device__ void decode_accumulate_dense(const DP& p, DecSmem& s, int r_begin, int r_end) {
     const long long gsz = (long long)gridDim.x * blockDim.x, gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    for (int r = 0; r < p.world; ++r) {
+    for (int r = r_begin; r < r_end; ++r) {
         const SkmlHeader& h = s.hdr[r];
         if (h.kind != SKML_KIND_DENSE) continue;
         const unsigned char* codes = p.payload[r] + h.off_dense_codes;
@@ -285,6 +300,10 @@ __device__ void decode_accumulate_dense(const DP& p, DecSmem& s) {
         for (long long i = gid; i < p.dim; i += gsz) {
             unsigned int code = h.cell_bits == 8 ? __ldcg(codes + i) : __ldcg(reinterpret_cast<const unsigned short*>(codes) + i);
             if (code >= h.bin_num) code = h.zero_idx;
+            if (s.direct) {
+                apply_direct(p, i, __ldcg(bv + code) * (float)s.inv_world);
+                continue;
+            }
             const long long fx = to_fixed((double)__ldcg(bv + code) * s.inv_world, s.shift);
             if (fx) atomicAdd(reinterpret_cast<unsigned long long*>(p.acc + i), (unsigned long long)fx);
         }
@@ -294,9 +313,7 @@ __device__ void decode_accumulate_dense(const DP& p, DecSmem& s) {
 // D2: claim and update.
 __device__ void decode_update(const DP& p, DecSmem& s) {
     const long long gsz = (long long)gridDim.x * blockDim.x, gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (s.direct) {
-        // already applied in D1
-    } else if (s.any_dense) {
+    if (s.any_dense) {
         for (long long i = gid; i < p.dim; i += gsz) {
             long long a = p.acc[i];
             if (a) {
@@ -344,11 +361,36 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) decode_update_kernel(DP p, int
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
         reinterpret_cast<unsigned long long*>(p.ctrl)[9] = t;
     }
-    if (FUSED || stage == 1) {
-        decode_accumulate(p, s);
-        if (s.any_dense) decode_accumulate_dense(p, s);
+    if (s.direct) {
+        // one pass per rank; un-fused launches run pass `stage - 1` each
+        for (int r = 0; r < p.world; ++r) {
+            if (FUSED || stage == r + 1) {
+                decode_accumulate(p, s, s.rank_chunk_begin[r], s.rank_chunk_begin[r + 1]);
+                if (s.any_dense) decode_accumulate_dense(p, s, r, r + 1);
+            }
+            if (FUSED && r + 1 < p.world) {
+                if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, 0x30u + r)) return;
+            }
+        }
+        if ((FUSED || stage == 1) && blockIdx.x == 0 && threadIdx.x == 0 && p.loss_out) {
+            double l[4] = {0, 0, 0, 0};
+            for (int r = 0; r < p.world; ++r)
+                for (int i = 0; i < 4; ++i) l[i] += s.hdr[r].loss_partials[i];
+            for (int i = 0; i < 4; ++i) p.loss_out[i] = l[i];
+        }
+        if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            reinterpret_cast<unsigned long long*>(p.ctrl)[10] = t;
+            reinterpret_cast<unsigned long long*>(p.ctrl)[11] = t;
+        }
+        return;
     }
-    if (FUSED && !s.direct) {
+    if (FUSED || stage == 1) {
+        decode_accumulate(p, s, 0, s.total_chunks);
+        if (s.any_dense) decode_accumulate_dense(p, s, 0, p.world);
+    }
+    if (FUSED) {
         if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, 0x21u)) return;
     }
     if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) {
@@ -424,7 +466,8 @@ extern "C" int skml_decode_update(const SkmlDecodeArgs* a, void* stream_) {
         return (int)cudaLaunchCooperativeKernel((const void*)decode_update_kernel<true>, dim3(grid), dim3(DEC_THREADS), args,
                                                 sizeof(DecSmem), stream);
     }
-    for (int st = 1; st <= 2; ++st) {
+    const int nst = a->adam_v ? 2 : (int)a->world;
+    for (int st = 1; st <= nst; ++st) {
         decode_update_kernel<false><<<grid, DEC_THREADS, sizeof(DecSmem), stream>>>(p, st);
         e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;

@@ -169,11 +169,11 @@ class GpuDecoder:
         a.budget_cycles = L.budget_cycles(self.budget_s)
         a.fused, a.grid = int(self.fused), self.grid
         L.check(self.lib.skml_decode_update(C.byref(a), L.stream()), "skml_decode_update")
-        L.count_launches(1 if self.fused else 2)
+        L.count_launches(1 if self.fused else (2 if adam_v is not None else world))
 
     def decode_sum(self, payloads: List[torch.Tensor], step: int = 0) -> torch.Tensor:
         """Single-GPU convenience: decodes the given payload buffers (one per rank, rank order)
-        and returns the dense fp32 mean over ranks."""
+        and returns the dense fp32 mean over ranks (accumulated into a zeroed buffer)."""
         out = torch.zeros(self.dim, dtype=torch.float32, device=self.device)
         status = torch.zeros(1, dtype=torch.int32, device=self.device)
         cap = min(p.numel() for p in payloads)
