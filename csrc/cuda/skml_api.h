@@ -106,3 +106,46 @@ int skml_enable_peer_access(int peer_device);
 #ifdef __cplusplus
 }
 #endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+// One training step (gradient -> compaction -> fused compress -> fused decode + update) as a
+// single call, so that the host spends one library call per step instead of five.
+typedef struct SkmlStepArgs {
+    const long long* rowptr;
+    const int* cols;
+    const float* vals;
+    const float* labels;
+    long long seg_lo[2], seg_cnt[2];   // up to two row ranges (a batch that wraps around the shard)
+    long long nnz_padded;
+    double avg_nnz;
+    float* w;
+    float* g;
+    unsigned int* bitmap;
+    long long loss_id;
+    double inv_batch;
+    long long hot;
+    double* partials;                  // device, 4 doubles: batch size, loss sum, reg loss, spare
+    const double* partials_template;   // device, copied into `partials` before the gradient kernel
+    unsigned int* status;
+    long long budget_cycles;
+    double lambda;
+    unsigned int* block_counts;
+    long long* meta;
+    int* keys;
+    float* gvals;
+    float* dense_vals;                 // null unless the dense kind is reachable
+    long long n_max;
+    long long dim;
+    SkmlCompressArgs* compress;        // prepared for this step's parity; step is filled in here
+    SkmlDecodeArgs* decode;
+    unsigned long long step;
+    double lr, adam_scale;
+    double* loss_out;                  // device, 4 doubles: this step's slot of the loss ring
+} SkmlStepArgs;
+
+int skml_train_step(SkmlStepArgs* args, void* stream);
+#ifdef __cplusplus
+}
+#endif

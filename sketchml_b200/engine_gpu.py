@@ -89,6 +89,7 @@ class GpuEngine:
         self.partials_template = torch.tensor([float(self.batch_rows), 0.0, 0.0, 0.0], dtype=torch.float64,
                                               device=self.device)
         self.batch_index = 0
+        self._template_rows = self.batch_rows
         m = self.t.model
         self.reg_every_step = bool(conf.extras.get("reg_loss_every_step", dim <= (1 << 22)))
         self.adam = conf.optimizer == "adam"
@@ -100,6 +101,7 @@ class GpuEngine:
                                   budget_s=conf.step_timeout_s)
             from .parallel.exchange import PeerExchange
             self.xchg = PeerExchange(comm, self.comp.capacity, self.device)
+            self._prepare_fast_step()
         elif self.mode == "nccl_kv":
             self.kv_keys = torch.zeros((comm.world, bound), dtype=torch.int32, device=self.device)
             self.kv_vals = torch.zeros((comm.world, bound), dtype=torch.float32, device=self.device)
@@ -107,6 +109,53 @@ class GpuEngine:
             self.kv_acc = torch.zeros(dim, dtype=torch.float32, device=self.device)
         else:
             self.dense_sum = torch.zeros(dim, dtype=torch.float32, device=self.device)
+
+    def _prepare_fast_step(self) -> None:
+        """Argument blocks of the single-call step (`skml_train_step`), one per slot parity."""
+        import ctypes as CT
+        m, st, comm, conf = self.t.model, self.st, self.t.comm, self.conf
+        opt = m.optimizer
+        am, av = (opt.m, opt.v) if self.adam else (None, None)
+        self._ca, self._da = [], []
+        for par in (0, 1):
+            sp, sf = self.xchg.send_ptrs(par)
+            rp, rf = self.xchg.recv_ptrs(par)
+            self._ca.append(self.comp.make_args(st.keys, st.vals, st.meta, 0, comm.rank, comm.world, sp[comm.rank],
+                                                self.xchg.slot_capacity, sp, sf, st.status, st.partials, None))
+            self._da.append(self.dec.make_args(rp, rf, self.xchg.slot_capacity, 0, st.status, m.weights, 0.0, am, av,
+                                               1.0, None))
+        a = L.StepArgs()
+        a.w, a.g, a.bitmap = L.ptr(m.weights), L.ptr(st.g), L.ptr(st.bitmap)
+        a.loss_id, a.hot = m.loss.loss_id, int(min(conf.hot_columns, st.dim) // 32 * 32)
+        a.partials, a.partials_template, a.status = L.ptr(st.partials), L.ptr(self.partials_template), L.ptr(st.status)
+        a.budget_cycles = L.budget_cycles(conf.step_timeout_s)
+        a.lam = m.loss.get_reg_param() if m.loss.is_l2_reg else 0.0
+        a.block_counts, a.meta, a.keys, a.gvals = L.ptr(st.block_counts), L.ptr(st.meta), L.ptr(st.keys), L.ptr(st.vals)
+        a.dense_vals, a.n_max, a.dim = L.ptr(st.dense_vals), st.n_max, st.dim
+        self._sa = a
+        self._step_fn = L.lib().skml_train_step
+        self._byref = CT.byref
+        import ctypes
+        self._ca_ptr = [ctypes.pointer(x) for x in self._ca]
+        self._da_ptr = [ctypes.pointer(x) for x in self._da]
+        self._pending = None
+
+    def _launch_fast_step(self, step: int, lr: float, adam_scale: float, ring_ptr: int) -> None:
+        csr, segs, rows = self._pending
+        self._pending = None
+        a = self._sa
+        a.rowptr, a.cols, a.vals, a.labels = L.ptr(csr.rowptr), L.ptr(csr.cols), L.ptr(csr.values), L.ptr(csr.labels)
+        a.nnz_padded, a.avg_nnz = csr.nnz_padded, float(csr.avg_nnz)
+        for i in range(2):
+            lo, hi = segs[i] if i < len(segs) else (0, 0)
+            a.seg_lo[i], a.seg_cnt[i] = lo, hi - lo
+        a.inv_batch = 1.0 / max(1, rows)
+        par = step & 1
+        a.compress = self._ca_ptr[par]
+        a.decode = self._da_ptr[par]
+        a.step, a.lr, a.adam_scale, a.loss_out = step, lr, adam_scale, ring_ptr
+        L.check(self._step_fn(self._byref(a), L.stream()), "skml_train_step")
+        L.count_launches(len(segs) + 3 + 1 + (1 if self.st.dense_vals is not None else 0) + 1)
 
     # ----------------------------------------------------------------- steps
     def _segments(self, count: int):
@@ -123,8 +172,18 @@ class GpuEngine:
         csr = csr or self.csr
         rows = self.batch_rows if batch_rows is None else batch_rows
         segs = self._segments(rows) if segments is None else segments
-        if rows != self.batch_rows:
+        if self._fast_ok() and len(segs) <= 2:
+            if rows != self._template_rows:
+                self.partials_template[0] = float(rows)
+                self._template_rows = rows
+            if self.reg_every_step and m.loss.is_l2_reg:
+                self.partials_template[2:3].copy_(torch.linalg.vector_norm(m.weights).double() * m.loss.lam)
+            self._pending = (csr, segs, rows)
+            m.optimizer.advance()
+            return _BatchHandle(rows, self.batch_index), None, None
+        if rows != self._template_rows:
             self.partials_template[0] = float(rows)
+            self._template_rows = rows
         if self.reg_every_step and m.loss.is_l2_reg:
             # reg loss = lambda * ||w||_2 (un-squared, ml/objective/Loss.scala:48-53); an O(dim) pass,
             # so large models refresh it once per epoch instead
@@ -136,6 +195,11 @@ class GpuEngine:
         m.optimizer.advance()
         h = _BatchHandle(rows, self.batch_index)
         return h, None, None
+
+    def _fast_ok(self) -> bool:
+        return (self.mode == "sketch" and bool(self.conf.extras.get("single_call_step", True)) and
+                bool(self.conf.extras.get("fused", True)) and
+                not (self.t.injector is not None and self.t.injector.skip_publish_steps))
 
     def _lr_and_scale(self):
         opt = self.t.model.optimizer
@@ -150,7 +214,11 @@ class GpuEngine:
         opt = m.optimizer
         am, av = (opt.m, opt.v) if self.adam else (None, None)
         ring = self.loss_ring[self.batch_index % self.loss_ring.shape[0]]
-        if self.mode == "sketch":
+        if self.mode == "sketch" and getattr(self, "_pending", None) is not None:
+            self._launch_fast_step(step, lr, adam_scale, ring.data_ptr())
+            if self.conf.extras.get("check_status_every_step", False):
+                self.check()
+        elif self.mode == "sketch":
             send_p, send_f = self.xchg.send_ptrs(step)
             recv_p, recv_f = self.xchg.recv_ptrs(step)
             skip = self.t.injector is not None and step in self.t.injector.skip_publish_steps

@@ -88,6 +88,9 @@ class GpuCompressor:
         a.fused, a.grid = int(self.fused), self.grid
         return a
 
+    def make_args(self, *a, **k) -> L.CompressArgs:
+        return self._args(*a, **k)
+
     def compress(self, keys: Optional[torch.Tensor], vals: torch.Tensor, meta: torch.Tensor, step: int, rank: int,
                  world: int, payload_ptr: int, slot_capacity: int, peer_payload: Sequence[int],
                  peer_flag: Sequence[Optional[int]], status: torch.Tensor, loss_partials: Optional[torch.Tensor] = None,
@@ -150,11 +153,11 @@ class GpuDecoder:
         self.workspace.zero_()
         self.acc.zero_()
 
-    def decode_update(self, payload_ptrs: Sequence[int], flag_ptrs: Sequence[Optional[int]], slot_capacity: int,
-                      step: int, status: torch.Tensor, w: Optional[torch.Tensor] = None, lr: float = 0.0,
-                      adam_m: Optional[torch.Tensor] = None, adam_v: Optional[torch.Tensor] = None,
-                      adam_scale: float = 1.0, loss_out: Optional[torch.Tensor] = None,
-                      out_sum: Optional[torch.Tensor] = None) -> None:
+    def make_args(self, payload_ptrs: Sequence[int], flag_ptrs: Sequence[Optional[int]], slot_capacity: int,
+                  step: int, status: torch.Tensor, w: Optional[torch.Tensor] = None, lr: float = 0.0,
+                  adam_m: Optional[torch.Tensor] = None, adam_v: Optional[torch.Tensor] = None,
+                  adam_scale: float = 1.0, loss_out: Optional[torch.Tensor] = None,
+                  out_sum: Optional[torch.Tensor] = None) -> L.DecodeArgs:
         a = L.DecodeArgs()
         world = len(payload_ptrs)
         for r in range(world):
@@ -168,6 +171,16 @@ class GpuDecoder:
         a.workspace, a.status = L.ptr(self.workspace), L.ptr(status)
         a.budget_cycles = L.budget_cycles(self.budget_s)
         a.fused, a.grid = int(self.fused), self.grid
+        return a
+
+    def decode_update(self, payload_ptrs: Sequence[int], flag_ptrs: Sequence[Optional[int]], slot_capacity: int,
+                      step: int, status: torch.Tensor, w: Optional[torch.Tensor] = None, lr: float = 0.0,
+                      adam_m: Optional[torch.Tensor] = None, adam_v: Optional[torch.Tensor] = None,
+                      adam_scale: float = 1.0, loss_out: Optional[torch.Tensor] = None,
+                      out_sum: Optional[torch.Tensor] = None) -> None:
+        a = self.make_args(payload_ptrs, flag_ptrs, slot_capacity, step, status, w, lr, adam_m, adam_v, adam_scale,
+                           loss_out, out_sum)
+        world = len(payload_ptrs)
         L.check(self.lib.skml_decode_update(C.byref(a), L.stream()), "skml_decode_update")
         L.count_launches(1 if self.fused else (2 if adam_v is not None else world))
 

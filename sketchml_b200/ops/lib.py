@@ -49,6 +49,17 @@ class DecodeArgs(C.Structure):
     ]
 
 
+class StepArgs(C.Structure):
+    _fields_ = [
+        ("rowptr", c_vp), ("cols", c_vp), ("vals", c_vp), ("labels", c_vp), ("seg_lo", c_ll * 2), ("seg_cnt", c_ll * 2),
+        ("nnz_padded", c_ll), ("avg_nnz", c_d), ("w", c_vp), ("g", c_vp), ("bitmap", c_vp), ("loss_id", c_ll),
+        ("inv_batch", c_d), ("hot", c_ll), ("partials", c_vp), ("partials_template", c_vp), ("status", c_vp),
+        ("budget_cycles", c_ll), ("lam", c_d), ("block_counts", c_vp), ("meta", c_vp), ("keys", c_vp), ("gvals", c_vp),
+        ("dense_vals", c_vp), ("n_max", c_ll), ("dim", c_ll), ("compress", C.POINTER(CompressArgs)),
+        ("decode", C.POINTER(DecodeArgs)), ("step", c_ull), ("lr", c_d), ("adam_scale", c_d), ("loss_out", c_vp),
+    ]
+
+
 _SIGS = {
     "skml_compress_workspace_bytes": (c_ll, [c_ll, c_ll, c_ll, c_ll, c_d, c_ll]),
     "skml_payload_capacity": (c_ll, [c_ll, c_ll, c_ll, c_ll, c_ll, c_d]),
@@ -68,6 +79,7 @@ _SIGS = {
     "skml_gen_wstar": (c_int, [c_vp, c_ll, c_d, c_ull, c_vp]),
     "skml_gen_rows": (c_int, [c_vp, c_vp, c_vp, c_ll, c_ll, c_int, c_int, c_d, c_int, c_int, c_f, c_vp, c_ull, c_vp]),
     "skml_sm_count": (c_int, []),
+    "skml_train_step": (c_int, [C.POINTER(StepArgs), c_vp]),
     "skml_ipc_get_handle": (c_int, [c_vp, c_vp]),
     "skml_ipc_open_handle": (c_int, [c_vp, C.POINTER(c_vp)]),
     "skml_ipc_close": (c_int, [c_vp]),
