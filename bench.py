@@ -40,6 +40,7 @@ def parse():
     p.add_argument("--compressor", default="Sketch", choices=["Sketch", "None", "Float"])
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--unfused", action="store_true")
+    p.add_argument("--pipeline-depth", type=int, default=0, choices=[0, 1])
     return p.parse_args()
 
 
@@ -122,6 +123,7 @@ def main():
                   epoch_num=1, batch_sample_ratio=args.batch_fraction, learn_rate=0.05, learn_decay=0.9, l2_reg=1e-4,
                   compressor=args.compressor, quant_bin_num=256, sketch_group_num=8, sketch_row_num=3,
                   sketch_col_ratio=0.2, optimizer="sgd", device="cuda", seed=17, syn_rows=args.rows,
+                  pipeline_depth=args.pipeline_depth,
                   syn_nnz_per_row=args.nnz_per_row, syn_zipf_s=1.1, syn_wstar_density=0.01,
                   extras={"fused": not args.unfused, "heartbeat": False})
     trainer = Trainer(conf)
@@ -188,7 +190,7 @@ def main():
                        "compressor": args.compressor, "sketch": "q=256, 8 groups, 3 rows x 0.2 cols, delta-binary keys",
                        "l2_policy": "inputs larger than L2: every step reads a fresh batch slice plus 200 MB of "
                                     "weights and 400 MB of accumulators",
-                       "fused": not args.unfused},
+                       "fused": not args.unfused, "pipeline_depth": args.pipeline_depth},
             "clocks": clocks, "gpu_launches": launches,
             "payload": {"nnz_per_rank": nnz, "bytes_per_rank": pbytes,
                         "ratio_vs_8B_per_nnz": 8.0 * nnz / max(pbytes, 1), "ratio_vs_12B_per_nnz": 12.0 * nnz / max(pbytes, 1)},

@@ -102,6 +102,16 @@ class GpuEngine:
             from .parallel.exchange import PeerExchange
             self.xchg = PeerExchange(comm, self.comp.capacity, self.device)
             self._prepare_fast_step()
+            self.depth = int(conf.pipeline_depth)
+            if self.depth == 1:
+                # gradient one step stale: batch t+1 is differentiated on its own stream while step t
+                # is still being compressed, exchanged and applied; the sparse-gradient buffers are doubled
+                self.sts = [self.st, GlmState.create(dim, bound, self.device, allow_dense)]
+                self.stream_g = torch.cuda.Stream(device=self.device)
+                self.ev_grad = [torch.cuda.Event(), torch.cuda.Event()]
+                self.ev_applied = [torch.cuda.Event(), torch.cuda.Event()]
+                for e in self.ev_applied:
+                    e.record()
         elif self.mode == "nccl_kv":
             self.kv_keys = torch.zeros((comm.world, bound), dtype=torch.int32, device=self.device)
             self.kv_vals = torch.zeros((comm.world, bound), dtype=torch.float32, device=self.device)
@@ -188,16 +198,28 @@ class GpuEngine:
             # reg loss = lambda * ||w||_2 (un-squared, ml/objective/Loss.scala:48-53); an O(dim) pass,
             # so large models refresh it once per epoch instead
             self.partials_template[2:3].copy_(torch.linalg.vector_norm(m.weights).double() * m.loss.lam)
+        lam = m.loss.get_reg_param() if m.loss.is_l2_reg else 0.0
+        if getattr(self, "depth", 0) == 1 and self.mode == "sketch":
+            par = self.batch_index & 1
+            st = self.sts[par]
+            with torch.cuda.stream(self.stream_g):
+                # the buffers of this parity were last read by step t-2's compress kernel
+                self.stream_g.wait_event(self.ev_applied[par])
+                st.partials.copy_(self.partials_template)
+                glm_grad(csr, segs, m.weights, st, m.loss.loss_id, rows, self.conf.hot_columns, self.conf.step_timeout_s)
+                compact_gradient(st, m.weights, lam)
+                self.ev_grad[par].record()
+            m.optimizer.advance()
+            return _BatchHandle(rows, self.batch_index), None, None
         st.partials.copy_(self.partials_template)
         glm_grad(csr, segs, m.weights, st, m.loss.loss_id, rows, self.conf.hot_columns, self.conf.step_timeout_s)
-        lam = m.loss.get_reg_param() if m.loss.is_l2_reg else 0.0
         compact_gradient(st, m.weights, lam)
         m.optimizer.advance()
         h = _BatchHandle(rows, self.batch_index)
         return h, None, None
 
     def _fast_ok(self) -> bool:
-        return (self.mode == "sketch" and bool(self.conf.extras.get("single_call_step", True)) and
+        return (self.mode == "sketch" and getattr(self, "depth", 0) == 0 and bool(self.conf.extras.get("single_call_step", True)) and
                 bool(self.conf.extras.get("fused", True)) and
                 not (self.t.injector is not None and self.t.injector.skip_publish_steps))
 
@@ -219,6 +241,10 @@ class GpuEngine:
             if self.conf.extras.get("check_status_every_step", False):
                 self.check()
         elif self.mode == "sketch":
+            par = self.batch_index & 1
+            if getattr(self, "depth", 0) == 1:
+                st = self.sts[par]
+                torch.cuda.current_stream().wait_event(self.ev_grad[par])
             send_p, send_f = self.xchg.send_ptrs(step)
             recv_p, recv_f = self.xchg.recv_ptrs(step)
             skip = self.t.injector is not None and step in self.t.injector.skip_publish_steps
@@ -227,6 +253,8 @@ class GpuEngine:
                                    self.xchg.slot_capacity, send_p, send_f, st.status, st.partials, st.dense_vals)
             self.dec.decode_update(recv_p, recv_f, self.xchg.slot_capacity, step, st.status, m.weights, lr, am, av,
                                    adam_scale, ring)
+            if getattr(self, "depth", 0) == 1:
+                self.ev_applied[par].record()
             if self.conf.extras.get("check_status_every_step", comm.world > 1 and bool(self.t.injector)):
                 self.check()
         elif self.mode == "nccl_dense":
@@ -264,6 +292,8 @@ class GpuEngine:
     def check(self) -> None:
         """Reads the status word (synchronises) and raises on a kernel-reported error."""
         s = read_status(self.st.status)
+        if not s and getattr(self, "depth", 0) == 1:
+            s = read_status(self.sts[1].status)
         if s:
             if self.mode == "sketch":
                 self.comp.reset()

@@ -68,3 +68,11 @@ def test_kv_baseline_and_checkpoint_resume(tmp_path):
     assert len(h3["train_loss"]) == 1
     # float atomics make two runs differ in the last bits, which can move a value across a bucket edge
     assert float((w3 - w4).abs().mean()) < 2e-4 and float((w3 - w4).abs().max()) < 5e-2
+
+
+def test_pipeline_depth_one_trains_like_depth_zero():
+    h0, w0, _ = _train(_conf(compressor="Sketch", epoch_num=3))
+    h1, w1, _ = _train(_conf(compressor="Sketch", epoch_num=3, pipeline_depth=1))
+    assert h1["train_loss"][-1] < h1["train_loss"][0]
+    # a gradient that is one step stale costs a little progress, not convergence
+    assert abs(h1["valid_loss"][-1] - h0["valid_loss"][-1]) / h0["valid_loss"][-1] < 0.01
