@@ -671,20 +671,8 @@ __device__ void element_pass(const CP& p, Smem& s, long long n) {
             unsigned int* tab = p.tables + L.tab32_off[g];
             SkmlKeyDigits kd;
             skml_key_digits(key, kd);
-            unsigned int* slot[SKML_MAX_ROWS];
-            unsigned int cur[SKML_MAX_ROWS];
-#pragma unroll
-            for (int r = 0; r < SKML_MAX_ROWS; ++r) {
-                slot[r] = nullptr;
-                cur[r] = 0;
-                if (r < p.rows) {
-                    slot[r] = tab + (long long)r * col + skml_hash_fast(L.hash_ids[g][r], key, kd, col, L.col_magic[g]);
-                    cur[r] = __ldcg(slot[r]);  // cells only decrease: a stale value only costs a redundant atomic
-                }
-            }
-#pragma unroll
-            for (int r = 0; r < SKML_MAX_ROWS; ++r)
-                if (r < p.rows && cell < cur[r]) atomicMin(slot[r], cell);
+            for (int r = 0; r < p.rows; ++r)
+                atomicMin(tab + (long long)r * col + skml_hash_fast(L.hash_ids[g][r], key, kd, col, L.col_magic[g]), cell);
         }
         __syncthreads();  // all readers of tile_rank / tile_bytes are done
         if (wg_on && wg_w == SKML_WARPS - 1) {

@@ -345,55 +345,94 @@ extern "C" int skml_glm_validate(const long long* rowptr, const int* cols, const
 #define COMPACT_WPT 4
 #define COMPACT_WORDS (SKML_BLOCK * COMPACT_WPT)
 #define COMPACT_SPARSE_BITS 4  // words with at most this many bits are walked by one lane
+#define COMPACT_DENSE_BATCH 8  // dense words whose loads are in flight together
 
 __global__ void __launch_bounds__(SKML_BLOCK)
 compact_count_kernel(float* __restrict__ g, const float* __restrict__ w, unsigned int* __restrict__ bitmap,
                      long long nwords, int dim, float lambda, unsigned int* __restrict__ block_counts) {
     // A warp owns COMPACT_WPT groups of 32 consecutive bitmap words. Words with few bits are
     // walked by their own lane; words with many bits are walked by the whole warp, one bit
-    // per lane, so that the g / w accesses of dense regions are coalesced. The filtered value
-    // g + lambda * w is stored back into g so that the write pass reads one array only.
+    // per lane, so that the g / w accesses of dense regions are coalesced. Loads are issued in
+    // batches before any of them is consumed (several memory round trips in flight per warp).
+    // The filtered value g + lambda * w is stored back into g so that the write pass reads one
+    // array only.
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long wbase = (long long)blockIdx.x * COMPACT_WORDS + (long long)warp * (32 * COMPACT_WPT);
+    unsigned int bitsv[COMPACT_WPT];
+#pragma unroll
+    for (int grp = 0; grp < COMPACT_WPT; ++grp) {
+        const long long wi = wbase + grp * 32 + lane;
+        bitsv[grp] = wi < nwords ? bitmap[wi] : 0u;
+    }
     unsigned int cnt = 0;
 #pragma unroll
     for (int grp = 0; grp < COMPACT_WPT; ++grp) {
         const long long gbase = wbase + grp * 32;
         const long long wi = gbase + lane;
-        const unsigned int bits = wi < nwords ? bitmap[wi] : 0u;
+        const unsigned int bits = bitsv[grp];
         unsigned int keep = bits;
         const int pc = __popc(bits);
         if (pc > 0 && pc <= COMPACT_SPARSE_BITS) {
+            int tpos[COMPACT_SPARSE_BITS];
+            bool inb[COMPACT_SPARSE_BITS];
+            float gv[COMPACT_SPARSE_BITS], wv[COMPACT_SPARSE_BITS];
             unsigned int b = bits;
-            while (b) {
-                const int t = __ffs(b) - 1;
+#pragma unroll
+            for (int j = 0; j < COMPACT_SPARSE_BITS; ++j) {
+                tpos[j] = b ? __ffs(b) - 1 : -1;
                 b &= b - 1;
-                const long long k = wi * 32 + t;
-                float v = 0.f;
-                if (k < dim) v = g[k] + lambda * w[k];
+                const long long k = wi * 32 + (tpos[j] < 0 ? 0 : tpos[j]);
+                inb[j] = tpos[j] >= 0 && k < dim;
+                gv[j] = inb[j] ? g[k] : 0.f;
+                wv[j] = inb[j] ? w[k] : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < COMPACT_SPARSE_BITS; ++j) {
+                if (tpos[j] < 0) continue;
+                if (!inb[j]) {  // a bit beyond dim (never set by the gradient kernel): drop it
+                    keep &= ~(1u << tpos[j]);
+                    continue;
+                }
+                const long long k = wi * 32 + tpos[j];
+                const float v = gv[j] + lambda * wv[j];
                 if (fabsf(v) > SKML_EPS) {
                     g[k] = v;
                 } else {
-                    keep &= ~(1u << t);
-                    if (k < dim) g[k] = 0.f;
+                    keep &= ~(1u << tpos[j]);
+                    g[k] = 0.f;
                 }
             }
         }
         unsigned int dense = __ballot_sync(0xFFFFFFFFu, pc > COMPACT_SPARSE_BITS);
         while (dense) {
-            const int j = __ffs(dense) - 1;
-            dense &= dense - 1;
-            const unsigned int wb = __shfl_sync(0xFFFFFFFFu, bits, j);
-            const long long k = (gbase + j) * 32 + lane;
-            const bool active = (wb >> lane) & 1u;
-            bool ok = false;
-            if (active && k < dim) {
-                const float v = g[k] + lambda * w[k];
-                ok = fabsf(v) > SKML_EPS;
-                g[k] = ok ? v : 0.f;
+            int jj[COMPACT_DENSE_BATCH];
+            unsigned int wb[COMPACT_DENSE_BATCH];
+            float gv[COMPACT_DENSE_BATCH], wv[COMPACT_DENSE_BATCH];
+#pragma unroll
+            for (int u = 0; u < COMPACT_DENSE_BATCH; ++u) {
+                jj[u] = dense ? __ffs(dense) - 1 : -1;
+                dense &= dense - 1;
+                wb[u] = __shfl_sync(0xFFFFFFFFu, bits, jj[u] < 0 ? 0 : jj[u]);
+                const long long k = (gbase + (jj[u] < 0 ? 0 : jj[u])) * 32 + lane;
+                const bool active = jj[u] >= 0 && ((wb[u] >> lane) & 1u) && k < dim;
+                gv[u] = active ? g[k] : 0.f;
+                wv[u] = active ? w[k] : 0.f;
+                if (!active) wb[u] &= ~(1u << lane);
             }
-            const unsigned int kb = __ballot_sync(0xFFFFFFFFu, ok);
-            if (lane == j) keep = kb;
+#pragma unroll
+            for (int u = 0; u < COMPACT_DENSE_BATCH; ++u) {
+                if (jj[u] < 0) continue;  // uniform over the warp
+                const bool active = (wb[u] >> lane) & 1u;
+                bool ok = false;
+                if (active) {
+                    const long long k = (gbase + jj[u]) * 32 + lane;
+                    const float v = gv[u] + lambda * wv[u];
+                    ok = fabsf(v) > SKML_EPS;
+                    g[k] = ok ? v : 0.f;
+                }
+                const unsigned int kb = __ballot_sync(0xFFFFFFFFu, ok);
+                if (lane == jj[u]) keep = kb;
+            }
         }
         if (keep != bits) bitmap[wi] = keep;
         cnt += __popc(keep);
@@ -494,15 +533,23 @@ compact_write_kernel(float* __restrict__ g, const float* __restrict__ w, unsigne
         const unsigned int ex = inc - (unsigned int)pc;
         const unsigned int grp_total = __shfl_sync(0xFFFFFFFFu, inc, 31);
         if (pc > 0 && pc <= COMPACT_SPARSE_BITS) {
+            int tpos[COMPACT_SPARSE_BITS];
+            float gv[COMPACT_SPARSE_BITS];
             unsigned int b = bits;
-            long long pos = out + ex;
-            while (b) {
-                const int t = __ffs(b) - 1;
+#pragma unroll
+            for (int j = 0; j < COMPACT_SPARSE_BITS; ++j) {
+                tpos[j] = b ? __ffs(b) - 1 : -1;
                 b &= b - 1;
-                const long long k = wi * 32 + t;
+                gv[j] = tpos[j] >= 0 ? g[wi * 32 + tpos[j]] : 0.f;
+            }
+            long long pos = out + ex;
+#pragma unroll
+            for (int j = 0; j < COMPACT_SPARSE_BITS; ++j) {
+                if (tpos[j] < 0) continue;
+                const long long k = wi * 32 + tpos[j];
                 if (pos < capacity) {
                     keys[pos] = (int)k;
-                    vals[pos] = g[k];
+                    vals[pos] = gv[j];
                 } else {
                     overflow = true;
                 }
@@ -512,16 +559,26 @@ compact_write_kernel(float* __restrict__ g, const float* __restrict__ w, unsigne
         }
         unsigned int dense = __ballot_sync(0xFFFFFFFFu, pc > COMPACT_SPARSE_BITS);
         while (dense) {
-            const int j = __ffs(dense) - 1;
-            dense &= dense - 1;
-            const unsigned int wb = __shfl_sync(0xFFFFFFFFu, bits, j);
-            const unsigned int exj = __shfl_sync(0xFFFFFFFFu, ex, j);
-            if ((wb >> lane) & 1u) {
-                const long long k = (gbase + j) * 32 + lane;
-                const long long pos = out + exj + __popc(wb & ((1u << lane) - 1u));
+            int jj[COMPACT_DENSE_BATCH];
+            unsigned int wb[COMPACT_DENSE_BATCH], exj[COMPACT_DENSE_BATCH];
+            float gv[COMPACT_DENSE_BATCH];
+#pragma unroll
+            for (int u = 0; u < COMPACT_DENSE_BATCH; ++u) {
+                jj[u] = dense ? __ffs(dense) - 1 : -1;
+                dense &= dense - 1;
+                const int src = jj[u] < 0 ? 0 : jj[u];
+                wb[u] = jj[u] < 0 ? 0u : __shfl_sync(0xFFFFFFFFu, bits, src);
+                exj[u] = __shfl_sync(0xFFFFFFFFu, ex, src);
+                gv[u] = ((wb[u] >> lane) & 1u) ? g[(gbase + src) * 32 + lane] : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < COMPACT_DENSE_BATCH; ++u) {
+                if (!((wb[u] >> lane) & 1u)) continue;
+                const long long k = (gbase + jj[u]) * 32 + lane;
+                const long long pos = out + exj[u] + __popc(wb[u] & ((1u << lane) - 1u));
                 if (pos < capacity) {
                     keys[pos] = (int)k;
-                    vals[pos] = g[k];
+                    vals[pos] = gv[u];
                 } else {
                     overflow = true;
                 }
