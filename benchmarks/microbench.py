@@ -39,7 +39,7 @@ def make_gradient(dim, nnz, seed, device):
     if k.numel() > nnz:
         sel = torch.randperm(k.numel(), generator=g, device=device)[:nnz]
         k = k[sel].sort().values
-    u = torch.rand(k.numel(), generator=g, device=device) - 0.5
+    u = (torch.rand(k.numel(), generator=g, device=device) - 0.5).clamp(-0.4999999, 0.4999999)
     v = -1e-3 * torch.sign(u) * torch.log1p(-2 * u.abs())      # Laplace(0, 1e-3)
     v = torch.where(v.abs() < 1e-8, torch.full_like(v, 1e-6), v)
     return k.to(torch.int32).contiguous(), v.float().contiguous()

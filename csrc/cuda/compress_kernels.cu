@@ -495,6 +495,8 @@ __device__ void load_quantizer(const CP& p, Smem& s) {
             q.minv = ord2f(~__ldcg(p.ctrl + 4));
             q.maxv = ord2f(__ldcg(p.ctrl + 5));
         }
+        // NaN or infinite gradient values cannot be bucketized (the reference's sketch throws on NaN)
+        if (!isfinite(q.minv) || !isfinite(q.maxv)) skml_set_status(p.status, SKML_BAD_INPUT, 0x35u);
         int z;
         if (q.minv > 0.f) z = 0;
         else if (q.maxv < 0.f) z = q.bin_num - 1;

@@ -215,3 +215,15 @@ def test_bad_header_and_timeout_are_reported_not_fatal():
     flag[0] = 4  # step + 1
     dec.decode_update([b.data_ptr()], [flag.data_ptr()], b.numel(), 3, status, w=w, lr=1.0)
     assert int(status.item()) == 0 and float(w.abs().max()) > 0
+
+
+def test_non_finite_values_are_reported():
+    from sketchml_b200.ops import GpuCompressor
+    keys, vals = _sparse_grad(5000, 100000, seed=3)
+    vals[17] = -np.inf
+    comp = GpuCompressor(100000, 5000, 64, 8, 2, 0.3, seed=1)
+    with pytest.raises(RuntimeError, match="invalid kernel input"):
+        comp.compress_local(torch.from_numpy(keys).cuda(), torch.from_numpy(vals).cuda())
+    # the compressor stays usable afterwards
+    vals[17] = 1e-3
+    comp.compress_local(torch.from_numpy(keys).cuda(), torch.from_numpy(vals).cuda())
