@@ -26,7 +26,9 @@
 #include "skml_device.cuh"
 
 #define DEC_MAX_ITEMS (SKML_MAX_PEERS * SKML_MAX_GROUPS)
-#define DEC_THREADS 512  // two keys of a 1024-key chunk per thread
+#define DEC_KPT 4        // keys of a 1024-key chunk per thread
+#define DEC_THREADS (SKML_RESTART_INTERVAL / DEC_KPT)
+#define DEC_BLOCKS_PER_SM 4
 
 struct DP {
     const unsigned char* payload[SKML_MAX_PEERS];
@@ -47,6 +49,7 @@ struct DP {
     unsigned int* ctrl;
     unsigned int* status;
     long long budget;
+    int max_items;
 };
 
 struct DecItem {  // one (rank, group) key stream
@@ -60,7 +63,6 @@ struct DecItem {  // one (rank, group) key stream
 
 struct DecSmem {
     SkmlHeader hdr[SKML_MAX_PEERS];
-    DecItem items[DEC_MAX_ITEMS];
     int nitems;
     unsigned long long total_chunks, total_keys;
     int any_dense;
@@ -69,6 +71,8 @@ struct DecSmem {
     int shift;       // fixed-point: accumulator = value * 2^shift
     double inv_world;
     int ok;
+    int max_items;
+    DecItem items[1];  // max_items entries (dynamic shared memory)
 };
 
 __device__ __forceinline__ long long to_fixed(double v, int shift) { return __double2ll_rn(ldexp(v, shift)); }
@@ -144,6 +148,11 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
                 continue;
             }
             for (unsigned int g = 0; g < h.group_num; ++g) {
+                if (ni >= p.max_items) {
+                    skml_set_status(p.status, SKML_BAD_HEADER, 0x300u | (unsigned int)r);
+                    s.ok = 0;
+                    break;
+                }
                 DecItem& it = s.items[ni];
                 it.base = p.payload[r];
                 it.e = *reinterpret_cast<const SkmlGroupEntry*>(p.payload[r] + h.off_group_table + g * sizeof(SkmlGroupEntry));
@@ -229,8 +238,9 @@ __device__ __forceinline__ void decode_one(const DP& p, const DecSmem& s, const 
     if (fx) atomicAdd(reinterpret_cast<unsigned long long*>(p.acc + key), (unsigned long long)fx);
 }
 
-// D1 for sparse payloads: one 1024-key chunk per block iteration, two adjacent keys per thread
-// (512 threads), so that every thread has two independent load chains in flight.
+// D1 for sparse payloads: one 1024-key chunk per block iteration, DEC_KPT adjacent keys per
+// thread (256 threads), so that every thread has several independent load chains in flight and
+// several blocks share an SM.
 __device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch_begin, unsigned long long ch_end) {
     for (unsigned long long ch = ch_begin + blockIdx.x; ch < ch_end; ch += gridDim.x) {
         int it_i = 0;
@@ -240,50 +250,68 @@ __device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch
         const unsigned int first = j * SKML_RESTART_INTERVAL;
         const unsigned int cnt = min((unsigned int)SKML_RESTART_INTERVAL, it.e.n - first);
         const SkmlRestart rs = *reinterpret_cast<const SkmlRestart*>(it.base + it.e.restart_off + 16ull * j);
-        const unsigned int i0 = 2 * threadIdx.x, i1 = i0 + 1;
-        unsigned int w0 = 0, w1 = 0;
+        const unsigned int i0 = DEC_KPT * threadIdx.x;
+        unsigned int w[DEC_KPT];
+        unsigned int wsum = 0;
+#pragma unroll
+        for (int u = 0; u < DEC_KPT; ++u) w[u] = 0;
         if (i0 < cnt) {
-            // the flags of keys 2t and 2t+1 are 4 adjacent bits of one 32-bit word
+            // the flags of DEC_KPT adjacent keys are 2 * DEC_KPT adjacent bits of one 32-bit word
             const unsigned long long fb = (unsigned long long)rs.flag_bit_off + 2ull * i0;
             const unsigned int word = __ldcg(reinterpret_cast<const unsigned int*>(it.base + it.e.flag_off) + (fb >> 5));
-            const unsigned int b = (word >> (fb & 31)) & 15u;
-            w0 = (((b & 1u) << 1) | ((b >> 1) & 1u)) + 1u;  // stream order is most significant bit first
-            if (w0 == 3) w0 = 4;                             // flag value 2 is never written
-            if (i1 < cnt) {
-                const unsigned int b2 = b >> 2;
-                w1 = (((b2 & 1u) << 1) | (b2 >> 1)) + 1u;
-                if (w1 == 3) w1 = 4;
-            }
-        }
-        unsigned int total_w;
-        const unsigned int boff = block_exclusive_scan<unsigned int>(w0 + w1, &total_w);
-        unsigned int d0 = 0, d1 = 0;
-        if (i0 < cnt) {
-            const unsigned long long byte0 = (rs.delta_bit_off >> 3) + boff;
-            if (byte0 + w0 + w1 <= 8ull * it.e.n_delta_words) {
-                const unsigned char* src = it.base + it.e.delta_off + byte0;
-                unsigned char raw[8];
+            const unsigned int b = word >> (fb & 31);
 #pragma unroll
-                for (unsigned int t = 0; t < 8; ++t) raw[t] = t < w0 + w1 ? __ldcg(src + t) : 0;
-#pragma unroll
-                for (unsigned int t = 0; t < 8; ++t) {
-                    if (t < w0) d0 = (d0 << 8) | skml_brev8(raw[t]);
-                    else if (t < w0 + w1) d1 = (d1 << 8) | skml_brev8(raw[t]);
+            for (int u = 0; u < DEC_KPT; ++u) {
+                if (i0 + u < cnt) {
+                    const unsigned int bb = (b >> (2 * u)) & 3u;
+                    unsigned int wu = (((bb & 1u) << 1) | (bb >> 1)) + 1u;  // stream order is most significant bit first
+                    if (wu == 3) wu = 4;                                     // flag value 2 is never written
+                    w[u] = wu;
+                    wsum += wu;
                 }
             }
         }
-        unsigned int total_d;
-        const unsigned int dex = block_exclusive_scan<unsigned int>(d0 + d1, &total_d);
+        unsigned int total_w;
+        const unsigned int boff = block_exclusive_scan<unsigned int>(wsum, &total_w);
+        unsigned int d[DEC_KPT];
+#pragma unroll
+        for (int u = 0; u < DEC_KPT; ++u) d[u] = 0;
         if (i0 < cnt) {
-            const unsigned int key0 = rs.prev_key + dex + d0;
-            const unsigned int key1 = key0 + d1;
-            int* ks = p.key_scratch + it.key_prefix + first;
-            if (!s.direct) {
-                ks[i0] = (int)key0;
-                if (i1 < cnt) ks[i1] = (int)key1;
+            const unsigned long long byte0 = (rs.delta_bit_off >> 3) + boff;
+            if (byte0 + wsum <= 8ull * it.e.n_delta_words) {
+                const unsigned char* src = it.base + it.e.delta_off + byte0;
+                unsigned char raw[4 * DEC_KPT];
+#pragma unroll
+                for (unsigned int t = 0; t < 4 * DEC_KPT; ++t) raw[t] = t < wsum ? __ldcg(src + t) : 0;
+                unsigned int edge = 0;
+#pragma unroll
+                for (int u = 0; u < DEC_KPT; ++u) {
+                    const unsigned int lo = edge;
+                    edge += w[u];
+#pragma unroll
+                    for (unsigned int t = 0; t < 4 * DEC_KPT; ++t)
+                        if (t >= lo && t < edge) d[u] = (d[u] << 8) | skml_brev8(raw[t]);
+                }
             }
-            decode_one(p, s, it, key0);
-            if (i1 < cnt) decode_one(p, s, it, key1);
+        }
+        unsigned int dsum = 0;
+#pragma unroll
+        for (int u = 0; u < DEC_KPT; ++u) dsum += d[u];
+        unsigned int total_d;
+        const unsigned int dex = block_exclusive_scan<unsigned int>(dsum, &total_d);
+        if (i0 < cnt) {
+            unsigned int key = rs.prev_key + dex;
+            int* ks = p.key_scratch + it.key_prefix + first;
+            unsigned int keys[DEC_KPT];
+#pragma unroll
+            for (int u = 0; u < DEC_KPT; ++u) {
+                key += d[u];
+                keys[u] = key;
+                if (!s.direct && i0 + u < cnt) ks[i0 + u] = (int)key;
+            }
+#pragma unroll
+            for (int u = 0; u < DEC_KPT; ++u)
+                if (i0 + u < cnt) decode_one(p, s, it, keys[u]);
         }
         __syncthreads();
     }
@@ -347,7 +375,7 @@ __device__ void decode_update(const DP& p, DecSmem& s) {
 }
 
 template <bool FUSED>
-__global__ void __launch_bounds__(DEC_THREADS, 2) decode_update_kernel(DP p, int stage) {
+__global__ void __launch_bounds__(DEC_THREADS, DEC_BLOCKS_PER_SM) decode_update_kernel(DP p, int stage) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     DecSmem& s = *reinterpret_cast<DecSmem*>(smem_raw);
     if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) {
@@ -439,24 +467,35 @@ extern "C" int skml_decode_update(const SkmlDecodeArgs* a, void* stream_) {
     p.ctrl = reinterpret_cast<unsigned int*>(a->workspace);
     p.status = a->status;
     p.budget = a->budget_cycles > 0 ? a->budget_cycles : 2000000000ll;
-    static int sms = 0, max_grid = 0;
+    // the (rank, group) table lives in dynamic shared memory: world x groups entries
+    long long groups = a->max_groups > 0 ? a->max_groups : SKML_MAX_GROUPS;
+    if (groups > SKML_MAX_GROUPS) groups = SKML_MAX_GROUPS;
+    p.max_items = (int)(a->world * groups);
+    const size_t smem = sizeof(DecSmem) + (size_t)p.max_items * sizeof(DecItem);
+    static int sms = 0;
+    static size_t cached_smem = 0;
+    static int max_grid = 0;
     if (sms == 0) {
         int dev = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
-        cudaError_t e0 = cudaFuncSetAttribute(decode_update_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DecSmem));
+        const int cap = (int)(sizeof(DecSmem) + (size_t)DEC_MAX_ITEMS * sizeof(DecItem));
+        cudaError_t e0 = cudaFuncSetAttribute(decode_update_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
         if (e0 == cudaSuccess)
-            e0 = cudaFuncSetAttribute(decode_update_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DecSmem));
+            e0 = cudaFuncSetAttribute(decode_update_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
         if (e0 != cudaSuccess) {
             sms = 0;
             return (int)e0;
         }
-        int per_sm = 0;
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_update_kernel<true>, DEC_THREADS, sizeof(DecSmem));
-        max_grid = per_sm * sms;
     }
-    int grid = a->grid > 0 ? (int)a->grid : 2 * sms;  // two 512-thread blocks per SM
+    if (cached_smem != smem) {
+        int per_sm = 0;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_update_kernel<true>, DEC_THREADS, smem);
+        max_grid = per_sm * sms;
+        cached_smem = smem;
+    }
+    int grid = a->grid > 0 ? (int)a->grid : DEC_BLOCKS_PER_SM * sms;
     cudaError_t e;
     if (a->fused) {
         if (max_grid < 1) return (int)cudaErrorLaunchOutOfResources;
@@ -464,11 +503,11 @@ extern "C" int skml_decode_update(const SkmlDecodeArgs* a, void* stream_) {
         int stage = -1;
         void* args[] = {&p, &stage};
         return (int)cudaLaunchCooperativeKernel((const void*)decode_update_kernel<true>, dim3(grid), dim3(DEC_THREADS), args,
-                                                sizeof(DecSmem), stream);
+                                                smem, stream);
     }
     const int nst = a->adam_v ? 2 : (int)a->world;
     for (int st = 1; st <= nst; ++st) {
-        decode_update_kernel<false><<<grid, DEC_THREADS, sizeof(DecSmem), stream>>>(p, st);
+        decode_update_kernel<false><<<grid, DEC_THREADS, smem, stream>>>(p, st);
         e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;
     }

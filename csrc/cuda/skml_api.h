@@ -68,6 +68,7 @@ typedef struct SkmlDecodeArgs {
     long long budget_cycles;
     long long fused;
     long long grid;
+    long long max_groups;      // upper bound of the payloads' group count (0 = 32): sizes the work table
 } SkmlDecodeArgs;
 
 long long skml_decode_workspace_bytes(long long world, long long group_num);

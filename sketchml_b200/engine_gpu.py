@@ -46,11 +46,12 @@ class GpuEngine:
         self.read_index = 0
         self.last_payload_bytes = 0
         self.last_raw_nnz = 0
-        self.mode = {C.COMPRESSOR_SKETCH: "sketch", C.COMPRESSOR_NONE: "nccl_dense",
-                     C.COMPRESSOR_FLOAT: "nccl_kv"}.get(self.conf.compressor)
+        self.mode = {C.COMPRESSOR_SKETCH: "sketch", C.COMPRESSOR_NONE: "nccl_dense", C.COMPRESSOR_FLOAT: "nccl_kv",
+                     C.COMPRESSOR_FIXED_POINT: "nccl_kv", C.COMPRESSOR_ZIP: "nccl_kv"}.get(self.conf.compressor)
+        # FixedPoint / Zip: values are quantized on the device (ops/baseline_quant.py), keys travel raw
+        self.value_quant = self.conf.compressor if self.conf.compressor in (C.COMPRESSOR_FIXED_POINT, C.COMPRESSOR_ZIP) else None
         if self.mode is None:
-            raise ValueError(f"the GPU engine supports the Sketch, None and Float compressors; "
-                             f"{self.conf.compressor} runs on the host engine")
+            raise ValueError(f"Unrecognizable gradient compressor: {self.conf.compressor}")
         if self.conf.dtype != "float32":
             raise ValueError("the GPU engine computes in float32")
 
@@ -98,7 +99,7 @@ class GpuEngine:
                                       conf.sketch_col_ratio, conf.seed, self.device,
                                       fused=bool(conf.extras.get("fused", True)), budget_s=conf.step_timeout_s)
             self.dec = GpuDecoder(dim, bound * comm.world, self.device, fused=bool(conf.extras.get("fused", True)),
-                                  budget_s=conf.step_timeout_s)
+                                  budget_s=conf.step_timeout_s, max_groups=conf.sketch_group_num)
             from .parallel.exchange import PeerExchange
             self.xchg = PeerExchange(comm, self.comp.capacity, self.device)
             self._prepare_fast_step()
@@ -257,6 +258,10 @@ class GpuEngine:
                 self.ev_applied[par].record()
             if self.conf.extras.get("check_status_every_step", comm.world > 1 and bool(self.t.injector)):
                 self.check()
+        if self.mode != "sketch" and self.value_quant:
+            self._quantize_values(step)
+        if self.mode == "sketch":
+            pass
         elif self.mode == "nccl_dense":
             # baseline: all-reduce of the dense fp32 gradient, then update of every coordinate
             self._densify()
@@ -280,6 +285,19 @@ class GpuEngine:
                 update_sparse(m.weights, st.keys, st.vals, st.meta, self.n_max, 1.0, lr, am, av, adam_scale)
             ring.copy_(st.partials)
         self.batch_index += 1
+
+    def _quantize_values(self, step: int) -> None:
+        from .ops.baseline_quant import fixed_point_roundtrip, zipml_roundtrip
+        st, conf = self.st, self.conf
+        targets = [(st.vals, st.meta[0])]
+        if st.dense_vals is not None:
+            targets.append((st.dense_vals, torch.where(st.meta[1] == 2, st.meta[0] * 0 + st.dim, st.meta[0] * 0)))
+        for vals, n in targets:
+            if self.value_quant == C.COMPRESSOR_FIXED_POINT:
+                fixed_point_roundtrip(vals, n, conf.fixed_point_bit_num,
+                                      conf.seed * 1315423911 + step * 8191 + self.t.comm.rank)
+            else:
+                zipml_roundtrip(vals, n, conf.quant_bin_num)
 
     def _densify(self) -> None:
         st = self.st

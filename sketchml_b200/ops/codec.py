@@ -140,8 +140,9 @@ class GpuDecoder:
     """Owns the scratch memory of the fused decode + aggregate + update kernel."""
 
     def __init__(self, dim: int, key_capacity: int, device="cuda", fused: bool = True, grid: int = 0,
-                 budget_s: float = 1.0):
+                 budget_s: float = 1.0, max_groups: int = 32):
         self.lib = L.lib()
+        self.max_groups = int(max_groups)
         self.dim, self.key_capacity = int(dim), int(max(key_capacity, 1))
         self.device = torch.device(device)
         self.fused, self.grid, self.budget_s = fused, grid, budget_s
@@ -170,7 +171,7 @@ class GpuDecoder:
         a.loss_out, a.out_sum = L.ptr(loss_out), L.ptr(out_sum)
         a.workspace, a.status = L.ptr(self.workspace), L.ptr(status)
         a.budget_cycles = L.budget_cycles(self.budget_s)
-        a.fused, a.grid = int(self.fused), self.grid
+        a.fused, a.grid, a.max_groups = int(self.fused), self.grid, self.max_groups
         return a
 
     def decode_update(self, payload_ptrs: Sequence[int], flag_ptrs: Sequence[Optional[int]], slot_capacity: int,

@@ -76,3 +76,11 @@ def test_pipeline_depth_one_trains_like_depth_zero():
     assert h1["train_loss"][-1] < h1["train_loss"][0]
     # a gradient that is one step stale costs a little progress, not convergence
     assert abs(h1["valid_loss"][-1] - h0["valid_loss"][-1]) / h0["valid_loss"][-1] < 0.01
+
+
+@pytest.mark.parametrize("name", ["FixedPoint", "Zip"])
+def test_baseline_compressors_train_on_gpu(name):
+    h, w, _ = _train(_conf(compressor=name, epoch_num=2, quant_bin_num=64))
+    h0, w0, _ = _train(_conf(compressor="None", epoch_num=2))
+    assert h["train_loss"][-1] < h["train_loss"][0]
+    assert abs(h["valid_loss"][-1] - h0["valid_loss"][-1]) / h0["valid_loss"][-1] < 0.05
