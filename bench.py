@@ -91,9 +91,9 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    # `pip install --target baseline/_ref /root/reference` answers "Directory is not installable.
-    # Neither 'setup.py' nor 'pyproject.toml' found": the reference is a Maven project of Java and
-    # Scala sources for Spark 2.2, and this image has no JDK, Maven, Scala or Spark.
+    # pip answers "Directory is not installable. Neither 'setup.py' nor 'pyproject.toml' found" for the
+    # reference tree: it is a Maven project of Java and Scala sources for Spark 2.2, and this image has
+    # no JDK, Maven, Scala or Spark.
     print(json.dumps({"impl": "reference", "unavailable":
                       "the reference is a Java/Scala Spark application (Maven build); no JDK, Maven, Scala or Spark "
                       "in this image and it is not pip-installable"}))

@@ -1,5 +1,5 @@
 // CPU oracle: a C++17 restatement of the SketchML compression algorithms. Every
-// sm_100a kernel of this project is judged against these functions.
+// sm_100a kernel of this project is tested against these functions.
 //
 // Reference behaviour restated (paths inside the reference project, module `sketch`):
 //   sketch/quantile/HeapQuantileSketch.java:73-124,126-143,186-217,293-323 -> QuantileSketch
