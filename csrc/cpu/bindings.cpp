@@ -163,7 +163,83 @@ static py::dict parse_payload(const std::string& buf) {
     return r;
 }
 
+// ---------------------------------------------------------------------------
+// Native text parser: one pass over the bytes of a libsvm / csv / dummy file slice.
+// Formats as in the reference's ml/data/Parser.scala:23-76 (libsvm "label idx:val ...",
+// csv "label,v,v,...", dummy "label,idx,idx,..." with implicit 1.0 values); labels that are not
+// within 1e-8 of 1 become -1 when neg_y is set. Columns of a row are sorted and duplicate
+// columns merged (values add up).
+// ---------------------------------------------------------------------------
+static py::tuple parse_text(const std::string& text, const std::string& fmt, long long max_dim, bool neg_y) {
+    const int kind = fmt == "libsvm" ? 0 : (fmt == "csv" ? 1 : (fmt == "dummy" ? 2 : -1));
+    if (kind < 0) throw Error("Unknown file format: " + fmt);
+    std::vector<int64_t> rowptr{0};
+    std::vector<int32_t> cols;
+    std::vector<double> vals, labels;
+    std::vector<std::pair<int32_t, double>> row;
+    const char* p = text.data();
+    const char* end = p + text.size();
+    bool dup = false;
+    while (p < end) {
+        const char* eol = static_cast<const char*>(memchr(p, '\n', end - p));
+        if (!eol) eol = end;
+        const char* q = p;
+        while (q < eol && (*q == ' ' || *q == '\t' || *q == '\r')) ++q;
+        if (q < eol) {
+            char* next = nullptr;
+            double y = strtod(q, &next);
+            if (next == q) throw Error("cannot parse label in line: " + std::string(p, std::min<size_t>(eol - p, 60)));
+            if (neg_y && std::fabs(y - 1.0) > 1e-8) y = -1.0;
+            q = next;
+            row.clear();
+            int dense_i = 0;
+            while (q < eol) {
+                while (q < eol && (*q == ' ' || *q == ',' || *q == '\t' || *q == '\r')) ++q;
+                if (q >= eol) break;
+                if (kind == 0) {
+                    long idx = strtol(q, &next, 10);
+                    if (next == q || next >= eol || *next != ':') throw Error("expected idx:val in line: " + std::string(p, std::min<size_t>(eol - p, 60)));
+                    q = next + 1;
+                    double v = strtod(q, &next);
+                    if (next == q) throw Error("expected a value after ':'");
+                    q = next;
+                    row.push_back({(int32_t)idx, v});
+                } else if (kind == 1) {
+                    double v = strtod(q, &next);
+                    if (next == q) throw Error("cannot parse csv value");
+                    q = next;
+                    row.push_back({dense_i++, v});
+                } else {
+                    long idx = strtol(q, &next, 10);
+                    if (next == q) throw Error("cannot parse feature index");
+                    q = next;
+                    row.push_back({(int32_t)idx, 1.0});
+                }
+            }
+            std::stable_sort(row.begin(), row.end(), [](const auto& a, const auto& b) { return a.first < b.first; });
+            int32_t last = -1;
+            for (auto& kv : row) {
+                if (kv.first < 0 || kv.first >= max_dim)
+                    throw Error("feature index out of range [0, " + std::to_string(max_dim) + ")");
+                if (kv.first == last) {
+                    vals.back() += kv.second;
+                    dup = true;
+                } else {
+                    cols.push_back(kv.first);
+                    vals.push_back(kv.second);
+                    last = kv.first;
+                }
+            }
+            labels.push_back(y);
+            rowptr.push_back((int64_t)cols.size());
+        }
+        p = eol + 1;
+    }
+    return py::make_tuple(to_array(rowptr), to_array(cols), to_array(vals), to_array(labels), kind == 2 && !dup);
+}
+
 PYBIND11_MODULE(_oracle, m) {
+    m.def("parse_text", &parse_text, py::arg("text"), py::arg("format"), py::arg("max_dim"), py::arg("neg_y") = true);
     m.doc() = "CPU oracle of the SketchML compression algorithms";
     py::register_exception<Error>(m, "SketchMLError");
 

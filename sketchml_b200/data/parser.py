@@ -101,6 +101,19 @@ def parse_lines(lines: Iterable[str], fmt: str, max_dim: int, neg_y: bool = True
         max_dim)
 
 
+def parse_text_native(text: str, fmt: str, max_dim: int, neg_y: bool = True,
+                      dtype: torch.dtype = torch.float32) -> CSRMatrix:
+    """Same result as ``parse_lines`` through the C++ parser of the oracle module (one pass over
+    the bytes; used for files, where the Python loop above would dominate the load time)."""
+    from ..compress import oracle
+    try:
+        rowptr, cols, vals, labels, implicit = oracle.parse_text(text, fmt, int(max_dim), bool(neg_y))
+    except oracle.SketchMLError as e:
+        raise ValueError(str(e)) from e
+    return CSRMatrix(torch.from_numpy(rowptr), torch.from_numpy(cols),
+                     None if implicit else torch.from_numpy(vals).to(dtype), torch.from_numpy(labels).to(dtype), max_dim)
+
+
 def load_data(path: str, fmt: str, max_dim: int, rank: int = 0, world: int = 1, neg_y: bool = True,
               dtype: torch.dtype = torch.float32, limit: Optional[int] = None) -> tuple:
     """Reads ``path`` and returns (this rank's contiguous shard, global offset of its
@@ -111,4 +124,4 @@ def load_data(path: str, fmt: str, max_dim: int, rank: int = 0, world: int = 1, 
     if limit is not None:
         lines = lines[:limit]
     lo, hi = shard_rows(len(lines), rank, world)
-    return parse_lines(lines[lo:hi], fmt, max_dim, neg_y, dtype), lo, len(lines)
+    return parse_text_native("".join(lines[lo:hi]), fmt, max_dim, neg_y, dtype), lo, len(lines)

@@ -68,6 +68,31 @@ def test_parsers_and_dataset(tmp_path):
     assert split_train_valid(big, 0.0, 0)[1].rows == 0
 
 
+def test_native_parser_matches_python_parser():
+    from sketchml_b200.data import parse_lines, parse_text_native
+    rng = np.random.default_rng(0)
+    lines = []
+    for i in range(300):
+        idx = rng.choice(500, rng.integers(1, 30), replace=True)
+        lines.append(f"{rng.choice([0, 1, -1, 0.5])} " + " ".join(f"{j}:{rng.normal():.6g}" for j in idx))
+    for neg in (True, False):
+        a = parse_lines(lines, "libsvm", 500, neg, torch.float64)
+        b = parse_text_native("\n".join(lines) + "\n", "libsvm", 500, neg, torch.float64)
+        assert torch.equal(a.rowptr, b.rowptr) and torch.equal(a.cols, b.cols) and torch.equal(a.labels, b.labels)
+        assert torch.allclose(a.values, b.values, rtol=0, atol=1e-12)
+    d = ["1,5,3,9", "0,2", "", "1,7,7"]
+    a, b = parse_lines(d, "dummy", 10), parse_text_native("\n".join(d), "dummy", 10)
+    assert torch.equal(a.cols, b.cols) and torch.equal(a.values, b.values)
+    c = ["1,0.5,0,2", "0, 1.5 ,2,3"]
+    a, b = parse_lines(c, "csv", 3), parse_text_native("\n".join(c), "csv", 3)
+    assert torch.equal(a.cols, b.cols) and torch.equal(a.values, b.values) and torch.equal(a.labels, b.labels)
+    assert parse_text_native("1,4,2\n", "dummy", 5).values is None
+    with pytest.raises(ValueError):
+        parse_text_native("1 9:1\n", "libsvm", 5)
+    with pytest.raises(ValueError):
+        parse_text_native("1 a:1\n", "libsvm", 5)
+
+
 def test_losses_match_reference_formulas():
     from sketchml_b200.models.loss import L2HingeLoss, L2LogLoss, L2SquareLoss
     pre = torch.tensor([-30.0, -2.0, 0.0, 0.5, 1.0, 3.0, 25.0], dtype=torch.float64)
