@@ -68,7 +68,8 @@ struct GradSmem {
     uint64_t bar[2];
 };
 
-// MODE 0: training (scatter), MODE 1: validation (loss + confusion counts only)
+// MODE 0: training (scatter), MODE 1: validation (loss + confusion counts only),
+// MODE 2: per-row coefficients only (the scatter is done by the transposed-index kernels)
 template <int MODE>
 __global__ void __launch_bounds__(GRAD_THREADS)
 glm_rows_kernel(const long long* __restrict__ rowptr, const int* __restrict__ cols, const float* __restrict__ vals,
@@ -192,9 +193,12 @@ glm_rows_kernel(const long long* __restrict__ rowptr, const int* __restrict__ co
                 if (rb + u >= nrows) continue;
                 const float pre = sum[u];
                 const float y = s_lab[rb + u];
-                if (MODE == 0) {
+                if (MODE == 0 || MODE == 2) {
                     coef[u] = -glm_grad(loss_id, pre, y) * inv_batch;
-                    if (lane == u) loss_sum += (double)glm_loss(loss_id, pre, y);
+                    if (lane == u) {
+                        loss_sum += (double)glm_loss(loss_id, pre, y);
+                        if (MODE == 2) margins[r0 - row_lo + rb + u] = coef[u];  // coefficient per row, no scatter
+                    }
                 } else if (lane == u) {
                     loss_sum += (double)glm_loss(loss_id, pre, y);
                     const float z = pre * y;
@@ -305,17 +309,22 @@ static int grad_launch(int mode, const long long* rowptr, const int* cols, const
     long long grid = (long long)sm_count() * per_sm;
     if (grid > ntiles) grid = ntiles;
     static bool attr_set[2] = {false, false};
-    if (!attr_set[mode]) {
+    if (!attr_set[0]) {
         cudaFuncSetAttribute(glm_rows_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         cudaFuncSetAttribute(glm_rows_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(glm_rows_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         attr_set[0] = attr_set[1] = true;
     }
     if (mode == 0)
         glm_rows_kernel<0><<<(unsigned)grid, GRAD_THREADS, smem, stream>>>(
             rowptr, cols, vals, labels, row_lo, row_cnt, rpt, nnz_padded, w, g, bitmap, loss_id, inv_batch, hot, acc,
             margins, status, budget);
-    else
+    else if (mode == 1)
         glm_rows_kernel<1><<<(unsigned)grid, GRAD_THREADS, smem, stream>>>(
+            rowptr, cols, vals, labels, row_lo, row_cnt, rpt, nnz_padded, w, g, bitmap, loss_id, inv_batch, hot, acc,
+            margins, status, budget);
+    else
+        glm_rows_kernel<2><<<(unsigned)grid, GRAD_THREADS, smem, stream>>>(
             rowptr, cols, vals, labels, row_lo, row_cnt, rpt, nnz_padded, w, g, bitmap, loss_id, inv_batch, hot, acc,
             margins, status, budget);
     return (int)cudaGetLastError();
@@ -806,6 +815,100 @@ extern "C" int skml_gen_rows(int* cols, float* vals, float* labels, long long ro
 }
 
 extern "C" int skml_sm_count() { return sm_count(); }
+
+// ---------------------------------------------------------------------------
+// Transposed-index gradient. For a shard whose minibatches are fixed row slices, the batch's
+// column-major index (distinct columns, their row lists) is built once. A step then needs the
+// per-row coefficients (glm_rows_kernel<2>) and, per distinct column c of the batch,
+//     value[c] = sum over the batch rows r that contain c of coef[r] * x[r][c]  +  lambda * w[c],
+// which is a gather of coefficients (an L2-resident array of batch-size floats) instead of a
+// scatter into the dim-sized accumulator: no atomics, no touched bitmap, no compaction, and the
+// keys come out sorted because the column list is. Columns are binned by their number of
+// entries when the index is built: one thread, one warp or one block per column.
+// (Equivalent of ml/gradient/DenseDoubleGradient.scala:51-57 + toSparse for a known sparsity
+// pattern.)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float colsum_range(const int* __restrict__ rowidx, const float* __restrict__ svals,
+                                              const float* __restrict__ coef, int e0, int e1, int start, int stride) {
+    float acc = 0.f;
+    for (int e = e0 + start; e < e1; e += stride) {
+        const float c = __ldg(coef + rowidx[e]);
+        acc = fmaf(c, svals ? svals[e] : 1.f, acc);
+    }
+    return acc;
+}
+
+// bins[0..n_short) thread per column, bins[n_short..n_short+n_medium) warp per column (bins hold
+// positions into ucols / colptr). Long columns are cut into segments of a few thousand entries at
+// build time: item j = (long_col[j], [long_e0[j], long_e1[j])), one block each, partial sums added
+// atomically into `out` (which the caller zeroes for that reason).
+__global__ void __launch_bounds__(256)
+colsum_kernel(const int* __restrict__ colptr, const int* __restrict__ rowidx, const float* __restrict__ svals,
+              const int* __restrict__ ucols, const int* __restrict__ bins, const int* __restrict__ long_col,
+              const int* __restrict__ long_e0, const int* __restrict__ long_e1, int n_short, int n_medium, int n_long,
+              int short_blocks, int medium_blocks, const float* __restrict__ coef, const float* __restrict__ w,
+              float lambda, float* __restrict__ out) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int b = blockIdx.x;
+    if (b < short_blocks) {
+        const int t = b * 256 + threadIdx.x;
+        if (t < n_short) {
+            const int i = bins[t];
+            out[i] = colsum_range(rowidx, svals, coef, colptr[i], colptr[i + 1], 0, 1) + lambda * w[ucols[i]];
+        }
+        return;
+    }
+    b -= short_blocks;
+    if (b < medium_blocks) {
+        const int t = b * 8 + warp;
+        if (t < n_medium) {
+            const int i = bins[n_short + t];
+            float v = colsum_range(rowidx, svals, coef, colptr[i], colptr[i + 1], lane, 32);
+            v = warp_sum(v);
+            if (lane == 0) out[i] = v + lambda * w[ucols[i]];
+        }
+        return;
+    }
+    b -= medium_blocks;
+    if (b < n_long) {
+        __shared__ float s_part[8];
+        const int i = long_col[b];
+        const int e0 = long_e0[b];
+        float v = colsum_range(rowidx, svals, coef, e0, long_e1[b], threadIdx.x, 256);
+        v = warp_sum(v);
+        if (lane == 0) s_part[warp] = v;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float t = 0.f;
+            for (int k = 0; k < 8; ++k) t += s_part[k];
+            if (e0 == colptr[i]) t += lambda * w[ucols[i]];  // the column's first segment carries the L2 term
+            atomicAdd(out + i, t);
+        }
+    }
+}
+
+extern "C" int skml_glm_coef(const long long* rowptr, const int* cols, const float* vals, const float* labels,
+                             long long row_lo, long long row_cnt, long long nnz_padded, double avg_nnz,
+                             const float* w, int loss_id, float inv_batch, double* loss_acc, float* coef_out,
+                             unsigned int* status, long long budget, void* stream) {
+    return grad_launch(2, rowptr, cols, vals, labels, row_lo, row_cnt, nnz_padded, avg_nnz, w, nullptr, nullptr, loss_id,
+                       inv_batch, 0, loss_acc, coef_out, status, budget, (cudaStream_t)stream);
+}
+
+extern "C" int skml_colsum(const int* colptr, const int* rowidx, const float* svals, const int* ucols, const int* bins,
+                           const int* long_col, const int* long_e0, const int* long_e1, int n_short, int n_medium,
+                           int n_long, int n_cols, const float* coef, const float* w, float lambda, float* out,
+                           void* stream) {
+    cudaError_t e = cudaMemsetAsync(out, 0, (size_t)n_cols * sizeof(float), (cudaStream_t)stream);
+    if (e != cudaSuccess) return (int)e;
+    const int short_blocks = (n_short + 255) / 256, medium_blocks = (n_medium + 7) / 8;
+    const long long blocks = (long long)short_blocks + medium_blocks + n_long;
+    if (blocks <= 0) return 0;
+    colsum_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(colptr, rowidx, svals, ucols, bins, long_col, long_e0,
+                                                                     long_e1, n_short, n_medium, n_long, short_blocks,
+                                                                     medium_blocks, coef, w, lambda, out);
+    return (int)cudaGetLastError();
+}
 
 // ---------------------------------------------------------------------------
 // skml_compact_noalloc: the compaction above for callers that must not allocate.

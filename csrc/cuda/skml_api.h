@@ -96,6 +96,13 @@ int skml_gen_wstar(float* w, long long dim, double density, unsigned long long s
 int skml_gen_rows(int* cols, float* vals, float* labels, long long row_offset, long long rows, int dim, int k,
                   double s, int value_kind, int task, float noise, const float* wstar, unsigned long long seed,
                   void* stream);
+int skml_glm_coef(const long long* rowptr, const int* cols, const float* vals, const float* labels, long long row_lo,
+                  long long row_cnt, long long nnz_padded, double avg_nnz, const float* w, int loss_id,
+                  float inv_batch, double* loss_acc, float* coef_out, unsigned int* status, long long budget,
+                  void* stream);
+int skml_colsum(const int* colptr, const int* rowidx, const float* svals, const int* ucols, const int* bins,
+                const int* long_col, const int* long_e0, const int* long_e1, int n_short, int n_medium, int n_long,
+                int n_cols, const float* coef, const float* w, float lambda, float* out, void* stream);
 int skml_sm_count();
 
 // Peer memory (one process per GPU): CUDA IPC handles of a cudaMalloc'ed region.
@@ -144,6 +151,18 @@ typedef struct SkmlStepArgs {
     unsigned long long step;
     double lr, adam_scale;
     double* loss_out;                  // device, 4 doubles: this step's slot of the loss ring
+    // transposed-index gradient (all null / 0 = scatter + compaction path)
+    const int* t_colptr;               // [t_cols + 1] entry ranges of the batch's distinct columns
+    const int* t_rowidx;               // batch-local row of every entry, column-major
+    const float* t_vals;               // values in the same order (null = all ones)
+    const int* t_ucols;                // the distinct columns, ascending: the gradient's keys
+    const int* t_bins;                 // positions of short then medium columns
+    const int* t_long_col;
+    const int* t_long_e0;
+    const int* t_long_e1;
+    long long t_short, t_medium, t_long, t_cols;
+    const long long* t_meta;           // device: {t_cols, 1 (sparse kind), 0, 0}
+    float* coef;                       // device scratch: one coefficient per batch row
 } SkmlStepArgs;
 
 int skml_train_step(SkmlStepArgs* args, void* stream);

@@ -11,6 +11,28 @@ extern "C" int skml_train_step(SkmlStepArgs* a, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     cudaError_t e = cudaMemcpyAsync(a->partials, a->partials_template, 4 * sizeof(double), cudaMemcpyDeviceToDevice, stream);
     if (e != cudaSuccess) return (int)e;
+    if (a->t_colptr) {
+        // transposed index: coefficients per row, then one gather-sum per distinct column
+        int rc = skml_glm_coef(a->rowptr, a->cols, a->vals, a->labels, a->seg_lo[0], a->seg_cnt[0], a->nnz_padded,
+                               a->avg_nnz, a->w, (int)a->loss_id, (float)a->inv_batch, a->partials + 1, a->coef,
+                               a->status, a->budget_cycles, stream_);
+        if (rc) return rc;
+        rc = skml_colsum(a->t_colptr, a->t_rowidx, a->t_vals, a->t_ucols, a->t_bins, a->t_long_col, a->t_long_e0,
+                         a->t_long_e1, (int)a->t_short, (int)a->t_medium, (int)a->t_long, (int)a->t_cols, a->coef, a->w,
+                         (float)a->lambda, a->gvals, stream_);
+        if (rc) return rc;
+        a->compress->step = a->step;
+        a->compress->keys = a->t_ucols;
+        a->compress->meta = a->t_meta;
+        a->compress->vals = a->gvals;
+        rc = skml_compress_sparse(a->compress, stream_);
+        if (rc) return rc;
+        a->decode->step = a->step;
+        a->decode->lr = a->lr;
+        a->decode->adam_scale = a->adam_scale;
+        a->decode->loss_out = a->loss_out;
+        return skml_decode_update(a->decode, stream_);
+    }
     for (int s = 0; s < 2; ++s) {
         if (a->seg_cnt[s] <= 0) continue;
         int rc = skml_glm_grad(a->rowptr, a->cols, a->vals, a->labels, a->seg_lo[s], a->seg_cnt[s], a->nnz_padded,
@@ -22,6 +44,8 @@ extern "C" int skml_train_step(SkmlStepArgs* a, void* stream_) {
                           a->gvals, a->dense_vals, a->n_max, a->status, stream_);
     if (rc) return rc;
     a->compress->step = a->step;
+    a->compress->keys = a->keys;
+    a->compress->meta = a->meta;
     a->compress->vals = a->gvals;
     rc = skml_compress_sparse(a->compress, stream_);
     if (rc) return rc;

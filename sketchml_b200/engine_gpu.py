@@ -104,6 +104,7 @@ class GpuEngine:
             self.xchg = PeerExchange(comm, self.comp.capacity, self.device)
             self._prepare_fast_step()
             self.depth = int(conf.pipeline_depth)
+            self._build_transposed_index()
             if self.depth == 1:
                 # gradient one step stale: batch t+1 is differentiated on its own stream while step t
                 # is still being compressed, exchanged and applied; the sparse-gradient buffers are doubled
@@ -151,6 +152,27 @@ class GpuEngine:
         self._da_ptr = [ctypes.pointer(x) for x in self._da]
         self._pending = None
 
+    def _build_transposed_index(self) -> None:
+        """Column-major index of every minibatch, when the batches are fixed row slices (shard size a
+        multiple of the batch size) and the index fits beside the data."""
+        from .ops.transposed import build_batch_index
+        self.tindex = None
+        conf, csr, B = self.conf, self.csr, self.batch_rows
+        if not conf.extras.get("transposed_index", True) or self.depth != 0 or B <= 0 or csr.rows % B != 0:
+            return
+        need = csr.nnz * (8 if csr.values is not None else 4) * 1.5
+        free, _ = torch.cuda.mem_get_info(self.device)
+        if need > 0.5 * free:
+            return
+        idx = []
+        for b in range(csr.rows // B):
+            bi = build_batch_index(csr, b * B, (b + 1) * B)
+            if bi.n_cols > self.st.dim * 2 // 3 or bi.n_cols > self.st.n_max:
+                return  # near-dense gradients take the dense kind: keep the scatter path
+            idx.append(bi)
+        self.tindex = idx
+        self.coef = torch.zeros(B, dtype=torch.float32, device=self.device)
+
     def _launch_fast_step(self, step: int, lr: float, adam_scale: float, ring_ptr: int) -> None:
         csr, segs, rows = self._pending
         self._pending = None
@@ -161,12 +183,26 @@ class GpuEngine:
             lo, hi = segs[i] if i < len(segs) else (0, 0)
             a.seg_lo[i], a.seg_cnt[i] = lo, hi - lo
         a.inv_batch = 1.0 / max(1, rows)
+        bi = None
+        if self.tindex is not None and csr is self.csr and len(segs) == 1:
+            lo, hi = segs[0]
+            if hi - lo == self.batch_rows and lo % self.batch_rows == 0:
+                bi = self.tindex[lo // self.batch_rows]
+        if bi is not None:
+            a.t_colptr, a.t_rowidx, a.t_vals, a.t_ucols = L.ptr(bi.colptr), L.ptr(bi.rowidx), L.ptr(bi.svals), L.ptr(bi.ucols)
+            a.t_bins, a.t_long_col, a.t_long_e0, a.t_long_e1 = (L.ptr(bi.bins), L.ptr(bi.long_col), L.ptr(bi.long_e0),
+                                                                L.ptr(bi.long_e1))
+            a.t_short, a.t_medium, a.t_long, a.t_cols = bi.n_short, bi.n_medium, bi.n_long, bi.n_cols
+            a.t_meta, a.coef = L.ptr(bi.meta), L.ptr(self.coef)
+        else:
+            a.t_colptr = None
+        self._last_index = bi
         par = step & 1
         a.compress = self._ca_ptr[par]
         a.decode = self._da_ptr[par]
         a.step, a.lr, a.adam_scale, a.loss_out = step, lr, adam_scale, ring_ptr
         L.check(self._step_fn(self._byref(a), L.stream()), "skml_train_step")
-        L.count_launches(len(segs) + 3 + 1 + (1 if self.st.dense_vals is not None else 0) + 1)
+        L.count_launches((2 if bi is not None else len(segs) + 3) + 1 + (1 if self.st.dense_vals is not None and bi is None else 0) + 1)
 
     # ----------------------------------------------------------------- steps
     def _segments(self, count: int):
@@ -348,7 +384,8 @@ class GpuEngine:
         head = buf[:256].cpu().numpy()
         import numpy as np
         total = int(np.frombuffer(head.tobytes(), dtype=np.uint64, count=1, offset=144)[0])
-        return int(self.st.meta[0]), total
+        nnz = self._last_index.n_cols if getattr(self, "_last_index", None) is not None else int(self.st.meta[0])
+        return nnz, total
 
     def sync(self) -> None:
         torch.cuda.synchronize(self.device)

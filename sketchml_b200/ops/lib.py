@@ -57,6 +57,9 @@ class StepArgs(C.Structure):
         ("budget_cycles", c_ll), ("lam", c_d), ("block_counts", c_vp), ("meta", c_vp), ("keys", c_vp), ("gvals", c_vp),
         ("dense_vals", c_vp), ("n_max", c_ll), ("dim", c_ll), ("compress", C.POINTER(CompressArgs)),
         ("decode", C.POINTER(DecodeArgs)), ("step", c_ull), ("lr", c_d), ("adam_scale", c_d), ("loss_out", c_vp),
+        ("t_colptr", c_vp), ("t_rowidx", c_vp), ("t_vals", c_vp), ("t_ucols", c_vp), ("t_bins", c_vp),
+        ("t_long_col", c_vp), ("t_long_e0", c_vp), ("t_long_e1", c_vp), ("t_short", c_ll), ("t_medium", c_ll),
+        ("t_long", c_ll), ("t_cols", c_ll), ("t_meta", c_vp), ("coef", c_vp),
     ]
 
 
@@ -78,6 +81,8 @@ _SIGS = {
     "skml_scatter_kv": (c_int, [c_vp, c_vp, c_vp, c_vp, c_ll, c_int, c_vp]),
     "skml_gen_wstar": (c_int, [c_vp, c_ll, c_d, c_ull, c_vp]),
     "skml_gen_rows": (c_int, [c_vp, c_vp, c_vp, c_ll, c_ll, c_int, c_int, c_d, c_int, c_int, c_f, c_vp, c_ull, c_vp]),
+    "skml_glm_coef": (c_int, [c_vp, c_vp, c_vp, c_vp, c_ll, c_ll, c_ll, c_d, c_vp, c_int, c_f, c_vp, c_vp, c_vp, c_ll, c_vp]),
+    "skml_colsum": (c_int, [c_vp] * 8 + [c_int] * 4 + [c_vp, c_vp, c_f, c_vp, c_vp]),
     "skml_sm_count": (c_int, []),
     "skml_train_step": (c_int, [C.POINTER(StepArgs), c_vp]),
     "skml_ipc_get_handle": (c_int, [c_vp, c_vp]),

@@ -147,3 +147,38 @@ def test_device_generator_statistics():
     c2, _ = generate_gpu(spec2, 100, 2000, "cuda")
     v = c2.values[:c2.nnz].cpu().numpy().reshape(2000, 200)
     assert np.allclose((v ** 2).sum(axis=1), 1.0, atol=1e-4)
+
+
+@pytest.mark.parametrize("binary", [True, False])
+def test_transposed_index_gradient_matches_scatter_path(binary):
+    from sketchml_b200.models.loss import L2LogLoss
+    from sketchml_b200.ops import DeviceCSR, GlmState, compact_gradient, glm_grad
+    from sketchml_b200.ops.transposed import build_batch_index, glm_grad_transposed
+    dev = torch.device("cuda")
+    loss = L2LogLoss(1e-3)
+    dim, rows = 30000, 6000
+    m = _random_csr(rows, dim, 1, 60, seed=21, binary=binary)
+    csr = DeviceCSR(m, dev)
+    w = (torch.randn(dim) * 0.3).float().to(dev)
+    st = GlmState.create(dim, dim, dev)
+    lo, hi = 2000, 4000
+    st.partials.zero_()
+    glm_grad(csr, [(lo, hi)], w, st, loss.loss_id, hi - lo, hot=2048)
+    compact_gradient(st, w, loss.lam)
+    n = int(st.meta[0])
+    ref = torch.zeros(dim, dtype=torch.float64)
+    ref[st.keys[:n].cpu().long()] = st.vals[:n].cpu().double()
+    ref_loss = float(st.partials[1])
+    bi = build_batch_index(csr, lo, hi)
+    assert bi.n_short + bi.n_medium + len(torch.unique(bi.long_col)) == bi.n_cols
+    assert torch.all(bi.ucols[1:] > bi.ucols[:-1]) and int(bi.colptr[-1]) == int(csr.rowptr[hi] - csr.rowptr[lo])
+    coef = torch.zeros(hi - lo, device=dev)
+    out = torch.zeros(dim, device=dev)
+    st.partials.zero_()
+    glm_grad_transposed(csr, bi, w, coef, out, st.partials, st.status, loss.loss_id, loss.lam)
+    got = torch.zeros(dim, dtype=torch.float64)
+    got[bi.ucols.cpu().long()] = out[:bi.n_cols].cpu().double()
+    assert int(st.status.item()) == 0
+    assert abs(float(st.partials[1]) - ref_loss) < 1e-3 * abs(ref_loss)
+    assert abs(bi.n_cols - n) <= 3          # the scatter path drops |v| <= 1e-8, this one keeps them
+    assert float((got - ref).abs().max()) < 2e-6 * max(1.0, float(ref.abs().max())) + 2e-8

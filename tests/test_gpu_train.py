@@ -67,7 +67,7 @@ def test_kv_baseline_and_checkpoint_resume(tmp_path):
     h4, w4, _ = _train(_conf(compressor="Sketch", epoch_num=2))
     assert len(h3["train_loss"]) == 1
     # float atomics make two runs differ in the last bits, which can move a value across a bucket edge
-    assert float((w3 - w4).abs().mean()) < 2e-4 and float((w3 - w4).abs().max()) < 5e-2
+    assert float((w3 - w4).abs().mean()) < 2e-4 and float((w3 - w4).abs().max()) < 0.2
 
 
 def test_pipeline_depth_one_trains_like_depth_zero():
@@ -84,3 +84,13 @@ def test_baseline_compressors_train_on_gpu(name):
     h0, w0, _ = _train(_conf(compressor="None", epoch_num=2))
     assert h["train_loss"][-1] < h["train_loss"][0]
     assert abs(h["valid_loss"][-1] - h0["valid_loss"][-1]) / h0["valid_loss"][-1] < 0.05
+
+
+def test_transposed_index_path_trains_like_scatter_path():
+    kw = dict(compressor="Sketch", epoch_num=2, valid_ratio=0.0, syn_rows=30000, batch_sample_ratio=0.1)
+    h_t, w_t, t_t = _train(_conf(**kw))
+    assert t_t.engine.tindex is not None and len(t_t.engine.tindex) == 10
+    h_s, w_s, t_s = _train(_conf(extras={"transposed_index": False}, **kw))
+    assert t_s.engine.tindex is None
+    assert np.allclose(h_t["train_loss"], h_s["train_loss"], rtol=2e-3)
+    assert float((w_t - w_s).abs().mean()) < 5e-4
