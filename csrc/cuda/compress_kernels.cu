@@ -87,9 +87,13 @@ struct Layout {
     unsigned long long bytes_g[SKML_MAX_GROUPS];
     unsigned long long table_off[SKML_MAX_GROUPS], flag_off[SKML_MAX_GROUPS], delta_off[SKML_MAX_GROUPS],
         restart_off[SKML_MAX_GROUPS], tab32_off[SKML_MAX_GROUPS];
-    unsigned int base_rank[SKML_MAX_GROUPS];
+    unsigned int base_rank[SKML_MAX_GROUPS];       // the same three for the block as a whole
     unsigned long long base_bytes[SKML_MAX_GROUPS];
-    int base_prev[SKML_MAX_GROUPS];
+    int base_prev[SKML_MAX_GROUPS];                // -1 = no key of the group before this block
+    // starting rank / delta-byte offset / previous key of every group for each warp of this block
+    unsigned int vbase_rank[SKML_WARPS][SKML_MAX_GROUPS];
+    unsigned long long vbase_bytes[SKML_WARPS][SKML_MAX_GROUPS];
+    int vbase_prev[SKML_WARPS][SKML_MAX_GROUPS];
     unsigned char hash_ids[SKML_MAX_GROUPS][8];
     unsigned long long col_magic[SKML_MAX_GROUPS];  // ceil(2^64 / col) for the division-free modulo
     unsigned long long off_bv, off_gt, off_flags, off_restart, off_tables, off_deltas, total_bytes;
@@ -111,7 +115,7 @@ static WsLayout ws_layout(long long n_max, long long q, long long G, long long r
     L.run_cnt = o; o += al256(grid * 4);
     L.run_w = o; o += al256(grid * 8);
     L.splits_raw = o; o += al256(q * 4);
-    L.stats = o; o += al256(grid * SKML_MAX_GROUPS * (long long)sizeof(CtaStat));
+    L.stats = o; o += al256(grid * (SKML_WARPS + 1) * SKML_MAX_GROUPS * (long long)sizeof(CtaStat));
     L.bins = o; o += al256(n_max * 2);
     L.tables_cap = rows * ((long long)(col_ratio * (double)n_max) + 2 + G) + 64;
     L.tables = o; o += al256(L.tables_cap * 4);
@@ -163,14 +167,6 @@ struct Smem {
     unsigned int wcnt[SKML_WARPS][SKML_MAX_GROUPS];
     unsigned int wbytes[SKML_WARPS][SKML_MAX_GROUPS];
     int cin[SKML_WARPS][SKML_MAX_GROUPS];
-    unsigned int wexc[SKML_WARPS][SKML_MAX_GROUPS];
-    unsigned int wexb[SKML_WARPS][SKML_MAX_GROUPS];
-    int carry_key[SKML_MAX_GROUPS];
-    int first_key[SKML_MAX_GROUPS];
-    unsigned int cnt[SKML_MAX_GROUPS];
-    unsigned long long bytes[SKML_MAX_GROUPS];
-    unsigned int tile_rank[SKML_MAX_GROUPS];
-    unsigned long long tile_bytes[SKML_MAX_GROUPS];
     unsigned long long unit_prefix[SKML_MAX_GROUPS + 1];
     int flag;
 };
@@ -522,37 +518,44 @@ __device__ __forceinline__ float bucket_value(const Smem& s, int b) {
 // Element passes. PACK = false: bucketize + per-block statistics (S3).
 // PACK = true: ranks, byte offsets, flag / delta / restart writes, sketch insert (S4).
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ long long chunk_size(long long n) {
-    long long c = (n + gridDim.x - 1) / gridDim.x;
-    return (c + SKML_BLOCK - 1) / SKML_BLOCK * SKML_BLOCK;
+
+// The unit of work is a warp: warp w of block b is "virtual block" b * 32 + w and owns one
+// contiguous slice of the keys. Everything inside a slice is warp-synchronous (no block barrier):
+// lane g keeps the running state of group g (last key, count, delta bytes) in registers, and the
+// lanes that hold a group's first / last key of an iteration hand them to lane g through a few
+// words of shared memory.
+__device__ __forceinline__ long long vslice_size(long long n) {
+    const long long nv = (long long)gridDim.x * SKML_WARPS;
+    long long c = (n + nv - 1) / nv;
+    return (c + 31) / 32 * 32;
 }
 
 template <bool PACK>
 __device__ void element_pass(const CP& p, Smem& s, long long n) {
     const int G = p.G;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const long long chunk = chunk_size(n);
-    long long lo = (long long)blockIdx.x * chunk, hi = lo + chunk;
+    const long long sub = vslice_size(n);
+    const long long vb = (long long)blockIdx.x * SKML_WARPS + warp;
+    long long lo = vb * sub, hi = lo + sub;
+    if (lo > n) lo = n;
     if (hi > n) hi = n;
-    if (threadIdx.x < SKML_MAX_GROUPS) {
-        s.carry_key[threadIdx.x] = -1;
-        s.first_key[threadIdx.x] = -1;
-        s.cnt[threadIdx.x] = 0;
-        s.bytes[threadIdx.x] = 0;
-        s.tile_rank[threadIdx.x] = 0;
-        s.tile_bytes[threadIdx.x] = 0;
-    }
-    __syncthreads();
-    // role of the first G warps: warp g owns group g, its lane w stands for warp w of the block,
-    // so cross-warp prefixes of one group are warp shuffles
-    const int wg_g = warp, wg_w = lane;
-    const bool wg_on = warp < G;
     const Layout& L = s.lay;
     const int zero = s.qi.zero_idx;
     const bool overflow = PACK && L.overflow;
-
-    for (long long tlo = lo; tlo < hi; tlo += SKML_BLOCK) {
-        const long long i = tlo + threadIdx.x;
+    // state of group `lane` (lanes >= G idle)
+    int carry = -1, first = -1;
+    unsigned int cnt_g = 0;
+    unsigned long long bytes_g = 0;
+    unsigned int rank_g = 0;            // PACK: rank of the group's next key inside the payload
+    unsigned long long boff_g = 0;      // PACK: byte offset of the group's next delta
+    int base_prev_g = 0;                // PACK: last key of the group before this slice
+    if (PACK && lane < G) {
+        rank_g = L.vbase_rank[warp][lane];
+        boff_g = L.vbase_bytes[warp][lane];
+        base_prev_g = L.vbase_prev[warp][lane];
+    }
+    for (long long i0 = lo; i0 < hi; i0 += 32) {
+        const long long i = i0 + lane;
         const bool valid = i < hi;
         int key = 0, bin = 0, g = 63;
         if (valid) {
@@ -565,37 +568,21 @@ __device__ void element_pass(const CP& p, Smem& s, long long n) {
             }
             g = skml_group_of(bin, s.qi.edges, G);
         }
-        if (wg_on) {
-            s.wlast[wg_w][wg_g] = -1;
-            s.wcnt[wg_w][wg_g] = 0;
-            s.wbytes[wg_w][wg_g] = 0;
-        }
-        __syncthreads();
+        s.wcnt[warp][lane] = 0;  // slot of group `lane`: filled below if the group occurs in this iteration
+        __syncwarp();
         const unsigned int peers = __match_any_sync(0xFFFFFFFFu, g);
         const unsigned int lower = peers & lanemask_lt();
         const int prev_lane = lower ? 31 - __clz(lower) : 0;
         const int prev_in_warp = __shfl_sync(0xFFFFFFFFu, key, prev_lane);
-        const bool last_in_warp = valid && (peers >> lane) == 1u;
-        if (last_in_warp) s.wlast[warp][g] = key;
-        __syncthreads();
-        int role_carry = -1;  // last key of group wg_g before warp wg_w (role threads)
-        if (wg_on) {
-            const int mine = s.wlast[wg_w][wg_g];
-            const unsigned int has = __ballot_sync(0xFFFFFFFFu, mine >= 0) & lanemask_lt();
-            const int src = has ? 31 - __clz(has) : 0;
-            const int from = __shfl_sync(0xFFFFFFFFu, mine, src);
-            role_carry = has ? from : s.carry_key[wg_g];
-            s.cin[wg_w][wg_g] = role_carry;
-        }
-        __syncthreads();
-        int prev = -1;
-        if (valid) prev = lower ? prev_in_warp : s.cin[warp][g];
+        const int gsrc = valid ? g : 0;
+        const int carry_of_g = __shfl_sync(0xFFFFFFFFu, carry, gsrc);
+        const int prev = valid ? (lower ? prev_in_warp : carry_of_g) : -1;
         int w = 0;
         unsigned int delta = 0;
+        const int bp = PACK ? __shfl_sync(0xFFFFFFFFu, base_prev_g, gsrc) : 0;
         if (valid) {
             if (PACK) {
-                const int pk = prev >= 0 ? prev : L.base_prev[g];
-                delta = (unsigned int)(key - pk);
+                delta = (unsigned int)(key - (prev >= 0 ? prev : bp));
                 w = skml_delta_bytes(delta);
             } else if (prev >= 0) {
                 w = skml_delta_bytes((unsigned int)(key - prev));
@@ -604,53 +591,21 @@ __device__ void element_pass(const CP& p, Smem& s, long long n) {
         const unsigned int b1 = __ballot_sync(0xFFFFFFFFu, w == 1);
         const unsigned int b2 = __ballot_sync(0xFFFFFFFFu, w == 2);
         const unsigned int b4 = __ballot_sync(0xFFFFFFFFu, w == 4);
-        if (!PACK) {
-            if (valid) {
-                if (prev < 0) s.first_key[g] = key;
-                if (lower == 0) {  // first lane of its group in this warp adds the warp's share
-                    atomicAdd(&s.cnt[g], (unsigned int)__popc(peers));
-                    const unsigned long long by = __popc(peers & b1) + 2 * __popc(peers & b2) + 4 * __popc(peers & b4);
-                    if (by) atomicAdd(&s.bytes[g], by);
-                }
-            }
-            // the last key of every group is carried into the next tile (the next tile's first
-            // barrier orders this write against its readers)
-            if (wg_on && wg_w == SKML_WARPS - 1) {
-                const int k2 = s.wlast[wg_w][wg_g];
-                s.carry_key[wg_g] = k2 >= 0 ? k2 : role_carry;
-            }
-            continue;
-        }
-        // ---- PACK ----
         const unsigned int r_w = __popc(lower);
         const unsigned int bw = __popc(lower & b1) + 2 * __popc(lower & b2) + 4 * __popc(lower & b4);
-        if (last_in_warp) {
-            s.wcnt[warp][g] = r_w + 1;
-            s.wbytes[warp][g] = bw + (unsigned int)w;
-        }
-        __syncthreads();
-        unsigned int role_cnt = 0, role_bytes = 0;
-        if (wg_on) {  // exclusive prefix over the warps, once per (warp, group)
-            const unsigned int c0 = s.wcnt[wg_w][wg_g], y0 = s.wbytes[wg_w][wg_g];
-            unsigned int ci = c0, yi = y0;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const unsigned int tc = __shfl_up_sync(0xFFFFFFFFu, ci, o);
-                const unsigned int ty = __shfl_up_sync(0xFFFFFFFFu, yi, o);
-                if (lane >= o) {
-                    ci += tc;
-                    yi += ty;
-                }
+        const unsigned int rank_of_g = __shfl_sync(0xFFFFFFFFu, rank_g, gsrc);
+        const unsigned long long boff_of_g = __shfl_sync(0xFFFFFFFFu, boff_g, gsrc);
+        if (valid) {
+            if (lower == 0) {  // first lane of its group in this iteration
+                s.wcnt[warp][g] = (unsigned int)__popc(peers);
+                s.wbytes[warp][g] = __popc(peers & b1) + 2 * __popc(peers & b2) + 4 * __popc(peers & b4);
+                s.cin[warp][g] = key;  // candidate for "first key of the group in this slice"
             }
-            role_cnt = ci - c0;
-            role_bytes = yi - y0;
-            s.wexc[wg_w][wg_g] = role_cnt;
-            s.wexb[wg_w][wg_g] = role_bytes;
+            if ((peers >> lane) == 1u) s.wlast[warp][g] = key;  // last lane of its group
         }
-        __syncthreads();
-        if (valid && !overflow) {
-            const unsigned long long prank = (unsigned long long)L.base_rank[g] + s.tile_rank[g] + s.wexc[warp][g] + r_w;
-            const unsigned long long boff = L.base_bytes[g] + s.tile_bytes[g] + s.wexb[warp][g] + bw;
+        if (PACK && valid && !overflow) {
+            const unsigned long long prank = (unsigned long long)rank_of_g + r_w;
+            const unsigned long long boff = boff_of_g + bw;
             // flags: (w - 1) most significant bit first at stream bits 2p, 2p+1
             const unsigned int fv = (unsigned int)(w - 1);
             if (fv) {
@@ -676,26 +631,67 @@ __device__ void element_pass(const CP& p, Smem& s, long long n) {
             for (int r = 0; r < p.rows; ++r)
                 atomicMin(tab + (long long)r * col + skml_hash_fast(L.hash_ids[g][r], key, kd, col, L.col_magic[g]), cell);
         }
-        __syncthreads();  // all readers of tile_rank / tile_bytes are done
-        if (wg_on && wg_w == SKML_WARPS - 1) {
-            const int k2 = s.wlast[wg_w][wg_g];
-            s.carry_key[wg_g] = k2 >= 0 ? k2 : role_carry;
-            s.tile_rank[wg_g] += role_cnt + s.wcnt[wg_w][wg_g];
-            s.tile_bytes[wg_g] += role_bytes + s.wbytes[wg_w][wg_g];
+        __syncwarp();
+        if (lane < G) {
+            const unsigned int c = s.wcnt[warp][lane];
+            if (c) {
+                if (first < 0 && carry < 0) first = s.cin[warp][lane];
+                carry = s.wlast[warp][lane];
+                cnt_g += c;
+                bytes_g += s.wbytes[warp][lane];
+                rank_g += c;
+                boff_g += s.wbytes[warp][lane];
+            }
         }
+        __syncwarp();
     }
     if (!PACK) {
-        __syncthreads();
-        if (threadIdx.x < G) {
+        // Per-warp statistics go to global memory (rows gridDim.x.. of the table, read again by
+        // compute_layout); the block's own summary (rows 0..gridDim.x-1) is chained from them here.
+        if (lane < G) {
             CtaStat st;
-            st.count = s.cnt[threadIdx.x];
-            st.first_key = s.first_key[threadIdx.x];
-            st.last_key = s.carry_key[threadIdx.x];
+            st.count = cnt_g;
+            st.first_key = first;
+            st.last_key = carry;
             st.pad = 0;
-            st.bytes = s.bytes[threadIdx.x];
+            st.bytes = bytes_g;
             st.pad2 = 0;
-            p.stats[(long long)blockIdx.x * SKML_MAX_GROUPS + threadIdx.x] = st;
+            p.stats[((long long)gridDim.x + vb) * SKML_MAX_GROUPS + lane] = st;
+            s.wcnt[warp][lane] = cnt_g;
+            s.wbytes[warp][lane] = (unsigned int)bytes_g;
+            s.cin[warp][lane] = first;
+            s.wlast[warp][lane] = carry;
         }
+        __syncthreads();
+        if (warp < G) {
+            const int g = warp;
+            const unsigned int c = s.wcnt[lane][g];
+            const int fk = s.cin[lane][g], lk = s.wlast[lane][g];
+            const unsigned int nonempty = __ballot_sync(0xFFFFFFFFu, c > 0);
+            const unsigned int lowm = nonempty & lanemask_lt();
+            const int before = __shfl_sync(0xFFFFFFFFu, lk, lowm ? 31 - __clz(lowm) : 0);
+            unsigned long long b = s.wbytes[lane][g];
+            if (c > 0 && lowm) b += (unsigned long long)skml_delta_bytes((unsigned int)(fk - before));
+            unsigned int csum = c;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                csum += __shfl_xor_sync(0xFFFFFFFFu, csum, o);
+                b += __shfl_xor_sync(0xFFFFFFFFu, b, o);
+            }
+            const int bf = __shfl_sync(0xFFFFFFFFu, fk, nonempty ? __ffs(nonempty) - 1 : 0);
+            const int bl = __shfl_sync(0xFFFFFFFFu, lk, nonempty ? 31 - __clz(nonempty) : 0);
+            if (lane == 0) {
+                CtaStat st;
+                st.count = csum;
+                st.first_key = nonempty ? bf : -1;
+                st.last_key = nonempty ? bl : -1;
+                st.pad = 0;
+                st.bytes = b;
+                st.pad2 = 0;
+                p.stats[(long long)blockIdx.x * SKML_MAX_GROUPS + g] = st;
+            }
+        }
+        __syncthreads();
     }
 }
 
@@ -729,9 +725,6 @@ __device__ void compute_layout(const CP& p, Smem& s, long long n) {
         unsigned int run_cnt = 0;
         unsigned long long run_bytes = 0;
         int carry_last = -1;
-        unsigned int my_rank = 0;
-        unsigned long long my_bytes = 0;
-        int my_prev = 0;
         for (int base = 0; base < nb; base += 32) {
             const int c = base + lane;
             CtaStat st;
@@ -754,12 +747,9 @@ __device__ void compute_layout(const CP& p, Smem& s, long long n) {
                 if (lane >= o) { ic += tc; ib += tb; }
             }
             if (c == (int)blockIdx.x) {
-                my_rank = run_cnt + ic - st.count;
-                my_bytes = run_bytes + ib - full;
-                my_prev = before >= 0 ? before : 0;
-                L.base_rank[g] = my_rank;
-                L.base_bytes[g] = my_bytes;
-                L.base_prev[g] = my_prev;
+                L.base_rank[g] = run_cnt + ic - st.count;
+                L.base_bytes[g] = run_bytes + ib - full;
+                L.base_prev[g] = before;
             }
             run_cnt += __shfl_sync(0xFFFFFFFFu, ic, 31);
             run_bytes += __shfl_sync(0xFFFFFFFFu, ib, 31);
@@ -771,6 +761,28 @@ __device__ void compute_layout(const CP& p, Smem& s, long long n) {
         if (lane == 0) {
             L.n_g[g] = run_cnt;
             L.bytes_g[g] = run_bytes;
+        }
+        __syncwarp();
+        // second level: the 32 warps of this block, lane = warp
+        {
+            const CtaStat st = p.stats[((long long)gridDim.x + (long long)blockIdx.x * SKML_WARPS + lane) * SKML_MAX_GROUPS + g];
+            const unsigned int nonempty = __ballot_sync(0xFFFFFFFFu, st.count > 0);
+            const unsigned int lowm = nonempty & lanemask_lt();
+            const int prev_last = __shfl_sync(0xFFFFFFFFu, st.last_key, lowm ? 31 - __clz(lowm) : 0);
+            const int before = lowm ? prev_last : L.base_prev[g];
+            unsigned long long full = st.bytes;
+            if (st.count > 0) full += (unsigned long long)skml_delta_bytes((unsigned int)(st.first_key - (before >= 0 ? before : 0)));
+            unsigned int ic = st.count;
+            unsigned long long ib = full;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                unsigned int tc = __shfl_up_sync(0xFFFFFFFFu, ic, o);
+                unsigned long long tb = __shfl_up_sync(0xFFFFFFFFu, ib, o);
+                if (lane >= o) { ic += tc; ib += tb; }
+            }
+            L.vbase_rank[lane][g] = L.base_rank[g] + ic - st.count;
+            L.vbase_bytes[lane][g] = L.base_bytes[g] + ib - full;
+            L.vbase_prev[lane][g] = before >= 0 ? before : 0;
         }
     }
     __syncthreads();

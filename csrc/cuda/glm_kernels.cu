@@ -186,30 +186,31 @@ glm_rows_kernel(const long long* __restrict__ rowptr, const int* __restrict__ co
 #pragma unroll
                 for (int u = 0; u < GRAD_RPI; ++u) sum[u] += __shfl_xor_sync(0xFFFFFFFFu, sum[u], o);
             }
-            float coef[GRAD_RPI];
+            // Loss and coefficient of the GRAD_RPI rows are evaluated once, by lanes 0..GRAD_RPI-1 in
+            // parallel (lane u owns row rb + u); the scatter mode then broadcasts the coefficients.
+            float pre_mine = sum[0];
 #pragma unroll
-            for (int u = 0; u < GRAD_RPI; ++u) {
-                coef[u] = 0.f;
-                if (rb + u >= nrows) continue;
-                const float pre = sum[u];
-                const float y = s_lab[rb + u];
+            for (int u = 1; u < GRAD_RPI; ++u) pre_mine = lane == u ? sum[u] : pre_mine;
+            float coef_mine = 0.f;
+            if (lane < GRAD_RPI && rb + lane < nrows) {
+                const float y = s_lab[rb + lane];
+                loss_sum += (double)glm_loss(loss_id, pre_mine, y);
                 if (MODE == 0 || MODE == 2) {
-                    coef[u] = -glm_grad(loss_id, pre, y) * inv_batch;
-                    if (lane == u) {
-                        loss_sum += (double)glm_loss(loss_id, pre, y);
-                        if (MODE == 2) margins[r0 - row_lo + rb + u] = coef[u];  // coefficient per row, no scatter
-                    }
-                } else if (lane == u) {
-                    loss_sum += (double)glm_loss(loss_id, pre, y);
-                    const float z = pre * y;
+                    coef_mine = -glm_grad(loss_id, pre_mine, y) * inv_batch;
+                    if (MODE == 2) margins[r0 - row_lo + rb + lane] = coef_mine;  // coefficient per row, no scatter
+                } else {
+                    const float z = pre_mine * y;
                     if (z > 0.f) {
-                        if (pre > 0.f) ++tp; else ++tn;
+                        if (pre_mine > 0.f) ++tp; else ++tn;
                     } else if (z < 0.f) {
-                        if (pre > 0.f) ++fp; else ++fn;
+                        if (pre_mine > 0.f) ++fp; else ++fn;
                     }
-                    if (margins) margins[r0 - row_lo + rb + u] = pre;
+                    if (margins) margins[r0 - row_lo + rb + lane] = pre_mine;
                 }
             }
+            float coef[GRAD_RPI];
+#pragma unroll
+            for (int u = 0; u < GRAD_RPI; ++u) coef[u] = MODE == 0 ? __shfl_sync(0xFFFFFFFFu, coef_mine, u) : 0.f;
             if (MODE == 0) {
                 for (int off = lane; off - lane < maxlen; off += 32) {
                     int c[GRAD_RPI];
