@@ -167,6 +167,7 @@ def main():
     clocks = sampler.stop()
     eng.check()
     nnz, pbytes = eng.payload_stats(trainer.step - 1)
+    stages = eng.stage_times_us()
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -196,7 +197,7 @@ def main():
                         "ratio_vs_8B_per_nnz": 8.0 * nnz / max(pbytes, 1), "ratio_vs_12B_per_nnz": 12.0 * nnz / max(pbytes, 1)},
             "loss_first_last": [float(losses[0, 1] / max(float(losses[0, 0]), 1)),
                                 float(losses[-1, 1] / max(float(losses[-1, 0]), 1))] if len(losses) else None,
-            "datagen_s": t_gen,
+            "datagen_s": t_gen, "stage_us_last_step_rank0": stages,
         }
         if e2e is not None:
             out["e2e"] = e2e

@@ -105,6 +105,21 @@ int skml_colsum(const int* colptr, const int* rowidx, const float* svals, const 
                 int n_cols, const float* coef, const float* w, float lambda, float* out, void* stream);
 int skml_sm_count();
 
+// FixedPoint baseline compressor: b-bit sign + magnitude codes (2 <= bits < 30), 8 values per
+// `bits` bytes, most significant bit first in java.util.BitSet order. `scratch` holds
+// skml_fixedpoint_scratch_bytes() bytes; `norm_out` receives the L2 norm the codes are relative to.
+long long skml_fixedpoint_scratch_bytes();
+long long skml_fixedpoint_code_bytes(long long n, int bits);
+int skml_fixedpoint_pack(const float* vals, const long long* n_ptr, long long n_max, int bits,
+                         unsigned long long seed, double* scratch, unsigned char* codes, double* norm_out,
+                         void* stream);
+// Decodes `lists` code streams (list l at codes + l * code_stride, keys + l * key_stride, counts[l]
+// entries, norms[l]); adds the values into acc[key] when acc is given and stores them to
+// vals_out[l * key_stride + i] when vals_out is given.
+int skml_fixedpoint_unpack_scatter(float* acc, const int* keys, const unsigned char* codes, const double* norms,
+                                   const long long* counts, long long key_stride, long long code_stride, int lists,
+                                   int bits, float* vals_out, void* stream);
+
 // Peer memory (one process per GPU): CUDA IPC handles of a cudaMalloc'ed region.
 int skml_ipc_get_handle(void* dev_ptr, unsigned char* handle64);
 int skml_ipc_open_handle(const unsigned char* handle64, void** dev_ptr);

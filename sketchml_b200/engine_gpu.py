@@ -119,6 +119,10 @@ class GpuEngine:
             self.kv_vals = torch.zeros((comm.world, bound), dtype=torch.float32, device=self.device)
             self.kv_counts = torch.zeros(comm.world, dtype=torch.int64, device=self.device)
             self.kv_acc = torch.zeros(dim, dtype=torch.float32, device=self.device)
+            self.fp_codec = None
+            if self.value_quant == C.COMPRESSOR_FIXED_POINT:
+                from .ops.baseline_quant import FixedPointCodec
+                self.fp_codec = FixedPointCodec(bound, conf.fixed_point_bit_num, comm.world, self.device)
         else:
             self.dense_sum = torch.zeros(dim, dtype=torch.float32, device=self.device)
 
@@ -296,6 +300,10 @@ class GpuEngine:
                 self.check()
         if self.mode != "sketch" and self.value_quant:
             self._quantize_values(step)
+        if self.mode == "nccl_kv" and self.fp_codec is not None:
+            self._exchange_fixed_point(step, lr, am, av, adam_scale, ring)
+            self.batch_index += 1
+            return
         if self.mode == "sketch":
             pass
         elif self.mode == "nccl_dense":
@@ -322,9 +330,32 @@ class GpuEngine:
             ring.copy_(st.partials)
         self.batch_index += 1
 
+    def _exchange_fixed_point(self, step, lr, am, av, adam_scale, ring) -> None:
+        """FixedPoint baseline: packed b-bit codes and raw keys are what crosses NVLink."""
+        st, comm, m, fp = self.st, self.t.comm, self.t.model, self.fp_codec
+        fp.pack(st.vals, st.meta[:1], self._fp_seed(step))
+        if comm.world > 1:
+            dist.all_gather_into_tensor(self.kv_keys.view(-1), st.keys)
+            dist.all_gather_into_tensor(fp.all_codes.view(-1), fp.codes)
+            dist.all_gather_into_tensor(self.kv_counts, st.meta[:1])
+            dist.all_gather_into_tensor(fp.all_norms, fp.norm)
+            dist.all_reduce(st.partials)
+            fp.unpack(self.kv_keys, fp.all_codes, fp.all_norms, self.kv_counts, comm.world, acc=self.kv_acc)
+            update_dense(m.weights, self.kv_acc, 1.0 / comm.world, lr, am, av, adam_scale, sparse_only=True)
+            self.kv_acc.zero_()
+        else:
+            fp.unpack(st.keys, fp.codes, fp.norm, st.meta[:1], 1, vals_out=st.vals)
+            update_sparse(m.weights, st.keys, st.vals, st.meta, self.n_max, 1.0, lr, am, av, adam_scale)
+        ring.copy_(st.partials)
+
+    def _fp_seed(self, step: int) -> int:
+        return self.conf.seed * 1315423911 + step * 8191 + self.t.comm.rank
+
     def _quantize_values(self, step: int) -> None:
         from .ops.baseline_quant import fixed_point_roundtrip, zipml_roundtrip
         st, conf = self.st, self.conf
+        if getattr(self, "fp_codec", None) is not None:
+            return  # sparse lists are quantized by the pack kernel
         targets = [(st.vals, st.meta[0])]
         if st.dense_vals is not None:
             targets.append((st.dense_vals, torch.where(st.meta[1] == 2, st.meta[0] * 0 + st.dim, st.meta[0] * 0)))
@@ -386,6 +417,19 @@ class GpuEngine:
         total = int(np.frombuffer(head.tobytes(), dtype=np.uint64, count=1, offset=144)[0])
         nnz = self._last_index.n_cols if getattr(self, "_last_index", None) is not None else int(self.st.meta[0])
         return nnz, total
+
+    def stage_times_us(self):
+        """Durations of the stages of this rank's last fused compress and decode launches, from the
+        `globaltimer` stamps the kernels leave in their workspaces (synchronises). Compress:
+        summary, split query, bucketize + statistics, pack + sketch insert, narrow + publish.
+        Decode: prepare (including the wait for the peers' payloads), accumulate, claims."""
+        if self.mode != "sketch":
+            return None
+        import numpy as np
+        c = self.comp.workspace[:256].cpu().numpy().view(np.int64)[8:14]
+        d = self.dec.workspace[:256].cpu().numpy().view(np.int64)[8:12]
+        return {"compress": [float(c[i + 1] - c[i]) / 1e3 for i in range(5)],
+                "decode": [float(d[i + 1] - d[i]) / 1e3 for i in range(3)]}
 
     def sync(self) -> None:
         torch.cuda.synchronize(self.device)

@@ -1,11 +1,14 @@
-"""Device versions of the two baseline value quantizers (torch ops on the GPU).
+"""Device versions of the two baseline value quantizers.
 
-They turn the values of a sparse gradient into the values the reference's baseline
-compressors would decode to, so that `compressor=FixedPoint` and `compressor=Zip` train on
-GPUs with the same numerics as on the host engine. Keys travel raw, as in the reference
-(ml/gradient/FixedPointGradient.scala:27-30, ml/gradient/ZipGradient.scala:27-30); the
-values are exchanged dequantized (fp32) through the raw key/value all-gather path, so the
-byte saving of the packed codes is not realised on the wire here.
+FixedPoint: `FixedPointCodec` wraps the pack / unpack kernels (csrc/cuda/baseline_kernels.cu):
+the b-bit codes are what travels between ranks (4 + b/8 bytes per non-zero), keys raw as in
+the reference (ml/gradient/FixedPointGradient.scala:27-30). `fixed_point_roundtrip` is the
+same arithmetic in torch ops, kept for the dense gradient kind.
+
+Zip: `zipml_roundtrip` (torch ops) turns the values into the values the reference's ZipML
+compressor would decode to (keys raw, ml/gradient/ZipGradient.scala:27-30); the values are
+exchanged dequantized (fp32) through the raw key/value all-gather path, so the byte saving of
+its packed codes is not realised on the wire.
 
 Reference: ml/gradient/FixedPointGradient.scala:39-75 (sign + (b-1)-bit magnitude of
 floor(|v| / ||v||_2 * max) + Bernoulli(1/2)), ml/gradient/ZipGradient.scala:70-129 (sorted
@@ -15,6 +18,44 @@ bin_num/2 adjacent pairs with the largest squared error, bucket midpoints as dec
 from __future__ import annotations
 
 import torch
+
+from . import lib as L
+
+
+class FixedPointCodec:
+    """Packs the values of a sparse gradient of up to ``n_max`` entries into ``bits``-bit codes
+    and decodes several ranks' (keys, codes, norm) lists back into a dense sum."""
+
+    def __init__(self, n_max: int, bits: int, world: int, device):
+        if not 2 <= bits < 30:
+            raise ValueError(f"Bit num out of range: {bits}")
+        self.lib = L.lib()
+        self.n_max, self.bits, self.world = int(n_max), int(bits), int(world)
+        self.code_stride = (int(self.lib.skml_fixedpoint_code_bytes(self.n_max, bits)) + 15) // 16 * 16
+        self.scratch = torch.zeros(int(self.lib.skml_fixedpoint_scratch_bytes()) // 8, dtype=torch.float64, device=device)
+        self.codes = torch.zeros(self.code_stride, dtype=torch.uint8, device=device)
+        self.norm = torch.zeros(1, dtype=torch.float64, device=device)
+        if world > 1:
+            self.all_codes = torch.zeros((world, self.code_stride), dtype=torch.uint8, device=device)
+            self.all_norms = torch.zeros(world, dtype=torch.float64, device=device)
+
+    def pack(self, vals: torch.Tensor, n: torch.Tensor, seed: int) -> None:
+        """vals[:n] -> self.codes, self.norm (n: device int64 scalar / 1-element view)."""
+        L.check(self.lib.skml_fixedpoint_pack(L.ptr(vals), L.ptr(n), self.n_max, self.bits, int(seed) & (2 ** 64 - 1),
+                                              L.ptr(self.scratch), L.ptr(self.codes), L.ptr(self.norm), L.stream()),
+                "skml_fixedpoint_pack")
+        L.count_launches(2)
+
+    def unpack(self, keys: torch.Tensor, codes: torch.Tensor, norms: torch.Tensor, counts: torch.Tensor, lists: int,
+               acc: torch.Tensor = None, vals_out: torch.Tensor = None) -> None:
+        L.check(self.lib.skml_fixedpoint_unpack_scatter(L.ptr(acc), L.ptr(keys), L.ptr(codes), L.ptr(norms), L.ptr(counts),
+                                                        self.n_max, self.code_stride, lists, self.bits, L.ptr(vals_out),
+                                                        L.stream()), "skml_fixedpoint_unpack_scatter")
+        L.count_launches(1)
+
+    def wire_bytes(self, n: int) -> int:
+        """Bytes one rank contributes for n non-zeros: raw keys, codes, count and norm."""
+        return 4 * n + (n + 7) // 8 * self.bits + 16
 
 
 def fixed_point_roundtrip(vals: torch.Tensor, n: torch.Tensor, num_bits: int, seed: int) -> None:

@@ -227,3 +227,38 @@ def test_non_finite_values_are_reported():
     # the compressor stays usable afterwards
     vals[17] = 1e-3
     comp.compress_local(torch.from_numpy(keys).cuda(), torch.from_numpy(vals).cuda())
+
+
+@pytest.mark.parametrize("bits", [8, 5, 13, 16])
+def test_fixed_point_pack_matches_oracle(bits):
+    """The pack kernel's code stream against the CPU oracle's BitSet words, and the unpack kernel
+    against the oracle's decode (the two norms differ in summation order, so a code may differ by
+    one where |v| / norm * max sits on an integer)."""
+    from sketchml_b200.compress import oracle
+    from sketchml_b200.ops.baseline_quant import FixedPointCodec
+    n, n_max, seed = 100003, 120000, 991
+    g = torch.Generator().manual_seed(bits)
+    vals = (torch.randn(n_max, generator=g) * 0.01).float()
+    keys = torch.sort(torch.randperm(1_000_000, generator=g)[:n_max]).values.int()
+    dv, dk = vals.cuda(), keys.cuda()
+    cnt = torch.tensor([n], dtype=torch.int64, device="cuda")
+    fp = FixedPointCodec(n_max, bits, 1, "cuda")
+    fp.pack(dv, cnt, seed)
+    out = torch.zeros(n_max, dtype=torch.float32, device="cuda")
+    acc = torch.zeros(1_000_000, dtype=torch.float32, device="cuda")
+    fp.unpack(dk, fp.codes, fp.norm, cnt, 1, acc=acc, vals_out=out)
+    torch.cuda.synchronize()
+    code = oracle.fixed_point_encode(vals[:n].double().numpy(), bits, seed)
+    assert abs(float(fp.norm.item()) - code["norm"]) <= 1e-12 * code["norm"]
+    want = np.asarray(code["words"], dtype=np.uint64).view(np.uint8)
+    nbytes = (n * bits + 7) // 8
+    got = fp.codes[:nbytes].cpu().numpy()
+    assert (got != want[:nbytes]).mean() < 1e-4
+    dec = oracle.fixed_point_decode(code)
+    step = code["norm"] / ((1 << (bits - 1)) - 1)
+    diff = np.abs(out[:n].cpu().numpy().astype(np.float64) - dec)
+    assert diff.max() <= step * 1.0001 and (diff > 1e-7 * code["norm"]).mean() < 1e-4
+    ref = torch.zeros(1_000_000, dtype=torch.float64)
+    ref[keys[:n].long()] = torch.from_numpy(dec)
+    assert float((acc.cpu().double() - ref).abs().max()) <= step * 1.0001
+    assert float(out[n:].abs().max()) == 0.0
