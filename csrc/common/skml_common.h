@@ -219,6 +219,59 @@ SKML_HD int32_t skml_hash_fast(int id, int32_t key, const SkmlKeyDigits& kd, int
     return m ? size - (int32_t)m : 0;
 }
 
+// All `rows` (<= MAXR) table positions of one key at once; equal to skml_hash(ids[r], key, size)
+// for every row. The BKDR members share ONE pass over the key's decimal digits: each keeps its own
+// accumulator and every digit costs one divide-by-constant plus one multiply-add per row.
+template <int MAXR>
+SKML_HD void skml_hash_rows(const uint8_t* ids, int rows, int32_t key, int32_t size, uint64_t magic, int32_t* out) {
+    if (key < 0) {
+        for (int r = 0; r < MAXR; ++r)
+            if (r < rows) out[r] = skml_hash(ids[r], key, size);
+        return;
+    }
+    uint32_t c[MAXR], seed[MAXR];
+    bool any = false;
+#ifdef __CUDA_ARCH__
+#pragma unroll
+#endif
+    for (int r = 0; r < MAXR; ++r) {
+        const int id = r < rows ? ids[r] : 0;
+        seed[r] = id < 3 ? 0u : (id == 3 ? 31u : (id == 4 ? 131u : (id == 5 ? 267u : (id == 6 ? 1313u : 13131u))));
+        c[r] = 0;
+        any = any || seed[r] != 0;
+    }
+    if (any) {
+        uint32_t k = (uint32_t)key;
+        while (k != 0) {
+            const uint32_t q = k / 10u;
+            const uint32_t d = k - q * 10u;
+#ifdef __CUDA_ARCH__
+#pragma unroll
+#endif
+            for (int r = 0; r < MAXR; ++r) c[r] = seed[r] * c[r] + d;
+            k = q;
+        }
+    }
+#ifdef __CUDA_ARCH__
+#pragma unroll
+#endif
+    for (int r = 0; r < MAXR; ++r) {
+        if (r >= rows) continue;
+        const int id = ids[r];
+        uint32_t h = c[r];
+        if (id == 0) h = skml_mix_bj((uint32_t)key);
+        else if (id == 1) h = skml_mix_64((uint32_t)key);
+        else if (id == 2) h = skml_mix_tw((uint32_t)key);
+        const int32_t sc = (int32_t)h;
+        if (sc >= 0) {
+            out[r] = (int32_t)skml_fastmod(h, magic, (uint32_t)size);
+        } else {  // Java: the remainder keeps the sign of the dividend
+            const uint32_t m = skml_fastmod((uint32_t)(-(int64_t)sc), magic, (uint32_t)size);
+            out[r] = m ? size - (int32_t)m : 0;
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Counter-based random numbers (splitmix64): every rank derives the same value
 // from (seed, step, rank, group, slot) without any shared state.
@@ -304,6 +357,9 @@ SKML_HD int skml_delta_bytes(uint32_t delta) { return delta < 256u ? 1 : (delta 
 // significant bit first at increasing java.util.BitSet indices, and BitSet index i is
 // bit (i & 63) of word (i >> 6), so each stream byte is a bit-reversed value byte.
 SKML_HD uint8_t skml_brev8(uint8_t b) {
+#if defined(__CUDA_ARCH__)
+    return (uint8_t)(__brev((unsigned int)b) >> 24);
+#endif
     b = (uint8_t)(((b & 0xF0u) >> 4) | ((b & 0x0Fu) << 4));
     b = (uint8_t)(((b & 0xCCu) >> 2) | ((b & 0x33u) << 2));
     b = (uint8_t)(((b & 0xAAu) >> 1) | ((b & 0x55u) << 1));

@@ -261,6 +261,25 @@ PYBIND11_MODULE(_oracle, m) {
         }
         return to_array(out);
     });
+    m.def("hash_rows", [](std::vector<int> ids, I32Array keys, int32_t size) {
+        // the kernels' multi-row hash (one shared digit pass): returns [len(keys)][len(ids)]
+        if (ids.empty() || ids.size() > 8 || size <= 0) throw Error("hash ids or range out of bounds");
+        uint8_t id8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (size_t r = 0; r < ids.size(); ++r) {
+            if (ids[r] < 0 || ids[r] > 7) throw Error("hash id out of range [0, 8)");
+            id8[r] = (uint8_t)ids[r];
+        }
+        const int rows = (int)ids.size();
+        std::vector<int32_t> out((size_t)keys.size() * rows);
+        uint64_t magic = skml_fastmod_magic((uint32_t)size);
+        for (ssize_t i = 0; i < keys.size(); ++i) {
+            int32_t pos[8];
+            if (rows <= 4) skml_hash_rows<4>(id8, rows, keys.data()[i], size, magic, pos);
+            else skml_hash_rows<8>(id8, rows, keys.data()[i], size, magic, pos);
+            for (int r = 0; r < rows; ++r) out[(size_t)i * rows + r] = pos[r];
+        }
+        return to_array(out);
+    });
     m.def("pick_hashes", [](uint64_t seed, uint64_t step, uint32_t rank, uint32_t group, int rows) {
         if (rows > 8 || rows < 1) throw Error("Currently only 8 hash functions are available");
         uint8_t ids[8];

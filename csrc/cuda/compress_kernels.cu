@@ -33,8 +33,7 @@
 #define TILE_W 16           // TILE / SK_K: weight of a sample taken from a full tile
 #define MAX_LEVELS 24
 #define FP_SHIFT 20         // fixed-point fraction bits of sample weights
-#define MIN_TILES_PER_BLOCK 4
-#define SUPER_TILES 4       // tiles folded into one sort by the bottom-level sampler
+#define MAX_SAMPLE 16        // largest sampling factor of the bottom-level sampler
 
 struct CtaStat {
     unsigned int count;
@@ -231,14 +230,20 @@ __device__ __forceinline__ void carry_run(Smem& s, unsigned int& occupied, int l
 }
 
 __device__ void stage_summary(const CP& p, Smem& s, const float* __restrict__ vals, long long n) {
+    // Bottom-level sampler (as in KLL sketches): of every f consecutive values one is kept at random
+    // with weight f, so one 2048-sort covers f * 2048 values and enters the level chain as one run
+    // of weight 16 f. f is the smallest power of two (<= MAX_SAMPLE) for which every block has one
+    // sort to do; min and max still see every value.
     const long long ntiles = (n + TILE - 1) / TILE;
-    long long CA = (ntiles + MIN_TILES_PER_BLOCK - 1) / MIN_TILES_PER_BLOCK;
-    if (CA > gridDim.x) CA = gridDim.x;
-    if (CA < 1) CA = 1;
-    const long long tpc = (ntiles + CA - 1) / CA;
-    long long t0 = (long long)blockIdx.x * tpc, t1 = t0 + tpc;
-    if (t1 > ntiles) t1 = ntiles;
-    if ((long long)blockIdx.x >= CA || t0 >= t1 || n <= 0) {
+    int f = 1, lf = 0;
+    while (f < MAX_SAMPLE && ntiles > (long long)f * gridDim.x) {
+        f <<= 1;
+        ++lf;
+    }
+    const long long ST = (long long)f * TILE;
+    const long long nst = (n + ST - 1) / ST;
+    const long long t0 = blockIdx.x;  // super tiles are dealt round-robin: t0, t0 + grid, ...
+    if (t0 >= nst || n <= 0) {
         if (threadIdx.x == 0) {
             p.run_cnt[blockIdx.x] = 0;
             p.run_w[blockIdx.x] = 0;
@@ -249,67 +254,82 @@ __device__ void stage_summary(const CP& p, Smem& s, const float* __restrict__ va
     int tail_cnt = 0;
     unsigned long long tail_w = 0;
     unsigned int kmin = 0xFFFFFFFFu, kmax = 0u;
-    unsigned long long n_c = 0;
-    for (long long tile = t0; tile < t1; ++tile) {
-        long long base = tile * TILE;
-        if (t1 - tile >= SUPER_TILES && base + (long long)SUPER_TILES * TILE <= n) {
-            // Bottom-level sampler (as in KLL sketches): of every 4 consecutive values one is kept
-            // at random with weight 4, so 8192 values cost one 2048-sort and enter the level chain
-            // as one run of weight 64. Min and max still see every value.
-            const float4* v4 = reinterpret_cast<const float4*>(vals + base);
+    const unsigned long long salt0 = p.seed ^ (p.step * 0x9E3779B97F4A7C15ull) ^ ((unsigned long long)p.rank << 40);
+    for (long long st = t0; st < nst; st += gridDim.x) {
+        const long long base = st * ST;
+        const long long m = (n - base) < ST ? (n - base) : ST;  // values of this super tile
+        if (m == ST) {
             for (int t = threadIdx.x; t < TILE; t += blockDim.x) {
-                const float4 q = v4[t];
-                const unsigned int k0 = f2ord(q.x), k1 = f2ord(q.y), k2 = f2ord(q.z), k3 = f2ord(q.w);
-                kmin = min(min(kmin, k0), min(min(k1, k2), k3));
-                kmax = max(max(kmax, k0), max(max(k1, k2), k3));
-                const unsigned int r = (unsigned int)(skml_splitmix64(p.seed ^ (p.step * 0x9E3779B97F4A7C15ull) ^
-                                                                      ((unsigned long long)p.rank << 40) ^ (unsigned long long)(base + t)) >> 62);
-                s.tile[t] = r == 0 ? k0 : (r == 1 ? k1 : (r == 2 ? k2 : k3));
+                const float* src = vals + base + (long long)t * f;
+                const unsigned int pick = (unsigned int)(skml_splitmix64(salt0 ^ (unsigned long long)(base + t)) >> 40) & (unsigned int)(f - 1);
+                unsigned int chosen = 0;
+                if (f == 1) {
+                    chosen = f2ord(src[0]);
+                    kmin = min(kmin, chosen);
+                    kmax = max(kmax, chosen);
+                } else if (f == 2) {
+                    const float2 q = *reinterpret_cast<const float2*>(src);
+                    const unsigned int k0 = f2ord(q.x), k1 = f2ord(q.y);
+                    kmin = min(kmin, min(k0, k1));
+                    kmax = max(kmax, max(k0, k1));
+                    chosen = pick ? k1 : k0;
+                } else {
+                    for (int j = 0; j < f / 4; ++j) {
+                        const float4 q = reinterpret_cast<const float4*>(src)[j];
+                        const unsigned int k0 = f2ord(q.x), k1 = f2ord(q.y), k2 = f2ord(q.z), k3 = f2ord(q.w);
+                        kmin = min(min(kmin, k0), min(min(k1, k2), k3));
+                        kmax = max(max(kmax, k0), max(max(k1, k2), k3));
+                        if ((int)(pick >> 2) == j) {
+                            const unsigned int r = pick & 3u;
+                            chosen = r == 0 ? k0 : (r == 1 ? k1 : (r == 2 ? k2 : k3));
+                        }
+                    }
+                }
+                s.tile[t] = chosen;
             }
             __syncthreads();
+            if (st == t0) stage_stamp(p.ctrl, 10);
             block_sort_2048(s.tile);
-            n_c += (unsigned long long)SUPER_TILES * TILE;
+            if (st == t0) stage_stamp(p.ctrl, 11);
             const unsigned int off = (unsigned int)(skml_rand(p.seed, p.step, ((unsigned long long)p.rank << 32) | blockIdx.x,
-                                                              0x7200u + (unsigned long long)(tile - t0)) & (TILE_W - 1));
+                                                              0x7200u + (unsigned long long)((st - t0) / gridDim.x)) & (TILE_W - 1));
             for (int t = threadIdx.x; t < SK_K; t += blockDim.x) s.run[t] = s.tile[t * TILE_W + off];
             __syncthreads();
-            carry_run(s, occupied, 2, p, (unsigned long long)(tile - t0) + 1);
-            tile += SUPER_TILES - 1;
+            carry_run(s, occupied, lf, p, (unsigned long long)((st - t0) / gridDim.x) + 1);
             continue;
         }
-        int m = (int)((n - base) < TILE ? (n - base) : TILE);
+        // the last, partial super tile of the whole input: slot t samples the valid part of its f values
+        const int ms = (int)((m + f - 1) / f);  // slots that hold a value
         for (int t = threadIdx.x; t < TILE; t += blockDim.x) {
-            unsigned int k = 0xFFFFFFFFu;
-            if (t < m) {
-                k = f2ord(vals[base + t]);
-                kmin = min(kmin, k);
-                kmax = max(kmax, k);
+            unsigned int chosen = 0xFFFFFFFFu;
+            const long long g0 = base + (long long)t * f;
+            if (g0 < n) {
+                const int valid = (int)((n - g0) < f ? (n - g0) : f);
+                const unsigned int pick = (unsigned int)((skml_splitmix64(salt0 ^ (unsigned long long)(base + t)) >> 40) % (unsigned int)valid);
+                for (int j = 0; j < valid; ++j) {
+                    const unsigned int k = f2ord(vals[g0 + j]);
+                    kmin = min(kmin, k);
+                    kmax = max(kmax, k);
+                    if ((unsigned int)j == pick) chosen = k;
+                }
             }
-            s.tile[t] = k;
+            s.tile[t] = chosen;
         }
         __syncthreads();
         block_sort_2048(s.tile);
-        n_c += (unsigned long long)m;
-        if (m == TILE) {
-            unsigned int off = (unsigned int)(skml_rand(p.seed, p.step, ((unsigned long long)p.rank << 32) | blockIdx.x,
-                                                        0x7000u + (unsigned long long)(tile - t0)) & (TILE_W - 1));
-            for (int t = threadIdx.x; t < SK_K; t += blockDim.x) s.run[t] = s.tile[t * TILE_W + off];
-            __syncthreads();
-            carry_run(s, occupied, 0, p, (unsigned long long)(tile - t0) + 1);
-        } else {
-            int stride = 1;
-            while ((m + stride - 1) / stride > SK_K) stride <<= 1;
-            tail_cnt = (m + stride - 1) / stride;
-            unsigned int off = stride > 1 ? (unsigned int)(skml_rand(p.seed, p.step, p.rank, 0x7100u) % stride) : 0u;
-            for (int t = threadIdx.x; t < tail_cnt; t += blockDim.x) {
-                int idx = t * stride + (int)off;
-                if (idx > m - 1) idx = m - 1;
-                s.tail[t] = s.tile[idx];
-            }
-            tail_w = (((unsigned long long)m) << FP_SHIFT) / (unsigned long long)tail_cnt;
-            __syncthreads();
+        int stride = 1;
+        while ((ms + stride - 1) / stride > SK_K) stride <<= 1;
+        tail_cnt = (ms + stride - 1) / stride;
+        const unsigned int off = stride > 1 ? (unsigned int)(skml_rand(p.seed, p.step, p.rank, 0x7100u) % stride) : 0u;
+        for (int t = threadIdx.x; t < tail_cnt; t += blockDim.x) {
+            int idx = t * stride + (int)off;
+            if (idx > ms - 1) idx = ms - 1;
+            s.tail[t] = s.tile[idx];
         }
+        tail_w = (((unsigned long long)m) << FP_SHIFT) / (unsigned long long)tail_cnt;
+        __syncthreads();
     }
+    stage_stamp(p.ctrl, 12);
     // block min / max -> global (stored so that an all-zero word means "nothing yet")
     {
         unsigned int a = kmin, b = kmax;
@@ -318,11 +338,28 @@ __device__ void stage_summary(const CP& p, Smem& s, const float* __restrict__ va
             a = min(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
             b = max(b, __shfl_xor_sync(0xFFFFFFFFu, b, o));
         }
+        // one pair of atomics per block: thousands of same-address atomics would serialise in L2
+        __shared__ unsigned int s_mn[SKML_WARPS], s_mx[SKML_WARPS];
         if ((threadIdx.x & 31) == 0) {
-            atomicMax(&p.ctrl[4], ~a);
-            atomicMax(&p.ctrl[5], b);
+            s_mn[threadIdx.x >> 5] = a;
+            s_mx[threadIdx.x >> 5] = b;
+        }
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            a = s_mn[threadIdx.x];
+            b = s_mx[threadIdx.x];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                a = min(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+                b = max(b, __shfl_xor_sync(0xFFFFFFFFu, b, o));
+            }
+            if (threadIdx.x == 0) {
+                atomicMax(&p.ctrl[4], ~a);
+                atomicMax(&p.ctrl[5], b);
+            }
         }
     }
+    stage_stamp(p.ctrl, 13);
     // collapse the levels (+ tail) into one published run
     int nruns = __popc(occupied) + (tail_cnt > 0 ? 1 : 0);
     unsigned int* out = p.run_vals + (long long)blockIdx.x * SK_K;
@@ -626,10 +663,18 @@ __device__ void element_pass(const CP& p, Smem& s, long long n) {
             const unsigned int cell = skml_pack_cell(bin, zero);
             const int col = (int)L.col[g];
             unsigned int* tab = p.tables + L.tab32_off[g];
-            SkmlKeyDigits kd;
-            skml_key_digits(key, kd);
-            for (int r = 0; r < p.rows; ++r)
-                atomicMin(tab + (long long)r * col + skml_hash_fast(L.hash_ids[g][r], key, kd, col, L.col_magic[g]), cell);
+            int pos[SKML_MAX_ROWS];
+            if (p.rows <= 4) {
+                skml_hash_rows<4>(L.hash_ids[g], p.rows, key, col, L.col_magic[g], pos);
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+                    if (r < p.rows) atomicMin(tab + (long long)r * col + pos[r], cell);
+            } else {
+                skml_hash_rows<SKML_MAX_ROWS>(L.hash_ids[g], p.rows, key, col, L.col_magic[g], pos);
+#pragma unroll
+                for (int r = 0; r < SKML_MAX_ROWS; ++r)
+                    if (r < p.rows) atomicMin(tab + (long long)r * col + pos[r], cell);
+            }
         }
         __syncwarp();
         if (lane < G) {
@@ -786,6 +831,18 @@ __device__ void compute_layout(const CP& p, Smem& s, long long n) {
         }
     }
     __syncthreads();
+    if (threadIdx.x < G) {  // per-group divisions and hash draws, one thread each
+        const int g = threadIdx.x;
+        unsigned int col = 0;
+        if (L.n_g[g]) {
+            col = (unsigned int)ceil((double)L.n_g[g] * p.col_ratio);
+            if (col < 1) col = 1;
+        }
+        L.col[g] = col;
+        L.col_magic[g] = col ? skml_fastmod_magic(col) : 0ull;
+        skml_pick_hashes(p.seed, p.step, p.rank, (unsigned int)g, p.rows, L.hash_ids[g]);
+    }
+    __syncthreads();
     if (threadIdx.x == 0) {
         const int cb = s.qi.cell_bits;
         L.off_bv = SKML_HEADER_BYTES;
@@ -804,18 +861,11 @@ __device__ void compute_layout(const CP& p, Smem& s, long long n) {
         L.off_tables = o;
         unsigned long long t32 = 0;
         for (int g = 0; g < G; ++g) {
-            unsigned int col = 0;
-            if (L.n_g[g]) {
-                col = (unsigned int)ceil((double)L.n_g[g] * p.col_ratio);
-                if (col < 1) col = 1;
-            }
-            L.col[g] = col;
-            L.col_magic[g] = col ? skml_fastmod_magic(col) : 0ull;
+            const unsigned int col = L.col[g];
             L.table_off[g] = o;
             L.tab32_off[g] = t32;
             o += skml_align16((unsigned long long)p.rows * col * (cb / 8));
             t32 += (unsigned long long)p.rows * col;
-            skml_pick_hashes(p.seed, p.step, p.rank, (unsigned int)g, p.rows, L.hash_ids[g]);
         }
         L.off_deltas = o;
         for (int g = 0; g < G; ++g) {

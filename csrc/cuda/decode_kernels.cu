@@ -43,6 +43,7 @@ struct DP {
     float lr, adam_scale;
     long long* acc;
     int* key_scratch;
+    float* val_scratch;
     long long key_capacity;
     double* loss_out;
     float* out_sum;
@@ -68,6 +69,8 @@ struct DecSmem {
     int any_dense;
     int direct;      // linear update (SGD / plain sum): payloads applied in rank order, no accumulators
     unsigned long long rank_chunk_begin[SKML_MAX_PEERS + 1];
+    unsigned long long rank_key_begin[SKML_MAX_PEERS + 1];
+    int two_phase;   // direct mode over several payloads: decode everything first, then ordered apply passes
     int shift;       // fixed-point: accumulator = value * 2^shift
     double inv_world;
     int ok;
@@ -122,6 +125,8 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
                     h.step == p.step && h.rank == (unsigned int)threadIdx.x && h.dim == (unsigned long long)p.dim &&
                     h.total_bytes <= (unsigned long long)p.slot_capacity && h.dtype == SKML_F32 &&
                     h.group_num <= SKML_MAX_GROUPS && h.row_num <= SKML_MAX_ROWS && h.kind <= SKML_KIND_DENSE &&
+                    (h.kind != SKML_KIND_SPARSE || ((h.off_group_table & 15ull) == 0 &&
+                                                    h.off_group_table + sizeof(SkmlGroupEntry) * h.group_num <= h.total_bytes)) &&
                     (h.kind == SKML_KIND_EMPTY || (h.bin_num >= 1 && h.bin_num <= SKML_GPU_MAX_BINS && h.zero_idx < h.bin_num)) &&
                     (h.kind != SKML_KIND_SPARSE || (h.key_encoder == SKML_KEYS_DELTA_BINARY &&
                                                     h.restart_interval == SKML_RESTART_INTERVAL &&
@@ -133,6 +138,39 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
     }
     __syncthreads();
     if (!s.ok) return false;
+    // group entries: one thread per (rank, group) fetches its 64-byte entry (independent loads)
+    const int gcap = p.max_items / p.world;
+    for (int t = threadIdx.x; t < p.world * gcap; t += blockDim.x) {
+        const int r = t / gcap, g = t % gcap;
+        const SkmlHeader& h = s.hdr[r];
+        DecItem& it = s.items[t];
+        it.e.n = 0;
+        if (h.kind == SKML_KIND_SPARSE && g < (int)h.group_num) {
+            const uint4* src = reinterpret_cast<const uint4*>(p.payload[r] + h.off_group_table + g * sizeof(SkmlGroupEntry));
+            unsigned long long* dst = reinterpret_cast<unsigned long long*>(&it.e);  // 8-byte aligned in DecItem
+#pragma unroll
+            for (int q = 0; q < (int)(sizeof(SkmlGroupEntry) / 16); ++q) {
+                const uint4 v = ld_cg_v4(src + q);
+                dst[2 * q] = (unsigned long long)v.x | ((unsigned long long)v.y << 32);
+                dst[2 * q + 1] = (unsigned long long)v.z | ((unsigned long long)v.w << 32);
+            }
+            if (it.e.n) {
+                const unsigned long long lim = h.total_bytes;
+                const bool good = it.e.col_num > 0 && it.e.table_off + (unsigned long long)h.row_num * it.e.col_num * (h.cell_bits / 8) <= lim &&
+                                  it.e.flag_off + 8ull * it.e.n_flag_words <= lim && it.e.delta_off + 8ull * it.e.n_delta_words <= lim &&
+                                  it.e.restart_off + 16ull * ((it.e.n + SKML_RESTART_INTERVAL - 1) / SKML_RESTART_INTERVAL) <= lim &&
+                                  2ull * it.e.n <= 64ull * it.e.n_flag_words;
+                it.base = p.payload[r];
+                it.zero = h.zero_idx;
+                it.cell_bits = h.cell_bits;
+                it.rows = h.row_num;
+                it.off_bv = h.off_bucket_values;
+                it.col_magic = good ? skml_fastmod_magic(it.e.col_num) : 0ull;
+                it.chunk_prefix = good ? 0ull : 1ull;  // scratch use until the compaction below: 1 = failed validation
+            }
+        }
+    }
+    __syncthreads();
     if (threadIdx.x == 0) {
         int ni = 0;
         unsigned long long chunks = 0, keys = 0;
@@ -141,54 +179,50 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
         for (int r = 0; r < p.world; ++r) {
             const SkmlHeader& h = s.hdr[r];
             s.rank_chunk_begin[r] = chunks;
+            s.rank_key_begin[r] = keys;
             if (h.kind == SKML_KIND_EMPTY) continue;
             mx = fmax(mx, fmax(fabs(h.min_value), fabs(h.max_value)));
             if (h.kind == SKML_KIND_DENSE) {
                 dense = 1;
                 continue;
             }
+            if ((int)h.group_num > gcap) {
+                skml_set_status(p.status, SKML_BAD_HEADER, 0x300u | (unsigned int)r);
+                s.ok = 0;
+                break;
+            }
             for (unsigned int g = 0; g < h.group_num; ++g) {
-                if (ni >= p.max_items) {
-                    skml_set_status(p.status, SKML_BAD_HEADER, 0x300u | (unsigned int)r);
-                    s.ok = 0;
-                    break;
-                }
-                DecItem& it = s.items[ni];
-                it.base = p.payload[r];
-                it.e = *reinterpret_cast<const SkmlGroupEntry*>(p.payload[r] + h.off_group_table + g * sizeof(SkmlGroupEntry));
-                if (it.e.n == 0) continue;
-                const unsigned long long lim = h.total_bytes;
-                bool good = it.e.col_num > 0 && it.e.table_off + (unsigned long long)h.row_num * it.e.col_num * (h.cell_bits / 8) <= lim &&
-                            it.e.flag_off + 8ull * it.e.n_flag_words <= lim && it.e.delta_off + 8ull * it.e.n_delta_words <= lim &&
-                            it.e.restart_off + 16ull * ((it.e.n + SKML_RESTART_INTERVAL - 1) / SKML_RESTART_INTERVAL) <= lim &&
-                            2ull * it.e.n <= 64ull * it.e.n_flag_words;
-                if (!good) {
+                const int src = r * gcap + (int)g;
+                if (s.items[src].e.n == 0) continue;
+                if (s.items[src].chunk_prefix) {
                     skml_set_status(p.status, SKML_BAD_HEADER, 0x100u | (unsigned int)r);
                     s.ok = 0;
                     break;
                 }
+                if (ni != src) s.items[ni] = s.items[src];  // ni <= src: compaction moves entries forward only
+                DecItem& it = s.items[ni];
                 it.chunk_prefix = chunks;
                 it.key_prefix = keys;
-                it.zero = h.zero_idx;
-                it.cell_bits = h.cell_bits;
-                it.rows = h.row_num;
-                it.off_bv = h.off_bucket_values;
-                it.col_magic = skml_fastmod_magic(it.e.col_num);
                 chunks += (it.e.n + SKML_RESTART_INTERVAL - 1) / SKML_RESTART_INTERVAL;
                 keys += it.e.n;
                 ++ni;
             }
+            if (!s.ok) break;
         }
         if (keys > (unsigned long long)p.key_capacity) {
             skml_set_status(p.status, SKML_CAPACITY, 0x40u);
             s.ok = 0;
         }
-        for (int r = p.world; r <= SKML_MAX_PEERS; ++r) s.rank_chunk_begin[r] = chunks;
+        for (int r = p.world; r <= SKML_MAX_PEERS; ++r) {
+            s.rank_chunk_begin[r] = chunks;
+            s.rank_key_begin[r] = keys;
+        }
         s.nitems = ni;
         s.total_chunks = chunks;
         s.total_keys = keys;
         s.any_dense = dense;
         s.direct = (p.adam_v == nullptr) ? 1 : 0;
+        s.two_phase = (s.direct && p.world > 1 && p.val_scratch != nullptr) ? 1 : 0;
         int e = 0;
         if (mx > 0.0 && isfinite(mx)) frexp(mx, &e);
         s.shift = 60 - e;
@@ -198,23 +232,20 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
     return s.ok != 0;
 }
 
-// Query of one key in its group's sketch and accumulation of the dequantized value.
-__device__ __forceinline__ void decode_one(const DP& p, const DecSmem& s, const DecItem& it, unsigned int key) {
-    if (key >= (unsigned long long)p.dim) {
-        skml_set_status(p.status, SKML_BAD_HEADER, 0x200u);
-        return;
-    }
+// Query of one key in its group's sketch: the bucket value of the cell farthest from the zero bucket.
+__device__ __forceinline__ float query_one(const DP& p, const DecItem& it, unsigned int key) {
     const int col = (int)it.e.col_num;
     const int zero = (int)it.zero;
-    SkmlKeyDigits kd;
-    skml_key_digits((int)key, kd);
     int cells[SKML_MAX_ROWS];
+    int pos[SKML_MAX_ROWS];
+    const int rows = (int)it.rows;
+    if (rows <= 4) skml_hash_rows<4>(it.e.hash_ids, rows, (int)key, col, it.col_magic, pos);
+    else skml_hash_rows<SKML_MAX_ROWS>(it.e.hash_ids, rows, (int)key, col, it.col_magic, pos);
 #pragma unroll
     for (int r = 0; r < SKML_MAX_ROWS; ++r) {  // independent loads first
         cells[r] = zero;
-        if (r < (int)it.rows) {
-            const unsigned long long c = (unsigned long long)r * col +
-                                         (unsigned int)skml_hash_fast(it.e.hash_ids[r], (int)key, kd, col, it.col_magic);
+        if (r < rows) {
+            const unsigned long long c = (unsigned long long)r * col + (unsigned int)pos[r];
             if (it.cell_bits == 8) cells[r] = __ldcg(it.base + it.e.table_off + c);
             else cells[r] = __ldcg(reinterpret_cast<const unsigned short*>(it.base + it.e.table_off) + c);
         }
@@ -229,13 +260,7 @@ __device__ __forceinline__ void decode_one(const DP& p, const DecSmem& s, const 
             res = cells[r];
         }
     }
-    const float bv = __ldcg(reinterpret_cast<const float*>(it.base + it.off_bv) + res);
-    if (s.direct) {  // rank-ordered pass: keys are unique inside a payload, plain read-modify-write
-        apply_direct(p, key, bv * (float)s.inv_world);
-        return;
-    }
-    const long long fx = to_fixed((double)bv * s.inv_world, s.shift);
-    if (fx) atomicAdd(reinterpret_cast<unsigned long long*>(p.acc + key), (unsigned long long)fx);
+    return __ldcg(reinterpret_cast<const float*>(it.base + it.off_bv) + res);
 }
 
 // D1 for sparse payloads: one 1024-key chunk per block iteration, DEC_KPT adjacent keys per
@@ -279,18 +304,25 @@ __device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch
         if (i0 < cnt) {
             const unsigned long long byte0 = (rs.delta_bit_off >> 3) + boff;
             if (byte0 + wsum <= 8ull * it.e.n_delta_words) {
-                const unsigned char* src = it.base + it.e.delta_off + byte0;
-                unsigned char raw[4 * DEC_KPT];
+                // The thread's <= 4 * DEC_KPT delta bytes sit in at most DEC_KPT + 1 aligned words.
+                // Bit-reversing a little-endian word yields its four stream bytes in most-significant-
+                // first order (java.util.BitSet order), so a delta is a funnel shift away.
+                const unsigned int* src = reinterpret_cast<const unsigned int*>(it.base + it.e.delta_off);
+                const unsigned long long w0 = byte0 >> 2, wlim = 2ull * it.e.n_delta_words;
+                unsigned int W[DEC_KPT + 1];
 #pragma unroll
-                for (unsigned int t = 0; t < 4 * DEC_KPT; ++t) raw[t] = t < wsum ? __ldcg(src + t) : 0;
-                unsigned int edge = 0;
+                for (int t = 0; t <= DEC_KPT; ++t) W[t] = (w0 + t < wlim) ? __brev(__ldcg(src + w0 + t)) : 0u;
+                unsigned int start = (unsigned int)(byte0 & 3);
 #pragma unroll
                 for (int u = 0; u < DEC_KPT; ++u) {
-                    const unsigned int lo = edge;
-                    edge += w[u];
+                    const unsigned int wi = start >> 2, sh = 8u * (start & 3u);
+                    unsigned int hi = W[0], lo = W[1];
 #pragma unroll
-                    for (unsigned int t = 0; t < 4 * DEC_KPT; ++t)
-                        if (t >= lo && t < edge) d[u] = (d[u] << 8) | skml_brev8(raw[t]);
+                    for (int t = 1; t < DEC_KPT; ++t)
+                        if (wi == (unsigned int)t) { hi = W[t]; lo = W[t + 1]; }
+                    const unsigned int v = __funnelshift_l(lo, hi, sh);
+                    d[u] = w[u] ? v >> (32u - 8u * w[u]) : 0u;
+                    start += w[u];
                 }
             }
         }
@@ -303,17 +335,72 @@ __device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch
             unsigned int key = rs.prev_key + dex;
             int* ks = p.key_scratch + it.key_prefix + first;
             unsigned int keys[DEC_KPT];
+            bool live[DEC_KPT];
 #pragma unroll
             for (int u = 0; u < DEC_KPT; ++u) {
                 key += d[u];
                 keys[u] = key;
-                if (!s.direct && i0 + u < cnt) ks[i0 + u] = (int)key;
+                live[u] = i0 + u < cnt;
+                if (live[u] && key >= (unsigned long long)p.dim) {
+                    skml_set_status(p.status, SKML_BAD_HEADER, 0x200u);
+                    live[u] = false;
+                    keys[u] = 0xFFFFFFFFu;
+                }
+                if (!s.direct && i0 + u < cnt) ks[i0 + u] = (int)keys[u];
             }
+            float bv[DEC_KPT];
 #pragma unroll
-            for (int u = 0; u < DEC_KPT; ++u)
-                if (i0 + u < cnt) decode_one(p, s, it, keys[u]);
+            for (int u = 0; u < DEC_KPT; ++u) bv[u] = live[u] ? query_one(p, it, keys[u]) : 0.f;
+            if (s.two_phase) {
+                // stash (key, value): the ordered apply passes read them back coalesced
+                float* vs = p.val_scratch + it.key_prefix + first;
+#pragma unroll
+                for (int u = 0; u < DEC_KPT; ++u)
+                    if (i0 + u < cnt) {
+                        ks[i0 + u] = (int)keys[u];
+                        vs[i0 + u] = bv[u] * (float)s.inv_world;
+                    }
+            } else if (s.direct) {  // single payload: keys are unique inside it, plain read-modify-write
+#pragma unroll
+                for (int u = 0; u < DEC_KPT; ++u)
+                    if (live[u]) apply_direct(p, keys[u], bv[u] * (float)s.inv_world);
+            } else {
+#pragma unroll
+                for (int u = 0; u < DEC_KPT; ++u) {
+                    const long long fx = live[u] ? to_fixed((double)bv[u] * s.inv_world, s.shift) : 0ll;
+                    if (fx) atomicAdd(reinterpret_cast<unsigned long long*>(p.acc + keys[u]), (unsigned long long)fx);
+                }
+            }
         }
         __syncthreads();
+    }
+}
+
+// Ordered apply of one rank's stashed (key, value) pairs: keys are unique inside a payload, so the
+// plain read-modify-write needs no atomics; four independent pairs per thread and iteration.
+__device__ void apply_stashed(const DP& p, unsigned long long begin, unsigned long long end) {
+    const unsigned long long gsz = (unsigned long long)gridDim.x * blockDim.x;
+    for (unsigned long long t = begin + (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; t < end; t += 4 * gsz) {
+        unsigned int k[4];
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const unsigned long long tt = t + u * gsz;
+            k[u] = tt < end ? (unsigned int)__ldcg(p.key_scratch + tt) : 0xFFFFFFFFu;
+            v[u] = tt < end ? __ldcg(p.val_scratch + tt) : 0.f;
+        }
+        float old[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            float* dst = p.out_sum ? p.out_sum : p.w;
+            old[u] = k[u] < (unsigned long long)p.dim ? dst[k[u]] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (k[u] < (unsigned long long)p.dim) {
+                if (p.out_sum) p.out_sum[k[u]] = old[u] + v[u];
+                else p.w[k[u]] = old[u] - p.lr * v[u];
+            }
     }
 }
 
@@ -390,14 +477,37 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_BLOCKS_PER_SM) decode_update_
         reinterpret_cast<unsigned long long*>(p.ctrl)[9] = t;
     }
     if (s.direct) {
-        // one pass per rank; un-fused launches run pass `stage - 1` each
-        for (int r = 0; r < p.world; ++r) {
-            if (FUSED || stage == r + 1) {
-                decode_accumulate(p, s, s.rank_chunk_begin[r], s.rank_chunk_begin[r + 1]);
-                if (s.any_dense) decode_accumulate_dense(p, s, r, r + 1);
+        if (s.two_phase) {
+            // Phase 1 (un-fused: stage 1): every payload's keys and values, no ordering needed.
+            if (FUSED || stage == 1) decode_accumulate(p, s, 0, s.total_chunks);
+            if (FUSED) {
+                if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, 0x2Fu)) return;
+                if (blockIdx.x == 0 && threadIdx.x == 0) {
+                    unsigned long long t;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+                    reinterpret_cast<unsigned long long*>(p.ctrl)[10] = t;
+                }
             }
-            if (FUSED && r + 1 < p.world) {
-                if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, 0x30u + r)) return;
+            // Phase 2 (un-fused: stage r + 2): one apply pass per rank, in rank order.
+            for (int r = 0; r < p.world; ++r) {
+                if (FUSED || stage == r + 2) {
+                    apply_stashed(p, s.rank_key_begin[r], s.rank_key_begin[r + 1]);
+                    if (s.any_dense) decode_accumulate_dense(p, s, r, r + 1);
+                }
+                if (FUSED && r + 1 < p.world) {
+                    if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, 0x30u + r)) return;
+                }
+            }
+        } else {
+            // one pass per rank; un-fused launches run pass `stage - 1` each
+            for (int r = 0; r < p.world; ++r) {
+                if (FUSED || stage == r + 1) {
+                    decode_accumulate(p, s, s.rank_chunk_begin[r], s.rank_chunk_begin[r + 1]);
+                    if (s.any_dense) decode_accumulate_dense(p, s, r, r + 1);
+                }
+                if (FUSED && r + 1 < p.world) {
+                    if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, 0x30u + r)) return;
+                }
             }
         }
         if ((FUSED || stage == 1) && blockIdx.x == 0 && threadIdx.x == 0 && p.loss_out) {
@@ -409,7 +519,7 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_BLOCKS_PER_SM) decode_update_
         if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) {
             unsigned long long t;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            reinterpret_cast<unsigned long long*>(p.ctrl)[10] = t;
+            if (!s.two_phase) reinterpret_cast<unsigned long long*>(p.ctrl)[10] = t;
             reinterpret_cast<unsigned long long*>(p.ctrl)[11] = t;
         }
         return;
@@ -461,6 +571,7 @@ extern "C" int skml_decode_update(const SkmlDecodeArgs* a, void* stream_) {
     p.adam_scale = (float)a->adam_scale;
     p.acc = a->acc;
     p.key_scratch = a->key_scratch;
+    p.val_scratch = a->val_scratch;
     p.key_capacity = a->key_capacity;
     p.loss_out = a->loss_out;
     p.out_sum = a->out_sum;
@@ -505,7 +616,9 @@ extern "C" int skml_decode_update(const SkmlDecodeArgs* a, void* stream_) {
         return (int)cudaLaunchCooperativeKernel((const void*)decode_update_kernel<true>, dim3(grid), dim3(DEC_THREADS), args,
                                                 smem, stream);
     }
-    const int nst = a->adam_v ? 2 : (int)a->world;
+    // stages: Adam = accumulate + claims; SGD over several payloads with a value scratch = decode +
+    // one apply pass per rank; otherwise one pass per rank
+    const int nst = a->adam_v ? 2 : ((a->world > 1 && a->val_scratch) ? (int)a->world + 1 : (int)a->world);
     for (int st = 1; st <= nst; ++st) {
         decode_update_kernel<false><<<grid, DEC_THREADS, smem, stream>>>(p, st);
         e = cudaGetLastError();

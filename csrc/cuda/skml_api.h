@@ -69,6 +69,7 @@ typedef struct SkmlDecodeArgs {
     long long fused;
     long long grid;
     long long max_groups;      // upper bound of the payloads' group count (0 = 32): sizes the work table
+    float* val_scratch;        // decoded values, capacity key_capacity (null: SGD applies payload by payload)
 } SkmlDecodeArgs;
 
 long long skml_decode_workspace_bytes(long long world, long long group_num);

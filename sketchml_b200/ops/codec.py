@@ -148,6 +148,7 @@ class GpuDecoder:
         self.fused, self.grid, self.budget_s = fused, grid, budget_s
         self.acc = torch.zeros(self.dim, dtype=torch.int64, device=self.device)
         self.key_scratch = torch.zeros(self.key_capacity, dtype=torch.int32, device=self.device)
+        self.val_scratch = torch.zeros(self.key_capacity, dtype=torch.float32, device=self.device)
         self.workspace = torch.zeros(256, dtype=torch.uint8, device=self.device)
 
     def reset(self) -> None:
@@ -172,6 +173,7 @@ class GpuDecoder:
         a.workspace, a.status = L.ptr(self.workspace), L.ptr(status)
         a.budget_cycles = L.budget_cycles(self.budget_s)
         a.fused, a.grid, a.max_groups = int(self.fused), self.grid, self.max_groups
+        a.val_scratch = L.ptr(self.val_scratch)
         return a
 
     def decode_update(self, payload_ptrs: Sequence[int], flag_ptrs: Sequence[Optional[int]], slot_capacity: int,
@@ -183,7 +185,7 @@ class GpuDecoder:
                            loss_out, out_sum)
         world = len(payload_ptrs)
         L.check(self.lib.skml_decode_update(C.byref(a), L.stream()), "skml_decode_update")
-        L.count_launches(1 if self.fused else (2 if adam_v is not None else world))
+        L.count_launches(1 if self.fused else (2 if adam_v is not None else (world + 1 if world > 1 else 1)))
 
     def decode_sum(self, payloads: List[torch.Tensor], step: int = 0) -> torch.Tensor:
         """Single-GPU convenience: decodes the given payload buffers (one per rank, rank order)

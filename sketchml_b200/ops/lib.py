@@ -45,7 +45,7 @@ class DecodeArgs(C.Structure):
         ("step", c_ull), ("dim", c_ll), ("w", c_vp), ("adam_m", c_vp), ("adam_v", c_vp), ("lr", c_d),
         ("adam_scale", c_d), ("acc", c_vp), ("key_scratch", c_vp), ("key_capacity", c_ll), ("loss_out", c_vp),
         ("out_sum", c_vp), ("workspace", c_vp), ("status", c_vp), ("budget_cycles", c_ll), ("fused", c_ll),
-        ("grid", c_ll), ("max_groups", c_ll),
+        ("grid", c_ll), ("max_groups", c_ll), ("val_scratch", c_vp),
     ]
 
 

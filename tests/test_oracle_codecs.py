@@ -83,6 +83,17 @@ def test_division_free_hash_equals_exact_hash():
             assert np.array_equal(o.hash(hid, keys, size), o.hash_fast(hid, keys, size))
 
 
+def test_multi_row_hash_equals_exact_hash():
+    rng = np.random.default_rng(1)
+    keys = np.concatenate([rng.integers(0, 2 ** 31 - 1, 20000), rng.integers(0, 1000, 2000),
+                           [0, 1, 9, 10, 99, 100, 2147483647, -5]]).astype(np.int32)
+    for size in (1, 7, 1000, 300001, 2147483647):
+        for ids in ([0, 1, 2], [3, 4, 5], [7, 2, 6], [5], [0, 3], [3, 4, 5, 6], [0, 1, 2, 3, 4, 5, 6, 7], [6, 0, 7, 1, 5]):
+            got = o.hash_rows(ids, keys, size).reshape(len(keys), len(ids))
+            for r, hid in enumerate(ids):
+                assert np.array_equal(got[:, r], o.hash(hid, keys, size)), (ids, size, r)
+
+
 def test_pick_hashes_distinct_and_deterministic():
     for rows in range(1, 9):
         a = o.pick_hashes(5, 7, 1, 3, rows)
