@@ -70,6 +70,8 @@ struct DecSmem {
     int direct;      // linear update (SGD / plain sum): payloads applied in rank order, no accumulators
     unsigned long long rank_chunk_begin[SKML_MAX_PEERS + 1];
     unsigned long long rank_key_begin[SKML_MAX_PEERS + 1];
+    int rank_item_begin[SKML_MAX_PEERS + 1];
+    int ref_item;    // the (rank, group) list with the most keys: its quantiles are the blocks' key-range bounds
     int two_phase;   // direct mode over several payloads: decode everything first, then ordered apply passes
     int shift;       // fixed-point: accumulator = value * 2^shift
     double inv_world;
@@ -180,6 +182,7 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
             const SkmlHeader& h = s.hdr[r];
             s.rank_chunk_begin[r] = chunks;
             s.rank_key_begin[r] = keys;
+            s.rank_item_begin[r] = ni;
             if (h.kind == SKML_KIND_EMPTY) continue;
             mx = fmax(mx, fmax(fabs(h.min_value), fabs(h.max_value)));
             if (h.kind == SKML_KIND_DENSE) {
@@ -216,7 +219,12 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
         for (int r = p.world; r <= SKML_MAX_PEERS; ++r) {
             s.rank_chunk_begin[r] = chunks;
             s.rank_key_begin[r] = keys;
+            s.rank_item_begin[r] = ni;
         }
+        int ref = 0;
+        for (int i = 1; i < ni; ++i)
+            if (s.items[i].e.n > s.items[ref].e.n) ref = i;
+        s.ref_item = ref;
         s.nitems = ni;
         s.total_chunks = chunks;
         s.total_keys = keys;
@@ -404,6 +412,74 @@ __device__ void apply_stashed(const DP& p, unsigned long long begin, unsigned lo
     }
 }
 
+// Barrier-free ordered apply. Every block owns a key range (bounds = quantiles of the longest key
+// list), finds its slice of every (rank, group) list by binary search in the stashed keys, and applies
+// the slices rank by rank with only a block barrier in between: all updates of one coordinate
+// happen in one block, in rank order, so replicas stay bit-identical.
+__device__ void apply_owned(const DP& p, DecSmem& s) {
+    if (s.nitems == 0) return;
+    unsigned long long* seg_b = reinterpret_cast<unsigned long long*>(&s.items[p.max_items]);
+    unsigned long long* seg_e = seg_b + p.max_items;
+    __shared__ unsigned long long s_bound[2];
+    if (threadIdx.x < 2) {
+        const DecItem& ref = s.items[s.ref_item];
+        const unsigned long long b = blockIdx.x + threadIdx.x, B = gridDim.x;
+        unsigned long long v;
+        if (b == 0) v = 0ull;
+        else if (b >= B) v = 1ull << 32;
+        else v = (unsigned long long)(unsigned int)__ldcg(p.key_scratch + ref.key_prefix + b * (unsigned long long)ref.e.n / B);
+        s_bound[threadIdx.x] = v;
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < 2 * s.nitems; t += blockDim.x) {
+        const DecItem& it = s.items[t >> 1];
+        const unsigned long long bound = s_bound[t & 1];
+        const int* list = p.key_scratch + it.key_prefix;
+        unsigned int lo = 0, hi = it.e.n;
+        while (lo < hi) {  // first position whose key is >= bound
+            const unsigned int mid = (lo + hi) >> 1;
+            if ((unsigned long long)(unsigned int)__ldcg(list + mid) < bound) lo = mid + 1;
+            else hi = mid;
+        }
+        ((t & 1) ? seg_e : seg_b)[t >> 1] = it.key_prefix + lo;
+    }
+    __syncthreads();
+    float* dst = p.out_sum ? p.out_sum : p.w;
+    for (int r = 0; r < p.world; ++r) {
+        const int i0 = s.rank_item_begin[r], i1 = s.rank_item_begin[r + 1];
+        unsigned int total = 0;
+        for (int i = i0; i < i1; ++i) total += (unsigned int)(seg_e[i] - seg_b[i]);
+        for (unsigned int q = threadIdx.x; q < total; q += 4 * blockDim.x) {
+            unsigned int k[4];
+            float v[4], old[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                unsigned int qq = q + u * blockDim.x;
+                k[u] = 0xFFFFFFFFu;
+                v[u] = 0.f;
+                if (qq < total) {
+                    int i = i0;
+                    unsigned int len = (unsigned int)(seg_e[i] - seg_b[i]);
+                    while (qq >= len) {  // the groups of one rank hold disjoint keys: their slices are concatenated
+                        qq -= len;
+                        ++i;
+                        len = (unsigned int)(seg_e[i] - seg_b[i]);
+                    }
+                    const unsigned long long pos = seg_b[i] + qq;
+                    k[u] = (unsigned int)__ldcg(p.key_scratch + pos);
+                    v[u] = __ldcg(p.val_scratch + pos);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) old[u] = k[u] < (unsigned long long)p.dim ? dst[k[u]] : 0.f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (k[u] < (unsigned long long)p.dim) dst[k[u]] = p.out_sum ? old[u] + v[u] : old[u] - p.lr * v[u];
+        }
+        __syncthreads();
+    }
+}
+
 // D1 for dense payloads: every coordinate carries a bucket code.
 __device__ void decode_accumulate_dense(const DP& p, DecSmem& s, int r_begin, int r_end) {
     const long long gsz = (long long)gridDim.x * blockDim.x, gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -488,7 +564,11 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_BLOCKS_PER_SM) decode_update_
                     reinterpret_cast<unsigned long long*>(p.ctrl)[10] = t;
                 }
             }
-            // Phase 2 (un-fused: stage r + 2): one apply pass per rank, in rank order.
+            // Phase 2 without dense payloads (un-fused: stage 2): key-range-owned apply, no grid barrier.
+            if (!s.any_dense) {
+                if (FUSED || stage == 2) apply_owned(p, s);
+            } else
+            // Phase 2 with dense payloads (un-fused: stage r + 2): one apply pass per rank, in rank order.
             for (int r = 0; r < p.world; ++r) {
                 if (FUSED || stage == r + 2) {
                     apply_stashed(p, s.rank_key_begin[r], s.rank_key_begin[r + 1]);
@@ -582,7 +662,7 @@ extern "C" int skml_decode_update(const SkmlDecodeArgs* a, void* stream_) {
     long long groups = a->max_groups > 0 ? a->max_groups : SKML_MAX_GROUPS;
     if (groups > SKML_MAX_GROUPS) groups = SKML_MAX_GROUPS;
     p.max_items = (int)(a->world * groups);
-    const size_t smem = sizeof(DecSmem) + (size_t)p.max_items * sizeof(DecItem);
+    const size_t smem = sizeof(DecSmem) + (size_t)p.max_items * (sizeof(DecItem) + 16);
     static int sms = 0;
     static size_t cached_smem = 0;
     static int max_grid = 0;
@@ -591,7 +671,7 @@ extern "C" int skml_decode_update(const SkmlDecodeArgs* a, void* stream_) {
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
-        const int cap = (int)(sizeof(DecSmem) + (size_t)DEC_MAX_ITEMS * sizeof(DecItem));
+        const int cap = (int)(sizeof(DecSmem) + (size_t)DEC_MAX_ITEMS * (sizeof(DecItem) + 16));
         cudaError_t e0 = cudaFuncSetAttribute(decode_update_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
         if (e0 == cudaSuccess)
             e0 = cudaFuncSetAttribute(decode_update_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
