@@ -280,6 +280,38 @@ PYBIND11_MODULE(_oracle, m) {
         }
         return to_array(out);
     });
+    m.def("pack_bits", [](I32Array v, int bits) {
+        // Little-endian bit stream: value i occupies stream bits [i * bits, (i + 1) * bits), stream bit b is
+        // bit (b & 31) of 32-bit word b >> 5. Two zero words of padding follow so that a reader may always
+        // fetch the word after the one a value starts in.
+        if (bits < 1 || bits > 32) throw Error("pack_bits: bits out of range [1, 32]");
+        const size_t n = (size_t)v.size();
+        const size_t words = (n * (size_t)bits + 31) / 32 + 2;
+        std::vector<uint32_t> out(words, 0u);
+        const uint64_t mask = bits == 32 ? 0xFFFFFFFFull : ((1ull << bits) - 1ull);
+        for (size_t i = 0; i < n; ++i) {
+            const uint64_t x = (uint64_t)(uint32_t)v.data()[i];
+            if (x & ~mask) throw Error("pack_bits: value does not fit in " + std::to_string(bits) + " bits");
+            const size_t bit = i * (size_t)bits, w = bit >> 5;
+            const unsigned sh = (unsigned)(bit & 31);
+            const uint64_t wide = x << sh;
+            out[w] |= (uint32_t)wide;
+            out[w + 1] |= (uint32_t)(wide >> 32);
+        }
+        return to_array(out);
+    }, py::arg("values"), py::arg("bits"));
+    m.def("unpack_bits", [](py::array_t<uint32_t, py::array::c_style | py::array::forcecast> w, size_t n, int bits) {
+        if (bits < 1 || bits > 32) throw Error("unpack_bits: bits out of range [1, 32]");
+        if ((n * (size_t)bits + 31) / 32 + 1 > (size_t)w.size()) throw Error("unpack_bits: stream too short");
+        std::vector<int32_t> out(n);
+        const uint64_t mask = bits == 32 ? 0xFFFFFFFFull : ((1ull << bits) - 1ull);
+        for (size_t i = 0; i < n; ++i) {
+            const size_t bit = i * (size_t)bits, k = bit >> 5;
+            const uint64_t wide = (uint64_t)w.data()[k] | ((uint64_t)w.data()[k + 1] << 32);
+            out[i] = (int32_t)((wide >> (bit & 31)) & mask);
+        }
+        return to_array(out);
+    }, py::arg("words"), py::arg("n"), py::arg("bits"));
     m.def("pick_hashes", [](uint64_t seed, uint64_t step, uint32_t rank, uint32_t group, int rows) {
         if (rows > 8 || rows < 1) throw Error("Currently only 8 hash functions are available");
         uint8_t ids[8];

@@ -72,7 +72,8 @@ struct DecSmem {
     unsigned long long rank_key_begin[SKML_MAX_PEERS + 1];
     int rank_item_begin[SKML_MAX_PEERS + 1];
     int ref_item;    // the (rank, group) list with the most keys: its quantiles are the blocks' key-range bounds
-    int two_phase;   // direct mode over several payloads: decode everything first, then ordered apply passes
+    int two_phase;   // several payloads: decode everything first, then ordered apply
+    int adam_plain;  // Adam without fixed-point accumulators (no dense payload, and one payload or a value scratch)
     int shift;       // fixed-point: accumulator = value * 2^shift
     double inv_world;
     int ok;
@@ -230,7 +231,8 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
         s.total_keys = keys;
         s.any_dense = dense;
         s.direct = (p.adam_v == nullptr) ? 1 : 0;
-        s.two_phase = (s.direct && p.world > 1 && p.val_scratch != nullptr) ? 1 : 0;
+        s.adam_plain = (!s.direct && !dense && (p.world == 1 || p.val_scratch != nullptr)) ? 1 : 0;
+        s.two_phase = ((s.direct || s.adam_plain) && p.world > 1 && p.val_scratch != nullptr) ? 1 : 0;
         int e = 0;
         if (mx > 0.0 && isfinite(mx)) frexp(mx, &e);
         s.shift = 60 - e;
@@ -271,11 +273,33 @@ __device__ __forceinline__ float query_one(const DP& p, const DecItem& it, unsig
     return __ldcg(reinterpret_cast<const float*>(it.base + it.off_bv) + res);
 }
 
+// Exclusive prefix sum over the block with ONE barrier: every warp publishes its total, every
+// thread adds up the totals of the warps before it. The caller alternates `part` between calls
+// so that no second barrier is needed to protect it.
+__device__ __forceinline__ unsigned int dec_scan(unsigned int v, unsigned int* part) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned int t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) part[warp] = inc;
+    __syncthreads();
+    unsigned int base = 0;
+#pragma unroll
+    for (int w = 0; w < DEC_THREADS / 32; ++w)
+        if (w < warp) base += part[w];
+    return base + inc - v;
+}
+
 // D1 for sparse payloads: one 1024-key chunk per block iteration, DEC_KPT adjacent keys per
 // thread (256 threads), so that every thread has several independent load chains in flight and
 // several blocks share an SM.
 __device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch_begin, unsigned long long ch_end) {
-    for (unsigned long long ch = ch_begin + blockIdx.x; ch < ch_end; ch += gridDim.x) {
+    __shared__ unsigned int s_part[4][DEC_THREADS / 32];  // [2 scans x chunk parity]
+    int par = 0;
+    for (unsigned long long ch = ch_begin + blockIdx.x; ch < ch_end; ch += gridDim.x, par ^= 1) {
         int it_i = 0;
         while (it_i + 1 < s.nitems && ch >= s.items[it_i + 1].chunk_prefix) ++it_i;
         const DecItem& it = s.items[it_i];
@@ -304,8 +328,7 @@ __device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch
                 }
             }
         }
-        unsigned int total_w;
-        const unsigned int boff = block_exclusive_scan<unsigned int>(wsum, &total_w);
+        const unsigned int boff = dec_scan(wsum, s_part[par]);
         unsigned int d[DEC_KPT];
 #pragma unroll
         for (int u = 0; u < DEC_KPT; ++u) d[u] = 0;
@@ -337,8 +360,7 @@ __device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch
         unsigned int dsum = 0;
 #pragma unroll
         for (int u = 0; u < DEC_KPT; ++u) dsum += d[u];
-        unsigned int total_d;
-        const unsigned int dex = block_exclusive_scan<unsigned int>(dsum, &total_d);
+        const unsigned int dex = dec_scan(dsum, s_part[2 + par]);
         if (i0 < cnt) {
             unsigned int key = rs.prev_key + dex;
             int* ks = p.key_scratch + it.key_prefix + first;
@@ -354,7 +376,7 @@ __device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch
                     live[u] = false;
                     keys[u] = 0xFFFFFFFFu;
                 }
-                if (!s.direct && i0 + u < cnt) ks[i0 + u] = (int)keys[u];
+                if (!s.direct && !s.adam_plain && i0 + u < cnt) ks[i0 + u] = (int)keys[u];
             }
             float bv[DEC_KPT];
 #pragma unroll
@@ -372,6 +394,10 @@ __device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch
 #pragma unroll
                 for (int u = 0; u < DEC_KPT; ++u)
                     if (live[u]) apply_direct(p, keys[u], bv[u] * (float)s.inv_world);
+            } else if (s.adam_plain) {  // single payload: the decoded value is the whole gradient of its key
+#pragma unroll
+                for (int u = 0; u < DEC_KPT; ++u)
+                    if (live[u] && bv[u] != 0.f) apply_one(p, keys[u], bv[u] * (float)s.inv_world);
             } else {
 #pragma unroll
                 for (int u = 0; u < DEC_KPT; ++u) {
@@ -380,8 +406,9 @@ __device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch
                 }
             }
         }
-        __syncthreads();
+        // no barrier here: the next chunk's scans use the other parity of s_part
     }
+    __syncthreads();
 }
 
 // Ordered apply of one rank's stashed (key, value) pairs: keys are unique inside a payload, so the
@@ -410,6 +437,54 @@ __device__ void apply_stashed(const DP& p, unsigned long long begin, unsigned lo
                 else p.w[k[u]] = old[u] - p.lr * v[u];
             }
     }
+}
+
+// One rank's slice of the block's key range. OP 0: SGD step / plain sum; OP 1: add into the float
+// accumulators; OP 2: Adam update of every coordinate whose accumulated sum is non-zero, then clear it.
+// The groups of one rank hold disjoint keys, so their slices are walked as one concatenated list,
+// four independent entries per thread and iteration; a block barrier ends the pass.
+template <int OP>
+__device__ __forceinline__ void owned_pass(const DP& p, DecSmem& s, const unsigned long long* seg_b,
+                                           const unsigned long long* seg_e, int r) {
+    const int i0 = s.rank_item_begin[r], i1 = s.rank_item_begin[r + 1];
+    float* dst = OP == 0 ? (p.out_sum ? p.out_sum : p.w) : reinterpret_cast<float*>(p.acc);
+    unsigned int total = 0;
+    for (int i = i0; i < i1; ++i) total += (unsigned int)(seg_e[i] - seg_b[i]);
+    for (unsigned int q = threadIdx.x; q < total; q += 4 * blockDim.x) {
+        unsigned int k[4];
+        float v[4], old[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            unsigned int qq = q + u * blockDim.x;
+            k[u] = 0xFFFFFFFFu;
+            v[u] = 0.f;
+            if (qq < total) {
+                int i = i0;
+                unsigned int len = (unsigned int)(seg_e[i] - seg_b[i]);
+                while (qq >= len) {
+                    qq -= len;
+                    ++i;
+                    len = (unsigned int)(seg_e[i] - seg_b[i]);
+                }
+                const unsigned long long pos = seg_b[i] + qq;
+                k[u] = (unsigned int)__ldcg(p.key_scratch + pos);
+                if (OP != 2) v[u] = __ldcg(p.val_scratch + pos);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) old[u] = k[u] < (unsigned long long)p.dim ? dst[k[u]] : 0.f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (k[u] >= (unsigned long long)p.dim) continue;
+            if (OP == 0) dst[k[u]] = p.out_sum ? old[u] + v[u] : old[u] - p.lr * v[u];
+            else if (OP == 1) dst[k[u]] = old[u] + v[u];
+            else if (old[u] != 0.f) {
+                dst[k[u]] = 0.f;
+                apply_one(p, k[u], old[u]);
+            }
+        }
+    }
+    __syncthreads();
 }
 
 // Barrier-free ordered apply. Every block owns a key range (bounds = quantiles of the longest key
@@ -444,39 +519,14 @@ __device__ void apply_owned(const DP& p, DecSmem& s) {
         ((t & 1) ? seg_e : seg_b)[t >> 1] = it.key_prefix + lo;
     }
     __syncthreads();
-    float* dst = p.out_sum ? p.out_sum : p.w;
-    for (int r = 0; r < p.world; ++r) {
-        const int i0 = s.rank_item_begin[r], i1 = s.rank_item_begin[r + 1];
-        unsigned int total = 0;
-        for (int i = i0; i < i1; ++i) total += (unsigned int)(seg_e[i] - seg_b[i]);
-        for (unsigned int q = threadIdx.x; q < total; q += 4 * blockDim.x) {
-            unsigned int k[4];
-            float v[4], old[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                unsigned int qq = q + u * blockDim.x;
-                k[u] = 0xFFFFFFFFu;
-                v[u] = 0.f;
-                if (qq < total) {
-                    int i = i0;
-                    unsigned int len = (unsigned int)(seg_e[i] - seg_b[i]);
-                    while (qq >= len) {  // the groups of one rank hold disjoint keys: their slices are concatenated
-                        qq -= len;
-                        ++i;
-                        len = (unsigned int)(seg_e[i] - seg_b[i]);
-                    }
-                    const unsigned long long pos = seg_b[i] + qq;
-                    k[u] = (unsigned int)__ldcg(p.key_scratch + pos);
-                    v[u] = __ldcg(p.val_scratch + pos);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) old[u] = k[u] < (unsigned long long)p.dim ? dst[k[u]] : 0.f;
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-                if (k[u] < (unsigned long long)p.dim) dst[k[u]] = p.out_sum ? old[u] + v[u] : old[u] - p.lr * v[u];
-        }
-        __syncthreads();
+    if (p.adam_v) {
+        // Adam: sum the ranks' values per coordinate in rank order (plain floats in the zeroed
+        // accumulator array), then let the first rank that holds a coordinate apply the update
+        // and clear the sum.
+        for (int r = 0; r < p.world; ++r) owned_pass<1>(p, s, seg_b, seg_e, r);
+        for (int r = 0; r < p.world; ++r) owned_pass<2>(p, s, seg_b, seg_e, r);
+    } else {
+        for (int r = 0; r < p.world; ++r) owned_pass<0>(p, s, seg_b, seg_e, r);
     }
 }
 
@@ -552,7 +602,7 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_BLOCKS_PER_SM) decode_update_
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
         reinterpret_cast<unsigned long long*>(p.ctrl)[9] = t;
     }
-    if (s.direct) {
+    if (s.direct || s.adam_plain) {
         if (s.two_phase) {
             // Phase 1 (un-fused: stage 1): every payload's keys and values, no ordering needed.
             if (FUSED || stage == 1) decode_accumulate(p, s, 0, s.total_chunks);

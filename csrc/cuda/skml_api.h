@@ -106,6 +106,12 @@ int skml_colsum(const int* colptr, const int* rowidx, const float* svals, const 
                 int n_cols, const float* coef, const float* w, float lambda, float* out, void* stream);
 int skml_sm_count();
 
+// Expands a minibatch from its transport form (bit-packed column indices, 32-bit row pointers,
+// 8-bit labels; the latter two optional = null) into CSR arrays. `packed` must end with two
+// padding words.
+int skml_unpack_batch(const unsigned int* packed, int bits, long long nnz, int* cols, const int* rowptr32,
+                      long long rows, long long* rowptr, const signed char* labels8, float* labels, void* stream);
+
 // FixedPoint baseline compressor: b-bit sign + magnitude codes (2 <= bits < 30), 8 values per
 // `bits` bytes, most significant bit first in java.util.BitSet order. `scratch` holds
 // skml_fixedpoint_scratch_bytes() bytes; `norm_out` receives the L2 norm the codes are relative to.

@@ -96,3 +96,45 @@ def test_transposed_index_path_trains_like_scatter_path():
     # to run; bucket boundaries and sketch collisions amplify that to a few 1e-3 of the loss
     assert np.allclose(h_t["train_loss"], h_s["train_loss"], rtol=1e-2)
     assert float((w_t - w_s).abs().mean()) < 2e-3
+
+
+def test_packed_batch_transport_matches_plain_and_trains():
+    """The bit-packed host->device batch form expands to exactly the plain CSR arrays, and a
+    streamed run through it equals a streamed run through the plain form."""
+    from sketchml_b200.data import HostBatchFeeder, PinnedBatch, SyntheticSpec, generate_cpu
+    from sketchml_b200.data.dataset import CSRMatrix
+    from sketchml_b200.trainer import Trainer
+    spec = SyntheticSpec(6000, 40001, 12, 1.1, "binary", "logistic", 0.1, 0.0, 5)
+    m, _ = generate_cpu(spec)
+    B = 1500
+    parts = []
+    for i in range(4):
+        lo, hi = int(m.rowptr[i * B]), int(m.rowptr[(i + 1) * B])
+        parts.append(CSRMatrix(m.rowptr[i * B:(i + 1) * B + 1].clone(), m.cols[lo:hi].clone(), None,
+                               m.labels[i * B:(i + 1) * B].clone(), m.dim))
+    plain = HostBatchFeeder([PinnedBatch(p) for p in parts], "cuda")
+    packed = HostBatchFeeder([PinnedBatch(p, packed=True) for p in parts], "cuda")
+    assert packed.batches[0].bits == 16 and packed.batches[0].labels8
+    assert packed.batches[0].h2d_bytes() < 0.62 * plain.batches[0].h2d_bytes()
+    for i in range(4):
+        plain.prefetch(i)
+        packed.prefetch(i)
+        a, rows = plain.get(i)
+        b, rows_b = packed.get(i)
+        torch.cuda.synchronize()
+        assert rows == rows_b == B
+        n = parts[i].nnz
+        assert torch.equal(a.rowptr[:B + 1], b.rowptr[:B + 1])
+        assert torch.equal(a.cols[:n], b.cols[:n])
+        assert torch.equal(a.labels[:B], b.labels[:B])
+        plain.release(i)
+        packed.release(i)
+    ws = []
+    for feeder in (plain, packed):
+        t = Trainer(_conf(feature_num=m.dim, compressor="None", valid_ratio=0.0, batch_sample_ratio=0.25))
+        t.load_data(m)
+        t.train_streamed(feeder, 4)
+        torch.cuda.synchronize()
+        ws.append(t.model.weights.detach().cpu().clone())
+        t.close()
+    assert float((ws[0] - ws[1]).abs().max()) < 1e-6

@@ -355,3 +355,15 @@ def test_sort_helpers():
     assert o.unique_sorted(np.array([1.0, 1.0, 2.0, 2.0, 3.0])).tolist() == [1.0, 2.0, 3.0]
     with pytest.raises(o.SketchMLError):
         o.quick_select(a, 6)
+
+
+def test_pack_bits_roundtrip():
+    rng = np.random.default_rng(3)
+    for bits in (1, 5, 16, 26, 31, 32):
+        hi = (1 << bits) - 1 if bits < 32 else (1 << 31) - 1
+        v = rng.integers(0, hi, 1001, endpoint=True).astype(np.int64).astype(np.uint32).view(np.int32)
+        w = o.pack_bits(v, bits)
+        assert w.dtype == np.uint32 and len(w) == (len(v) * bits + 31) // 32 + 2
+        assert np.array_equal(o.unpack_bits(w, len(v), bits), v)
+    with pytest.raises(Exception):
+        o.pack_bits(np.array([8], dtype=np.int32), 3)
