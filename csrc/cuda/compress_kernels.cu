@@ -440,13 +440,35 @@ __device__ void stage_query(const CP& p, Smem& s, long long n) {
         s.runs_w[t] = p.run_w[t];
     }
     __syncthreads();
-    for (int t = threadIdx.x; t < nb * SK_K; t += blockDim.x) {
-        int c = t / SK_K, i = t % SK_K;
-        s.runs_all[t] = i < (int)s.runs_cnt[c] ? __ldcg(p.run_vals + t) : 0xFFFFFFFFu;
+    {
+        // all published runs -> shared memory, 16 bytes per load and several loads in flight per thread
+        const uint4* src = reinterpret_cast<const uint4*>(p.run_vals);
+        const int nv = nb * (SK_K / 4);
+        for (int t0 = threadIdx.x; t0 < nv; t0 += 4 * blockDim.x) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int t = t0 + u * blockDim.x;
+                v[u] = t < nv ? ld_cg_v4(src + t) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int t = t0 + u * blockDim.x;
+                if (t >= nv) continue;
+                const int c = (4 * t) / SK_K, i = (4 * t) % SK_K, cnt = (int)s.runs_cnt[c];
+                s.runs_all[4 * t] = i < cnt ? v[u].x : 0xFFFFFFFFu;
+                s.runs_all[4 * t + 1] = i + 1 < cnt ? v[u].y : 0xFFFFFFFFu;
+                s.runs_all[4 * t + 2] = i + 2 < cnt ? v[u].z : 0xFFFFFFFFu;
+                s.runs_all[4 * t + 3] = i + 3 < cnt ? v[u].w : 0xFFFFFFFFu;
+            }
+        }
     }
     __syncthreads();
+    // total weight: every warp sums a strided share, lanes combine by shuffle (all threads need it)
     unsigned long long Wtot = 0;
-    for (int c = 0; c < nb; ++c) Wtot += (unsigned long long)s.runs_cnt[c] * s.runs_w[c];
+    for (int c = threadIdx.x & 31; c < nb; c += 32) Wtot += (unsigned long long)s.runs_cnt[c] * s.runs_w[c];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) Wtot += __shfl_xor_sync(0xFFFFFFFFu, Wtot, o);
     const double inv_q = 1.0 / (double)p.q;
     const int i = threadIdx.x & (SK_K - 1), part = threadIdx.x / SK_K, parts = blockDim.x / SK_K;
     for (int c = blockIdx.x; c < nb; c += gridDim.x) {

@@ -270,7 +270,10 @@ __device__ __forceinline__ float query_one(const DP& p, const DecItem& it, unsig
             res = cells[r];
         }
     }
-    return __ldcg(reinterpret_cast<const float*>(it.base + it.off_bv) + res);
+    // Bucket values (<= 16 KB per payload, read by every key) go through L1: the SM cannot hold a stale
+    // line of them, because it first touches a payload after the arrival flag was acquired and L1 is
+    // invalidated between dependent grids. Everything else of the payload is read once: L2 only.
+    return reinterpret_cast<const float*>(it.base + it.off_bv)[res];
 }
 
 // Exclusive prefix sum over the block with ONE barrier: every warp publishes its total, every
