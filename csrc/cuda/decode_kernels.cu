@@ -29,6 +29,7 @@
 #define DEC_KPT 4        // keys of a 1024-key chunk per thread
 #define DEC_THREADS (SKML_RESTART_INTERVAL / DEC_KPT)
 #define DEC_BLOCKS_PER_SM 4
+#define DEC_TAB_SMEM 36864   // bytes of shared memory per block for a staged sketch table
 
 struct DP {
     const unsigned char* payload[SKML_MAX_PEERS];
@@ -51,6 +52,7 @@ struct DP {
     unsigned int* status;
     long long budget;
     int max_items;
+    int tab_off;     // byte offset of the staged-table area inside the dynamic shared memory (0 = none)
 };
 
 struct DecItem {  // one (rank, group) key stream
@@ -159,7 +161,8 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
             }
             if (it.e.n) {
                 const unsigned long long lim = h.total_bytes;
-                const bool good = it.e.col_num > 0 && it.e.table_off + (unsigned long long)h.row_num * it.e.col_num * (h.cell_bits / 8) <= lim &&
+                const bool good = it.e.col_num > 0 && (unsigned long long)h.row_num * it.e.col_num < (1ull << 31) &&
+                                  it.e.table_off + (unsigned long long)h.row_num * it.e.col_num * (h.cell_bits / 8) <= lim &&
                                   it.e.flag_off + 8ull * it.e.n_flag_words <= lim && it.e.delta_off + 8ull * it.e.n_delta_words <= lim &&
                                   it.e.restart_off + 16ull * ((it.e.n + SKML_RESTART_INTERVAL - 1) / SKML_RESTART_INTERVAL) <= lim &&
                                   2ull * it.e.n <= 64ull * it.e.n_flag_words;
@@ -232,7 +235,13 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
         s.any_dense = dense;
         s.direct = (p.adam_v == nullptr) ? 1 : 0;
         s.adam_plain = (!s.direct && !dense && (p.world == 1 || p.val_scratch != nullptr)) ? 1 : 0;
-        s.two_phase = ((s.direct || s.adam_plain) && p.world > 1 && p.val_scratch != nullptr) ? 1 : 0;
+        // Several payloads are decoded into the scratch first and applied by key range when a per-rank
+        // pass would leave most blocks with one chunk or none (the pass latency then dominates). Long
+        // payloads keep the blocks busy in per-rank passes and skip the scratch round trip; Adam has no
+        // per-rank mode, so it always takes the scratch.
+        const bool small_passes = chunks < 4ull * gridDim.x * (unsigned long long)p.world;
+        s.two_phase = ((s.direct || s.adam_plain) && p.world > 1 && p.val_scratch != nullptr &&
+                       (small_passes || s.adam_plain)) ? 1 : 0;
         int e = 0;
         if (mx > 0.0 && isfinite(mx)) frexp(mx, &e);
         s.shift = 60 - e;
@@ -243,26 +252,32 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
 }
 
 // Query of one key in its group's sketch: the bucket value of the cell farthest from the zero bucket.
-__device__ __forceinline__ float query_one(const DP& p, const DecItem& it, unsigned int key) {
+template <int MAXR>
+__device__ __forceinline__ float query_one(const DP& p, const DecItem& it, unsigned int key, const unsigned char* stab) {
     const int col = (int)it.e.col_num;
     const int zero = (int)it.zero;
-    int cells[SKML_MAX_ROWS];
-    int pos[SKML_MAX_ROWS];
+    int cells[MAXR];
+    int pos[MAXR];
     const int rows = (int)it.rows;
-    if (rows <= 4) skml_hash_rows<4>(it.e.hash_ids, rows, (int)key, col, it.col_magic, pos);
-    else skml_hash_rows<SKML_MAX_ROWS>(it.e.hash_ids, rows, (int)key, col, it.col_magic, pos);
+    skml_hash_rows<MAXR>(it.e.hash_ids, rows, (int)key, col, it.col_magic, pos);
 #pragma unroll
-    for (int r = 0; r < SKML_MAX_ROWS; ++r) {  // independent loads first
+    for (int r = 0; r < MAXR; ++r) {  // independent loads first
         cells[r] = zero;
         if (r < rows) {
-            const unsigned long long c = (unsigned long long)r * col + (unsigned int)pos[r];
-            if (it.cell_bits == 8) cells[r] = __ldcg(it.base + it.e.table_off + c);
-            else cells[r] = __ldcg(reinterpret_cast<const unsigned short*>(it.base + it.e.table_off) + c);
+            const unsigned int c = (unsigned int)r * (unsigned int)col + (unsigned int)pos[r];  // rows * col < 2^31 (checked in prepare)
+            if (stab) {  // the group's whole table sits in shared memory
+                if (it.cell_bits == 8) cells[r] = stab[c];
+                else cells[r] = reinterpret_cast<const unsigned short*>(stab)[c];
+            } else if (it.cell_bits == 8) {
+                cells[r] = __ldcg(it.base + it.e.table_off + c);
+            } else {
+                cells[r] = __ldcg(reinterpret_cast<const unsigned short*>(it.base + it.e.table_off) + c);
+            }
         }
     }
     int res = zero, best = 0;
 #pragma unroll
-    for (int r = 0; r < SKML_MAX_ROWS; ++r) {
+    for (int r = 0; r < MAXR; ++r) {
         int d = cells[r] - zero;
         if (d < 0) d = -d;
         if (d > best) {
@@ -302,10 +317,32 @@ __device__ __forceinline__ unsigned int dec_scan(unsigned int v, unsigned int* p
 __device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch_begin, unsigned long long ch_end) {
     __shared__ unsigned int s_part[4][DEC_THREADS / 32];  // [2 scans x chunk parity]
     int par = 0;
-    for (unsigned long long ch = ch_begin + blockIdx.x; ch < ch_end; ch += gridDim.x, par ^= 1) {
-        int it_i = 0;
+    // Every block takes a contiguous run of chunks, so that consecutive chunks belong to the same
+    // (rank, group) list and its sketch table, when it fits, is staged in shared memory once and
+    // then queried there: three random L2 sectors per key become one coalesced read of the table.
+    const unsigned long long per = (ch_end - ch_begin + gridDim.x - 1) / gridDim.x;
+    const unsigned long long my_begin = ch_begin + per * blockIdx.x;
+    const unsigned long long my_end = my_begin + per < ch_end ? my_begin + per : ch_end;
+    unsigned char* tab_area = p.tab_off ? reinterpret_cast<unsigned char*>(&s) + p.tab_off : nullptr;
+    int staged = -1, it_i = 0;
+    const unsigned char* stab = nullptr;
+    for (unsigned long long ch = my_begin; ch < my_end; ++ch, par ^= 1) {
         while (it_i + 1 < s.nitems && ch >= s.items[it_i + 1].chunk_prefix) ++it_i;
         const DecItem& it = s.items[it_i];
+        if (it_i != staged) {
+            staged = it_i;
+            const unsigned long long tbytes = (unsigned long long)it.rows * it.e.col_num * (it.cell_bits / 8);
+            stab = nullptr;
+            if (tab_area && tbytes <= DEC_TAB_SMEM) {
+                __syncthreads();  // the previous table's readers are done
+                const uint4* src = reinterpret_cast<const uint4*>(it.base + it.e.table_off);
+                uint4* dst = reinterpret_cast<uint4*>(tab_area);
+                const int nv = (int)((tbytes + 15) / 16);  // table sections are padded to 16 bytes
+                for (int t = threadIdx.x; t < nv; t += blockDim.x) dst[t] = ld_cg_v4(src + t);
+                __syncthreads();
+                stab = tab_area;
+            }
+        }
         const unsigned int j = (unsigned int)(ch - it.chunk_prefix);
         const unsigned int first = j * SKML_RESTART_INTERVAL;
         const unsigned int cnt = min((unsigned int)SKML_RESTART_INTERVAL, it.e.n - first);
@@ -382,8 +419,13 @@ __device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch
                 if (!s.direct && !s.adam_plain && i0 + u < cnt) ks[i0 + u] = (int)keys[u];
             }
             float bv[DEC_KPT];
+            if (it.rows <= 4) {
 #pragma unroll
-            for (int u = 0; u < DEC_KPT; ++u) bv[u] = live[u] ? query_one(p, it, keys[u]) : 0.f;
+                for (int u = 0; u < DEC_KPT; ++u) bv[u] = live[u] ? query_one<4>(p, it, keys[u], stab) : 0.f;
+            } else {
+#pragma unroll
+                for (int u = 0; u < DEC_KPT; ++u) bv[u] = live[u] ? query_one<SKML_MAX_ROWS>(p, it, keys[u], stab) : 0.f;
+            }
             if (s.two_phase) {
                 // stash (key, value): the ordered apply passes read them back coalesced
                 float* vs = p.val_scratch + it.key_prefix + first;
@@ -715,7 +757,10 @@ extern "C" int skml_decode_update(const SkmlDecodeArgs* a, void* stream_) {
     long long groups = a->max_groups > 0 ? a->max_groups : SKML_MAX_GROUPS;
     if (groups > SKML_MAX_GROUPS) groups = SKML_MAX_GROUPS;
     p.max_items = (int)(a->world * groups);
-    const size_t smem = sizeof(DecSmem) + (size_t)p.max_items * (sizeof(DecItem) + 16);
+    // dynamic shared memory: work table, two slice bounds per entry, then the staged-table area
+    const size_t smem_items = (sizeof(DecSmem) + (size_t)p.max_items * (sizeof(DecItem) + 16) + 15) & ~(size_t)15;
+    p.tab_off = (int)smem_items;
+    const size_t smem = smem_items + DEC_TAB_SMEM;
     static int sms = 0;
     static size_t cached_smem = 0;
     static int max_grid = 0;
@@ -724,7 +769,7 @@ extern "C" int skml_decode_update(const SkmlDecodeArgs* a, void* stream_) {
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
-        const int cap = (int)(sizeof(DecSmem) + (size_t)DEC_MAX_ITEMS * (sizeof(DecItem) + 16));
+        const int cap = (int)(sizeof(DecSmem) + (size_t)DEC_MAX_ITEMS * (sizeof(DecItem) + 16) + 16 + DEC_TAB_SMEM);
         cudaError_t e0 = cudaFuncSetAttribute(decode_update_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
         if (e0 == cudaSuccess)
             e0 = cudaFuncSetAttribute(decode_update_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
