@@ -1254,6 +1254,16 @@ static int fill_params(const SkmlCompressArgs* a, CP& p, int& grid) {
     return 0;
 }
 
+// Byte offset, inside the workspace, of the q - 1 split points the last launch queried from its
+// summary (order-preserving 32-bit images of the floats, before duplicates are dropped). Debug
+// tooling reads them to recompute a payload on the CPU from the same splits.
+extern "C" long long skml_compress_splits_offset(long long n_max, long long bin_num, long long group_num,
+                                                 long long row_num, double col_ratio, long long grid) {
+    long long g = grid > 0 ? grid : device_sms();
+    if (g > MAX_GRID) g = MAX_GRID;
+    return ws_layout(n_max, bin_num, group_num, row_num, col_ratio, g).splits_raw;
+}
+
 // Function attributes and the co-residency limit are looked up once per kernel (one process
 // drives one GPU), so a steady-state launch makes a single runtime call.
 struct LaunchCache {

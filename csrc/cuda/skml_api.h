@@ -43,6 +43,8 @@ long long skml_compress_workspace_bytes(long long n_max, long long bin_num, long
                                         double col_ratio, long long grid);
 long long skml_payload_capacity(long long n_max, long long dim, long long bin_num, long long group_num,
                                 long long row_num, double col_ratio);
+long long skml_compress_splits_offset(long long n_max, long long bin_num, long long group_num, long long row_num,
+                                      double col_ratio, long long grid);
 int skml_compress_sparse(const SkmlCompressArgs* args, void* stream);
 int skml_compress_dense(const SkmlCompressArgs* args, void* stream);
 

@@ -281,6 +281,7 @@ class GpuEngine:
             self._launch_fast_step(step, lr, adam_scale, ring.data_ptr())
             if self.conf.extras.get("check_status_every_step", False):
                 self.check()
+            self._maybe_shadow(step, st, self._last_index)
         elif self.mode == "sketch":
             par = self.batch_index & 1
             if getattr(self, "depth", 0) == 1:
@@ -298,6 +299,8 @@ class GpuEngine:
                 self.ev_applied[par].record()
             if self.conf.extras.get("check_status_every_step", comm.world > 1 and bool(self.t.injector)):
                 self.check()
+            if not skip:
+                self._maybe_shadow(step, st, None)
         if self.mode != "sketch" and self.value_quant:
             self._quantize_values(step)
         if self.mode == "nccl_kv" and self.fp_codec is not None:
@@ -329,6 +332,28 @@ class GpuEngine:
                 update_sparse(m.weights, st.keys, st.vals, st.meta, self.n_max, 1.0, lr, am, av, adam_scale)
             ring.copy_(st.partials)
         self.batch_index += 1
+
+    def _maybe_shadow(self, step: int, st, index) -> None:
+        """Debug mode `extras={"shadow_every": k}`: every k-th step this rank's payload is recomputed
+        by the CPU oracle from the same keys, values and split points and compared bit for bit
+        (synchronises; raises `ShadowMismatch`)."""
+        k = int(self.conf.extras.get("shadow_every", 0) or 0)
+        if k <= 0 or step % k:
+            return
+        from .utils.shadow import check_payload
+        self.sync()
+        self.check()
+        if index is not None:
+            n, keys, kind = index.n_cols, index.ucols, 1
+        else:
+            n, keys, kind = int(st.meta[0]), st.keys, int(st.meta[1])
+        if kind != 1 or n == 0:
+            return
+        conf = self.conf
+        payload = self.comp.payload_bytes(self.xchg.local_slot(step, self.t.comm.rank))
+        check_payload(payload, keys[:n].cpu().numpy(), st.vals[:n].cpu().numpy(), conf.feature_num, self.comp.last_splits(),
+                      conf.sketch_group_num, conf.sketch_row_num, conf.sketch_col_ratio, self.comp.seed)
+        self.shadow_checks = getattr(self, "shadow_checks", 0) + 1
 
     def _exchange_fixed_point(self, step, lr, am, av, adam_scale, ring) -> None:
         """FixedPoint baseline: packed b-bit codes and raw keys are what crosses NVLink."""

@@ -129,6 +129,19 @@ class GpuCompressor:
             check_status(st, "in the compress kernel")
         return buf
 
+    def last_splits(self):
+        """The distinct split points the last launch used (float32 numpy array, ascending): the
+        q - 1 queried order statistics with duplicates dropped, read back from the workspace
+        (synchronises). Not meaningful after a launch that was given its splits."""
+        off = int(self.lib.skml_compress_splits_offset(self.n_max, self.bin_num, self.group_num, self.row_num,
+                                                       self.col_ratio, self.grid))
+        raw = self.workspace[off:off + 4 * (self.bin_num - 1)].cpu().numpy().view(np.uint32)
+        bits = np.where(raw & np.uint32(0x80000000), raw & np.uint32(0x7FFFFFFF), ~raw).astype(np.uint32)
+        v = bits.view(np.float32)
+        keep = np.ones(len(v), dtype=bool)
+        keep[1:] = v[1:] != v[:-1]
+        return v[keep]
+
     @staticmethod
     def payload_bytes(buf: torch.Tensor) -> bytes:
         head = buf[:256].cpu().numpy().tobytes()

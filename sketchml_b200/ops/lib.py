@@ -66,6 +66,7 @@ class StepArgs(C.Structure):
 _SIGS = {
     "skml_compress_workspace_bytes": (c_ll, [c_ll, c_ll, c_ll, c_ll, c_d, c_ll]),
     "skml_payload_capacity": (c_ll, [c_ll, c_ll, c_ll, c_ll, c_ll, c_d]),
+    "skml_compress_splits_offset": (c_ll, [c_ll, c_ll, c_ll, c_ll, c_d, c_ll]),
     "skml_compress_sparse": (c_int, [C.POINTER(CompressArgs), c_vp]),
     "skml_compress_dense": (c_int, [C.POINTER(CompressArgs), c_vp]),
     "skml_decode_workspace_bytes": (c_ll, [c_ll, c_ll]),

@@ -138,3 +138,31 @@ def test_packed_batch_transport_matches_plain_and_trains():
         ws.append(t.model.weights.detach().cpu().clone())
         t.close()
     assert float((ws[0] - ws[1]).abs().max()) < 1e-6
+
+
+@pytest.mark.parametrize("transposed", [True, False])
+def test_shadow_mode_recomputes_every_payload_on_the_cpu(transposed):
+    """Debug mode: each step's payload equals the oracle's for the same keys, values and splits."""
+    kw = dict(compressor="Sketch", epoch_num=1, valid_ratio=0.0, syn_rows=20000, batch_sample_ratio=0.1,
+              extras={"shadow_every": 1, "transposed_index": transposed})
+    h, w, t = _train(_conf(**kw))
+    assert t.engine.shadow_checks == 10
+    assert (t.engine.tindex is not None) == transposed
+
+
+def test_shadow_compare_reports_a_wrong_payload():
+    from sketchml_b200.ops import GpuCompressor
+    from sketchml_b200.utils.shadow import ShadowMismatch, check_payload, compare_payload
+    rng = np.random.default_rng(0)
+    dim, n = 100000, 6000
+    keys = np.sort(rng.choice(dim, n, replace=False)).astype(np.int32)
+    vals = rng.laplace(0, 1e-3, n).astype(np.float32)
+    comp = GpuCompressor(dim, n, 128, 8, 3, 0.2, seed=9)
+    buf = comp.compress_local(torch.from_numpy(keys).cuda(), torch.from_numpy(vals).cuda(), step=4, rank=1, world=2)
+    payload = comp.payload_bytes(buf)
+    splits = comp.last_splits()
+    assert compare_payload(payload, keys, vals, dim, splits, 8, 3, 0.2, 9) == []
+    wrong = vals.copy()
+    wrong[::7] *= -3.0
+    with pytest.raises(ShadowMismatch):
+        check_payload(payload, keys, wrong, dim, splits, 8, 3, 0.2, 9)
