@@ -159,7 +159,9 @@ def main():
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     a.record()
+    t_issue = time.perf_counter()
     run_steps(args.steps)
+    t_issue = time.perf_counter() - t_issue  # host time to enqueue the steps (the device runs behind)
     b.record()
     barrier()
     ms = a.elapsed_time(b)
@@ -198,6 +200,7 @@ def main():
             "loss_first_last": [float(losses[0, 1] / max(float(losses[0, 0]), 1)),
                                 float(losses[-1, 1] / max(float(losses[-1, 0]), 1))] if len(losses) else None,
             "datagen_s": t_gen, "stage_us_last_step_rank0": stages,
+            "host_issue_ms_per_step_rank0": 1e3 * t_issue / args.steps,
         }
         if e2e is not None:
             out["e2e"] = e2e
@@ -243,8 +246,7 @@ def run_e2e(args, trainer, csr, dev, world, barrier):
     eng.check()
     return {"value": B * world * args.steps / (ms / 1e3), "unit": "samples/s", "ms_per_step": ms / args.steps,
             "h2d_bytes_per_step": batches[0].h2d_bytes(), "d2h_bytes_per_step": 32,
-            "input_transport": f"rowptr int32, labels {'int8' if batches[0].labels8 else 'fp32'}, "
-                               f"column indices bit-packed at {batches[0].bits} bits, expanded on the device",
+            "input_transport": batches[0].transport(),
             "last_loss": float(loss_host[-1, 1] / max(float(loss_host[-1, 0]), 1.0))}
 
 

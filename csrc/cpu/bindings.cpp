@@ -312,6 +312,49 @@ PYBIND11_MODULE(_oracle, m) {
         }
         return to_array(out);
     }, py::arg("words"), py::arg("n"), py::arg("bits"));
+    m.def("pack_varbytes", [](I32Array v) {
+        // Byte-aligned variable-width code for non-negative integers: value i takes 1..4 little-endian
+        // bytes (the fewest that hold it); its width - 1 sits in bits [2 (i & 15), 2 (i & 15) + 2) of
+        // 32-bit flag word i >> 4; `block_offsets[b]` is the byte offset of value 1024 b, so that blocks
+        // of 1024 values decode independently. The byte stream ends with 24 bytes of padding (a reader fetches five aligned words per 4 values).
+        const size_t n = (size_t)v.size();
+        std::vector<uint32_t> flags((n + 15) / 16 + 1, 0u);
+        std::vector<uint32_t> offs((n + 1023) / 1024 + 1, 0u);
+        std::vector<uint8_t> bytes;
+        bytes.reserve(n * 2 + 16);
+        for (size_t i = 0; i < n; ++i) {
+            if ((i & 1023) == 0) offs[i >> 10] = (uint32_t)bytes.size();
+            const int32_t sv = v.data()[i];
+            if (sv < 0) throw Error("pack_varbytes: negative value");
+            const uint32_t x = (uint32_t)sv;
+            const int w = x < (1u << 8) ? 1 : (x < (1u << 16) ? 2 : (x < (1u << 24) ? 3 : 4));
+            flags[i >> 4] |= (uint32_t)(w - 1) << (2 * (i & 15));
+            for (int j = 0; j < w; ++j) bytes.push_back((uint8_t)(x >> (8 * j)));
+            if (bytes.size() > 0xFFFFFF00ull) throw Error("pack_varbytes: stream too long");
+        }
+        offs[(n + 1023) / 1024] = (uint32_t)bytes.size();
+        bytes.resize(bytes.size() + 24, 0);
+        py::dict r;
+        r["flags"] = to_array(flags);
+        r["block_offsets"] = to_array(offs);
+        r["bytes"] = to_array(bytes);
+        return r;
+    }, py::arg("values"));
+    m.def("unpack_varbytes", [](py::array_t<uint32_t, py::array::c_style | py::array::forcecast> flags,
+                                py::array_t<uint8_t, py::array::c_style | py::array::forcecast> bytes, size_t n) {
+        std::vector<int32_t> out(n);
+        size_t pos = 0;
+        for (size_t i = 0; i < n; ++i) {
+            if ((i >> 4) >= (size_t)flags.size()) throw Error("unpack_varbytes: flags too short");
+            const int w = (int)((flags.data()[i >> 4] >> (2 * (i & 15))) & 3u) + 1;
+            if (pos + w > (size_t)bytes.size()) throw Error("unpack_varbytes: bytes too short");
+            uint32_t x = 0;
+            for (int j = 0; j < w; ++j) x |= (uint32_t)bytes.data()[pos + j] << (8 * j);
+            out[i] = (int32_t)x;
+            pos += w;
+        }
+        return to_array(out);
+    }, py::arg("flags"), py::arg("bytes"), py::arg("n"));
     m.def("pick_hashes", [](uint64_t seed, uint64_t step, uint32_t rank, uint32_t group, int rows) {
         if (rows > 8 || rows < 1) throw Error("Currently only 8 hash functions are available");
         uint8_t ids[8];

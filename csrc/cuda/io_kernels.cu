@@ -31,7 +31,104 @@ unpack_batch_kernel(const unsigned int* __restrict__ packed, int bits, long long
         for (long long i = gid; i < rows; i += gsz) labels[i] = (float)labels8[i];
 }
 
+// Variable-width column indices: value i takes 1..4 little-endian bytes, its width - 1 in two flag
+// bits (16 values per 32-bit flag word); block_offsets[b] is the byte offset of value 1024 b. One
+// block decodes 1024 values: 4 per thread (one flag byte), a block scan of the byte counts, then at
+// most 16 bytes per thread fetched as aligned words.
+__global__ void __launch_bounds__(256)
+unpack_varbytes_kernel(const unsigned int* __restrict__ flags, const unsigned int* __restrict__ block_offsets,
+                       const unsigned char* __restrict__ bytes, long long n, int* __restrict__ cols) {
+    __shared__ unsigned int s_part[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long nblocks = (n + 1023) / 1024;
+    for (long long b = blockIdx.x; b < nblocks; b += gridDim.x) {
+        const long long i0 = b * 1024 + 4 * threadIdx.x;
+        unsigned int w[4] = {0, 0, 0, 0}, wsum = 0;
+        if (i0 < n) {
+            const unsigned int fb = (flags[i0 >> 4] >> (2 * (i0 & 15))) & 0xFFu;  // i0 is a multiple of 4
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (i0 + u < n) {
+                    w[u] = ((fb >> (2 * u)) & 3u) + 1u;
+                    wsum += w[u];
+                }
+        }
+        unsigned int inc = wsum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned int t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+            if (lane >= o) inc += t;
+        }
+        __syncthreads();  // s_part of the previous iteration has been read
+        if (lane == 31) s_part[warp] = inc;
+        __syncthreads();
+        unsigned int base = block_offsets[b];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (k < warp) base += s_part[k];
+        if (i0 < n) {
+            const unsigned int byte0 = base + inc - wsum;
+            const unsigned int* src = reinterpret_cast<const unsigned int*>(bytes) + (byte0 >> 2);
+            unsigned int W[5];
+#pragma unroll
+            for (int t = 0; t < 5; ++t) W[t] = src[t];  // the stream ends with 24 bytes of padding
+            unsigned int start = byte0 & 3u;
+            int out[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const unsigned int wi = start >> 2, sh = 8u * (start & 3u);
+                unsigned int lo = W[0], hi = W[1];
+#pragma unroll
+                for (int t = 1; t < 4; ++t)
+                    if (wi == (unsigned int)t) { lo = W[t]; hi = W[t + 1]; }
+                const unsigned int v = __funnelshift_r(lo, hi, sh);
+                out[u] = (int)(w[u] >= 4 ? v : (v & ((1u << (8u * w[u])) - 1u)));
+                start += w[u];
+            }
+            if (i0 + 3 < n) {
+                *reinterpret_cast<int4*>(cols + i0) = make_int4(out[0], out[1], out[2], out[3]);
+            } else {
+                for (int u = 0; u < 4; ++u)
+                    if (i0 + u < n) cols[i0 + u] = out[u];
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+widen_kernel(const int* __restrict__ rowptr32, long long rows, long long* __restrict__ rowptr,
+             const signed char* __restrict__ labels8, float* __restrict__ labels) {
+    const long long gsz = (long long)gridDim.x * blockDim.x, gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (rowptr32)
+        for (long long i = gid; i <= rows; i += gsz) rowptr[i] = (long long)rowptr32[i];
+    if (labels8)
+        for (long long i = gid; i < rows; i += gsz) labels[i] = (float)labels8[i];
+}
+
 }  // namespace
+
+static int io_sms() {
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    return sms;
+}
+
+// Variable-width form of skml_unpack_batch: `bytes` must be 4-byte aligned and end with 24 bytes of
+// padding; `cols` must be 16-byte aligned.
+extern "C" int skml_unpack_batch_varbytes(const unsigned int* flags, const unsigned int* block_offsets,
+                                          const unsigned char* bytes, long long nnz, int* cols, const int* rowptr32,
+                                          long long rows, long long* rowptr, const signed char* labels8, float* labels,
+                                          void* stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (nnz > 0) unpack_varbytes_kernel<<<io_sms() * 8, 256, 0, s>>>(flags, block_offsets, bytes, nnz, cols);
+    if (rowptr32 || labels8) widen_kernel<<<io_sms() * 4, 256, 0, s>>>(rowptr32, rows, rowptr, labels8, labels);
+    return (int)cudaGetLastError();
+}
 
 extern "C" int skml_unpack_batch(const unsigned int* packed, int bits, long long nnz, int* cols, const int* rowptr32,
                                  long long rows, long long* rowptr, const signed char* labels8, float* labels,

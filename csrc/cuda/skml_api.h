@@ -113,6 +113,11 @@ int skml_sm_count();
 // padding words.
 int skml_unpack_batch(const unsigned int* packed, int bits, long long nnz, int* cols, const int* rowptr32,
                       long long rows, long long* rowptr, const signed char* labels8, float* labels, void* stream);
+// The same for column indices in the byte-aligned variable-width form (1..4 bytes each, 2 flag bits,
+// one byte offset per 1024 values).
+int skml_unpack_batch_varbytes(const unsigned int* flags, const unsigned int* block_offsets, const unsigned char* bytes,
+                               long long nnz, int* cols, const int* rowptr32, long long rows, long long* rowptr,
+                               const signed char* labels8, float* labels, void* stream);
 
 // FixedPoint baseline compressor: b-bit sign + magnitude codes (2 <= bits < 30), 8 values per
 // `bits` bytes, most significant bit first in java.util.BitSet order. `scratch` holds

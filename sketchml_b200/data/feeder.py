@@ -16,13 +16,13 @@ from .dataset import CSRMatrix
 class PinnedBatch:
     """One minibatch in pinned host memory.
 
-    ``packed=True`` stores the transport form that `skml_unpack_batch` expands on the device:
-    one contiguous buffer ``[rowptr int32 | labels int8 (or fp32) | column indices at
-    ceil(log2(dim)) bits each]`` (sections 16-byte aligned), about 20 % fewer bytes per step than the
-    plain int64 / fp32 / int32 arrays for a 50M-feature problem. Values (absent for binary features)
-    always travel as fp32."""
+    ``packed=True`` stores the transport form that `skml_unpack_batch*` expands on the device:
+    one contiguous buffer ``[rowptr int32 | labels int8 (or fp32) | column indices]`` (sections
+    16-byte aligned). The column indices take ceil(log2(dim)) bits each, or 1..4 bytes + 2 flag bits
+    each when that is shorter (``transport="bits"`` / ``"varbytes"`` forces one). Values (absent for
+    binary features) always travel as fp32."""
 
-    def __init__(self, m: CSRMatrix, packed: bool = False):
+    def __init__(self, m: CSRMatrix, packed: bool = False, transport: str = None):
         self.rows, self.nnz, self.dim = m.rows, m.nnz, m.dim
         self.packed = bool(packed)
         pad = (m.nnz + 3) // 4 * 4 + 4
@@ -48,20 +48,47 @@ class PinnedBatch:
         self.bits = max(1, int(m.dim - 1).bit_length())
         lab = m.labels.to(torch.float32)
         self.labels8 = bool(torch.all(lab == lab.round()) and float(lab.abs().max() if m.rows else 0) <= 127)
-        words = oracle.pack_bits(m.cols.to(torch.int32).numpy(), self.bits)  # uint32, two padding words included
+        cols_np = m.cols.to(torch.int32).numpy()
+        # column indices: fixed width (ceil(log2(dim)) bits each) or byte-aligned variable width (1..4
+        # bytes + 2 flag bits each, smaller when frequent features have small indices), whichever is shorter
+        var = oracle.pack_varbytes(cols_np)
+        fixed_bytes = 4 * ((m.nnz * self.bits + 31) // 32 + 2)
         a16 = lambda x: (x + 15) // 16 * 16
+        var_bytes = a16(4 * len(var["flags"])) + a16(4 * len(var["block_offsets"])) + a16(len(var["bytes"]))
+        self.varbytes = var_bytes < fixed_bytes
+        if transport is not None:
+            self.varbytes = transport == "varbytes"
         self.off_rowptr = 0
         self.off_labels = a16(4 * (m.rows + 1))
         self.off_cols = a16(self.off_labels + (m.rows if self.labels8 else 4 * m.rows))
-        total = a16(self.off_cols + 4 * len(words))
-        self.buffer = torch.zeros(total, dtype=torch.uint8).pin_memory()
-        self.buffer[:4 * (m.rows + 1)].view(torch.int32).copy_(rowptr.to(torch.int32))
-        if self.labels8:
-            self.buffer[self.off_labels:self.off_labels + m.rows].view(torch.int8).copy_(lab.to(torch.int8))
+
+        def put(off, arr):
+            raw = torch.from_numpy(np.ascontiguousarray(arr).view(np.uint8))
+            self.buffer[off:off + raw.numel()].copy_(raw)
+
+        if self.varbytes:
+            self.off_flags = self.off_cols
+            self.off_blocks = a16(self.off_flags + 4 * len(var["flags"]))
+            self.off_bytes = a16(self.off_blocks + 4 * len(var["block_offsets"]))
+            total = a16(self.off_bytes + len(var["bytes"]))
+            self.buffer = torch.zeros(total, dtype=torch.uint8).pin_memory()
+            put(self.off_flags, var["flags"])
+            put(self.off_blocks, var["block_offsets"])
+            put(self.off_bytes, var["bytes"])
         else:
-            self.buffer[self.off_labels:self.off_labels + 4 * m.rows].view(torch.float32).copy_(lab)
-        self.buffer[self.off_cols:self.off_cols + 4 * len(words)].view(torch.int32).copy_(
-            torch.from_numpy(words.view(np.int32)))
+            words = oracle.pack_bits(cols_np, self.bits)  # uint32, two padding words included
+            total = a16(self.off_cols + 4 * len(words))
+            self.buffer = torch.zeros(total, dtype=torch.uint8).pin_memory()
+            put(self.off_cols, words)
+        put(self.off_rowptr, rowptr.to(torch.int32).numpy())
+        put(self.off_labels, lab.to(torch.int8).numpy() if self.labels8 else lab.numpy())
+
+    def transport(self) -> str:
+        if not self.packed:
+            return "rowptr int64, labels fp32, column indices int32"
+        cols = ("column indices 1-4 bytes each + 2 flag bits (byte-aligned variable width)" if self.varbytes
+                else f"column indices bit-packed at {self.bits} bits")
+        return f"rowptr int32, labels {'int8' if self.labels8 else 'fp32'}, {cols}, expanded on the device"
 
     def h2d_bytes(self) -> int:
         extra = self.values.numel() * 4 if self.values is not None else 0
@@ -113,9 +140,17 @@ class HostBatchFeeder:
                 raw = self.raw[slot]
                 raw[:b.buffer.numel()].copy_(b.buffer, non_blocking=True)
                 base = raw.data_ptr()
-                L.check(L.lib().skml_unpack_batch(base + b.off_cols, b.bits, b.nnz, L.ptr(st.cols), base + b.off_rowptr,
-                                                  b.rows, L.ptr(st.rowptr), base + b.off_labels if b.labels8 else None,
-                                                  L.ptr(st.labels), self.copy_stream.cuda_stream), "skml_unpack_batch")
+                lab8 = base + b.off_labels if b.labels8 else None
+                if b.varbytes:
+                    L.check(L.lib().skml_unpack_batch_varbytes(base + b.off_flags, base + b.off_blocks, base + b.off_bytes,
+                                                               b.nnz, L.ptr(st.cols), base + b.off_rowptr, b.rows,
+                                                               L.ptr(st.rowptr), lab8, L.ptr(st.labels),
+                                                               self.copy_stream.cuda_stream), "skml_unpack_batch_varbytes")
+                    L.count_launches(1)
+                else:
+                    L.check(L.lib().skml_unpack_batch(base + b.off_cols, b.bits, b.nnz, L.ptr(st.cols), base + b.off_rowptr,
+                                                      b.rows, L.ptr(st.rowptr), lab8, L.ptr(st.labels),
+                                                      self.copy_stream.cuda_stream), "skml_unpack_batch")
                 L.count_launches(1)
                 if not b.labels8:
                     st.labels[:b.rows].copy_(raw[b.off_labels:b.off_labels + 4 * b.rows].view(torch.float32))

@@ -86,6 +86,7 @@ _SIGS = {
     "skml_colsum": (c_int, [c_vp] * 8 + [c_int] * 4 + [c_vp, c_vp, c_f, c_vp, c_vp]),
     "skml_sm_count": (c_int, []),
     "skml_unpack_batch": (c_int, [c_vp, c_int, c_ll, c_vp, c_vp, c_ll, c_vp, c_vp, c_vp, c_vp]),
+    "skml_unpack_batch_varbytes": (c_int, [c_vp, c_vp, c_vp, c_ll, c_vp, c_vp, c_ll, c_vp, c_vp, c_vp, c_vp]),
     "skml_fixedpoint_scratch_bytes": (c_ll, []),
     "skml_fixedpoint_code_bytes": (c_ll, [c_ll, c_int]),
     "skml_fixedpoint_pack": (c_int, [c_vp, c_vp, c_ll, c_int, c_ull, c_vp, c_vp, c_vp, c_vp]),

@@ -113,31 +113,35 @@ def test_packed_batch_transport_matches_plain_and_trains():
         parts.append(CSRMatrix(m.rowptr[i * B:(i + 1) * B + 1].clone(), m.cols[lo:hi].clone(), None,
                                m.labels[i * B:(i + 1) * B].clone(), m.dim))
     plain = HostBatchFeeder([PinnedBatch(p) for p in parts], "cuda")
-    packed = HostBatchFeeder([PinnedBatch(p, packed=True) for p in parts], "cuda")
-    assert packed.batches[0].bits == 16 and packed.batches[0].labels8
+    packed = HostBatchFeeder([PinnedBatch(p, packed=True, transport="bits") for p in parts], "cuda")
+    varb = HostBatchFeeder([PinnedBatch(p, packed=True, transport="varbytes") for p in parts], "cuda")
+    auto = PinnedBatch(parts[0], packed=True)
+    assert packed.batches[0].bits == 16 and packed.batches[0].labels8 and not packed.batches[0].varbytes
     assert packed.batches[0].h2d_bytes() < 0.62 * plain.batches[0].h2d_bytes()
+    assert auto.h2d_bytes() == min(packed.batches[0].h2d_bytes(), varb.batches[0].h2d_bytes())
     for i in range(4):
         plain.prefetch(i)
-        packed.prefetch(i)
         a, rows = plain.get(i)
-        b, rows_b = packed.get(i)
-        torch.cuda.synchronize()
-        assert rows == rows_b == B
-        n = parts[i].nnz
-        assert torch.equal(a.rowptr[:B + 1], b.rowptr[:B + 1])
-        assert torch.equal(a.cols[:n], b.cols[:n])
-        assert torch.equal(a.labels[:B], b.labels[:B])
+        for other in (packed, varb):
+            other.prefetch(i)
+            b, rows_b = other.get(i)
+            torch.cuda.synchronize()
+            assert rows == rows_b == B
+            n = parts[i].nnz
+            assert torch.equal(a.rowptr[:B + 1], b.rowptr[:B + 1])
+            assert torch.equal(a.cols[:n], b.cols[:n])
+            assert torch.equal(a.labels[:B], b.labels[:B])
+            other.release(i)
         plain.release(i)
-        packed.release(i)
     ws = []
-    for feeder in (plain, packed):
+    for feeder in (plain, packed, varb):
         t = Trainer(_conf(feature_num=m.dim, compressor="None", valid_ratio=0.0, batch_sample_ratio=0.25))
         t.load_data(m)
         t.train_streamed(feeder, 4)
         torch.cuda.synchronize()
         ws.append(t.model.weights.detach().cpu().clone())
         t.close()
-    assert float((ws[0] - ws[1]).abs().max()) < 1e-6
+    assert float((ws[0] - ws[1]).abs().max()) < 1e-6 and float((ws[0] - ws[2]).abs().max()) < 1e-6
 
 
 @pytest.mark.parametrize("transposed", [True, False])

@@ -367,3 +367,18 @@ def test_pack_bits_roundtrip():
         assert np.array_equal(o.unpack_bits(w, len(v), bits), v)
     with pytest.raises(Exception):
         o.pack_bits(np.array([8], dtype=np.int32), 3)
+
+
+def test_pack_varbytes_roundtrip():
+    rng = np.random.default_rng(4)
+    for n in (0, 1, 3, 1023, 1024, 1025, 5000):
+        v = (rng.integers(0, 2 ** 31 - 1, n) >> rng.integers(0, 31, n)).astype(np.int32)
+        d = o.pack_varbytes(v)
+        assert len(d["block_offsets"]) == (n + 1023) // 1024 + 1
+        widths = np.where(v < 256, 1, np.where(v < 65536, 2, np.where(v < 2 ** 24, 3, 4)))
+        assert len(d["bytes"]) == widths.sum() + 24
+        if n > 1024:
+            assert d["block_offsets"][1] == widths[:1024].sum()
+        assert np.array_equal(o.unpack_varbytes(d["flags"], d["bytes"], n), v)
+    with pytest.raises(Exception):
+        o.pack_varbytes(np.array([-1], dtype=np.int32))
