@@ -108,6 +108,21 @@ int skml_colsum(const int* colptr, const int* rowidx, const float* svals, const 
                 int n_cols, const float* coef, const float* w, float lambda, float* out, void* stream);
 int skml_sm_count();
 
+// DeltaAdaptive key encoder, stand-alone (csrc/cuda/keys_kernels.cu). The caller computes the
+// inclusive prefix sums of the width arrays between the calls. Word buffers are 32-bit views of
+// the 64-bit BitSet words, zero-filled by the caller, with one spare word at the end.
+int skml_da_analyze(const int* keys, long long n, unsigned int* hist32, unsigned int* params, unsigned int* status,
+                    void* stream);   // params[0] = interval count, params[1] = 1 for unary flags; status bit 0 = unsorted keys
+int skml_da_widths(const int* keys, long long n, const unsigned int* params, int* flag_w, int* delta_w, void* stream);
+int skml_da_pack(const int* keys, long long n, const unsigned int* params, const long long* flag_incl,
+                 const long long* delta_incl, unsigned int* flag_words, unsigned int* delta_words, void* stream);
+int skml_da_fixed_iv(const unsigned int* flag_words, long long n, int flag_bits_per_key, int* iv, void* stream);
+int skml_da_zero_count(const unsigned int* flag_words, long long flag_bits, int* zeros, void* stream);
+int skml_da_zero_pos(const unsigned int* flag_words, long long flag_bits, const long long* zeros_incl, long long n,
+                     long long* pos, void* stream);
+int skml_da_extract(const unsigned int* delta_words, long long n, const int* delta_w, const long long* delta_incl,
+                    long long* deltas, void* stream);
+
 // Expands a minibatch from its transport form (bit-packed column indices, 32-bit row pointers,
 // 8-bit labels; the latter two optional = null) into CSR arrays. `packed` must end with two
 // padding words.

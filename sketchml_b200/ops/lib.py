@@ -85,6 +85,13 @@ _SIGS = {
     "skml_glm_coef": (c_int, [c_vp, c_vp, c_vp, c_vp, c_ll, c_ll, c_ll, c_d, c_vp, c_int, c_f, c_vp, c_vp, c_vp, c_ll, c_vp]),
     "skml_colsum": (c_int, [c_vp] * 8 + [c_int] * 4 + [c_vp, c_vp, c_f, c_vp, c_vp]),
     "skml_sm_count": (c_int, []),
+    "skml_da_analyze": (c_int, [c_vp, c_ll, c_vp, c_vp, c_vp, c_vp]),
+    "skml_da_widths": (c_int, [c_vp, c_ll, c_vp, c_vp, c_vp, c_vp]),
+    "skml_da_pack": (c_int, [c_vp, c_ll, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "skml_da_fixed_iv": (c_int, [c_vp, c_ll, c_int, c_vp, c_vp]),
+    "skml_da_zero_count": (c_int, [c_vp, c_ll, c_vp, c_vp]),
+    "skml_da_zero_pos": (c_int, [c_vp, c_ll, c_vp, c_ll, c_vp, c_vp]),
+    "skml_da_extract": (c_int, [c_vp, c_ll, c_vp, c_vp, c_vp, c_vp]),
     "skml_unpack_batch": (c_int, [c_vp, c_int, c_ll, c_vp, c_vp, c_ll, c_vp, c_vp, c_vp, c_vp]),
     "skml_unpack_batch_varbytes": (c_int, [c_vp, c_vp, c_vp, c_ll, c_vp, c_vp, c_ll, c_vp, c_vp, c_vp, c_vp]),
     "skml_fixedpoint_scratch_bytes": (c_ll, []),

@@ -306,3 +306,38 @@ def test_several_overlapping_payloads_sgd_and_adam(fused):
     v2 = torch.zeros(dim, device="cuda")
     dec.decode_update(ptrs, [None] * P, cap, 7, status, w=w2, lr=0.1, adam_m=m2, adam_v=v2, adam_scale=scale)
     assert torch.equal(w, w2) and torch.equal(m, m2) and torch.equal(vv, v2)
+
+
+def _key_sets():
+    rng = np.random.default_rng(11)
+    yield "empty", np.zeros(0, dtype=np.int32)
+    yield "single zero", np.array([0], dtype=np.int32)
+    yield "single big", np.array([2 ** 31 - 1], dtype=np.int32)
+    yield "consecutive", np.arange(5000, dtype=np.int32)
+    yield "small gaps", np.cumsum(rng.integers(1, 4, 70001)).astype(np.int32)
+    yield "byte gaps", np.cumsum(rng.integers(1, 300, 33333)).astype(np.int32)
+    yield "wide gaps", np.sort(rng.choice(2 ** 31 - 2, 20000, replace=False)).astype(np.int32)
+    yield "mixed", np.unique(np.concatenate([rng.integers(0, 5000, 3000), rng.integers(0, 2 ** 30, 3000)])).astype(np.int32)
+    yield "zipf", np.unique(np.minimum(rng.zipf(1.1, 200000), 50_000_000 - 1)).astype(np.int32)
+
+
+@pytest.mark.parametrize("name,keys", list(_key_sets()), ids=[n for n, _ in _key_sets()])
+def test_delta_adaptive_device_codec_is_bit_exact(name, keys):
+    """Device DeltaAdaptive encode equals the CPU oracle word for word; device decode inverts both."""
+    from sketchml_b200.compress import oracle
+    from sketchml_b200.ops import keys as K
+    ref = oracle.delta_adaptive_encode(keys)
+    got = K.encode(torch.from_numpy(keys).cuda())
+    assert (got.size, got.num_intervals, got.flag_kind) == (ref["size"], ref["num_intervals"], ref["flag_kind"])
+    assert (got.flag_bits, got.delta_bits) == (ref["flag_bits"], ref["delta_bits"])
+    d = got.to_oracle_dict()
+    assert np.array_equal(d["flag_words"], np.asarray(ref["flag_words"], dtype=np.uint64))
+    assert np.array_equal(d["delta_words"], np.asarray(ref["delta_words"], dtype=np.uint64))
+    assert np.array_equal(oracle.delta_adaptive_decode(d), keys)
+    assert np.array_equal(K.decode(got).cpu().numpy(), keys)
+
+
+def test_delta_adaptive_device_codec_rejects_unsorted_keys():
+    from sketchml_b200.ops import keys as K
+    with pytest.raises(ValueError):
+        K.encode(torch.tensor([1, 5, 5, 9], dtype=torch.int32, device="cuda"))
