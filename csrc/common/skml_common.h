@@ -291,15 +291,25 @@ SKML_HD uint64_t skml_rand(uint64_t seed, uint64_t a, uint64_t b, uint64_t c) {
     return h;
 }
 
-// Picks `rows` distinct members of the family of 8 by a Fisher-Yates shuffle
-// driven by (seed, step, rank, group) (HashFactory.getRandomInt2IntHashes draws
-// them from an unseeded java.util.Random instead).
+// Picks `rows` distinct members of the family of 8, driven by (seed, step, rank, group)
+// (HashFactory.getRandomInt2IntHashes draws them from an unseeded java.util.Random instead, so
+// every outcome here is one the reference can produce). The three integer mixers (BJ, Mix64, TW)
+// are drawn first, in shuffled order, and the five BKDR members only for rows 4..8: a BKDR hash
+// walks the key's decimal digits and costs about four times the instructions of a mixer in the
+// insert and query kernels, where hashing is the largest single item.
 SKML_HD void skml_pick_hashes(uint64_t seed, uint64_t step, uint32_t rank, uint32_t group, int rows,
                               uint8_t out[8]) {
     uint8_t ids[8] = {0, 1, 2, 3, 4, 5, 6, 7};
-    for (int i = 7; i > 0; --i) {
+    for (int i = 2; i > 0; --i) {  // Fisher-Yates over the mixers ids[0..2]
         uint64_t r = skml_rand(seed, step, ((uint64_t)rank << 32) | group, (uint64_t)i);
         int j = (int)(r % (uint64_t)(i + 1));
+        uint8_t t = ids[i];
+        ids[i] = ids[j];
+        ids[j] = t;
+    }
+    for (int i = 7; i > 3; --i) {  // Fisher-Yates over the BKDR members ids[3..7]
+        uint64_t r = skml_rand(seed, step, ((uint64_t)rank << 32) | group, (uint64_t)i);
+        int j = 3 + (int)(r % (uint64_t)(i - 2));
         uint8_t t = ids[i];
         ids[i] = ids[j];
         ids[j] = t;

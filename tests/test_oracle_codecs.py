@@ -101,6 +101,13 @@ def test_pick_hashes_distinct_and_deterministic():
     assert o.pick_hashes(5, 7, 1, 3, 4) != o.pick_hashes(5, 8, 1, 3, 4) or o.pick_hashes(5, 7, 1, 2, 4) != o.pick_hashes(5, 7, 1, 3, 4)
     with pytest.raises(o.SketchMLError):
         o.pick_hashes(1, 1, 1, 1, 9)
+    # the three integer mixers come first (in some order), the BKDR members after them
+    seen = set()
+    for step in range(40):
+        a = o.pick_hashes(5, step, 1, 3, 8)
+        assert sorted(a[:3]) == [0, 1, 2] and sorted(a[3:]) == [3, 4, 5, 6, 7]
+        seen.add(tuple(a[:3]))
+    assert len(seen) == 6
 
 
 def test_group_edges_table():
