@@ -639,13 +639,13 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_BLOCKS_PER_SM) decode_update_
     if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        reinterpret_cast<unsigned long long*>(p.ctrl)[8] = t;
+        reinterpret_cast<unsigned long long*>(p.ctrl)[8 + 4 * (int)(p.step & 1)] = t;
     }
     if (!decode_prepare(p, s)) return;
     if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        reinterpret_cast<unsigned long long*>(p.ctrl)[9] = t;
+        reinterpret_cast<unsigned long long*>(p.ctrl)[9 + 4 * (int)(p.step & 1)] = t;
     }
     if (s.direct || s.adam_plain) {
         if (s.two_phase) {
@@ -656,7 +656,7 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_BLOCKS_PER_SM) decode_update_
                 if (blockIdx.x == 0 && threadIdx.x == 0) {
                     unsigned long long t;
                     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-                    reinterpret_cast<unsigned long long*>(p.ctrl)[10] = t;
+                    reinterpret_cast<unsigned long long*>(p.ctrl)[10 + 4 * (int)(p.step & 1)] = t;
                 }
             }
             // Phase 2 without dense payloads (un-fused: stage 2): key-range-owned apply, no grid barrier.
@@ -694,8 +694,8 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_BLOCKS_PER_SM) decode_update_
         if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) {
             unsigned long long t;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            if (!s.two_phase) reinterpret_cast<unsigned long long*>(p.ctrl)[10] = t;
-            reinterpret_cast<unsigned long long*>(p.ctrl)[11] = t;
+            if (!s.two_phase) reinterpret_cast<unsigned long long*>(p.ctrl)[10 + 4 * (int)(p.step & 1)] = t;
+            reinterpret_cast<unsigned long long*>(p.ctrl)[11 + 4 * (int)(p.step & 1)] = t;
         }
         return;
     }
@@ -709,13 +709,13 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_BLOCKS_PER_SM) decode_update_
     if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        reinterpret_cast<unsigned long long*>(p.ctrl)[10] = t;
+        reinterpret_cast<unsigned long long*>(p.ctrl)[10 + 4 * (int)(p.step & 1)] = t;
     }
     if (FUSED || stage == 2) decode_update(p, s);
     if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        reinterpret_cast<unsigned long long*>(p.ctrl)[11] = t;
+        reinterpret_cast<unsigned long long*>(p.ctrl)[11 + 4 * (int)(p.step & 1)] = t;
     }
 }
 

@@ -896,12 +896,47 @@ extern "C" int skml_glm_coef(const long long* rowptr, const int* cols, const flo
                        inv_batch, 0, loss_acc, coef_out, status, budget, (cudaStream_t)stream);
 }
 
+// Start-of-step housekeeping in one small launch: the loss partials are reset from their template
+// and the output slots of the long columns (the only ones the column-sum kernel accumulates into
+// with atomics) are cleared.
+__global__ void step_prep_kernel(double* __restrict__ partials, const double* __restrict__ partials_template,
+                                 float* __restrict__ out, const int* __restrict__ long_col, int n_long) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < 4) partials[t] = partials_template[t];
+    for (int i = t; i < n_long; i += gridDim.x * blockDim.x) out[long_col[i]] = 0.f;  // duplicates store the same zero
+}
+
+extern "C" int skml_step_prep(double* partials, const double* partials_template, float* out, const int* long_col,
+                              int n_long, void* stream) {
+    int blocks = (n_long + 255) / 256;
+    if (blocks < 1) blocks = 1;
+    if (blocks > 1024) blocks = 1024;
+    step_prep_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(partials, partials_template, out, long_col, n_long);
+    return (int)cudaGetLastError();
+}
+
+// `out_is_prepared` != 0: the long columns' slots are already zero (skml_step_prep), skip the full clear.
+extern "C" int skml_colsum_ex(const int* colptr, const int* rowidx, const float* svals, const int* ucols, const int* bins,
+                              const int* long_col, const int* long_e0, const int* long_e1, int n_short, int n_medium,
+                              int n_long, int n_cols, const float* coef, const float* w, float lambda, float* out,
+                              int out_is_prepared, void* stream);
+
 extern "C" int skml_colsum(const int* colptr, const int* rowidx, const float* svals, const int* ucols, const int* bins,
                            const int* long_col, const int* long_e0, const int* long_e1, int n_short, int n_medium,
                            int n_long, int n_cols, const float* coef, const float* w, float lambda, float* out,
                            void* stream) {
-    cudaError_t e = cudaMemsetAsync(out, 0, (size_t)n_cols * sizeof(float), (cudaStream_t)stream);
-    if (e != cudaSuccess) return (int)e;
+    return skml_colsum_ex(colptr, rowidx, svals, ucols, bins, long_col, long_e0, long_e1, n_short, n_medium, n_long,
+                          n_cols, coef, w, lambda, out, 0, stream);
+}
+
+extern "C" int skml_colsum_ex(const int* colptr, const int* rowidx, const float* svals, const int* ucols, const int* bins,
+                              const int* long_col, const int* long_e0, const int* long_e1, int n_short, int n_medium,
+                              int n_long, int n_cols, const float* coef, const float* w, float lambda, float* out,
+                              int out_is_prepared, void* stream) {
+    if (!out_is_prepared) {
+        cudaError_t e = cudaMemsetAsync(out, 0, (size_t)n_cols * sizeof(float), (cudaStream_t)stream);
+        if (e != cudaSuccess) return (int)e;
+    }
     const int short_blocks = (n_short + 255) / 256, medium_blocks = (n_medium + 7) / 8;
     const long long blocks = (long long)short_blocks + medium_blocks + n_long;
     if (blocks <= 0) return 0;

@@ -106,6 +106,12 @@ int skml_glm_coef(const long long* rowptr, const int* cols, const float* vals, c
 int skml_colsum(const int* colptr, const int* rowidx, const float* svals, const int* ucols, const int* bins,
                 const int* long_col, const int* long_e0, const int* long_e1, int n_short, int n_medium, int n_long,
                 int n_cols, const float* coef, const float* w, float lambda, float* out, void* stream);
+int skml_colsum_ex(const int* colptr, const int* rowidx, const float* svals, const int* ucols, const int* bins,
+                   const int* long_col, const int* long_e0, const int* long_e1, int n_short, int n_medium, int n_long,
+                   int n_cols, const float* coef, const float* w, float lambda, float* out, int out_is_prepared,
+                   void* stream);
+int skml_step_prep(double* partials, const double* partials_template, float* out, const int* long_col, int n_long,
+                   void* stream);
 int skml_sm_count();
 
 // DeltaAdaptive key encoder, stand-alone (csrc/cuda/keys_kernels.cu). The caller computes the

@@ -1,7 +1,8 @@
 // skml_train_step: the launch sequence of one training step behind a single C call.
 // Reference: ml/algorithm/GeneralizedLinearModel.scala:116-123 (trainOneIteration =
 // computeGradient + aggregateAndUpdate); here the whole iteration is five kernel launches
-// and one 32-byte device copy, issued back to back on one stream with no host round trip.
+// (housekeeping, coefficients, column sums, fused compress, fused decode + update) issued back to
+// back on one stream with no host round trip.
 #include <cuda_runtime.h>
 
 #include "skml_api.h"
@@ -9,17 +10,17 @@
 extern "C" int skml_train_step(SkmlStepArgs* a, void* stream_) {
     if (!a || !a->compress || !a->decode) return (int)cudaErrorInvalidValue;
     cudaStream_t stream = (cudaStream_t)stream_;
-    cudaError_t e = cudaMemcpyAsync(a->partials, a->partials_template, 4 * sizeof(double), cudaMemcpyDeviceToDevice, stream);
-    if (e != cudaSuccess) return (int)e;
     if (a->t_colptr) {
         // transposed index: coefficients per row, then one gather-sum per distinct column
-        int rc = skml_glm_coef(a->rowptr, a->cols, a->vals, a->labels, a->seg_lo[0], a->seg_cnt[0], a->nnz_padded,
+        int rc = skml_step_prep(a->partials, a->partials_template, a->gvals, a->t_long_col, (int)a->t_long, stream_);
+        if (rc) return rc;
+        rc = skml_glm_coef(a->rowptr, a->cols, a->vals, a->labels, a->seg_lo[0], a->seg_cnt[0], a->nnz_padded,
                                a->avg_nnz, a->w, (int)a->loss_id, (float)a->inv_batch, a->partials + 1, a->coef,
                                a->status, a->budget_cycles, stream_);
         if (rc) return rc;
-        rc = skml_colsum(a->t_colptr, a->t_rowidx, a->t_vals, a->t_ucols, a->t_bins, a->t_long_col, a->t_long_e0,
-                         a->t_long_e1, (int)a->t_short, (int)a->t_medium, (int)a->t_long, (int)a->t_cols, a->coef, a->w,
-                         (float)a->lambda, a->gvals, stream_);
+        rc = skml_colsum_ex(a->t_colptr, a->t_rowidx, a->t_vals, a->t_ucols, a->t_bins, a->t_long_col, a->t_long_e0,
+                            a->t_long_e1, (int)a->t_short, (int)a->t_medium, (int)a->t_long, (int)a->t_cols, a->coef, a->w,
+                            (float)a->lambda, a->gvals, 1, stream_);
         if (rc) return rc;
         a->compress->step = a->step;
         a->compress->keys = a->t_ucols;
@@ -33,6 +34,8 @@ extern "C" int skml_train_step(SkmlStepArgs* a, void* stream_) {
         a->decode->loss_out = a->loss_out;
         return skml_decode_update(a->decode, stream_);
     }
+    cudaError_t e = cudaMemcpyAsync(a->partials, a->partials_template, 4 * sizeof(double), cudaMemcpyDeviceToDevice, stream);
+    if (e != cudaSuccess) return (int)e;
     for (int s = 0; s < 2; ++s) {
         if (a->seg_cnt[s] <= 0) continue;
         int rc = skml_glm_grad(a->rowptr, a->cols, a->vals, a->labels, a->seg_lo[s], a->seg_cnt[s], a->nnz_padded,

@@ -206,7 +206,7 @@ class GpuEngine:
         a.decode = self._da_ptr[par]
         a.step, a.lr, a.adam_scale, a.loss_out = step, lr, adam_scale, ring_ptr
         L.check(self._step_fn(self._byref(a), L.stream()), "skml_train_step")
-        L.count_launches((2 if bi is not None else len(segs) + 3) + 1 + (1 if self.st.dense_vals is not None and bi is None else 0) + 1)
+        L.count_launches((3 if bi is not None else len(segs) + 3) + 1 + (1 if self.st.dense_vals is not None and bi is None else 0) + 1)
 
     # ----------------------------------------------------------------- steps
     def _segments(self, count: int):
@@ -451,10 +451,17 @@ class GpuEngine:
         if self.mode != "sketch":
             return None
         import numpy as np
+        last = (self.t.step - 1) & 1  # the decode kernel keeps the stamps of even and odd steps apart
         c = self.comp.workspace[:256].cpu().numpy().view(np.int64)[8:14]
-        d = self.dec.workspace[:256].cpu().numpy().view(np.int64)[8:12]
+        dall = self.dec.workspace[:256].cpu().numpy().view(np.int64)
+        d, dprev = dall[8 + 4 * last:12 + 4 * last], dall[8 + 4 * (1 - last):12 + 4 * (1 - last)]
         return {"compress": [float(c[i + 1] - c[i]) / 1e3 for i in range(5)],
-                "decode": [float(d[i + 1] - d[i]) / 1e3 for i in range(3)]}
+                "decode": [float(d[i + 1] - d[i]) / 1e3 for i in range(3)],
+                # idle time between the end of the compress kernel's last stage and the start of the decode kernel
+                "compress_to_decode_gap": float(d[0] - c[5]) / 1e3,
+                # from the end of the previous step's decode kernel to the start of this step's compress kernel:
+                # the gradient kernels and the launch gaps around them
+                "prev_decode_to_compress": float(c[0] - dprev[3]) / 1e3 if dprev[3] else None}
 
     def sync(self) -> None:
         torch.cuda.synchronize(self.device)
