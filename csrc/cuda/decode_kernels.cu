@@ -697,6 +697,19 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_BLOCKS_PER_SM) decode_update_
             if (!s.two_phase) reinterpret_cast<unsigned long long*>(p.ctrl)[10 + 4 * (int)(p.step & 1)] = t;
             reinterpret_cast<unsigned long long*>(p.ctrl)[11 + 4 * (int)(p.step & 1)] = t;
         }
+        if (FUSED) {
+            // the last block to finish leaves the kernel's true end time (block 0's stamp above is its own)
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                const unsigned int prev = atomicAdd(&p.ctrl[2], 1u);
+                if (prev == gridDim.x - 1) {
+                    p.ctrl[2] = 0;
+                    unsigned long long t;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+                    reinterpret_cast<unsigned long long*>(p.ctrl)[16 + (int)(p.step & 1)] = t;
+                }
+            }
+        }
         return;
     }
     if (FUSED || stage == 1) {

@@ -461,7 +461,9 @@ class GpuEngine:
                 "compress_to_decode_gap": float(d[0] - c[5]) / 1e3,
                 # from the end of the previous step's decode kernel to the start of this step's compress kernel:
                 # the gradient kernels and the launch gaps around them
-                "prev_decode_to_compress": float(c[0] - dprev[3]) / 1e3 if dprev[3] else None}
+                "prev_decode_to_compress": float(c[0] - dprev[3]) / 1e3 if dprev[3] else None,
+                # how long after block 0 the last block of the decode kernel finished (SGD / plain-Adam modes)
+                "decode_last_block_after_block0": float(dall[16 + last] - d[3]) / 1e3 if dall[16 + last] else None}
 
     def sync(self) -> None:
         torch.cuda.synchronize(self.device)
