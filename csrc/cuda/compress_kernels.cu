@@ -613,19 +613,34 @@ __device__ void element_pass(const CP& p, Smem& s, long long n) {
         boff_g = L.vbase_bytes[warp][lane];
         base_prev_g = L.vbase_prev[warp][lane];
     }
+    // The next iteration's key and value (or bucket) are fetched one iteration ahead: a warp's
+    // iteration is a dependent chain, so the global load latency would otherwise sit on it every time.
+    int nkey = 0, nbin = 0;
+    float nval = 0.f;
+    if (lo + lane < hi) {
+        nkey = p.keys[lo + lane];
+        if (PACK) nbin = p.bins[lo + lane];
+        else nval = p.vals[lo + lane];
+    }
     for (long long i0 = lo; i0 < hi; i0 += 32) {
         const long long i = i0 + lane;
         const bool valid = i < hi;
-        int key = 0, bin = 0, g = 63;
+        int key = nkey, bin = nbin, g = 63;
+        const float val = nval;
+        if (i + 32 < hi) {
+            nkey = p.keys[i + 32];
+            if (PACK) nbin = p.bins[i + 32];
+            else nval = p.vals[i + 32];
+        }
         if (valid) {
-            key = p.keys[i];
-            if (PACK) {
-                bin = p.bins[i];
-            } else {
-                bin = upper_bound_f(s.splits, s.qi.nsplits, p.vals[i]);
+            if (!PACK) {
+                bin = upper_bound_f(s.splits, s.qi.nsplits, val);
                 p.bins[i] = (unsigned short)bin;
             }
             g = skml_group_of(bin, s.qi.edges, G);
+        } else {
+            key = 0;
+            bin = 0;
         }
         s.wcnt[warp][lane] = 0;  // slot of group `lane`: filled below if the group occurs in this iteration
         __syncwarp();
