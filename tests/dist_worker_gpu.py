@@ -26,6 +26,10 @@ def main():
         kw["compressor"] = "None"
     elif scenario == "kv":
         kw["compressor"] = "Float"
+    elif scenario == "sketch_adam":
+        kw.update(optimizer="adam", learn_rate=0.01)
+    elif scenario == "fixedpoint":
+        kw.update(compressor="FixedPoint", fixed_point_bit_num=8)
     elif scenario == "skip" and rank == 1:
         inj = FaultInjector(skip_publish_steps={3})
     res = {"rank": rank, "scenario": scenario}

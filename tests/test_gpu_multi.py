@@ -62,6 +62,17 @@ def test_fused_exchange_matches_nccl_baselines(tmp_path):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+@pytest.mark.parametrize("scenario", ["sketch_adam", "fixedpoint"])
+def test_adam_and_packed_fixed_point_keep_replicas_identical(tmp_path, scenario):
+    """Lazy Adam over the fused exchange (plain float sums in rank order inside the owning block) and
+    the FixedPoint baseline with its packed codes on the wire: every rank ends with the same bits."""
+    res = _run(scenario, tmp_path, _world())
+    assert all(r["ok"] for r in res), res
+    assert len({r["hash"] for r in res}) == 1, "replicas drifted apart"
+    assert res[0]["train_loss"][-1] < res[0]["train_loss"][0]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
 def test_missing_publish_times_out_cleanly(tmp_path):
     res = _run("skip", tmp_path, 2)
     assert not any(r["ok"] for r in res), res
