@@ -896,6 +896,38 @@ extern "C" int skml_glm_coef(const long long* rowptr, const int* cols, const flo
                        inv_batch, 0, loss_acc, coef_out, status, budget, (cudaStream_t)stream);
 }
 
+// Local-id batches (streamed minibatches whose column indices were replaced on the host by their
+// position in the batch's sorted list of distinct columns): the weights of those columns are
+// gathered once into a compact array, the gradient is scattered into a compact accumulator, and
+// the sparse gradient's values are read off it in key order. The accumulators and the touched-bit
+// words of the range are cleared for the next step.
+__global__ void gather_compact_kernel(const float* __restrict__ w, const int* __restrict__ ucols, int n,
+                                      float* __restrict__ wc) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) wc[i] = w[ucols[i]];
+}
+
+__global__ void finalize_compact_kernel(float* __restrict__ gc, const float* __restrict__ wc, float lambda, int n,
+                                        float* __restrict__ vals, unsigned int* __restrict__ bitmap) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        vals[i] = gc[i] + lambda * wc[i];
+        gc[i] = 0.f;
+        if (i < (n + 31) / 32) bitmap[i] = 0u;
+    }
+}
+
+extern "C" int skml_gather_compact(const float* w, const int* ucols, int n, float* wc, void* stream) {
+    if (n <= 0) return 0;
+    gather_compact_kernel<<<sm_count() * 8, 256, 0, (cudaStream_t)stream>>>(w, ucols, n, wc);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int skml_finalize_compact(float* gc, const float* wc, float lambda, int n, float* vals, unsigned int* bitmap,
+                                     void* stream) {
+    if (n <= 0) return 0;
+    finalize_compact_kernel<<<sm_count() * 8, 256, 0, (cudaStream_t)stream>>>(gc, wc, lambda, n, vals, bitmap);
+    return (int)cudaGetLastError();
+}
+
 // Start-of-step housekeeping in one small launch: the loss partials are reset from their template
 // and the output slots of the long columns (the only ones the column-sum kernel accumulates into
 // with atomics) are cleared.

@@ -112,6 +112,9 @@ int skml_colsum_ex(const int* colptr, const int* rowidx, const float* svals, con
                    void* stream);
 int skml_step_prep(double* partials, const double* partials_template, float* out, const int* long_col, int n_long,
                    void* stream);
+int skml_gather_compact(const float* w, const int* ucols, int n, float* wc, void* stream);
+int skml_finalize_compact(float* gc, const float* wc, float lambda, int n, float* vals, unsigned int* bitmap,
+                          void* stream);
 int skml_sm_count();
 
 // DeltaAdaptive key encoder, stand-alone (csrc/cuda/keys_kernels.cu). The caller computes the
@@ -213,6 +216,13 @@ typedef struct SkmlStepArgs {
     long long t_short, t_medium, t_long, t_cols;
     const long long* t_meta;           // device: {t_cols, 1 (sparse kind), 0, 0}
     float* coef;                       // device scratch: one coefficient per batch row
+    // local-id batch (null = not one): `cols` holds positions in l_ucols instead of feature indices
+    const int* l_ucols;                // the batch's distinct columns, ascending: the gradient's keys
+    const long long* l_meta;           // device: {l_ncols, 1 (sparse kind), 0, 0}
+    long long l_ncols;
+    float* wc;                         // device scratch [>= l_ncols]: weights of the batch's columns
+    float* gc;                         // device scratch [>= l_ncols], all zero between steps: compact gradient
+    void* grad_done_event;             // optional cudaEvent_t, recorded after the last kernel that reads the batch
 } SkmlStepArgs;
 
 int skml_train_step(SkmlStepArgs* args, void* stream);

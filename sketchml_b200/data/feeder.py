@@ -20,11 +20,17 @@ class PinnedBatch:
     one contiguous buffer ``[rowptr int32 | labels int8 (or fp32) | column indices]`` (sections
     16-byte aligned). The column indices take ceil(log2(dim)) bits each, or 1..4 bytes + 2 flag bits
     each when that is shorter (``transport="bits"`` / ``"varbytes"`` forces one). Values (absent for
-    binary features) always travel as fp32."""
+    binary features) always travel as fp32.
 
-    def __init__(self, m: CSRMatrix, packed: bool = False, transport: str = None):
+    ``local_ids=True`` (implies ``packed``) additionally replaces every column index by its position
+    in the batch's sorted list of distinct columns and ships that list (delta-coded) with the batch.
+    The distinct columns are the keys of the batch's sparse gradient, so the device scatters into a
+    compact accumulator instead of a ``dim``-sized one and needs no touched-bitmap compaction."""
+
+    def __init__(self, m: CSRMatrix, packed: bool = False, transport: str = None, local_ids: bool = False):
         self.rows, self.nnz, self.dim = m.rows, m.nnz, m.dim
-        self.packed = bool(packed)
+        self.packed = bool(packed) or bool(local_ids)
+        self.local_ids = bool(local_ids)
         pad = (m.nnz + 3) // 4 * 4 + 4
         self.pad = pad
         rowptr = (m.rowptr - m.rowptr[0]).to(torch.int64)
@@ -49,6 +55,14 @@ class PinnedBatch:
         lab = m.labels.to(torch.float32)
         self.labels8 = bool(torch.all(lab == lab.round()) and float(lab.abs().max() if m.rows else 0) <= 127)
         cols_np = m.cols.to(torch.int32).numpy()
+        self.n_cols = 0
+        ucol_var = None
+        if self.local_ids:
+            ucols = np.unique(cols_np)  # ascending
+            self.n_cols = int(len(ucols))
+            cols_np = np.searchsorted(ucols, cols_np).astype(np.int32)
+            self.bits = max(1, int(max(self.n_cols - 1, 1)).bit_length())
+            ucol_var = oracle.pack_varbytes(np.diff(ucols, prepend=0).astype(np.int32))
         # column indices: fixed width (ceil(log2(dim)) bits each) or byte-aligned variable width (1..4
         # bytes + 2 flag bits each, smaller when frequent features have small indices), whichever is shorter
         var = oracle.pack_varbytes(cols_np)
@@ -60,7 +74,13 @@ class PinnedBatch:
             self.varbytes = transport == "varbytes"
         self.off_rowptr = 0
         self.off_labels = a16(4 * (m.rows + 1))
-        self.off_cols = a16(self.off_labels + (m.rows if self.labels8 else 4 * m.rows))
+        self.off_meta = a16(self.off_labels + (m.rows if self.labels8 else 4 * m.rows))
+        self.off_cols = self.off_meta + 32
+        if ucol_var is not None:  # [flags | block offsets | bytes] of the distinct-column deltas
+            self.off_uflags = self.off_cols
+            self.off_ublocks = a16(self.off_uflags + 4 * len(ucol_var["flags"]))
+            self.off_ubytes = a16(self.off_ublocks + 4 * len(ucol_var["block_offsets"]))
+            self.off_cols = a16(self.off_ubytes + len(ucol_var["bytes"]))
 
         def put(off, arr):
             raw = torch.from_numpy(np.ascontiguousarray(arr).view(np.uint8))
@@ -80,6 +100,11 @@ class PinnedBatch:
             total = a16(self.off_cols + 4 * len(words))
             self.buffer = torch.zeros(total, dtype=torch.uint8).pin_memory()
             put(self.off_cols, words)
+        put(self.off_meta, np.array([self.n_cols, 1 if self.n_cols else 0, 0, 0], dtype=np.int64))
+        if ucol_var is not None:
+            put(self.off_uflags, ucol_var["flags"])
+            put(self.off_ublocks, ucol_var["block_offsets"])
+            put(self.off_ubytes, ucol_var["bytes"])
         put(self.off_rowptr, rowptr.to(torch.int32).numpy())
         put(self.off_labels, lab.to(torch.int8).numpy() if self.labels8 else lab.numpy())
 
@@ -88,7 +113,10 @@ class PinnedBatch:
             return "rowptr int64, labels fp32, column indices int32"
         cols = ("column indices 1-4 bytes each + 2 flag bits (byte-aligned variable width)" if self.varbytes
                 else f"column indices bit-packed at {self.bits} bits")
-        return f"rowptr int32, labels {'int8' if self.labels8 else 'fp32'}, {cols}, expanded on the device"
+        what = "batch-local column ids" if self.local_ids else "column indices"
+        cols = cols.replace("column indices", what)
+        extra = ", plus the batch's distinct columns as variable-width deltas" if self.local_ids else ""
+        return f"rowptr int32, labels {'int8' if self.labels8 else 'fp32'}, {cols}{extra}, expanded on the device"
 
     def h2d_bytes(self) -> int:
         extra = self.values.numel() * 4 if self.values is not None else 0
@@ -120,6 +148,13 @@ class HostBatchFeeder:
             self.stage.append(DeviceCSR.from_parts(rp, cols, vals, lab, batches[0].dim, 0))
             if self.packed:
                 self.raw.append(torch.zeros(max(b.buffer.numel() for b in batches), dtype=torch.uint8, device=self.device))
+        self.local_ids = batches[0].local_ids
+        if any(b.local_ids != self.local_ids for b in batches):
+            raise ValueError("all batches of a feeder use the same transport form")
+        if self.local_ids:
+            nc = max(b.n_cols for b in batches) + 8
+            self.ucols = [torch.zeros(nc, dtype=torch.int32, device=self.device) for _ in range(2)]
+            self.udelta = torch.zeros(nc, dtype=torch.int32, device=self.device)
         self.ready = [torch.cuda.Event(), torch.cuda.Event()]
         self.free = [torch.cuda.Event(), torch.cuda.Event()]
         for e in self.free:
@@ -154,6 +189,13 @@ class HostBatchFeeder:
                 L.count_launches(1)
                 if not b.labels8:
                     st.labels[:b.rows].copy_(raw[b.off_labels:b.off_labels + 4 * b.rows].view(torch.float32))
+                if b.local_ids and b.n_cols:
+                    # the distinct columns: variable-width deltas -> int32 -> running sum
+                    L.check(L.lib().skml_unpack_batch_varbytes(base + b.off_uflags, base + b.off_ublocks, base + b.off_ubytes,
+                                                               b.n_cols, L.ptr(self.udelta), None, 0, None, None, None,
+                                                               self.copy_stream.cuda_stream), "skml_unpack_batch_varbytes")
+                    torch.cumsum(self.udelta[:b.n_cols], 0, dtype=torch.int32, out=self.ucols[slot][:b.n_cols])
+                    L.count_launches(2)
             else:
                 st.rowptr[:b.rows + 1].copy_(b.rowptr, non_blocking=True)
                 st.cols[:b.cols.numel()].copy_(b.cols, non_blocking=True)
@@ -169,6 +211,8 @@ class HostBatchFeeder:
         torch.cuda.current_stream().wait_event(self.ready[slot])
         st = self.stage[slot]
         st.rows, st.nnz = b.rows, b.nnz
+        # local-id batch: (distinct columns on the device, their count, device address of {count, kind, 0, 0})
+        st.lid = (self.ucols[slot], b.n_cols, self.raw[slot].data_ptr() + b.off_meta) if b.local_ids else None
         return st, b.rows
 
     def release(self, i: int) -> None:

@@ -178,9 +178,10 @@ class GpuEngine:
         self.coef = torch.zeros(B, dtype=torch.float32, device=self.device)
 
     def _launch_fast_step(self, step: int, lr: float, adam_scale: float, ring_ptr: int) -> None:
-        csr, segs, rows = self._pending
+        csr, segs, rows, done_event = self._pending
         self._pending = None
         a = self._sa
+        a.grad_done_event = done_event.cuda_event if done_event is not None else None
         a.rowptr, a.cols, a.vals, a.labels = L.ptr(csr.rowptr), L.ptr(csr.cols), L.ptr(csr.values), L.ptr(csr.labels)
         a.nnz_padded, a.avg_nnz = csr.nnz_padded, float(csr.avg_nnz)
         for i in range(2):
@@ -200,13 +201,30 @@ class GpuEngine:
             a.t_meta, a.coef = L.ptr(bi.meta), L.ptr(self.coef)
         else:
             a.t_colptr = None
+        lid = getattr(csr, "lid", None) if bi is None else None
+        if lid is not None:
+            ucols, n_cols, meta_ptr = lid
+            if n_cols > self.st.n_max:
+                raise ValueError(f"a local-id batch with {n_cols} distinct columns exceeds the engine's bound {self.st.n_max}")
+            if getattr(self, "_wc", None) is None:
+                self._wc = torch.zeros(self.st.n_max + 8, dtype=torch.float32, device=self.device)
+                self._gc = torch.zeros(self.st.n_max + 8, dtype=torch.float32, device=self.device)
+            a.l_ucols, a.l_meta, a.l_ncols, a.wc, a.gc = L.ptr(ucols), meta_ptr, n_cols, L.ptr(self._wc), L.ptr(self._gc)
+            from types import SimpleNamespace
+            bi = SimpleNamespace(n_cols=n_cols, ucols=ucols, local=True)  # what payload_stats / the shadow check need
+        else:
+            a.l_ucols = None
         self._last_index = bi
         par = step & 1
         a.compress = self._ca_ptr[par]
         a.decode = self._da_ptr[par]
         a.step, a.lr, a.adam_scale, a.loss_out = step, lr, adam_scale, ring_ptr
         L.check(self._step_fn(self._byref(a), L.stream()), "skml_train_step")
-        L.count_launches((3 if bi is not None else len(segs) + 3) + 1 + (1 if self.st.dense_vals is not None and bi is None else 0) + 1)
+        if lid is not None:
+            L.count_launches(len(segs) + 2 + 2)  # gather, gradient segment(s), finalize, compress, decode
+        else:
+            L.count_launches((3 if bi is not None else len(segs) + 3) + 1 +
+                             (1 if self.st.dense_vals is not None and bi is None else 0) + 1)
 
     # ----------------------------------------------------------------- steps
     def _segments(self, count: int):
@@ -218,8 +236,13 @@ class GpuEngine:
             left -= take
         return segs
 
-    def compute_gradient(self, csr: Optional[DeviceCSR] = None, segments=None, batch_rows: Optional[int] = None):
+    def compute_gradient(self, csr: Optional[DeviceCSR] = None, segments=None, batch_rows: Optional[int] = None,
+                         done_event=None):
+        """``done_event`` (a recorded torch.cuda.Event): where the gradient kernels are launched later, inside the
+        single-call step, the event is recorded right after them and ``deferred_release`` is set, so that a
+        feeder can reuse the batch's staging buffers no earlier than that."""
         m, st = self.t.model, self.st
+        self.deferred_release = False
         csr = csr or self.csr
         rows = self.batch_rows if batch_rows is None else batch_rows
         segs = self._segments(rows) if segments is None else segments
@@ -229,9 +252,12 @@ class GpuEngine:
                 self._template_rows = rows
             if self.reg_every_step and m.loss.is_l2_reg:
                 self.partials_template[2:3].copy_(torch.linalg.vector_norm(m.weights).double() * m.loss.lam)
-            self._pending = (csr, segs, rows)
+            self._pending = (csr, segs, rows, done_event)
+            self.deferred_release = done_event is not None
             m.optimizer.advance()
             return _BatchHandle(rows, self.batch_index), None, None
+        if getattr(csr, "lid", None) is not None:
+            raise NotImplementedError("local-id batches need the fused sketch engine's single-call step")
         if rows != self._template_rows:
             self.partials_template[0] = float(rows)
             self._template_rows = rows

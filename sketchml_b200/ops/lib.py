@@ -60,6 +60,8 @@ class StepArgs(C.Structure):
         ("t_colptr", c_vp), ("t_rowidx", c_vp), ("t_vals", c_vp), ("t_ucols", c_vp), ("t_bins", c_vp),
         ("t_long_col", c_vp), ("t_long_e0", c_vp), ("t_long_e1", c_vp), ("t_short", c_ll), ("t_medium", c_ll),
         ("t_long", c_ll), ("t_cols", c_ll), ("t_meta", c_vp), ("coef", c_vp),
+        ("l_ucols", c_vp), ("l_meta", c_vp), ("l_ncols", c_ll), ("wc", c_vp), ("gc", c_vp),
+        ("grad_done_event", c_vp),
     ]
 
 

@@ -254,9 +254,10 @@ class Trainer:
             if k + 1 < steps:
                 feeder.prefetch(i + 1)
             csr, rows = feeder.get(i)
-            h, _, _ = eng.compute_gradient(csr=csr, segments=[(0, rows)], batch_rows=rows)
-            feeder.release(i)
-            eng.aggregate_and_update(self.step, None)
+            h, _, _ = eng.compute_gradient(csr=csr, segments=[(0, rows)], batch_rows=rows, done_event=feeder.free[i & 1])
+            if not getattr(eng, "deferred_release", False):
+                feeder.release(i)  # the gradient kernels are already in the stream
+            eng.aggregate_and_update(self.step, None)  # otherwise they are launched here and record the event
             loss_host[k].copy_(eng.loss_ring[h.index % eng.loss_ring.shape[0]], non_blocking=True)
             self.step += 1
         return loss_host
