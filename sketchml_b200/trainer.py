@@ -246,6 +246,8 @@ class Trainer:
         side stream) and copies the step's loss partials device->host into ``loss_host``
         (pinned, shape [steps, 4]). Returns ``loss_host``; synchronise before reading it."""
         eng = self.engine
+        if not hasattr(eng, "attach_device_csr"):
+            raise NotImplementedError("train_streamed feeds device staging buffers: it needs the GPU engine (device='cuda')")
         if loss_host is None:
             loss_host = torch.zeros((steps, 4), dtype=torch.float64).pin_memory()
         feeder.prefetch(first)
