@@ -1,5 +1,6 @@
 // Python bindings of the CPU oracle (module sketchml_b200._oracle).
 #include <pybind11/numpy.h>
+#include <algorithm>
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
@@ -355,6 +356,24 @@ PYBIND11_MODULE(_oracle, m) {
         }
         return to_array(out);
     }, py::arg("flags"), py::arg("bytes"), py::arg("n"));
+    m.def("row_sort_delta", [](py::array_t<int64_t, py::array::c_style | py::array::forcecast> rowptr, I32Array cols) {
+        // Every row's indices sorted ascending and replaced by their gaps (the first one stays): the order
+        // inside a row carries no information, and gaps between sorted indices are shorter than the indices.
+        const ssize_t rows = rowptr.size() - 1;
+        std::vector<int32_t> out(cols.data(), cols.data() + cols.size());
+        for (ssize_t r = 0; r < rows; ++r) {
+            const int64_t lo = rowptr.data()[r] - rowptr.data()[0], hi = rowptr.data()[r + 1] - rowptr.data()[0];
+            if (lo < 0 || hi < lo || hi > (int64_t)out.size()) throw Error("row_sort_delta: bad row pointers");
+            std::sort(out.begin() + lo, out.begin() + hi);
+            int32_t prev = 0;
+            for (int64_t e = lo; e < hi; ++e) {
+                const int32_t v = out[e];
+                out[e] = v - prev;
+                prev = v;
+            }
+        }
+        return to_array(out);
+    }, py::arg("rowptr"), py::arg("cols"));
     m.def("pick_hashes", [](uint64_t seed, uint64_t step, uint32_t rank, uint32_t group, int rows) {
         if (rows > 8 || rows < 1) throw Error("Currently only 8 hash functions are available");
         uint8_t ids[8];

@@ -105,6 +105,30 @@ widen_kernel(const int* __restrict__ rowptr32, long long rows, long long* __rest
         for (long long i = gid; i < rows; i += gsz) labels[i] = (float)labels8[i];
 }
 
+// Undoes the per-row gap coding: every row's indices become the running sum of its gaps. One warp per
+// row: 32 consecutive entries per step (coalesced), shuffle scan, carry into the next 32; in place.
+__global__ void __launch_bounds__(256) row_prefix_kernel(const long long* __restrict__ rowptr, long long rows,
+                                                        int* __restrict__ cols) {
+    const int lane = threadIdx.x & 31;
+    const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
+        const long long lo = rowptr[r], hi = rowptr[r + 1];
+        int carry = 0;
+        for (long long base = lo; base < hi; base += 32) {
+            const long long e = base + lane;
+            int v = e < hi ? cols[e] : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xFFFFFFFFu, v, o);
+                if (lane >= o) v += t;
+            }
+            v += carry;
+            if (e < hi) cols[e] = v;
+            carry = __shfl_sync(0xFFFFFFFFu, v, 31);
+        }
+    }
+}
+
 }  // namespace
 
 static int io_sms() {
@@ -143,5 +167,15 @@ extern "C" int skml_unpack_batch(const unsigned int* packed, int bits, long long
     }
     unpack_batch_kernel<<<sms * 8, 256, 0, (cudaStream_t)stream>>>(packed, bits, nnz, cols, rowptr32, rows, rowptr,
                                                                    labels8, labels);
+    return (int)cudaGetLastError();
+}
+
+// In place: cols[e] <- sum of cols[rowptr[r] .. e] for every row r (the inverse of the host's per-row
+// gap coding). `rowptr` is the expanded 64-bit array of the same batch.
+extern "C" int skml_row_prefix(const long long* rowptr, long long rows, int* cols, void* stream) {
+    if (rows <= 0) return 0;
+    long long blocks = (rows + 7) / 8;  // eight warps per block, one row per warp and step
+    if (blocks > io_sms() * 16) blocks = io_sms() * 16;
+    row_prefix_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(rowptr, rows, cols);
     return (int)cudaGetLastError();
 }

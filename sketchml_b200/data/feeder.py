@@ -61,6 +61,10 @@ class PinnedBatch:
             ucols = np.unique(cols_np)  # ascending
             self.n_cols = int(len(ucols))
             cols_np = np.searchsorted(ucols, cols_np).astype(np.int32)
+            # inside a row the order of the entries is free: sort them and ship the gaps
+            cols_np = oracle.row_sort_delta(rowptr.numpy(), cols_np)
+            if m.values is not None:
+                raise NotImplementedError("local-id batches reorder the entries of a row: binary features only")
             self.bits = max(1, int(max(self.n_cols - 1, 1)).bit_length())
             ucol_var = oracle.pack_varbytes(np.diff(ucols, prepend=0).astype(np.int32))
         # column indices: fixed width (ceil(log2(dim)) bits each) or byte-aligned variable width (1..4
@@ -113,7 +117,7 @@ class PinnedBatch:
             return "rowptr int64, labels fp32, column indices int32"
         cols = ("column indices 1-4 bytes each + 2 flag bits (byte-aligned variable width)" if self.varbytes
                 else f"column indices bit-packed at {self.bits} bits")
-        what = "batch-local column ids" if self.local_ids else "column indices"
+        what = "batch-local column ids (sorted inside each row, as gaps)" if self.local_ids else "column indices"
         cols = cols.replace("column indices", what)
         extra = ", plus the batch's distinct columns as variable-width deltas" if self.local_ids else ""
         return f"rowptr int32, labels {'int8' if self.labels8 else 'fp32'}, {cols}{extra}, expanded on the device"
@@ -139,6 +143,10 @@ class HostBatchFeeder:
         if any(b.packed != self.packed for b in batches):
             raise ValueError("all batches of a feeder use the same transport form")
         self.copy_stream = torch.cuda.Stream(device=self.device)
+        # the expansion kernels run on their own stream, so that the copy engine can start the next
+        # batch's transfer while this batch is being expanded
+        self.unpack_stream = torch.cuda.Stream(device=self.device)
+        self.copied = [torch.cuda.Event(), torch.cuda.Event()]
         self.stage, self.raw = [], []
         for _ in range(2):
             rp = torch.zeros(rows + 1, dtype=torch.int64, device=self.device)
@@ -168,40 +176,50 @@ class HostBatchFeeder:
         b = self.batches[i % len(self.batches)]
         slot = i & 1
         st = self.stage[slot]
-        with torch.cuda.stream(self.copy_stream):
-            self.copy_stream.wait_event(self.free[slot])
+        cs, us = self.copy_stream, self.unpack_stream
+        with torch.cuda.stream(cs):
+            cs.wait_event(self.free[slot])
             if self.packed:
-                from ..ops import lib as L
                 raw = self.raw[slot]
                 raw[:b.buffer.numel()].copy_(b.buffer, non_blocking=True)
-                base = raw.data_ptr()
-                lab8 = base + b.off_labels if b.labels8 else None
-                if b.varbytes:
-                    L.check(L.lib().skml_unpack_batch_varbytes(base + b.off_flags, base + b.off_blocks, base + b.off_bytes,
-                                                               b.nnz, L.ptr(st.cols), base + b.off_rowptr, b.rows,
-                                                               L.ptr(st.rowptr), lab8, L.ptr(st.labels),
-                                                               self.copy_stream.cuda_stream), "skml_unpack_batch_varbytes")
-                    L.count_launches(1)
-                else:
-                    L.check(L.lib().skml_unpack_batch(base + b.off_cols, b.bits, b.nnz, L.ptr(st.cols), base + b.off_rowptr,
-                                                      b.rows, L.ptr(st.rowptr), lab8, L.ptr(st.labels),
-                                                      self.copy_stream.cuda_stream), "skml_unpack_batch")
-                L.count_launches(1)
-                if not b.labels8:
-                    st.labels[:b.rows].copy_(raw[b.off_labels:b.off_labels + 4 * b.rows].view(torch.float32))
-                if b.local_ids and b.n_cols:
-                    # the distinct columns: variable-width deltas -> int32 -> running sum
-                    L.check(L.lib().skml_unpack_batch_varbytes(base + b.off_uflags, base + b.off_ublocks, base + b.off_ubytes,
-                                                               b.n_cols, L.ptr(self.udelta), None, 0, None, None, None,
-                                                               self.copy_stream.cuda_stream), "skml_unpack_batch_varbytes")
-                    torch.cumsum(self.udelta[:b.n_cols], 0, dtype=torch.int32, out=self.ucols[slot][:b.n_cols])
-                    L.count_launches(2)
             else:
                 st.rowptr[:b.rows + 1].copy_(b.rowptr, non_blocking=True)
                 st.cols[:b.cols.numel()].copy_(b.cols, non_blocking=True)
                 st.labels[:b.rows].copy_(b.labels, non_blocking=True)
             if b.values is not None:
                 st.values[:b.values.numel()].copy_(b.values, non_blocking=True)
+            self.copied[slot].record()
+        if not self.packed:
+            with torch.cuda.stream(cs):
+                self.ready[slot].record()
+            return
+        from ..ops import lib as L
+        with torch.cuda.stream(us):
+            us.wait_event(self.copied[slot])
+            base = raw.data_ptr()
+            lab8 = base + b.off_labels if b.labels8 else None
+            if b.varbytes:
+                L.check(L.lib().skml_unpack_batch_varbytes(base + b.off_flags, base + b.off_blocks, base + b.off_bytes,
+                                                           b.nnz, L.ptr(st.cols), base + b.off_rowptr, b.rows,
+                                                           L.ptr(st.rowptr), lab8, L.ptr(st.labels), us.cuda_stream),
+                        "skml_unpack_batch_varbytes")
+            else:
+                L.check(L.lib().skml_unpack_batch(base + b.off_cols, b.bits, b.nnz, L.ptr(st.cols), base + b.off_rowptr,
+                                                  b.rows, L.ptr(st.rowptr), lab8, L.ptr(st.labels), us.cuda_stream),
+                        "skml_unpack_batch")
+            L.count_launches(1)
+            if not b.labels8:
+                st.labels[:b.rows].copy_(raw[b.off_labels:b.off_labels + 4 * b.rows].view(torch.float32))
+            if b.local_ids:
+                L.check(L.lib().skml_row_prefix(L.ptr(st.rowptr), b.rows, L.ptr(st.cols), us.cuda_stream), "skml_row_prefix")
+                L.count_launches(1)
+            if b.local_ids and b.n_cols:
+                # the distinct columns: variable-width deltas -> int32 -> running sum
+                L.check(L.lib().skml_unpack_batch_varbytes(base + b.off_uflags, base + b.off_ublocks, base + b.off_ubytes,
+                                                           b.n_cols, L.ptr(self.udelta), None, 0, None, None, None,
+                                                           us.cuda_stream), "skml_unpack_batch_varbytes")
+                torch.cumsum(self.udelta[:b.n_cols], 0, dtype=torch.int32, out=self.ucols[slot][:b.n_cols])
+                L.count_launches(2)
             self.ready[slot].record()
 
     def get(self, i: int):

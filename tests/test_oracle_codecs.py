@@ -389,3 +389,12 @@ def test_pack_varbytes_roundtrip():
         assert np.array_equal(o.unpack_varbytes(d["flags"], d["bytes"], n), v)
     with pytest.raises(Exception):
         o.pack_varbytes(np.array([-1], dtype=np.int32))
+
+
+def test_row_sort_delta():
+    rowptr = np.array([10, 13, 13, 17], dtype=np.int64)  # offsets may start anywhere
+    cols = np.array([7, 2, 9, 5, 5, 1, 30], dtype=np.int32)
+    got = o.row_sort_delta(rowptr, cols)
+    assert got.tolist() == [2, 5, 2, 1, 4, 0, 25]
+    back = np.concatenate([np.cumsum(got[0:3]), np.cumsum(got[3:7])])
+    assert back.tolist() == [2, 7, 9, 1, 5, 5, 30]
