@@ -77,7 +77,8 @@ class PinnedBatch:
         if transport is not None:
             self.varbytes = transport == "varbytes"
         self.off_rowptr = 0
-        self.off_labels = a16(4 * (m.rows + 1))
+        self.rowlen8 = self.max_row_nnz <= 255  # row lengths as bytes instead of 32-bit row pointers
+        self.off_labels = a16(m.rows if self.rowlen8 else 4 * (m.rows + 1))
         self.off_meta = a16(self.off_labels + (m.rows if self.labels8 else 4 * m.rows))
         self.off_cols = self.off_meta + 32
         if ucol_var is not None:  # [flags | block offsets | bytes] of the distinct-column deltas
@@ -109,7 +110,8 @@ class PinnedBatch:
             put(self.off_uflags, ucol_var["flags"])
             put(self.off_ublocks, ucol_var["block_offsets"])
             put(self.off_ubytes, ucol_var["bytes"])
-        put(self.off_rowptr, rowptr.to(torch.int32).numpy())
+        put(self.off_rowptr, (rowptr[1:] - rowptr[:-1]).to(torch.uint8).numpy() if self.rowlen8
+            else rowptr.to(torch.int32).numpy())
         put(self.off_labels, lab.to(torch.int8).numpy() if self.labels8 else lab.numpy())
 
     def transport(self) -> str:
@@ -120,7 +122,8 @@ class PinnedBatch:
         what = "batch-local column ids (sorted inside each row, as gaps)" if self.local_ids else "column indices"
         cols = cols.replace("column indices", what)
         extra = ", plus the batch's distinct columns as variable-width deltas" if self.local_ids else ""
-        return f"rowptr int32, labels {'int8' if self.labels8 else 'fp32'}, {cols}{extra}, expanded on the device"
+        rp = "row lengths uint8" if self.rowlen8 else "rowptr int32"
+        return f"{rp}, labels {'int8' if self.labels8 else 'fp32'}, {cols}{extra}, expanded on the device"
 
     def h2d_bytes(self) -> int:
         extra = self.values.numel() * 4 if self.values is not None else 0
@@ -198,13 +201,16 @@ class HostBatchFeeder:
             us.wait_event(self.copied[slot])
             base = raw.data_ptr()
             lab8 = base + b.off_labels if b.labels8 else None
+            rp32 = None if b.rowlen8 else base + b.off_rowptr
+            if b.rowlen8:  # st.rowptr[0] is and stays 0
+                torch.cumsum(raw[b.off_rowptr:b.off_rowptr + b.rows], 0, dtype=torch.int64, out=st.rowptr[1:b.rows + 1])
             if b.varbytes:
                 L.check(L.lib().skml_unpack_batch_varbytes(base + b.off_flags, base + b.off_blocks, base + b.off_bytes,
-                                                           b.nnz, L.ptr(st.cols), base + b.off_rowptr, b.rows,
+                                                           b.nnz, L.ptr(st.cols), rp32, b.rows,
                                                            L.ptr(st.rowptr), lab8, L.ptr(st.labels), us.cuda_stream),
                         "skml_unpack_batch_varbytes")
             else:
-                L.check(L.lib().skml_unpack_batch(base + b.off_cols, b.bits, b.nnz, L.ptr(st.cols), base + b.off_rowptr,
+                L.check(L.lib().skml_unpack_batch(base + b.off_cols, b.bits, b.nnz, L.ptr(st.cols), rp32,
                                                   b.rows, L.ptr(st.rowptr), lab8, L.ptr(st.labels), us.cuda_stream),
                         "skml_unpack_batch")
             L.count_launches(1)
