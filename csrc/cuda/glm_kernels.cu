@@ -226,7 +226,7 @@ glm_rows_kernel(const long long* __restrict__ rowptr, const int* __restrict__ co
                     // the atomicOr is only issued for bits that are not set yet
 #pragma unroll
                     for (int u = 0; u < GRAD_RPI; ++u)
-                        seen[u] = c[u] >= hot ? *(volatile unsigned int*)(bitmap + (c[u] >> 5)) : ~0u;
+                        seen[u] = (bitmap && c[u] >= hot) ? *(volatile unsigned int*)(bitmap + (c[u] >> 5)) : ~0u;  // no bitmap: nothing to mark
 #pragma unroll
                     for (int u = 0; u < GRAD_RPI; ++u) {
                         if (c[u] < 0) continue;
@@ -263,7 +263,7 @@ glm_rows_kernel(const long long* __restrict__ rowptr, const int* __restrict__ co
             float v = i < hot ? s_hot[i] : 0.f;
             unsigned int m = __ballot_sync(0xFFFFFFFFu, v != 0.f);
             if (v != 0.f) red_add_f32(g + i, v);
-            if (lane == 0 && m) atomicOr(bitmap + (base >> 5), m);
+            if (bitmap && lane == 0 && m) atomicOr(bitmap + (base >> 5), m);
         }
     }
     double tot = block_sum_double(loss_sum);
@@ -911,7 +911,7 @@ __global__ void finalize_compact_kernel(float* __restrict__ gc, const float* __r
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         vals[i] = gc[i] + lambda * wc[i];
         gc[i] = 0.f;
-        if (i < (n + 31) / 32) bitmap[i] = 0u;
+        if (bitmap && i < (n + 31) / 32) bitmap[i] = 0u;
     }
 }
 

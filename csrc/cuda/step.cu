@@ -53,11 +53,11 @@ extern "C" int skml_train_step(SkmlStepArgs* a, void* stream_) {
         for (int s = 0; s < 2; ++s) {
             if (a->seg_cnt[s] <= 0) continue;
             rc = skml_glm_grad(a->rowptr, a->cols, a->vals, a->labels, a->seg_lo[s], a->seg_cnt[s], a->nnz_padded,
-                               a->avg_nnz, a->wc, a->gc, a->bitmap, (int)a->loss_id, (float)a->inv_batch, (int)a->hot,
+                               a->avg_nnz, a->wc, a->gc, nullptr, (int)a->loss_id, (float)a->inv_batch, (int)a->hot,
                                a->partials + 1, a->status, a->budget_cycles, stream_);
             if (rc) return rc;
         }
-        rc = skml_finalize_compact(a->gc, a->wc, (float)a->lambda, n, a->gvals, a->bitmap, stream_);
+        rc = skml_finalize_compact(a->gc, a->wc, (float)a->lambda, n, a->gvals, nullptr, stream_);  // no touched bitmap: every slot is a key
         if (rc) return rc;
         a->compress->step = a->step;
         a->compress->keys = a->l_ucols;
