@@ -356,6 +356,62 @@ PYBIND11_MODULE(_oracle, m) {
         }
         return to_array(out);
     }, py::arg("flags"), py::arg("bytes"), py::arg("n"));
+    m.def("pack_varnibbles", [](I32Array v) {
+        // Nibble-aligned variable-width code for non-negative integers: value i takes 1..8 nibbles (the
+        // fewest that hold it), lowest nibble first, nibble p of the stream in bits [4 (p & 7), +4) of 32-bit
+        // word p >> 3; its width - 1 sits in 3 flag bits at bit 3 i of the flag stream (same word order);
+        // `block_offsets[b]` is the nibble offset of value 1024 b. Both streams end with padding words.
+        const size_t n = (size_t)v.size();
+        std::vector<uint32_t> flags((3 * n + 31) / 32 + 2, 0u);
+        std::vector<uint32_t> offs((n + 1023) / 1024 + 1, 0u);
+        std::vector<uint32_t> words;
+        words.reserve(n / 2 + 16);
+        uint64_t nib = 0;
+        for (size_t i = 0; i < n; ++i) {
+            if ((i & 1023) == 0) offs[i >> 10] = (uint32_t)nib;
+            const int32_t sv = v.data()[i];
+            if (sv < 0) throw Error("pack_varnibbles: negative value");
+            const uint32_t x = (uint32_t)sv;
+            int w = 1;
+            while (w < 8 && (x >> (4 * w)) != 0) ++w;
+            const size_t fb = 3 * i;
+            const uint64_t fw = (uint64_t)(w - 1) << (fb & 31);
+            flags[fb >> 5] |= (uint32_t)fw;
+            flags[(fb >> 5) + 1] |= (uint32_t)(fw >> 32);
+            const size_t bit = (size_t)nib * 4, wi = bit >> 5;
+            if (words.size() < wi + 2) words.resize(wi + 2, 0u);
+            const uint64_t wide = (uint64_t)x << (bit & 31);
+            words[wi] |= (uint32_t)wide;
+            words[wi + 1] |= (uint32_t)(wide >> 32);
+            nib += (uint64_t)w;
+            if (nib > 0xFFFFFF00ull) throw Error("pack_varnibbles: stream too long");
+        }
+        offs[(n + 1023) / 1024] = (uint32_t)nib;
+        words.resize((size_t)((nib * 4 + 31) / 32) + 6, 0u);
+        py::dict r;
+        r["flags"] = to_array(flags);
+        r["block_offsets"] = to_array(offs);
+        r["words"] = to_array(words);
+        return r;
+    }, py::arg("values"));
+    m.def("unpack_varnibbles", [](py::array_t<uint32_t, py::array::c_style | py::array::forcecast> flags,
+                                  py::array_t<uint32_t, py::array::c_style | py::array::forcecast> words, size_t n) {
+        std::vector<int32_t> out(n);
+        uint64_t nib = 0;
+        for (size_t i = 0; i < n; ++i) {
+            const size_t fb = 3 * i;
+            if ((fb >> 5) + 1 >= (size_t)flags.size()) throw Error("unpack_varnibbles: flags too short");
+            const uint64_t fwide = (uint64_t)flags.data()[fb >> 5] | ((uint64_t)flags.data()[(fb >> 5) + 1] << 32);
+            const int w = (int)((fwide >> (fb & 31)) & 7u) + 1;
+            const size_t bit = (size_t)nib * 4, wi = bit >> 5;
+            if (wi + 1 >= (size_t)words.size()) throw Error("unpack_varnibbles: words too short");
+            const uint64_t wide = (uint64_t)words.data()[wi] | ((uint64_t)words.data()[wi + 1] << 32);
+            const uint64_t x = wide >> (bit & 31);
+            out[i] = (int32_t)(w == 8 ? (uint32_t)x : (uint32_t)(x & ((1ull << (4 * w)) - 1ull)));
+            nib += (uint64_t)w;
+        }
+        return to_array(out);
+    }, py::arg("flags"), py::arg("words"), py::arg("n"));
     m.def("row_sort_delta", [](py::array_t<int64_t, py::array::c_style | py::array::forcecast> rowptr, I32Array cols) {
         // Every row's indices sorted ascending and replaced by their gaps (the first one stays): the order
         // inside a row carries no information, and gaps between sorted indices are shorter than the indices.

@@ -95,6 +95,71 @@ unpack_varbytes_kernel(const unsigned int* __restrict__ flags, const unsigned in
     }
 }
 
+// Nibble-aligned variable width: value i takes 1..8 nibbles (lowest first), its width - 1 in 3 flag bits
+// at bit 3 i of the flag stream; block_offsets[b] is the nibble offset of value 1024 b. Same structure
+// as the byte-aligned kernel: 4 values per thread (12 flag bits), a block scan of the nibble counts,
+// at most 32 nibbles per thread fetched as five aligned words.
+__global__ void __launch_bounds__(256)
+unpack_varnibbles_kernel(const unsigned int* __restrict__ flags, const unsigned int* __restrict__ block_offsets,
+                         const unsigned int* __restrict__ words, long long n, int* __restrict__ cols) {
+    __shared__ unsigned int s_part[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long nblocks = (n + 1023) / 1024;
+    for (long long b = blockIdx.x; b < nblocks; b += gridDim.x) {
+        const long long i0 = b * 1024 + 4 * threadIdx.x;
+        unsigned int w[4] = {0, 0, 0, 0}, wsum = 0;
+        if (i0 < n) {
+            const unsigned long long fb = 3ull * (unsigned long long)i0;
+            const unsigned int f = __funnelshift_r(flags[fb >> 5], flags[(fb >> 5) + 1], (unsigned int)(fb & 31)) & 0xFFFu;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (i0 + u < n) {
+                    w[u] = ((f >> (3 * u)) & 7u) + 1u;
+                    wsum += w[u];
+                }
+        }
+        unsigned int inc = wsum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned int t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+            if (lane >= o) inc += t;
+        }
+        __syncthreads();  // s_part of the previous iteration has been read
+        if (lane == 31) s_part[warp] = inc;
+        __syncthreads();
+        unsigned int base = block_offsets[b];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (k < warp) base += s_part[k];
+        if (i0 < n) {
+            const unsigned int nib0 = base + inc - wsum;
+            const unsigned int* src = words + (nib0 >> 3);
+            unsigned int W[5];
+#pragma unroll
+            for (int t = 0; t < 5; ++t) W[t] = src[t];  // the stream ends with padding words
+            unsigned int start = nib0 & 7u;
+            int out[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const unsigned int wi = start >> 3, sh = 4u * (start & 7u);
+                unsigned int lo = W[0], hi = W[1];
+#pragma unroll
+                for (int t = 1; t < 4; ++t)
+                    if (wi == (unsigned int)t) { lo = W[t]; hi = W[t + 1]; }
+                const unsigned int v = __funnelshift_r(lo, hi, sh);
+                out[u] = (int)(w[u] >= 8 ? v : (v & ((1u << (4u * w[u])) - 1u)));
+                start += w[u];
+            }
+            if (i0 + 3 < n) {
+                *reinterpret_cast<int4*>(cols + i0) = make_int4(out[0], out[1], out[2], out[3]);
+            } else {
+                for (int u = 0; u < 4; ++u)
+                    if (i0 + u < n) cols[i0 + u] = out[u];
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256)
 widen_kernel(const int* __restrict__ rowptr32, long long rows, long long* __restrict__ rowptr,
              const signed char* __restrict__ labels8, float* __restrict__ labels) {
@@ -177,5 +242,17 @@ extern "C" int skml_row_prefix(const long long* rowptr, long long rows, int* col
     long long blocks = (rows + 7) / 8;  // eight warps per block, one row per warp and step
     if (blocks > io_sms() * 16) blocks = io_sms() * 16;
     row_prefix_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(rowptr, rows, cols);
+    return (int)cudaGetLastError();
+}
+
+// Nibble-aligned form of skml_unpack_batch_varbytes (`words`: the nibble stream as 32-bit words with
+// six words of padding; `flags`: 3 bits per value with two words of padding).
+extern "C" int skml_unpack_batch_varnibbles(const unsigned int* flags, const unsigned int* block_offsets,
+                                            const unsigned int* words, long long nnz, int* cols, const int* rowptr32,
+                                            long long rows, long long* rowptr, const signed char* labels8, float* labels,
+                                            void* stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (nnz > 0) unpack_varnibbles_kernel<<<io_sms() * 8, 256, 0, s>>>(flags, block_offsets, words, nnz, cols);
+    if (rowptr32 || labels8) widen_kernel<<<io_sms() * 4, 256, 0, s>>>(rowptr32, rows, rowptr, labels8, labels);
     return (int)cudaGetLastError();
 }

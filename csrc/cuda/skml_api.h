@@ -140,6 +140,9 @@ int skml_unpack_batch(const unsigned int* packed, int bits, long long nnz, int* 
 // The same for column indices in the byte-aligned variable-width form (1..4 bytes each, 2 flag bits,
 // one byte offset per 1024 values).
 int skml_row_prefix(const long long* rowptr, long long rows, int* cols, void* stream);
+int skml_unpack_batch_varnibbles(const unsigned int* flags, const unsigned int* block_offsets, const unsigned int* words,
+                                 long long nnz, int* cols, const int* rowptr32, long long rows, long long* rowptr,
+                                 const signed char* labels8, float* labels, void* stream);
 int skml_unpack_batch_varbytes(const unsigned int* flags, const unsigned int* block_offsets, const unsigned char* bytes,
                                long long nnz, int* cols, const int* rowptr32, long long rows, long long* rowptr,
                                const signed char* labels8, float* labels, void* stream);

@@ -19,7 +19,8 @@ class PinnedBatch:
     ``packed=True`` stores the transport form that `skml_unpack_batch*` expands on the device:
     one contiguous buffer ``[rowptr int32 | labels int8 (or fp32) | column indices]`` (sections
     16-byte aligned). The column indices take ceil(log2(dim)) bits each, or 1..4 bytes + 2 flag bits
-    each when that is shorter (``transport="bits"`` / ``"varbytes"`` forces one). Values (absent for
+    each, or 1..8 nibbles + 3 flag bits each, whichever is shortest (``transport="bits"`` /
+    ``"varbytes"`` / ``"varnibbles"`` forces one). Values (absent for
     binary features) always travel as fp32.
 
     ``local_ids=True`` (implies ``packed``) additionally replaces every column index by its position
@@ -73,9 +74,15 @@ class PinnedBatch:
         fixed_bytes = 4 * ((m.nnz * self.bits + 31) // 32 + 2)
         a16 = lambda x: (x + 15) // 16 * 16
         var_bytes = a16(4 * len(var["flags"])) + a16(4 * len(var["block_offsets"])) + a16(len(var["bytes"]))
-        self.varbytes = var_bytes < fixed_bytes
-        if transport is not None:
-            self.varbytes = transport == "varbytes"
+        nibv = oracle.pack_varnibbles(cols_np)
+        nib_bytes = a16(4 * len(nibv["flags"])) + a16(4 * len(nibv["block_offsets"])) + a16(4 * len(nibv["words"]))
+        sizes = {"bits": fixed_bytes, "varbytes": var_bytes, "varnibbles": nib_bytes}
+        self.col_form = transport if transport is not None else min(sizes, key=sizes.get)
+        if self.col_form not in sizes:
+            raise ValueError(f"unknown column transport {self.col_form!r}")
+        self.varbytes = self.col_form == "varbytes"
+        if self.col_form == "varnibbles":  # same three sections as the byte-aligned form
+            var = {"flags": nibv["flags"], "block_offsets": nibv["block_offsets"], "bytes": nibv["words"].view(np.uint8)}
         self.off_rowptr = 0
         self.rowlen8 = self.max_row_nnz <= 255  # row lengths as bytes instead of 32-bit row pointers
         self.off_labels = a16(m.rows if self.rowlen8 else 4 * (m.rows + 1))
@@ -91,7 +98,7 @@ class PinnedBatch:
             raw = torch.from_numpy(np.ascontiguousarray(arr).view(np.uint8))
             self.buffer[off:off + raw.numel()].copy_(raw)
 
-        if self.varbytes:
+        if self.col_form != "bits":
             self.off_flags = self.off_cols
             self.off_blocks = a16(self.off_flags + 4 * len(var["flags"]))
             self.off_bytes = a16(self.off_blocks + 4 * len(var["block_offsets"]))
@@ -117,8 +124,9 @@ class PinnedBatch:
     def transport(self) -> str:
         if not self.packed:
             return "rowptr int64, labels fp32, column indices int32"
-        cols = ("column indices 1-4 bytes each + 2 flag bits (byte-aligned variable width)" if self.varbytes
-                else f"column indices bit-packed at {self.bits} bits")
+        cols = {"varbytes": "column indices 1-4 bytes each + 2 flag bits (byte-aligned variable width)",
+                "varnibbles": "column indices 1-8 nibbles each + 3 flag bits (nibble-aligned variable width)",
+                "bits": f"column indices bit-packed at {self.bits} bits"}[self.col_form]
         what = "batch-local column ids (sorted inside each row, as gaps)" if self.local_ids else "column indices"
         cols = cols.replace("column indices", what)
         extra = ", plus the batch's distinct columns as variable-width deltas" if self.local_ids else ""
@@ -204,11 +212,10 @@ class HostBatchFeeder:
             rp32 = None if b.rowlen8 else base + b.off_rowptr
             if b.rowlen8:  # st.rowptr[0] is and stays 0
                 torch.cumsum(raw[b.off_rowptr:b.off_rowptr + b.rows], 0, dtype=torch.int64, out=st.rowptr[1:b.rows + 1])
-            if b.varbytes:
-                L.check(L.lib().skml_unpack_batch_varbytes(base + b.off_flags, base + b.off_blocks, base + b.off_bytes,
-                                                           b.nnz, L.ptr(st.cols), rp32, b.rows,
-                                                           L.ptr(st.rowptr), lab8, L.ptr(st.labels), us.cuda_stream),
-                        "skml_unpack_batch_varbytes")
+            if b.col_form != "bits":
+                fn = L.lib().skml_unpack_batch_varbytes if b.varbytes else L.lib().skml_unpack_batch_varnibbles
+                L.check(fn(base + b.off_flags, base + b.off_blocks, base + b.off_bytes, b.nnz, L.ptr(st.cols), rp32, b.rows,
+                           L.ptr(st.rowptr), lab8, L.ptr(st.labels), us.cuda_stream), "skml_unpack_batch_var*")
             else:
                 L.check(L.lib().skml_unpack_batch(base + b.off_cols, b.bits, b.nnz, L.ptr(st.cols), rp32,
                                                   b.rows, L.ptr(st.rowptr), lab8, L.ptr(st.labels), us.cuda_stream),

@@ -95,6 +95,7 @@ _SIGS = {
     "skml_da_zero_pos": (c_int, [c_vp, c_ll, c_vp, c_ll, c_vp, c_vp]),
     "skml_da_extract": (c_int, [c_vp, c_ll, c_vp, c_vp, c_vp, c_vp]),
     "skml_unpack_batch": (c_int, [c_vp, c_int, c_ll, c_vp, c_vp, c_ll, c_vp, c_vp, c_vp, c_vp]),
+    "skml_unpack_batch_varnibbles": (c_int, [c_vp, c_vp, c_vp, c_ll, c_vp, c_vp, c_ll, c_vp, c_vp, c_vp, c_vp]),
     "skml_row_prefix": (c_int, [c_vp, c_ll, c_vp, c_vp]),
     "skml_unpack_batch_varbytes": (c_int, [c_vp, c_vp, c_vp, c_ll, c_vp, c_vp, c_ll, c_vp, c_vp, c_vp, c_vp]),
     "skml_fixedpoint_scratch_bytes": (c_ll, []),

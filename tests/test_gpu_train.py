@@ -115,14 +115,15 @@ def test_packed_batch_transport_matches_plain_and_trains():
     plain = HostBatchFeeder([PinnedBatch(p) for p in parts], "cuda")
     packed = HostBatchFeeder([PinnedBatch(p, packed=True, transport="bits") for p in parts], "cuda")
     varb = HostBatchFeeder([PinnedBatch(p, packed=True, transport="varbytes") for p in parts], "cuda")
+    varn = HostBatchFeeder([PinnedBatch(p, packed=True, transport="varnibbles") for p in parts], "cuda")
     auto = PinnedBatch(parts[0], packed=True)
     assert packed.batches[0].bits == 16 and packed.batches[0].labels8 and not packed.batches[0].varbytes
     assert packed.batches[0].h2d_bytes() < 0.62 * plain.batches[0].h2d_bytes()
-    assert auto.h2d_bytes() == min(packed.batches[0].h2d_bytes(), varb.batches[0].h2d_bytes())
+    assert auto.h2d_bytes() == min(packed.batches[0].h2d_bytes(), varb.batches[0].h2d_bytes(), varn.batches[0].h2d_bytes())
     for i in range(4):
         plain.prefetch(i)
         a, rows = plain.get(i)
-        for other in (packed, varb):
+        for other in (packed, varb, varn):
             other.prefetch(i)
             b, rows_b = other.get(i)
             torch.cuda.synchronize()

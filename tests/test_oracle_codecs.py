@@ -398,3 +398,15 @@ def test_row_sort_delta():
     assert got.tolist() == [2, 5, 2, 1, 4, 0, 25]
     back = np.concatenate([np.cumsum(got[0:3]), np.cumsum(got[3:7])])
     assert back.tolist() == [2, 7, 9, 1, 5, 5, 30]
+
+
+def test_pack_varnibbles_roundtrip():
+    rng = np.random.default_rng(5)
+    for n in (0, 1, 5, 1023, 1024, 1025, 7000):
+        v = (rng.integers(0, 2 ** 31 - 1, n) >> rng.integers(0, 31, n)).astype(np.int32)
+        d = o.pack_varnibbles(v)
+        widths = np.ones(n, dtype=np.int64)
+        for k in range(1, 8):
+            widths += (v >> (4 * k)) != 0
+        assert d["block_offsets"][-1] == widths.sum()
+        assert np.array_equal(o.unpack_varnibbles(d["flags"], d["words"], n), v)
