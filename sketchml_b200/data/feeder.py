@@ -17,8 +17,8 @@ class PinnedBatch:
     """One minibatch in pinned host memory.
 
     ``packed=True`` stores the transport form that `skml_unpack_batch*` expands on the device:
-    one contiguous buffer ``[rowptr int32 | labels int8 (or fp32) | column indices]`` (sections
-    16-byte aligned). The column indices take ceil(log2(dim)) bits each, or 1..4 bytes + 2 flag bits
+    one contiguous buffer ``[row lengths uint8 (or rowptr int32) | labels int8 (or fp32) | meta |
+    column indices]`` (sections 16-byte aligned). The column indices take ceil(log2(dim)) bits each, or 1..4 bytes + 2 flag bits
     each, or 1..8 nibbles + 3 flag bits each, whichever is shortest (``transport="bits"`` /
     ``"varbytes"`` / ``"varnibbles"`` forces one). Values (absent for
     binary features) always travel as fp32.
@@ -52,6 +52,8 @@ class PinnedBatch:
         from ..compress import oracle
         if m.nnz >= 2 ** 31:
             raise ValueError("a packed batch holds fewer than 2^31 non-zeros")
+        if self.local_ids and m.values is not None:
+            raise NotImplementedError("local-id batches reorder the entries of a row: binary features only")
         self.bits = max(1, int(m.dim - 1).bit_length())
         lab = m.labels.to(torch.float32)
         self.labels8 = bool(torch.all(lab == lab.round()) and float(lab.abs().max() if m.rows else 0) <= 127)
@@ -64,8 +66,6 @@ class PinnedBatch:
             cols_np = np.searchsorted(ucols, cols_np).astype(np.int32)
             # inside a row the order of the entries is free: sort them and ship the gaps
             cols_np = oracle.row_sort_delta(rowptr.numpy(), cols_np)
-            if m.values is not None:
-                raise NotImplementedError("local-id batches reorder the entries of a row: binary features only")
             self.bits = max(1, int(max(self.n_cols - 1, 1)).bit_length())
             ucol_var = oracle.pack_varbytes(np.diff(ucols, prepend=0).astype(np.int32))
         # column indices: fixed width (ceil(log2(dim)) bits each) or byte-aligned variable width (1..4
