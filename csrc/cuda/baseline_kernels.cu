@@ -163,7 +163,13 @@ extern "C" int skml_fixedpoint_unpack_scatter(float* acc, const int* keys, const
                                               long long code_stride, int lists, int bits, float* vals_out,
                                               void* stream) {
     if (bits < 2 || bits >= 30) return (int)cudaErrorInvalidValue;
-    fp_unpack_scatter_kernel<<<fp_sm_count() * 8, FP_THREADS, 0, (cudaStream_t)stream>>>(
-        acc, keys, codes, norms, counts, key_stride, code_stride, lists, bits, vals_out);
-    return (int)cudaGetLastError();
+    // one launch per list, in list order: every rank adds the lists to a coordinate in the same order
+    for (int l = 0; l < lists; ++l) {
+        fp_unpack_scatter_kernel<<<fp_sm_count() * 8, FP_THREADS, 0, (cudaStream_t)stream>>>(
+            acc, keys + (long long)l * key_stride, codes + (long long)l * code_stride, norms + l, counts + l, key_stride,
+            code_stride, 1, bits, vals_out ? vals_out + (long long)l * key_stride : nullptr);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
 }

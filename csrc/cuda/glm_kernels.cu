@@ -687,10 +687,19 @@ __global__ void scatter_kv_kernel(float* acc, const int* keys, const float* vals
     }
 }
 
+// One launch per list: inside a list every key occurs once, so its adds touch distinct words, and
+// stream order fixes the order in which the lists reach a word. Every rank therefore computes the
+// same floating-point sums (a single launch over all lists would let blocks run ahead into later
+// lists, and three or more addends in varying order round differently).
 extern "C" int skml_scatter_kv(float* acc, const int* keys, const float* vals, const long long* counts,
                                long long stride, int lists, void* stream) {
-    scatter_kv_kernel<<<sm_count() * 8, 256, 0, (cudaStream_t)stream>>>(acc, keys, vals, counts, stride, lists);
-    return (int)cudaGetLastError();
+    for (int l = 0; l < lists; ++l) {
+        scatter_kv_kernel<<<sm_count() * 8, 256, 0, (cudaStream_t)stream>>>(acc, keys + (long long)l * stride,
+                                                                            vals + (long long)l * stride, counts + l, stride, 1);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
 }
 
 // ---------------------------------------------------------------------------

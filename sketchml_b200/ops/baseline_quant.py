@@ -51,7 +51,7 @@ class FixedPointCodec:
         L.check(self.lib.skml_fixedpoint_unpack_scatter(L.ptr(acc), L.ptr(keys), L.ptr(codes), L.ptr(norms), L.ptr(counts),
                                                         self.n_max, self.code_stride, lists, self.bits, L.ptr(vals_out),
                                                         L.stream()), "skml_fixedpoint_unpack_scatter")
-        L.count_launches(1)
+        L.count_launches(lists)  # one launch per list: the lists reach a coordinate in list order on every rank
 
     def wire_bytes(self, n: int) -> int:
         """Bytes one rank contributes for n non-zeros: raw keys, codes, count and norm."""
