@@ -6,7 +6,7 @@ cursor (ml/data/DataSet.scala:15-21); this is the same walk for data that does n
 resident on the GPU."""
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import List
 
 import torch
 

@@ -13,14 +13,13 @@ actions with a driver round-trip each).
 """
 from __future__ import annotations
 
-import math
 from typing import List, Optional
 
 import torch
 import torch.distributed as dist
 
 from . import config as C
-from .data import CSRMatrix, DataSet, SyntheticSpec
+from .data import SyntheticSpec
 from .ops import lib as L
 from .ops.codec import GpuCompressor, GpuDecoder, read_status
 from .ops.datagen import generate_gpu
