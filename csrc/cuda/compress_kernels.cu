@@ -95,6 +95,8 @@ struct Layout {
     int vbase_prev[SKML_WARPS][SKML_MAX_GROUPS];
     unsigned char hash_ids[SKML_MAX_GROUPS][8];
     unsigned long long col_magic[SKML_MAX_GROUPS];  // ceil(2^64 / col) for the division-free modulo
+    unsigned int recip[SKML_MAX_GROUPS];            // floor(2^32 / col) for the mixer-only hash path
+    int mixers;                                     // every row of every group uses an integer mixer (<= 3 rows)
     unsigned long long off_bv, off_gt, off_flags, off_restart, off_tables, off_deltas, total_bytes;
     int overflow;
 };
@@ -701,7 +703,12 @@ __device__ void element_pass(const CP& p, Smem& s, long long n) {
             const int col = (int)L.col[g];
             unsigned int* tab = p.tables + L.tab32_off[g];
             int pos[SKML_MAX_ROWS];
-            if (p.rows <= 4) {
+            if (L.mixers) {
+                skml_hash_rows_mixers<3>(L.hash_ids[g], p.rows, key, (unsigned int)col, L.recip[g], pos);
+#pragma unroll
+                for (int r = 0; r < 3; ++r)
+                    if (r < p.rows) atomicMin(tab + (long long)r * col + pos[r], cell);
+            } else if (p.rows <= 4) {
                 skml_hash_rows<4>(L.hash_ids[g], p.rows, key, col, L.col_magic[g], pos);
 #pragma unroll
                 for (int r = 0; r < 4; ++r)
@@ -877,9 +884,15 @@ __device__ void compute_layout(const CP& p, Smem& s, long long n) {
         }
         L.col[g] = col;
         L.col_magic[g] = col ? skml_fastmod_magic(col) : 0ull;
+        L.recip[g] = skml_recip32(col);
         skml_pick_hashes(p.seed, p.step, p.rank, (unsigned int)g, p.rows, L.hash_ids[g]);
     }
     __syncthreads();
+    if (threadIdx.x == 0) {
+        bool mix = p.rows <= 3;
+        for (int g = 0; g < G && mix; ++g) mix = skml_rows_are_mixers(L.hash_ids[g], p.rows);
+        L.mixers = mix ? 1 : 0;
+    }
     if (threadIdx.x == 0) {
         const int cb = s.qi.cell_bits;
         L.off_bv = SKML_HEADER_BYTES;

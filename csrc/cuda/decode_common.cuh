@@ -1,0 +1,261 @@
+// Building blocks of the fused decode + aggregate + update kernel (decode_kernels.cu): kernel
+// parameters, the (rank, group) work item, the sketch query, the one-barrier block scan and the
+// decode of one 1024-key chunk.
+//
+// Reference behaviour restated (paths inside the reference project):
+//   sketch/.../binary/DeltaBinaryEncoder.java:42-53 (key decode),
+//   sketch/.../sketch/frequency/MinMaxSketch.java:64-73, GroupedMinMaxSketch.java:123-146 (query),
+//   ml/.../gradient/SketchGradient.scala:57-68 (dequantize).
+#pragma once
+#include <math.h>
+
+#include "skml_api.h"
+#include "skml_device.cuh"
+
+#define DEC_MAX_ITEMS (SKML_MAX_PEERS * SKML_MAX_GROUPS)
+#define DEC_KPT 4        // keys of a 1024-key chunk per thread
+#define DEC_THREADS (SKML_RESTART_INTERVAL / DEC_KPT)
+#define DEC_BLOCKS_PER_SM 4
+#define DEC_TAB_SMEM 36864   // bytes of shared memory per block for a staged sketch table
+
+struct DP {
+    const unsigned char* payload[SKML_MAX_PEERS];
+    const unsigned long long* flag[SKML_MAX_PEERS];
+    int world;
+    long long slot_capacity;
+    unsigned long long step;
+    long long dim;
+    float* w;
+    float* adam_m;
+    float* adam_v;
+    float lr, adam_scale;
+    long long* acc;
+    int* key_scratch;
+    float* val_scratch;
+    long long key_capacity;
+    double* loss_out;
+    float* out_sum;
+    unsigned int* ctrl;
+    unsigned int* status;
+    long long budget;
+    int max_items;
+    int tab_off;     // byte offset of the staged-table area inside the dynamic shared memory (0 = none)
+};
+
+struct DecItem {  // one (rank, group) key stream
+    const unsigned char* base;
+    SkmlGroupEntry e;
+    unsigned long long chunk_prefix, key_prefix;
+    unsigned int zero, cell_bits, rows;
+    unsigned int recip;       // floor(2^32 / col_num) for the mixer-only hash path
+    unsigned long long off_bv;
+    unsigned long long col_magic;
+    int mixers;               // every row uses one of the three integer mixers (at most three rows)
+};
+
+
+__device__ __forceinline__ long long to_fixed(double v, int shift) { return __double2ll_rn(ldexp(v, shift)); }
+__device__ __forceinline__ double from_fixed(long long a, int shift) { return ldexp((double)a, -shift); }
+
+__device__ __forceinline__ void apply_one(const DP& p, long long k, float g) {
+    if (p.out_sum) {
+        p.out_sum[k] = g;
+    } else if (!p.adam_v) {
+        p.w[k] -= p.lr * g;
+    } else {
+        float mt = 0.9f * p.adam_m[k] + 0.1f * g;
+        float vt = 0.999f * p.adam_v[k] + 0.001f * g * g;
+        p.w[k] -= p.lr * p.adam_scale * mt / (sqrtf(vt) + 1e-8f);
+        p.adam_m[k] = mt;
+        p.adam_v[k] = vt;
+    }
+}
+
+// Linear modes: SGD step on w, or accumulation of the plain mean into out_sum.
+__device__ __forceinline__ void apply_direct(const DP& p, long long k, float g) {
+    if (p.out_sum) p.out_sum[k] += g;
+    else p.w[k] -= p.lr * g;
+}
+
+// Query of one key in its group's sketch: the bucket value of the cell farthest from the zero bucket.
+template <int MAXR>
+__device__ __forceinline__ float query_one(const DP& p, const DecItem& it, unsigned int key, const unsigned char* stab) {
+    const int col = (int)it.e.col_num;
+    const int zero = (int)it.zero;
+    int cells[MAXR];
+    int pos[MAXR];
+    const int rows = (int)it.rows;
+    if (it.mixers) skml_hash_rows_mixers<(MAXR < 3 ? MAXR : 3)>(it.e.hash_ids, rows, (int)key, (unsigned int)col, it.recip, pos);
+    else skml_hash_rows<MAXR>(it.e.hash_ids, rows, (int)key, col, it.col_magic, pos);
+#pragma unroll
+    for (int r = 0; r < MAXR; ++r) {  // independent loads first
+        cells[r] = zero;
+        if (r < rows) {
+            const unsigned int c = (unsigned int)r * (unsigned int)col + (unsigned int)pos[r];  // rows * col < 2^31 (checked in prepare)
+            if (stab) {  // the group's whole table sits in shared memory
+                if (it.cell_bits == 8) cells[r] = stab[c];
+                else cells[r] = reinterpret_cast<const unsigned short*>(stab)[c];
+            } else if (it.cell_bits == 8) {
+                cells[r] = __ldcg(it.base + it.e.table_off + c);
+            } else {
+                cells[r] = __ldcg(reinterpret_cast<const unsigned short*>(it.base + it.e.table_off) + c);
+            }
+        }
+    }
+    int res = zero, best = 0;
+#pragma unroll
+    for (int r = 0; r < MAXR; ++r) {
+        int d = cells[r] - zero;
+        if (d < 0) d = -d;
+        if (d > best) {
+            best = d;
+            res = cells[r];
+        }
+    }
+    // Bucket values (<= 16 KB per payload, read by every key) go through L1: the SM cannot hold a stale
+    // line of them, because it first touches a payload after the arrival flag was acquired and L1 is
+    // invalidated between dependent grids. Everything else of the payload is read once: L2 only.
+    return reinterpret_cast<const float*>(it.base + it.off_bv)[res];
+}
+
+// Exclusive prefix sum over the block with ONE barrier: every warp publishes its total, every
+// thread adds up the totals of the warps before it. The caller alternates `part` between calls
+// so that no second barrier is needed to protect it.
+__device__ __forceinline__ unsigned int dec_scan(unsigned int v, unsigned int* part) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned int t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) part[warp] = inc;
+    __syncthreads();
+    unsigned int base = 0;
+#pragma unroll
+    for (int w = 0; w < DEC_THREADS / 32; ++w)
+        if (w < warp) base += part[w];
+    return base + inc - v;
+}
+
+// Decode of one 1024-key chunk of a (rank, group) key stream by the whole block (DEC_THREADS
+// threads, DEC_KPT adjacent keys each; restart points make chunks independent): flag bits -> delta
+// widths -> block scan -> delta bytes gathered from aligned words -> block scan -> keys; then the
+// sketch query and the bucket value of every key. `part_a` / `part_b` are two scan scratch rows
+// (DEC_THREADS / 32 words each) that the caller alternates between consecutive chunks, so that no
+// extra barrier is needed between chunks. All threads of the block must call this together.
+struct ChunkKeys {
+    unsigned int i0;              // index inside the chunk of this thread's first key
+    unsigned int cnt;             // keys in the chunk
+    unsigned int first;           // index inside the list of the chunk's first key
+    unsigned int keys[DEC_KPT];
+    unsigned int d0;              // delta of keys[0]: keys[0] - d0 is the key before it in the list
+    float bv[DEC_KPT];            // dequantized values (not yet divided by the world size)
+    bool live[DEC_KPT];           // key exists and is inside [0, dim)
+};
+
+__device__ __forceinline__ void decode_chunk(const DP& p, const DecItem& it, unsigned int j, const unsigned char* stab,
+                                             unsigned int* part_a, unsigned int* part_b, ChunkKeys& o) {
+    const unsigned int first = j * SKML_RESTART_INTERVAL;
+    const unsigned int cnt = min((unsigned int)SKML_RESTART_INTERVAL, it.e.n - first);
+    const SkmlRestart rs = *reinterpret_cast<const SkmlRestart*>(it.base + it.e.restart_off + 16ull * j);
+    const unsigned int i0 = DEC_KPT * threadIdx.x;
+    o.i0 = i0;
+    o.cnt = cnt;
+    o.first = first;
+    unsigned int w[DEC_KPT];
+    unsigned int wsum = 0;
+#pragma unroll
+    for (int u = 0; u < DEC_KPT; ++u) w[u] = 0;
+    if (i0 < cnt) {
+        // the flags of DEC_KPT adjacent keys are 2 * DEC_KPT adjacent bits of one 32-bit word
+        const unsigned long long fb = (unsigned long long)rs.flag_bit_off + 2ull * i0;
+        const unsigned int word = __ldcg(reinterpret_cast<const unsigned int*>(it.base + it.e.flag_off) + (fb >> 5));
+        const unsigned int b = word >> (fb & 31);
+#pragma unroll
+        for (int u = 0; u < DEC_KPT; ++u) {
+            if (i0 + u < cnt) {
+                const unsigned int bb = (b >> (2 * u)) & 3u;
+                unsigned int wu = (((bb & 1u) << 1) | (bb >> 1)) + 1u;  // stream order is most significant bit first
+                if (wu == 3) wu = 4;                                     // flag value 2 is never written
+                w[u] = wu;
+                wsum += wu;
+            }
+        }
+    }
+    const unsigned int boff = dec_scan(wsum, part_a);
+    unsigned int d[DEC_KPT];
+#pragma unroll
+    for (int u = 0; u < DEC_KPT; ++u) d[u] = 0;
+    if (i0 < cnt) {
+        const unsigned long long byte0 = (rs.delta_bit_off >> 3) + boff;
+        if (byte0 + wsum <= 8ull * it.e.n_delta_words) {
+            // The thread's <= 4 * DEC_KPT delta bytes sit in at most DEC_KPT + 1 aligned words.
+            // Bit-reversing a little-endian word yields its four stream bytes in most-significant-
+            // first order (java.util.BitSet order), so a delta is a funnel shift away.
+            const unsigned int* src = reinterpret_cast<const unsigned int*>(it.base + it.e.delta_off);
+            const unsigned long long w0 = byte0 >> 2, wlim = 2ull * it.e.n_delta_words;
+            unsigned int W[DEC_KPT + 1];
+#pragma unroll
+            for (int t = 0; t <= DEC_KPT; ++t) W[t] = (w0 + t < wlim) ? __brev(__ldcg(src + w0 + t)) : 0u;
+            unsigned int start = (unsigned int)(byte0 & 3);
+#pragma unroll
+            for (int u = 0; u < DEC_KPT; ++u) {
+                const unsigned int wi = start >> 2, sh = 8u * (start & 3u);
+                unsigned int hi = W[0], lo = W[1];
+#pragma unroll
+                for (int t = 1; t < DEC_KPT; ++t)
+                    if (wi == (unsigned int)t) { hi = W[t]; lo = W[t + 1]; }
+                const unsigned int v = __funnelshift_l(lo, hi, sh);
+                d[u] = w[u] ? v >> (32u - 8u * w[u]) : 0u;
+                start += w[u];
+            }
+        }
+    }
+    unsigned int dsum = 0;
+#pragma unroll
+    for (int u = 0; u < DEC_KPT; ++u) dsum += d[u];
+    const unsigned int dex = dec_scan(dsum, part_b);
+    o.d0 = d[0];
+#pragma unroll
+    for (int u = 0; u < DEC_KPT; ++u) {
+        o.keys[u] = 0xFFFFFFFFu;
+        o.live[u] = false;
+        o.bv[u] = 0.f;
+    }
+    if (i0 < cnt) {
+        unsigned int key = rs.prev_key + dex;
+#pragma unroll
+        for (int u = 0; u < DEC_KPT; ++u) {
+            key += d[u];
+            o.keys[u] = key;
+            o.live[u] = i0 + u < cnt;
+            if (o.live[u] && key >= (unsigned long long)p.dim) {
+                skml_set_status(p.status, SKML_BAD_HEADER, 0x200u);
+                o.live[u] = false;
+                o.keys[u] = 0xFFFFFFFFu;
+            }
+        }
+        if (it.rows <= 4) {
+#pragma unroll
+            for (int u = 0; u < DEC_KPT; ++u) o.bv[u] = o.live[u] ? query_one<4>(p, it, o.keys[u], stab) : 0.f;
+        } else {
+#pragma unroll
+            for (int u = 0; u < DEC_KPT; ++u) o.bv[u] = o.live[u] ? query_one<SKML_MAX_ROWS>(p, it, o.keys[u], stab) : 0.f;
+        }
+    }
+}
+
+// Stages the item's sketch table in shared memory when it fits (one coalesced read instead of `rows`
+// random L2 sectors per key); returns the staged copy or null. Block-wide call.
+__device__ __forceinline__ const unsigned char* stage_table(const DecItem& it, unsigned char* tab_area) {
+    const unsigned long long tbytes = (unsigned long long)it.rows * it.e.col_num * (it.cell_bits / 8);
+    if (!tab_area || tbytes > DEC_TAB_SMEM) return nullptr;
+    __syncthreads();  // the previous table's readers are done
+    const uint4* src = reinterpret_cast<const uint4*>(it.base + it.e.table_off);
+    uint4* dst = reinterpret_cast<uint4*>(tab_area);
+    const int nv = (int)((tbytes + 15) / 16);  // table sections are padded to 16 bytes
+    for (int t = threadIdx.x; t < nv; t += blockDim.x) dst[t] = ld_cg_v4(src + t);
+    __syncthreads();
+    return tab_area;
+}

@@ -1,18 +1,22 @@
 // Fused decode + aggregate + update for sm_100a: the receiving side of the gradient
 // exchange in one persistent cooperative kernel.
 //   D0  bounded wait for the arrival flags of all ranks' payloads (written by the peers'
-//       compress kernels straight into this GPU's memory), header validation
+//       compress kernels straight into this GPU's memory), header validation, work table
 //   D1  per 1024-key chunk (restart points make chunks independent): flag bits -> delta
 //       widths -> scan -> gather -> prefix sum = keys; grouped MinMaxSketch query
 //       (furthest-from-zero over the rows); dequantize
-//   SGD (linear update): the payloads are applied one rank after the other with a grid
-//       barrier in between. Keys are unique inside a payload, so each pass is a plain
-//       read-modify-write of w without atomics, and the fixed rank order makes every
-//       replica bit-identical. One random access per key, no scratch.
-//   Adam (needs the cross-rank sum first): value / world is added into 64-bit fixed-point
-//       accumulators (integer adds commute, so every replica gets the same sums whatever
-//       the arrival order); D2 claims each touched coordinate once (atomic exchange with
-//       zero) and applies the reference's lazy Adam with per-epoch beta powers
+//   Replicas must end bit-identical, so the order of the float adds per coordinate is fixed:
+//   * one payload: keys are unique inside it, every value is applied by the thread that
+//     decoded it (SGD step, lazy Adam step, or plain sum);
+//   * several short payloads: D1 stashes (key, value) pairs; after one grid barrier every
+//     block owns a key range (quantiles of the longest key list), finds its slice of every
+//     (rank, group) list by binary search and applies the slices rank by rank with block
+//     barriers only. Lazy Adam first sums the ranks' values per coordinate (plain floats in
+//     the zeroed accumulator array), then the first rank holding the coordinate applies the
+//     moment update and clears the sum;
+//   * several long payloads (SGD): one decode-and-apply pass per rank, grid barrier in between;
+//   * a dense-kind payload among them: per-rank passes for SGD; for Adam 64-bit fixed-point
+//     accumulators (integer adds commute) and a claim pass (atomic exchange with zero).
 //
 // Reference behaviour restated (paths inside the reference project):
 //   sketch/.../binary/DeltaBinaryEncoder.java:42-53 (key decode),
@@ -20,49 +24,7 @@
 //   ml/.../gradient/SketchGradient.scala:57-68, Gradient.scala:44-49 (sum over workers),
 //   ml/.../algorithm/GeneralizedLinearModel.scala:150 (1/workerNum),
 //   ml/.../objective/GradientDescent.scala:89-117, Adam.scala:27-77 (updates).
-#include <math.h>
-
-#include "skml_api.h"
-#include "skml_device.cuh"
-
-#define DEC_MAX_ITEMS (SKML_MAX_PEERS * SKML_MAX_GROUPS)
-#define DEC_KPT 4        // keys of a 1024-key chunk per thread
-#define DEC_THREADS (SKML_RESTART_INTERVAL / DEC_KPT)
-#define DEC_BLOCKS_PER_SM 4
-#define DEC_TAB_SMEM 36864   // bytes of shared memory per block for a staged sketch table
-
-struct DP {
-    const unsigned char* payload[SKML_MAX_PEERS];
-    const unsigned long long* flag[SKML_MAX_PEERS];
-    int world;
-    long long slot_capacity;
-    unsigned long long step;
-    long long dim;
-    float* w;
-    float* adam_m;
-    float* adam_v;
-    float lr, adam_scale;
-    long long* acc;
-    int* key_scratch;
-    float* val_scratch;
-    long long key_capacity;
-    double* loss_out;
-    float* out_sum;
-    unsigned int* ctrl;
-    unsigned int* status;
-    long long budget;
-    int max_items;
-    int tab_off;     // byte offset of the staged-table area inside the dynamic shared memory (0 = none)
-};
-
-struct DecItem {  // one (rank, group) key stream
-    const unsigned char* base;
-    SkmlGroupEntry e;
-    unsigned long long chunk_prefix, key_prefix;
-    unsigned int zero, cell_bits, rows;
-    unsigned long long off_bv;
-    unsigned long long col_magic;
-};
+#include "decode_common.cuh"
 
 struct DecSmem {
     SkmlHeader hdr[SKML_MAX_PEERS];
@@ -82,29 +44,6 @@ struct DecSmem {
     int max_items;
     DecItem items[1];  // max_items entries (dynamic shared memory)
 };
-
-__device__ __forceinline__ long long to_fixed(double v, int shift) { return __double2ll_rn(ldexp(v, shift)); }
-__device__ __forceinline__ double from_fixed(long long a, int shift) { return ldexp((double)a, -shift); }
-
-__device__ __forceinline__ void apply_one(const DP& p, long long k, float g) {
-    if (p.out_sum) {
-        p.out_sum[k] = g;
-    } else if (!p.adam_v) {
-        p.w[k] -= p.lr * g;
-    } else {
-        float mt = 0.9f * p.adam_m[k] + 0.1f * g;
-        float vt = 0.999f * p.adam_v[k] + 0.001f * g * g;
-        p.w[k] -= p.lr * p.adam_scale * mt / (sqrtf(vt) + 1e-8f);
-        p.adam_m[k] = mt;
-        p.adam_v[k] = vt;
-    }
-}
-
-// Linear modes: SGD step on w, or accumulation of the plain mean into out_sum.
-__device__ __forceinline__ void apply_direct(const DP& p, long long k, float g) {
-    if (p.out_sum) p.out_sum[k] += g;
-    else p.w[k] -= p.lr * g;
-}
 
 // D0: wait, validate, build the work table (identically in every block).
 __device__ bool decode_prepare(const DP& p, DecSmem& s) {
@@ -172,6 +111,8 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
                 it.rows = h.row_num;
                 it.off_bv = h.off_bucket_values;
                 it.col_magic = good ? skml_fastmod_magic(it.e.col_num) : 0ull;
+                it.recip = skml_recip32(it.e.col_num);
+                it.mixers = (h.row_num <= 3 && skml_rows_are_mixers(it.e.hash_ids, (int)h.row_num)) ? 1 : 0;
                 it.chunk_prefix = good ? 0ull : 1ull;  // scratch use until the compaction below: 1 = failed validation
             }
         }
@@ -251,66 +192,6 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
     return s.ok != 0;
 }
 
-// Query of one key in its group's sketch: the bucket value of the cell farthest from the zero bucket.
-template <int MAXR>
-__device__ __forceinline__ float query_one(const DP& p, const DecItem& it, unsigned int key, const unsigned char* stab) {
-    const int col = (int)it.e.col_num;
-    const int zero = (int)it.zero;
-    int cells[MAXR];
-    int pos[MAXR];
-    const int rows = (int)it.rows;
-    skml_hash_rows<MAXR>(it.e.hash_ids, rows, (int)key, col, it.col_magic, pos);
-#pragma unroll
-    for (int r = 0; r < MAXR; ++r) {  // independent loads first
-        cells[r] = zero;
-        if (r < rows) {
-            const unsigned int c = (unsigned int)r * (unsigned int)col + (unsigned int)pos[r];  // rows * col < 2^31 (checked in prepare)
-            if (stab) {  // the group's whole table sits in shared memory
-                if (it.cell_bits == 8) cells[r] = stab[c];
-                else cells[r] = reinterpret_cast<const unsigned short*>(stab)[c];
-            } else if (it.cell_bits == 8) {
-                cells[r] = __ldcg(it.base + it.e.table_off + c);
-            } else {
-                cells[r] = __ldcg(reinterpret_cast<const unsigned short*>(it.base + it.e.table_off) + c);
-            }
-        }
-    }
-    int res = zero, best = 0;
-#pragma unroll
-    for (int r = 0; r < MAXR; ++r) {
-        int d = cells[r] - zero;
-        if (d < 0) d = -d;
-        if (d > best) {
-            best = d;
-            res = cells[r];
-        }
-    }
-    // Bucket values (<= 16 KB per payload, read by every key) go through L1: the SM cannot hold a stale
-    // line of them, because it first touches a payload after the arrival flag was acquired and L1 is
-    // invalidated between dependent grids. Everything else of the payload is read once: L2 only.
-    return reinterpret_cast<const float*>(it.base + it.off_bv)[res];
-}
-
-// Exclusive prefix sum over the block with ONE barrier: every warp publishes its total, every
-// thread adds up the totals of the warps before it. The caller alternates `part` between calls
-// so that no second barrier is needed to protect it.
-__device__ __forceinline__ unsigned int dec_scan(unsigned int v, unsigned int* part) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    unsigned int inc = v;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const unsigned int t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
-        if (lane >= o) inc += t;
-    }
-    if (lane == 31) part[warp] = inc;
-    __syncthreads();
-    unsigned int base = 0;
-#pragma unroll
-    for (int w = 0; w < DEC_THREADS / 32; ++w)
-        if (w < warp) base += part[w];
-    return base + inc - v;
-}
-
 // D1 for sparse payloads: one 1024-key chunk per block iteration, DEC_KPT adjacent keys per
 // thread (256 threads), so that every thread has several independent load chains in flight and
 // several blocks share an SM.
@@ -331,123 +212,35 @@ __device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch
         const DecItem& it = s.items[it_i];
         if (it_i != staged) {
             staged = it_i;
-            const unsigned long long tbytes = (unsigned long long)it.rows * it.e.col_num * (it.cell_bits / 8);
-            stab = nullptr;
-            if (tab_area && tbytes <= DEC_TAB_SMEM) {
-                __syncthreads();  // the previous table's readers are done
-                const uint4* src = reinterpret_cast<const uint4*>(it.base + it.e.table_off);
-                uint4* dst = reinterpret_cast<uint4*>(tab_area);
-                const int nv = (int)((tbytes + 15) / 16);  // table sections are padded to 16 bytes
-                for (int t = threadIdx.x; t < nv; t += blockDim.x) dst[t] = ld_cg_v4(src + t);
-                __syncthreads();
-                stab = tab_area;
-            }
+            stab = stage_table(it, tab_area);
         }
-        const unsigned int j = (unsigned int)(ch - it.chunk_prefix);
-        const unsigned int first = j * SKML_RESTART_INTERVAL;
-        const unsigned int cnt = min((unsigned int)SKML_RESTART_INTERVAL, it.e.n - first);
-        const SkmlRestart rs = *reinterpret_cast<const SkmlRestart*>(it.base + it.e.restart_off + 16ull * j);
-        const unsigned int i0 = DEC_KPT * threadIdx.x;
-        unsigned int w[DEC_KPT];
-        unsigned int wsum = 0;
-#pragma unroll
-        for (int u = 0; u < DEC_KPT; ++u) w[u] = 0;
-        if (i0 < cnt) {
-            // the flags of DEC_KPT adjacent keys are 2 * DEC_KPT adjacent bits of one 32-bit word
-            const unsigned long long fb = (unsigned long long)rs.flag_bit_off + 2ull * i0;
-            const unsigned int word = __ldcg(reinterpret_cast<const unsigned int*>(it.base + it.e.flag_off) + (fb >> 5));
-            const unsigned int b = word >> (fb & 31);
-#pragma unroll
-            for (int u = 0; u < DEC_KPT; ++u) {
-                if (i0 + u < cnt) {
-                    const unsigned int bb = (b >> (2 * u)) & 3u;
-                    unsigned int wu = (((bb & 1u) << 1) | (bb >> 1)) + 1u;  // stream order is most significant bit first
-                    if (wu == 3) wu = 4;                                     // flag value 2 is never written
-                    w[u] = wu;
-                    wsum += wu;
-                }
-            }
-        }
-        const unsigned int boff = dec_scan(wsum, s_part[par]);
-        unsigned int d[DEC_KPT];
-#pragma unroll
-        for (int u = 0; u < DEC_KPT; ++u) d[u] = 0;
-        if (i0 < cnt) {
-            const unsigned long long byte0 = (rs.delta_bit_off >> 3) + boff;
-            if (byte0 + wsum <= 8ull * it.e.n_delta_words) {
-                // The thread's <= 4 * DEC_KPT delta bytes sit in at most DEC_KPT + 1 aligned words.
-                // Bit-reversing a little-endian word yields its four stream bytes in most-significant-
-                // first order (java.util.BitSet order), so a delta is a funnel shift away.
-                const unsigned int* src = reinterpret_cast<const unsigned int*>(it.base + it.e.delta_off);
-                const unsigned long long w0 = byte0 >> 2, wlim = 2ull * it.e.n_delta_words;
-                unsigned int W[DEC_KPT + 1];
-#pragma unroll
-                for (int t = 0; t <= DEC_KPT; ++t) W[t] = (w0 + t < wlim) ? __brev(__ldcg(src + w0 + t)) : 0u;
-                unsigned int start = (unsigned int)(byte0 & 3);
-#pragma unroll
-                for (int u = 0; u < DEC_KPT; ++u) {
-                    const unsigned int wi = start >> 2, sh = 8u * (start & 3u);
-                    unsigned int hi = W[0], lo = W[1];
-#pragma unroll
-                    for (int t = 1; t < DEC_KPT; ++t)
-                        if (wi == (unsigned int)t) { hi = W[t]; lo = W[t + 1]; }
-                    const unsigned int v = __funnelshift_l(lo, hi, sh);
-                    d[u] = w[u] ? v >> (32u - 8u * w[u]) : 0u;
-                    start += w[u];
-                }
-            }
-        }
-        unsigned int dsum = 0;
-#pragma unroll
-        for (int u = 0; u < DEC_KPT; ++u) dsum += d[u];
-        const unsigned int dex = dec_scan(dsum, s_part[2 + par]);
-        if (i0 < cnt) {
-            unsigned int key = rs.prev_key + dex;
-            int* ks = p.key_scratch + it.key_prefix + first;
-            unsigned int keys[DEC_KPT];
-            bool live[DEC_KPT];
-#pragma unroll
-            for (int u = 0; u < DEC_KPT; ++u) {
-                key += d[u];
-                keys[u] = key;
-                live[u] = i0 + u < cnt;
-                if (live[u] && key >= (unsigned long long)p.dim) {
-                    skml_set_status(p.status, SKML_BAD_HEADER, 0x200u);
-                    live[u] = false;
-                    keys[u] = 0xFFFFFFFFu;
-                }
-                if (!s.direct && !s.adam_plain && i0 + u < cnt) ks[i0 + u] = (int)keys[u];
-            }
-            float bv[DEC_KPT];
-            if (it.rows <= 4) {
-#pragma unroll
-                for (int u = 0; u < DEC_KPT; ++u) bv[u] = live[u] ? query_one<4>(p, it, keys[u], stab) : 0.f;
-            } else {
-#pragma unroll
-                for (int u = 0; u < DEC_KPT; ++u) bv[u] = live[u] ? query_one<SKML_MAX_ROWS>(p, it, keys[u], stab) : 0.f;
-            }
+        ChunkKeys c;
+        decode_chunk(p, it, (unsigned int)(ch - it.chunk_prefix), stab, s_part[par], s_part[2 + par], c);
+        if (c.i0 < c.cnt) {
+            int* ks = p.key_scratch + it.key_prefix + c.first;
             if (s.two_phase) {
                 // stash (key, value): the ordered apply passes read them back coalesced
-                float* vs = p.val_scratch + it.key_prefix + first;
+                float* vs = p.val_scratch + it.key_prefix + c.first;
 #pragma unroll
                 for (int u = 0; u < DEC_KPT; ++u)
-                    if (i0 + u < cnt) {
-                        ks[i0 + u] = (int)keys[u];
-                        vs[i0 + u] = bv[u] * (float)s.inv_world;
+                    if (c.i0 + u < c.cnt) {
+                        ks[c.i0 + u] = (int)c.keys[u];
+                        vs[c.i0 + u] = c.bv[u] * (float)s.inv_world;
                     }
             } else if (s.direct) {  // single payload: keys are unique inside it, plain read-modify-write
 #pragma unroll
                 for (int u = 0; u < DEC_KPT; ++u)
-                    if (live[u]) apply_direct(p, keys[u], bv[u] * (float)s.inv_world);
+                    if (c.live[u]) apply_direct(p, c.keys[u], c.bv[u] * (float)s.inv_world);
             } else if (s.adam_plain) {  // single payload: the decoded value is the whole gradient of its key
 #pragma unroll
                 for (int u = 0; u < DEC_KPT; ++u)
-                    if (live[u] && bv[u] != 0.f) apply_one(p, keys[u], bv[u] * (float)s.inv_world);
+                    if (c.live[u] && c.bv[u] != 0.f) apply_one(p, c.keys[u], c.bv[u] * (float)s.inv_world);
             } else {
 #pragma unroll
                 for (int u = 0; u < DEC_KPT; ++u) {
-                    const long long fx = live[u] ? to_fixed((double)bv[u] * s.inv_world, s.shift) : 0ll;
-                    if (fx) atomicAdd(reinterpret_cast<unsigned long long*>(p.acc + keys[u]), (unsigned long long)fx);
+                    if (c.i0 + u < c.cnt) ks[c.i0 + u] = (int)c.keys[u];
+                    const long long fx = c.live[u] ? to_fixed((double)c.bv[u] * s.inv_world, s.shift) : 0ll;
+                    if (fx) atomicAdd(reinterpret_cast<unsigned long long*>(p.acc + c.keys[u]), (unsigned long long)fx);
                 }
             }
         }

@@ -54,6 +54,41 @@ __device__ __forceinline__ void st_v4(uint4* p, uint4 v) {
 }
 
 // ---------------------------------------------------------------------------
+// Table positions of one key for sketches whose rows all use the three integer mixers (BJ, Mix64,
+// TW: what skml_pick_hashes draws for up to three rows). Equal to skml_hash(ids[r], key, size) for
+// every row and every key, with about a third of the instructions of the general routine: the three
+// mixers are computed once and handed to the rows, and `x % size` is a 32-bit reciprocal
+// multiplication with one correction step (q = mulhi(x, floor(2^32 / size)) is the quotient or one
+// less). Java semantics: the remainder keeps the sign of the dividend and is then moved up by size.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ unsigned int skml_recip32(unsigned int size) {
+    return size <= 1u ? 0xFFFFFFFFu : (unsigned int)((1ull << 32) / size);
+}
+__device__ __forceinline__ bool skml_rows_are_mixers(const unsigned char* ids, int rows) {
+    bool ok = true;
+    for (int r = 0; r < rows; ++r) ok = ok && ids[r] < 3;
+    return ok;
+}
+__device__ __forceinline__ int skml_java_mod(unsigned int code, unsigned int size, unsigned int recip) {
+    const bool neg = (int)code < 0;
+    const unsigned int a = neg ? 0u - code : code;
+    unsigned int r = a - __umulhi(a, recip) * size;
+    if (r >= size) r -= size;
+    return (int)(neg ? (r ? size - r : 0u) : r);
+}
+template <int MAXR>
+__device__ __forceinline__ void skml_hash_rows_mixers(const unsigned char* ids, int rows, int key, unsigned int size,
+                                                      unsigned int recip, int* out) {
+    const unsigned int h0 = skml_mix_bj((unsigned int)key), h1 = skml_mix_64((unsigned int)key), h2 = skml_mix_tw((unsigned int)key);
+#pragma unroll
+    for (int r = 0; r < MAXR; ++r) {
+        if (r >= rows) continue;
+        const int id = ids[r];
+        out[r] = skml_java_mod(id == 0 ? h0 : (id == 1 ? h1 : h2), size, recip);
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Grid barrier for cooperative launches. bar[0] = arrival count, bar[1] = generation.
 // Returns false (on every thread of the block) when the wait budget ran out.
 // ---------------------------------------------------------------------------
@@ -73,11 +108,16 @@ __device__ __forceinline__ bool skml_grid_barrier(unsigned int* bar, unsigned in
                 st_release_gpu(&bar[1], gen + 1);
             } else {
                 long long t0 = clock64();
-                unsigned int ns = 20;
+                unsigned int ns = 20, polls = 0;
                 while (ld_acquire_gpu(&bar[1]) == gen) {
                     if (clock64() - t0 > budget) {
                         ok = 0;
                         skml_set_status(status, SKML_TIMEOUT_BARRIER, stage);
+                        break;
+                    }
+                    // a block that reported an error has left the kernel and will never arrive
+                    if ((++polls & 63u) == 0 && (ld_acquire_gpu(status) & 0xFFu) != SKML_OK) {
+                        ok = 0;
                         break;
                     }
                     __nanosleep(ns);

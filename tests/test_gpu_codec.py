@@ -94,11 +94,15 @@ def test_quantile_splits_rank_error(fused, n):
     assert np.all(np.sign(v2) == np.sign(vals)) or (np.sign(v2) != np.sign(vals)).mean() < 0.06
 
 
-@pytest.mark.parametrize("fused", [False, True])
-def test_decode_sum_matches_oracle(fused):
+DECODE_MODES = {"staged": dict(fused=False), "fused": dict(fused=True)}
+
+
+@pytest.mark.parametrize("mode", list(DECODE_MODES))
+def test_decode_sum_matches_oracle(mode):
     from sketchml_b200.compress import oracle
     from sketchml_b200.ops import GpuCompressor, GpuDecoder
     dim, world = 300000, 3
+    fused = mode != "staged"
     comp = GpuCompressor(dim, 20000, 128, 8, 3, 0.2, seed=5, fused=fused)
     bufs, ref = [], np.zeros(dim)
     for r in range(world):
@@ -107,7 +111,7 @@ def test_decode_sum_matches_oracle(fused):
         bufs.append(b.clone())
         _, k, v = oracle.decompress(comp.payload_bytes(b))
         ref[k] += v.astype(np.float64) / world
-    dec = GpuDecoder(dim, 20000 * world, fused=fused)
+    dec = GpuDecoder(dim, 20000 * world, **DECODE_MODES[mode])
     out = dec.decode_sum(bufs, step=4).cpu().numpy().astype(np.float64)
     assert np.abs(out - ref).max() <= 1e-6 * np.abs(ref).max()
     assert int(dec.acc.abs().max()) == 0
@@ -264,8 +268,8 @@ def test_fixed_point_pack_matches_oracle(bits):
     assert float(out[n:].abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("fused", [False, True])
-def test_several_overlapping_payloads_sgd_and_adam(fused):
+@pytest.mark.parametrize("mode", list(DECODE_MODES))
+def test_several_overlapping_payloads_sgd_and_adam(mode):
     """Four payloads with many shared keys: the key-range-owned apply must equal the oracle's
     decoded mean for SGD and one lazy-Adam step on exactly the touched coordinates."""
     from sketchml_b200.compress import oracle
@@ -282,7 +286,7 @@ def test_several_overlapping_payloads_sgd_and_adam(fused):
     cap = min(b.numel() for b in bufs)
     ptrs = [b.data_ptr() for b in bufs]
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    dec = GpuDecoder(dim, P * n, fused=fused)
+    dec = GpuDecoder(dim, P * n, **DECODE_MODES[mode])
     w = torch.ones(dim, device="cuda")
     dec.decode_update(ptrs, [None] * P, cap, 7, status, w=w, lr=0.5)
     assert int(status.item()) == 0
@@ -306,6 +310,45 @@ def test_several_overlapping_payloads_sgd_and_adam(fused):
     v2 = torch.zeros(dim, device="cuda")
     dec.decode_update(ptrs, [None] * P, cap, 7, status, w=w2, lr=0.1, adam_m=m2, adam_v=v2, adam_scale=scale)
     assert torch.equal(w, w2) and torch.equal(m, m2) and torch.equal(vv, v2)
+
+
+def test_decode_skewed_keys_many_ranks():
+    """Eight payloads with Zipf-like keys (many shared coordinates, one nearly empty payload): the fused
+    launch must give the bits of the staged launches, which apply the ranks in the same order per
+    coordinate, for SGD and for lazy Adam, and the same bits on every repetition."""
+    from sketchml_b200.ops import GpuCompressor, GpuDecoder
+    dim, P, n = 3_000_000, 8, 40000
+    comp = GpuCompressor(dim, n, 256, 8, 3, 0.2, seed=9)
+    rng = np.random.default_rng(5)
+    bufs = []
+    for r in range(P):
+        keys = np.unique(np.minimum(rng.zipf(1.2, 3 * n), dim - 1))[: n - 1000 * r].astype(np.int32)
+        if r == 5:
+            keys = keys[:3]   # a payload whose groups are nearly all empty
+        vals = rng.laplace(0, 1e-2, len(keys)).astype(np.float32)
+        bufs.append(comp.compress_local(torch.from_numpy(keys).cuda(), torch.from_numpy(vals).cuda(), step=3, rank=r, world=P).clone())
+    cap = min(b.numel() for b in bufs)
+    ptrs = [b.data_ptr() for b in bufs]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ref_dec = GpuDecoder(dim, P * n, fused=False)
+    w_ref = torch.ones(dim, device="cuda")
+    ref_dec.decode_update(ptrs, [None] * P, cap, 3, status, w=w_ref, lr=0.5)
+    assert int(status.item()) == 0
+    dec = GpuDecoder(dim, P * n, max_groups=8)
+    for _ in range(3):
+        w = torch.ones(dim, device="cuda")
+        dec.decode_update(ptrs, [None] * P, cap, 3, status, w=w, lr=0.5)
+        assert int(status.item()) == 0
+        assert torch.equal(w, w_ref)
+
+    def adam(d):
+        w, m, v = torch.ones(dim, device="cuda"), torch.zeros(dim, device="cuda"), torch.zeros(dim, device="cuda")
+        d.decode_update(ptrs, [None] * P, cap, 3, status, w=w, lr=0.1, adam_m=m, adam_v=v, adam_scale=0.3)
+        assert int(status.item()) == 0
+        return w, m, v
+    for a, b in zip(adam(dec), adam(ref_dec)):
+        assert torch.equal(a, b)
+    assert float(dec.acc.abs().max()) == 0
 
 
 def _key_sets():
