@@ -46,6 +46,9 @@ def run_arm(args, compressor, algo):
     wall = time.perf_counter() - t0
     out = {"compressor": compressor, "algo": algo, "world": t.comm.world, "train_loss": h["train_loss"],
            "valid_loss": h["valid_loss"], "time_ms": h["time_ms"], "wall_s": wall, "accuracy": h["accuracy"]}
+    if hasattr(t.engine, "payload_stats"):
+        nnz, nbytes = t.engine.payload_stats(t.step - 1)
+        out["payload_bytes_per_nnz"] = nbytes / max(nnz, 1)
     rank = t.comm.rank
     t.close()
     return out, rank

@@ -10,7 +10,7 @@ reproduces that load without P GPUs (the payloads are P local buffers, nothing w
 
 Prints one JSON line: median CUDA-event times of the two launches (they include the launch latency of
 an idle GPU), the stage times from the kernels' `globaltimer` stamps (compress: summary, split query,
-bucketize, pack + sketch insert, narrow + publish; decode: prepare, decode, apply as seen by block 0)
+bucketize + count, scatter + sketch insert, key code, narrow + publish; decode: prepare, decode, apply as seen by block 0)
 and how long after block 0 the last decode block finished.
 """
 from __future__ import annotations
@@ -77,13 +77,13 @@ def main():
     if int(status.item()):
         raise SystemExit(f"kernel status {int(status.item()):#x}")
     last = (args.iters - 1) & 1
-    cs = comp.workspace[:256].cpu().numpy().view(np.int64)[8:14]
+    cs = comp.workspace[:256].cpu().numpy().view(np.int64)[8:15]
     dall = dec.workspace[:256].cpu().numpy().view(np.int64)
     ds = dall[8 + 4 * last:12 + 4 * last]
     print(json.dumps({
         "ranks": P, "optimizer": "adam" if args.adam else "sgd", "nnz_per_rank": int(keys[0].numel()),
         "compress_launch_ms": float(np.median(tc)), "decode_launch_ms": float(np.median(td)),
-        "compress_stages_us": [float(cs[i + 1] - cs[i]) / 1e3 for i in range(5)],
+        "compress_stages_us": [float(cs[i + 1] - cs[i]) / 1e3 for i in range(6)],
         "decode_stages_us": [float(ds[i + 1] - ds[i]) / 1e3 for i in range(3)],
         "decode_last_block_after_block0_us": float(dall[16 + last] - ds[3]) / 1e3 if dall[16 + last] else None}))
 

@@ -5,13 +5,17 @@
 //   S1  mergeable quantile summary of the values (sorted shared-memory tiles, k = 128
 //       samples per run, pairwise merge + keep-every-second carry chain), min / max
 //   S2  weighted-rank query of the merged summaries -> q-1 raw split points
-//   S3  dedupe splits, zero bucket, bucket midpoints, group edges; bucketize every
-//       value; per-block per-group counts / key-delta byte sums
-//   S4  payload layout; grouped MinMaxSketch insert (atomicMin on packed cells);
-//       delta-binary key code (2 flag bits + 1/2/4 bytes), restart points; header
-//   S5  narrow the sketch tables to 8/16-bit bucket codes and store the finished payload
-//       into every peer's receive slot with 16-byte peer stores, then release the
-//       arrival flags (system scope). There is no separate all-gather.
+//   S3  dedupe splits, zero bucket, bucket midpoints, group edges; bucketize every value and
+//       count the keys of every bucket group per warp slice
+//   S4  group sizes -> payload layout; every key goes to its group's contiguous (still key-sorted)
+//       staging list; grouped MinMaxSketch insert (atomicMin on packed cells)
+//   S5  the groups' key lists are coded in 1024-key chunks like a plain array: delta widths, byte
+//       offsets by a block scan, flag bytes, delta bytes, one restart point per chunk. A block owns a
+//       contiguous run of chunks and learns its byte offset from the blocks before it (their
+//       published byte counts), so no grid barrier sits inside this stage
+//   S6  header and group table; sketch tables narrowed to 8/16-bit bucket codes; the finished
+//       payload is stored into every peer's receive slot with 16-byte peer stores, then the
+//       arrival flags are released (system scope). There is no separate all-gather.
 // Grid-wide dependencies are bounded software barriers (cooperative launch guarantees
 // co-residency). With `fused = 0` the same stage functions run as separate launches.
 //
@@ -35,15 +39,6 @@
 #define FP_SHIFT 20         // fixed-point fraction bits of sample weights
 #define MAX_SAMPLE 16        // largest sampling factor of the bottom-level sampler
 
-struct CtaStat {
-    unsigned int count;
-    int first_key;
-    int last_key;
-    unsigned int pad;
-    unsigned long long bytes;  // delta bytes of this block's keys except the first of the group
-    unsigned long long pad2;
-};
-
 struct CP {
     const int* keys;
     const float* vals;
@@ -63,8 +58,13 @@ struct CP {
     unsigned int* run_cnt;
     unsigned long long* run_w;
     unsigned int* splits_raw;
-    CtaStat* stats;
+    unsigned int* warp_cnt;          // [grid * 32 warps][SKML_MAX_GROUPS]: keys of every group in every warp slice
+    unsigned int* blk_cnt;           // [grid][SKML_MAX_GROUPS]: the same per block
+    unsigned long long* blk_bytes;   // [grid][SKML_MAX_GROUPS]: delta bytes of the chunks every block owns, per group
+    unsigned int* blk_flag;          // [grid]: epoch in which blk_bytes was published
+    unsigned int* chunk_off;         // [chunks]: delta-byte offset of a chunk inside its owner's part of the group
     unsigned short* bins;
+    int* gkeys;                      // keys, grouped: group g's list starts at Layout::goff[g]
     unsigned int* tables;
     long long tables_cap;
     unsigned int* status;
@@ -83,16 +83,12 @@ struct QInfo {
 struct Layout {
     unsigned int n_g[SKML_MAX_GROUPS];
     unsigned int col[SKML_MAX_GROUPS];
-    unsigned long long bytes_g[SKML_MAX_GROUPS];
+    unsigned int goff[SKML_MAX_GROUPS];            // start of the group's staging list (a multiple of 4 entries)
+    unsigned int chunk_prefix[SKML_MAX_GROUPS + 1]; // chunks of the groups before, group-major chunk numbering
+    unsigned int base_rank[SKML_MAX_GROUPS];       // keys of the group in the blocks before this one
+    unsigned long long bytes_g[SKML_MAX_GROUPS];   // delta bytes of the group (known to every block from S6 on)
     unsigned long long table_off[SKML_MAX_GROUPS], flag_off[SKML_MAX_GROUPS], delta_off[SKML_MAX_GROUPS],
         restart_off[SKML_MAX_GROUPS], tab32_off[SKML_MAX_GROUPS];
-    unsigned int base_rank[SKML_MAX_GROUPS];       // the same three for the block as a whole
-    unsigned long long base_bytes[SKML_MAX_GROUPS];
-    int base_prev[SKML_MAX_GROUPS];                // -1 = no key of the group before this block
-    // starting rank / delta-byte offset / previous key of every group for each warp of this block
-    unsigned int vbase_rank[SKML_WARPS][SKML_MAX_GROUPS];
-    unsigned long long vbase_bytes[SKML_WARPS][SKML_MAX_GROUPS];
-    int vbase_prev[SKML_WARPS][SKML_MAX_GROUPS];
     unsigned char hash_ids[SKML_MAX_GROUPS][8];
     unsigned long long col_magic[SKML_MAX_GROUPS];  // ceil(2^64 / col) for the division-free modulo
     unsigned int recip[SKML_MAX_GROUPS];            // floor(2^32 / col) for the mixer-only hash path
@@ -102,7 +98,8 @@ struct Layout {
 };
 
 struct WsLayout {
-    long long ctrl, run_vals, run_cnt, run_w, splits_raw, stats, bins, tables, total;
+    long long ctrl, run_vals, run_cnt, run_w, splits_raw, warp_cnt, blk_cnt, blk_bytes, blk_flag, chunk_off, bins, gkeys, tables,
+        total;
     long long tables_cap;
 };
 
@@ -116,8 +113,13 @@ static WsLayout ws_layout(long long n_max, long long q, long long G, long long r
     L.run_cnt = o; o += al256(grid * 4);
     L.run_w = o; o += al256(grid * 8);
     L.splits_raw = o; o += al256(q * 4);
-    L.stats = o; o += al256(grid * (SKML_WARPS + 1) * SKML_MAX_GROUPS * (long long)sizeof(CtaStat));
+    L.warp_cnt = o; o += al256(grid * SKML_WARPS * SKML_MAX_GROUPS * 4);
+    L.blk_cnt = o; o += al256(grid * SKML_MAX_GROUPS * 4);
+    L.blk_bytes = o; o += al256(grid * SKML_MAX_GROUPS * 8);
+    L.blk_flag = o; o += al256(grid * 4);
+    L.chunk_off = o; o += al256((n_max / SKML_RESTART_INTERVAL + SKML_MAX_GROUPS + 8) * 4);
     L.bins = o; o += al256(n_max * 2);
+    L.gkeys = o; o += al256((n_max + 4 * SKML_MAX_GROUPS + 8) * 4);
     L.tables_cap = rows * ((long long)(col_ratio * (double)n_max) + 2 + G) + 64;
     L.tables = o; o += al256(L.tables_cap * 4);
     L.total = o;
@@ -160,17 +162,21 @@ struct Smem {
     unsigned int runs_all[MAX_GRID * SK_K];
     unsigned int runs_cnt[MAX_GRID];
     unsigned long long runs_w[MAX_GRID];
-    // stages S3..S5
+    // stages S3..S6
     float splits[SKML_GPU_MAX_BINS];
+    unsigned char grp_lut[SKML_GPU_MAX_BINS];      // bucket -> group
     QInfo qi;
     Layout lay;
-    int wlast[SKML_WARPS][SKML_MAX_GROUPS];
     unsigned int wcnt[SKML_WARPS][SKML_MAX_GROUPS];
-    unsigned int wbytes[SKML_WARPS][SKML_MAX_GROUPS];
-    int cin[SKML_WARPS][SKML_MAX_GROUPS];
+    unsigned int wbase[SKML_WARPS][SKML_MAX_GROUPS];
+    unsigned long long my_bytes[SKML_MAX_GROUPS];   // delta bytes of the chunks this block owns, per group
+    unsigned long long pre_bytes[SKML_MAX_GROUPS];  // the same, summed over the blocks before this one
+    unsigned int sub_part[4][8];                    // scan scratch of the four 256-thread sub-blocks
+    unsigned int sub_total[4];
     unsigned long long unit_prefix[SKML_MAX_GROUPS + 1];
     int flag;
 };
+
 
 __device__ __forceinline__ unsigned int lanemask_lt() {
     unsigned int m;
@@ -576,129 +582,180 @@ __device__ __forceinline__ float bucket_value(const Smem& s, int b) {
 }
 
 // ---------------------------------------------------------------------------
-// Element passes. PACK = false: bucketize + per-block statistics (S3).
-// PACK = true: ranks, byte offsets, flag / delta / restart writes, sketch insert (S4).
+// Element stages. The unit of work of S3 and S4 is a warp: warp w of block b owns one contiguous
+// slice of the (key-sorted) input. S5 works on the groups' contiguous lists in 1024-key chunks.
 // ---------------------------------------------------------------------------
-
-// The unit of work is a warp: warp w of block b is "virtual block" b * 32 + w and owns one
-// contiguous slice of the keys. Everything inside a slice is warp-synchronous (no block barrier):
-// lane g keeps the running state of group g (last key, count, delta bytes) in registers, and the
-// lanes that hold a group's first / last key of an iteration hand them to lane g through a few
-// words of shared memory.
 __device__ __forceinline__ long long vslice_size(long long n) {
     const long long nv = (long long)gridDim.x * SKML_WARPS;
     long long c = (n + nv - 1) / nv;
     return (c + 31) / 32 * 32;
 }
 
-template <bool PACK>
-__device__ void element_pass(const CP& p, Smem& s, long long n) {
-    const int G = p.G;
+__device__ __forceinline__ void build_group_lut(const CP& p, Smem& s) {
+    for (int b = threadIdx.x; b < s.qi.bin_num; b += blockDim.x) s.grp_lut[b] = (unsigned char)skml_group_of(b, s.qi.edges, p.G);
+    for (int t = threadIdx.x; t < SKML_WARPS * SKML_MAX_GROUPS; t += blockDim.x) (&s.wcnt[0][0])[t] = 0;
+    __syncthreads();
+}
+
+// S3: bucket of every value; keys of every group in every warp slice.
+__device__ void stage_count(const CP& p, Smem& s, long long n) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    build_group_lut(p, s);
     const long long sub = vslice_size(n);
     const long long vb = (long long)blockIdx.x * SKML_WARPS + warp;
     long long lo = vb * sub, hi = lo + sub;
     if (lo > n) lo = n;
     if (hi > n) hi = n;
-    const Layout& L = s.lay;
-    const int zero = s.qi.zero_idx;
-    const bool overflow = PACK && L.overflow;
-    // state of group `lane` (lanes >= G idle)
-    int carry = -1, first = -1;
-    unsigned int cnt_g = 0;
-    unsigned long long bytes_g = 0;
-    unsigned int rank_g = 0;            // PACK: rank of the group's next key inside the payload
-    unsigned long long boff_g = 0;      // PACK: byte offset of the group's next delta
-    int base_prev_g = 0;                // PACK: last key of the group before this slice
-    if (PACK && lane < G) {
-        rank_g = L.vbase_rank[warp][lane];
-        boff_g = L.vbase_bytes[warp][lane];
-        base_prev_g = L.vbase_prev[warp][lane];
-    }
-    // The next iteration's key and value (or bucket) are fetched one iteration ahead: a warp's
-    // iteration is a dependent chain, so the global load latency would otherwise sit on it every time.
-    int nkey = 0, nbin = 0;
     float nval = 0.f;
+    if (lo + lane < hi) nval = p.vals[lo + lane];  // one iteration ahead: the load latency stays off the chain
+    for (long long i0 = lo; i0 < hi; i0 += 32) {
+        const long long i = i0 + lane;
+        const bool valid = i < hi;
+        const float val = nval;
+        if (i + 32 < hi) nval = p.vals[i + 32];
+        int g = 63;
+        if (valid) {
+            const int bin = upper_bound_f(s.splits, s.qi.nsplits, val);
+            p.bins[i] = (unsigned short)bin;
+            g = s.grp_lut[bin];
+        }
+        const unsigned int peers = __match_any_sync(0xFFFFFFFFu, g);
+        if (valid && (peers & lanemask_lt()) == 0) s.wcnt[warp][g] += (unsigned int)__popc(peers);  // one leader per group
+        __syncwarp();
+    }
+    if (lane < p.G) p.warp_cnt[vb * SKML_MAX_GROUPS + lane] = s.wcnt[warp][lane];
+    __syncthreads();
+    if (warp < p.G) {  // the block's totals: warp g adds up group g over the 32 slices
+        const unsigned int tot = warp_sum(s.wcnt[lane][warp]);
+        if (lane == 0) p.blk_cnt[(long long)blockIdx.x * SKML_MAX_GROUPS + warp] = tot;
+    }
+}
+
+// S4 prelude: group sizes, table sizes, hash rows and every section offset that does not depend on
+// the key code (every block computes the same layout); this block's and its warps' starting ranks.
+__device__ void layout_from_counts(const CP& p, Smem& s) {
+    const int G = p.G, nb = gridDim.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    Layout& L = s.lay;
+    if (warp < G) {
+        const int g = warp;
+        // the blocks' totals (before this block / all blocks), lanes striding over the blocks; this
+        // block's own 32 slices are scanned over the lanes for the warps' starting ranks
+        unsigned int before = 0, total = 0;
+        for (int b = lane; b < nb; b += 32) {
+            const unsigned int c = __ldcg(&p.blk_cnt[(long long)b * SKML_MAX_GROUPS + g]);
+            total += c;
+            if (b < (int)blockIdx.x) before += c;
+        }
+        const unsigned int own = __ldcg(&p.warp_cnt[((long long)blockIdx.x * SKML_WARPS + lane) * SKML_MAX_GROUPS + g]);
+        total = warp_sum(total);
+        before = warp_sum(before);
+        unsigned int inc = own;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned int t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+            if (lane >= o) inc += t;
+        }
+        s.wbase[lane][g] = inc - own;
+        if (lane == 0) {
+            L.n_g[g] = total;
+            L.base_rank[g] = before;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < G) {  // per-group divisions and hash draws, one thread each
+        const int g = threadIdx.x;
+        unsigned int col = 0;
+        if (L.n_g[g]) {
+            col = (unsigned int)ceil((double)L.n_g[g] * p.col_ratio);
+            if (col < 1) col = 1;
+        }
+        L.col[g] = col;
+        L.col_magic[g] = col ? skml_fastmod_magic(col) : 0ull;
+        L.recip[g] = skml_recip32(col);
+        skml_pick_hashes(p.seed, p.step, p.rank, (unsigned int)g, p.rows, L.hash_ids[g]);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        bool mix = p.rows <= 3;
+        for (int g = 0; g < G && mix; ++g) mix = skml_rows_are_mixers(L.hash_ids[g], p.rows);
+        L.mixers = mix ? 1 : 0;
+        const int cb = s.qi.cell_bits;
+        L.off_bv = SKML_HEADER_BYTES;
+        L.off_gt = L.off_bv + skml_align16(4ull * p.q);
+        L.off_flags = L.off_gt + (unsigned long long)SKML_GROUP_ENTRY_BYTES * G;
+        unsigned long long o = L.off_flags;
+        unsigned int go = 0, ch = 0;
+        for (int g = 0; g < G; ++g) {
+            L.flag_off[g] = o;
+            if (L.n_g[g]) o += skml_align16(8ull * ((2ull * L.n_g[g] + 63) / 64));
+            L.goff[g] = go;
+            go += (L.n_g[g] + 3u) & ~3u;
+            L.chunk_prefix[g] = ch;
+            ch += (L.n_g[g] + SKML_RESTART_INTERVAL - 1) / SKML_RESTART_INTERVAL;
+        }
+        L.chunk_prefix[G] = ch;
+        L.off_restart = o;
+        for (int g = 0; g < G; ++g) {
+            L.restart_off[g] = o;
+            if (L.n_g[g]) o += 16ull * ((L.n_g[g] + SKML_RESTART_INTERVAL - 1) / SKML_RESTART_INTERVAL);
+        }
+        L.off_tables = o;
+        unsigned long long t32 = 0;
+        for (int g = 0; g < G; ++g) {
+            const unsigned int col = L.col[g];
+            L.table_off[g] = o;
+            L.tab32_off[g] = t32;
+            o += skml_align16((unsigned long long)p.rows * col * (cb / 8));
+            t32 += (unsigned long long)p.rows * col;
+        }
+        L.off_deltas = o;
+        // the key code adds at most four bytes per key: refuse now what cannot fit in the worst case
+        unsigned long long worst = o;
+        for (int g = 0; g < G; ++g) worst += skml_align16(4ull * L.n_g[g] + 8);
+        L.overflow = (worst > (unsigned long long)p.slot_capacity) || (t32 + 4 > (unsigned long long)p.tables_cap);
+        if (L.overflow) skml_set_status(p.status, SKML_CAPACITY, 0x30u);
+    }
+    __syncthreads();
+}
+
+// S4: every key goes to its group's staging list (stable, so the lists stay sorted);
+// grouped MinMaxSketch insert.
+__device__ void stage_scatter(const CP& p, Smem& s, long long n) {
+    const int G = p.G;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const Layout& L = s.lay;
+    if (L.overflow) return;
+    build_group_lut(p, s);  // (also clears the per-iteration counters)
+    const long long sub = vslice_size(n);
+    const long long vb = (long long)blockIdx.x * SKML_WARPS + warp;
+    long long lo = vb * sub, hi = lo + sub;
+    if (lo > n) lo = n;
+    if (hi > n) hi = n;
+    const int zero = s.qi.zero_idx;
+    unsigned int run = 0;   // lane g: staging position of the next key of group g in this slice
+    if (lane < G) run = L.goff[lane] + L.base_rank[lane] + s.wbase[warp][lane];
+    int nkey = 0, nbin = 0;
     if (lo + lane < hi) {
         nkey = p.keys[lo + lane];
-        if (PACK) nbin = p.bins[lo + lane];
-        else nval = p.vals[lo + lane];
+        nbin = p.bins[lo + lane];
     }
     for (long long i0 = lo; i0 < hi; i0 += 32) {
         const long long i = i0 + lane;
         const bool valid = i < hi;
-        int key = nkey, bin = nbin, g = 63;
-        const float val = nval;
+        const int key = nkey, bin = nbin;
         if (i + 32 < hi) {
             nkey = p.keys[i + 32];
-            if (PACK) nbin = p.bins[i + 32];
-            else nval = p.vals[i + 32];
+            nbin = p.bins[i + 32];
         }
-        if (valid) {
-            if (!PACK) {
-                bin = upper_bound_f(s.splits, s.qi.nsplits, val);
-                p.bins[i] = (unsigned short)bin;
-            }
-            g = skml_group_of(bin, s.qi.edges, G);
-        } else {
-            key = 0;
-            bin = 0;
-        }
-        s.wcnt[warp][lane] = 0;  // slot of group `lane`: filled below if the group occurs in this iteration
-        __syncwarp();
+        const int g = valid ? (int)s.grp_lut[bin] : 63;
         const unsigned int peers = __match_any_sync(0xFFFFFFFFu, g);
         const unsigned int lower = peers & lanemask_lt();
-        const int prev_lane = lower ? 31 - __clz(lower) : 0;
-        const int prev_in_warp = __shfl_sync(0xFFFFFFFFu, key, prev_lane);
-        const int gsrc = valid ? g : 0;
-        const int carry_of_g = __shfl_sync(0xFFFFFFFFu, carry, gsrc);
-        const int prev = valid ? (lower ? prev_in_warp : carry_of_g) : -1;
-        int w = 0;
-        unsigned int delta = 0;
-        const int bp = PACK ? __shfl_sync(0xFFFFFFFFu, base_prev_g, gsrc) : 0;
+        const unsigned int base = __shfl_sync(0xFFFFFFFFu, run, valid ? g : 0);
         if (valid) {
-            if (PACK) {
-                delta = (unsigned int)(key - (prev >= 0 ? prev : bp));
-                w = skml_delta_bytes(delta);
-            } else if (prev >= 0) {
-                w = skml_delta_bytes((unsigned int)(key - prev));
-            }
-        }
-        const unsigned int b1 = __ballot_sync(0xFFFFFFFFu, w == 1);
-        const unsigned int b2 = __ballot_sync(0xFFFFFFFFu, w == 2);
-        const unsigned int b4 = __ballot_sync(0xFFFFFFFFu, w == 4);
-        const unsigned int r_w = __popc(lower);
-        const unsigned int bw = __popc(lower & b1) + 2 * __popc(lower & b2) + 4 * __popc(lower & b4);
-        const unsigned int rank_of_g = __shfl_sync(0xFFFFFFFFu, rank_g, gsrc);
-        const unsigned long long boff_of_g = __shfl_sync(0xFFFFFFFFu, boff_g, gsrc);
-        if (valid) {
-            if (lower == 0) {  // first lane of its group in this iteration
-                s.wcnt[warp][g] = (unsigned int)__popc(peers);
-                s.wbytes[warp][g] = __popc(peers & b1) + 2 * __popc(peers & b2) + 4 * __popc(peers & b4);
-                s.cin[warp][g] = key;  // candidate for "first key of the group in this slice"
-            }
-            if ((peers >> lane) == 1u) s.wlast[warp][g] = key;  // last lane of its group
-        }
-        if (PACK && valid && !overflow) {
-            const unsigned long long prank = (unsigned long long)rank_of_g + r_w;
-            const unsigned long long boff = boff_of_g + bw;
-            // flags: (w - 1) most significant bit first at stream bits 2p, 2p+1
-            const unsigned int fv = (unsigned int)(w - 1);
-            if (fv) {
-                const unsigned int bits = ((fv >> 1) & 1u) | ((fv & 1u) << 1);
-                unsigned int* fw = reinterpret_cast<unsigned int*>(p.payload + L.flag_off[g]) + ((2 * prank) >> 5);
-                atomicOr(fw, bits << ((2 * prank) & 31));
-            }
-            unsigned char* dst = p.payload + L.delta_off[g] + boff;
-            for (int j = 0; j < w; ++j) dst[j] = skml_delta_stream_byte(delta, w, j);
-            if ((prank % SKML_RESTART_INTERVAL) == 0) {
-                SkmlRestart r;
-                r.prev_key = (unsigned int)key - delta;
-                r.flag_bit_off = (unsigned int)(2 * prank);
-                r.delta_bit_off = 8ull * boff;
-                *reinterpret_cast<SkmlRestart*>(p.payload + L.restart_off[g] +
-                                                (prank / SKML_RESTART_INTERVAL) * sizeof(SkmlRestart)) = r;
-            }
+            if (lower == 0) s.wcnt[warp][g] = (unsigned int)__popc(peers);
+            const unsigned int dst = base + (unsigned int)__popc(lower);
+            p.gkeys[dst] = key;
             const unsigned int cell = skml_pack_cell(bin, zero);
             const int col = (int)L.col[g];
             unsigned int* tab = p.tables + L.tab32_off[g];
@@ -722,66 +779,252 @@ __device__ void element_pass(const CP& p, Smem& s, long long n) {
         }
         __syncwarp();
         if (lane < G) {
-            const unsigned int c = s.wcnt[warp][lane];
-            if (c) {
-                if (first < 0 && carry < 0) first = s.cin[warp][lane];
-                carry = s.wlast[warp][lane];
-                cnt_g += c;
-                bytes_g += s.wbytes[warp][lane];
-                rank_g += c;
-                boff_g += s.wbytes[warp][lane];
-            }
+            run += s.wcnt[warp][lane];
+            s.wcnt[warp][lane] = 0;
         }
         __syncwarp();
     }
-    if (!PACK) {
-        // Per-warp statistics go to global memory (rows gridDim.x.. of the table, read again by
-        // compute_layout); the block's own summary (rows 0..gridDim.x-1) is chained from them here.
-        if (lane < G) {
-            CtaStat st;
-            st.count = cnt_g;
-            st.first_key = first;
-            st.last_key = carry;
-            st.pad = 0;
-            st.bytes = bytes_g;
-            st.pad2 = 0;
-            p.stats[((long long)gridDim.x + vb) * SKML_MAX_GROUPS + lane] = st;
-            s.wcnt[warp][lane] = cnt_g;
-            s.wbytes[warp][lane] = (unsigned int)bytes_g;
-            s.cin[warp][lane] = first;
-            s.wlast[warp][lane] = carry;
-        }
-        __syncthreads();
-        if (warp < G) {
-            const int g = warp;
-            const unsigned int c = s.wcnt[lane][g];
-            const int fk = s.cin[lane][g], lk = s.wlast[lane][g];
-            const unsigned int nonempty = __ballot_sync(0xFFFFFFFFu, c > 0);
-            const unsigned int lowm = nonempty & lanemask_lt();
-            const int before = __shfl_sync(0xFFFFFFFFu, lk, lowm ? 31 - __clz(lowm) : 0);
-            unsigned long long b = s.wbytes[lane][g];
-            if (c > 0 && lowm) b += (unsigned long long)skml_delta_bytes((unsigned int)(fk - before));
-            unsigned int csum = c;
+}
+
+// ---------------------------------------------------------------------------
+// S5: delta-binary key code of the groups' lists. Chunks of 1024 keys are numbered group-major; a
+// block owns a contiguous run of them and works on four at a time (one per 256-thread sub-block,
+// four adjacent keys per thread).
+// ---------------------------------------------------------------------------
+struct ChunkWork {
+    int g;                  // group, -1 = no chunk for this sub-block
+    unsigned int j;         // chunk index inside the group
+    unsigned int cnt;       // keys in the chunk
+    int k[4];               // this thread's keys
+    unsigned int w[4];      // their delta widths in bytes (0 = no key)
+    unsigned int d[4];      // their deltas
+    unsigned int wsum;
+    int prev0;              // key before the chunk's first key (0 at the start of a group)
+};
+
+__device__ __forceinline__ void load_chunk(const CP& p, const Layout& L, unsigned int ch, unsigned int ch_end, int G, ChunkWork& c) {
+    const int t = threadIdx.x & 255, lane = threadIdx.x & 31;
+    c.g = -1;
+    c.wsum = 0;
+    c.cnt = 0;
+    c.j = 0;
+    c.prev0 = 0;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                csum += __shfl_xor_sync(0xFFFFFFFFu, csum, o);
-                b += __shfl_xor_sync(0xFFFFFFFFu, b, o);
-            }
-            const int bf = __shfl_sync(0xFFFFFFFFu, fk, nonempty ? __ffs(nonempty) - 1 : 0);
-            const int bl = __shfl_sync(0xFFFFFFFFu, lk, nonempty ? 31 - __clz(nonempty) : 0);
-            if (lane == 0) {
-                CtaStat st;
-                st.count = csum;
-                st.first_key = nonempty ? bf : -1;
-                st.last_key = nonempty ? bl : -1;
-                st.pad = 0;
-                st.bytes = b;
-                st.pad2 = 0;
-                p.stats[(long long)blockIdx.x * SKML_MAX_GROUPS + g] = st;
+    for (int u = 0; u < 4; ++u) {
+        c.w[u] = 0;
+        c.d[u] = 0;
+        c.k[u] = 0;
+    }
+    if (ch >= ch_end) return;
+    int g = 0;
+    while (g + 1 < G && ch >= L.chunk_prefix[g + 1]) ++g;
+    c.g = g;
+    c.j = ch - L.chunk_prefix[g];
+    const unsigned int first = c.j * SKML_RESTART_INTERVAL;
+    c.cnt = min((unsigned int)SKML_RESTART_INTERVAL, L.n_g[g] - first);
+    const int* list = p.gkeys + L.goff[g];
+    const unsigned int i0 = 4u * t;
+    int4 kk = make_int4(0, 0, 0, 0);
+    if (i0 < c.cnt) kk = *reinterpret_cast<const int4*>(list + first + i0);  // goff and first are multiples of 4
+    c.k[0] = kk.x; c.k[1] = kk.y; c.k[2] = kk.z; c.k[3] = kk.w;
+    // the key before this thread's first key: the lane below holds it, except at a warp's start
+    int prev = __shfl_up_sync(0xFFFFFFFFu, c.k[3], 1);
+    if (lane == 0) prev = (first + i0 > 0 && i0 < c.cnt) ? list[first + i0 - 1] : 0;
+    if (t == 0) c.prev0 = first > 0 ? list[first - 1] : 0;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        if (i0 + u < c.cnt) {
+            c.d[u] = (unsigned int)(c.k[u] - prev);
+            c.w[u] = (unsigned int)skml_delta_bytes(c.d[u]);
+            c.wsum += c.w[u];
+            prev = c.k[u];
+        }
+    }
+}
+
+// Exclusive scan of `v` over the 256 threads of this thread's sub-block; `total` = the sub-block's sum.
+// One block barrier inside; `par` alternates between calls.
+__device__ __forceinline__ unsigned int sub_scan(Smem& s, unsigned int v, unsigned int& total) {
+    const int lane = threadIdx.x & 31, sw = (threadIdx.x >> 5) & 7, sb = threadIdx.x >> 8;
+    unsigned int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned int t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    __syncthreads();  // the previous call's readers are done
+    if (lane == 31) s.sub_part[sb][sw] = inc;
+    __syncthreads();
+    unsigned int base = 0, tot = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        const unsigned int x = s.sub_part[sb][w];
+        if (w < sw) base += x;
+        tot += x;
+    }
+    total = tot;
+    return base + inc - v;
+}
+
+// Pass A: byte counts of this block's chunks -> chunk offsets inside the block's part of each group,
+// the block's byte totals per group (published for the blocks after it).
+__device__ void pack_measure(const CP& p, Smem& s, unsigned int my_begin, unsigned int my_end) {
+    const Layout& L = s.lay;
+    if (threadIdx.x < SKML_MAX_GROUPS) s.my_bytes[threadIdx.x] = 0;
+    __syncthreads();
+    for (unsigned int c0 = my_begin; c0 < my_end; c0 += 4) {
+        ChunkWork c;
+        load_chunk(p, L, c0 + (threadIdx.x >> 8), my_end, p.G, c);
+        unsigned int total;
+        sub_scan(s, c.wsum, total);
+        if ((threadIdx.x & 255) == 0) s.sub_total[threadIdx.x >> 8] = total;
+        __syncthreads();
+        if (threadIdx.x == 0) {  // the four chunks of this round, in order
+            for (int q = 0; q < 4 && c0 + q < my_end; ++q) {
+                int g = 0;
+                while (g + 1 < p.G && c0 + q >= L.chunk_prefix[g + 1]) ++g;
+                p.chunk_off[c0 + q] = (unsigned int)s.my_bytes[g];
+                s.my_bytes[g] += s.sub_total[q];
             }
         }
         __syncthreads();
     }
+    if (threadIdx.x < SKML_MAX_GROUPS) p.blk_bytes[(long long)blockIdx.x * SKML_MAX_GROUPS + threadIdx.x] = s.my_bytes[threadIdx.x];
+}
+
+// Byte totals of the blocks before this one (they own the chunks before this block's run, so the
+// sums give this block's starting offsets and the sizes of all earlier groups).
+__device__ void pack_prefix(const CP& p, Smem& s, bool wait, unsigned int epoch) {
+    if (threadIdx.x < SKML_MAX_GROUPS) s.pre_bytes[threadIdx.x] = 0;
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < blockIdx.x) {
+        const unsigned int b = threadIdx.x;
+        bool ok = true;
+        if (wait) {
+            const long long t0 = clock64();
+            unsigned int ns = 20;
+            while (ld_acquire_gpu(&p.blk_flag[b]) != epoch) {
+                if (clock64() - t0 > p.budget) {
+                    skml_set_status(p.status, SKML_TIMEOUT_BARRIER, 0x50u);
+                    ok = false;
+                    break;
+                }
+                __nanosleep(ns);
+                if (ns < 400) ns *= 2;
+            }
+        }
+        if (ok) {
+            for (int g = 0; g < p.G; ++g) {
+                const unsigned long long v = __ldcg(&p.blk_bytes[(long long)b * SKML_MAX_GROUPS + g]);
+                if (v) atomicAdd(&s.pre_bytes[g], v);
+            }
+        } else {
+            s_ok = 0;
+        }
+    }
+    __syncthreads();
+    Layout& L = s.lay;
+    if (threadIdx.x == 0) {
+        // section starts of the groups this block can reach: all earlier groups are complete in pre_bytes
+        // (plus this block's own part of the group its run starts in)
+        unsigned long long o = L.off_deltas;
+        for (int g = 0; g < p.G; ++g) {
+            L.delta_off[g] = o;
+            const unsigned long long bytes = s.pre_bytes[g] + s.my_bytes[g];
+            if (L.n_g[g]) o += skml_align16(8ull * ((bytes + 7) / 8));
+        }
+        if (!s_ok) L.overflow = 1;
+    }
+    __syncthreads();
+}
+
+// Pass B: flag bytes, delta bytes and restart points of this block's chunks.
+__device__ void pack_write(const CP& p, Smem& s, unsigned int my_begin, unsigned int my_end) {
+    const Layout& L = s.lay;
+    if (L.overflow) return;
+    const int t = threadIdx.x & 255;
+    for (unsigned int c0 = my_begin; c0 < my_end; c0 += 4) {
+        ChunkWork c;
+        const unsigned int ch = c0 + (threadIdx.x >> 8);
+        load_chunk(p, L, ch, my_end, p.G, c);
+        unsigned int total;
+        const unsigned int boff = sub_scan(s, c.wsum, total);
+        if (c.g < 0) continue;  // (no barrier follows in this iteration)
+        const int g = c.g;
+        const unsigned int first = c.j * SKML_RESTART_INTERVAL, i0 = 4u * t;
+        const unsigned long long chunk_off = s.pre_bytes[g] + __ldcg(&p.chunk_off[ch]);
+        // flags: (w - 1) most significant bit first at stream bits 2i, 2i+1 -> one byte per four keys
+        // (a group's last chunk also writes the zero padding up to the section's 16-byte end: there the
+        // threads beyond the last key hold widths of zero)
+        const unsigned long long flag_bytes = skml_align16(8ull * ((2ull * L.n_g[g] + 63) / 64));
+        const unsigned long long fbyte = first / 4 + t;
+        if (fbyte < flag_bytes) {
+            unsigned int fb = 0;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const unsigned int fv = c.w[u] ? c.w[u] - 1u : 0u;
+                fb |= (((fv >> 1) & 1u) | ((fv & 1u) << 1)) << (2 * u);
+            }
+            p.payload[L.flag_off[g] + fbyte] = (unsigned char)fb;
+        }
+        if (i0 < c.cnt) {
+            unsigned char* dst = p.payload + L.delta_off[g] + chunk_off + boff;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                for (unsigned int j = 0; j < c.w[u]; ++j) dst[j] = skml_delta_stream_byte(c.d[u], (int)c.w[u], (int)j);
+                dst += c.w[u];
+            }
+        }
+        if (t == 0 && c.j + 1 == (L.n_g[g] + SKML_RESTART_INTERVAL - 1) / SKML_RESTART_INTERVAL) {
+            // the group's last chunk: clear the padding between the last delta byte and the section's end
+            const unsigned long long endb = chunk_off + total;
+            for (unsigned long long a = endb; a < skml_align16(8ull * ((endb + 7) / 8)); ++a) p.payload[L.delta_off[g] + a] = 0;
+        }
+        if (t == 0) {
+            SkmlRestart r;
+            r.prev_key = (unsigned int)c.prev0;
+            r.flag_bit_off = 2u * first;
+            r.delta_bit_off = 8ull * chunk_off;
+            *reinterpret_cast<SkmlRestart*>(p.payload + L.restart_off[g] + (unsigned long long)c.j * sizeof(SkmlRestart)) = r;
+        }
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ void chunk_run(const Layout& L, int G, unsigned int& my_begin, unsigned int& my_end) {
+    const unsigned int total = L.chunk_prefix[G];
+    unsigned int per = (total + gridDim.x - 1) / gridDim.x;
+    per = (per + 3u) & ~3u;  // four chunks per round
+    my_begin = min(total, per * blockIdx.x);
+    my_end = min(total, my_begin + per);
+}
+
+// S6 prelude: every group's delta bytes from all blocks' counts -> delta section offsets, total size.
+__device__ void layout_finish(const CP& p, Smem& s) {
+    Layout& L = s.lay;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (warp < p.G) {
+        unsigned long long v = 0;
+        for (int b = lane; b < (int)gridDim.x; b += 32) v += __ldcg(&p.blk_bytes[(long long)b * SKML_MAX_GROUPS + warp]);
+        v = warp_sum(v);
+        if (lane == 0) L.bytes_g[warp] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long o = L.off_deltas;
+        for (int g = 0; g < p.G; ++g) {
+            L.delta_off[g] = o;
+            if (L.n_g[g]) o += skml_align16(8ull * ((L.bytes_g[g] + 7) / 8));
+        }
+        L.total_bytes = o;
+        if (o > (unsigned long long)p.slot_capacity) {
+            L.overflow = 1;
+            skml_set_status(p.status, SKML_CAPACITY, 0x36u);
+        }
+    }
+    __syncthreads();
 }
 
 // Fill helpers run inside S1 (they do not depend on the summary).
@@ -793,144 +1036,9 @@ __device__ void stage_prepare(const CP& p, long long n) {
     uint4 ones = make_uint4(~0u, ~0u, ~0u, ~0u);
     uint4* t4 = reinterpret_cast<uint4*>(p.tables);
     for (long long i = gid; i < (cells + 3) / 4; i += gsz) t4[i] = ones;
-    // the flag region is written with atomicOr and must start at zero
-    const long long off_flags = SKML_HEADER_BYTES + (long long)skml_align16(4ull * p.q) + SKML_GROUP_ENTRY_BYTES * p.G;
-    long long flag_bytes = (long long)skml_align16((unsigned long long)(n / 4 + 24 * p.G + 16));
-    if (off_flags + flag_bytes > p.slot_capacity) flag_bytes = p.slot_capacity > off_flags ? ((p.slot_capacity - off_flags) & ~15ll) : 0;
-    uint4 z = make_uint4(0, 0, 0, 0);
-    uint4* f4 = reinterpret_cast<uint4*>(p.payload + off_flags);
-    for (long long i = gid; i < flag_bytes / 16; i += gsz) f4[i] = z;
 }
 
-// ---------------------------------------------------------------------------
-// S4 prelude: payload layout from the per-block statistics (every block)
-// ---------------------------------------------------------------------------
-__device__ void compute_layout(const CP& p, Smem& s, long long n) {
-    const int G = p.G, nb = gridDim.x;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    Layout& L = s.lay;
-    if (warp < G) {
-        const int g = warp;
-        unsigned int run_cnt = 0;
-        unsigned long long run_bytes = 0;
-        int carry_last = -1;
-        for (int base = 0; base < nb; base += 32) {
-            const int c = base + lane;
-            CtaStat st;
-            st.count = 0; st.first_key = -1; st.last_key = -1; st.bytes = 0;
-            if (c < nb) st = p.stats[(long long)c * SKML_MAX_GROUPS + g];
-            const unsigned int nonempty = __ballot_sync(0xFFFFFFFFu, st.count > 0);
-            const unsigned int lowm = nonempty & lanemask_lt();
-            const int src = lowm ? 31 - __clz(lowm) : 0;
-            const int prev_last_lane = __shfl_sync(0xFFFFFFFFu, st.last_key, src);
-            const int before = lowm ? prev_last_lane : carry_last;  // last key of the group before block c
-            unsigned long long full = st.bytes;
-            if (st.count > 0) full += (unsigned long long)skml_delta_bytes((unsigned int)(st.first_key - (before >= 0 ? before : 0)));
-            // inclusive scans over the 32 blocks of this chunk
-            unsigned int ic = st.count;
-            unsigned long long ib = full;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                unsigned int tc = __shfl_up_sync(0xFFFFFFFFu, ic, o);
-                unsigned long long tb = __shfl_up_sync(0xFFFFFFFFu, ib, o);
-                if (lane >= o) { ic += tc; ib += tb; }
-            }
-            if (c == (int)blockIdx.x) {
-                L.base_rank[g] = run_cnt + ic - st.count;
-                L.base_bytes[g] = run_bytes + ib - full;
-                L.base_prev[g] = before;
-            }
-            run_cnt += __shfl_sync(0xFFFFFFFFu, ic, 31);
-            run_bytes += __shfl_sync(0xFFFFFFFFu, ib, 31);
-            if (nonempty) {
-                const int hl = 31 - __clz(nonempty);
-                carry_last = __shfl_sync(0xFFFFFFFFu, st.last_key, hl);
-            }
-        }
-        if (lane == 0) {
-            L.n_g[g] = run_cnt;
-            L.bytes_g[g] = run_bytes;
-        }
-        __syncwarp();
-        // second level: the 32 warps of this block, lane = warp
-        {
-            const CtaStat st = p.stats[((long long)gridDim.x + (long long)blockIdx.x * SKML_WARPS + lane) * SKML_MAX_GROUPS + g];
-            const unsigned int nonempty = __ballot_sync(0xFFFFFFFFu, st.count > 0);
-            const unsigned int lowm = nonempty & lanemask_lt();
-            const int prev_last = __shfl_sync(0xFFFFFFFFu, st.last_key, lowm ? 31 - __clz(lowm) : 0);
-            const int before = lowm ? prev_last : L.base_prev[g];
-            unsigned long long full = st.bytes;
-            if (st.count > 0) full += (unsigned long long)skml_delta_bytes((unsigned int)(st.first_key - (before >= 0 ? before : 0)));
-            unsigned int ic = st.count;
-            unsigned long long ib = full;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                unsigned int tc = __shfl_up_sync(0xFFFFFFFFu, ic, o);
-                unsigned long long tb = __shfl_up_sync(0xFFFFFFFFu, ib, o);
-                if (lane >= o) { ic += tc; ib += tb; }
-            }
-            L.vbase_rank[lane][g] = L.base_rank[g] + ic - st.count;
-            L.vbase_bytes[lane][g] = L.base_bytes[g] + ib - full;
-            L.vbase_prev[lane][g] = before >= 0 ? before : 0;
-        }
-    }
-    __syncthreads();
-    if (threadIdx.x < G) {  // per-group divisions and hash draws, one thread each
-        const int g = threadIdx.x;
-        unsigned int col = 0;
-        if (L.n_g[g]) {
-            col = (unsigned int)ceil((double)L.n_g[g] * p.col_ratio);
-            if (col < 1) col = 1;
-        }
-        L.col[g] = col;
-        L.col_magic[g] = col ? skml_fastmod_magic(col) : 0ull;
-        L.recip[g] = skml_recip32(col);
-        skml_pick_hashes(p.seed, p.step, p.rank, (unsigned int)g, p.rows, L.hash_ids[g]);
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        bool mix = p.rows <= 3;
-        for (int g = 0; g < G && mix; ++g) mix = skml_rows_are_mixers(L.hash_ids[g], p.rows);
-        L.mixers = mix ? 1 : 0;
-    }
-    if (threadIdx.x == 0) {
-        const int cb = s.qi.cell_bits;
-        L.off_bv = SKML_HEADER_BYTES;
-        L.off_gt = L.off_bv + skml_align16(4ull * p.q);
-        L.off_flags = L.off_gt + (unsigned long long)SKML_GROUP_ENTRY_BYTES * G;
-        unsigned long long o = L.off_flags;
-        for (int g = 0; g < G; ++g) {
-            L.flag_off[g] = o;
-            if (L.n_g[g]) o += skml_align16(8ull * ((2ull * L.n_g[g] + 63) / 64));
-        }
-        L.off_restart = o;
-        for (int g = 0; g < G; ++g) {
-            L.restart_off[g] = o;
-            if (L.n_g[g]) o += 16ull * ((L.n_g[g] + SKML_RESTART_INTERVAL - 1) / SKML_RESTART_INTERVAL);
-        }
-        L.off_tables = o;
-        unsigned long long t32 = 0;
-        for (int g = 0; g < G; ++g) {
-            const unsigned int col = L.col[g];
-            L.table_off[g] = o;
-            L.tab32_off[g] = t32;
-            o += skml_align16((unsigned long long)p.rows * col * (cb / 8));
-            t32 += (unsigned long long)p.rows * col;
-        }
-        L.off_deltas = o;
-        for (int g = 0; g < G; ++g) {
-            L.delta_off[g] = o;
-            if (L.n_g[g]) o += skml_align16(8ull * ((L.bytes_g[g] + 7) / 8));
-        }
-        L.total_bytes = o;
-        L.overflow = (o > (unsigned long long)p.slot_capacity) || (t32 + 4 > (unsigned long long)p.tables_cap);
-        if (L.overflow) skml_set_status(p.status, SKML_CAPACITY, 0x30u);
-    }
-    __syncthreads();
-    (void)n;
-}
-
-// Header, bucket values, group table and zero padding of the delta sections (block 0).
+// Header, bucket values and group table (block 0), stored locally and into every peer's slot.
 __device__ void write_header(const CP& p, Smem& s, long long n, int kind) {
     if (blockIdx.x != 0) return;
     const Layout& L = s.lay;
@@ -957,10 +1065,6 @@ __device__ void write_header(const CP& p, Smem& s, long long n, int kind) {
             e.flag_kind = 0;
             e.restart_off = L.n_g[g] ? L.restart_off[g] : 0;
             *reinterpret_cast<SkmlGroupEntry*>(p.payload + L.off_gt + (unsigned long long)g * sizeof(SkmlGroupEntry)) = e;
-            // zero the padding after the last delta byte of the group
-            unsigned long long endb = L.delta_off[g] + L.bytes_g[g];
-            unsigned long long endp = L.delta_off[g] + (L.n_g[g] ? skml_align16(8ull * ((L.bytes_g[g] + 7) / 8)) : 0);
-            for (unsigned long long a = endb; a < endp; ++a) p.payload[a] = 0;
         }
     }
     if (threadIdx.x == 0) {
@@ -1009,10 +1113,24 @@ __device__ void write_header(const CP& p, Smem& s, long long n, int kind) {
         uint4* dst = reinterpret_cast<uint4*>(p.payload);
         for (int i = 0; i < SKML_HEADER_BYTES / 16; ++i) dst[i] = src[i];
     }
+    // this block wrote the head of the payload (header, bucket values, group table): it also stores it
+    // into the peers' slots, so that no other block has to wait for it
+    __syncthreads();
+    if (p.world > 1) {
+        unsigned long long head = SKML_HEADER_BYTES;
+        if (sparse) head = L.off_flags;
+        else if (kind == SKML_KIND_DENSE) head = SKML_HEADER_BYTES + skml_align16(4ull * p.q);
+        const uint4* src = reinterpret_cast<const uint4*>(p.payload);
+        for (unsigned long long i = threadIdx.x; i < head / 16; i += blockDim.x) {
+            const uint4 v = ld_cg_v4(src + i);
+            for (unsigned int r = 0; r < p.world; ++r)
+                if (r != p.rank && p.peer_payload[r]) st_v4(reinterpret_cast<uint4*>(p.peer_payload[r]) + i, v);
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------
-// S5: narrow tables, store everything into the peers' slots, release the flags
+// S6: narrow tables, store everything into the peers' slots, release the flags
 // ---------------------------------------------------------------------------
 __device__ void copy_range_to_peers(const CP& p, unsigned long long lo, unsigned long long hi) {
     if (p.world <= 1 || hi <= lo) return;
@@ -1042,51 +1160,112 @@ __device__ void finish_publish(const CP& p) {
     }
 }
 
-__device__ void stage_push_sparse(const CP& p, Smem& s) {
+// Sketch tables: 32-bit working cells -> 8/16-bit bucket codes, stored locally and into the peers' slots.
+__device__ void narrow_tables(const CP& p, Smem& s) {
     const Layout& L = s.lay;
+    if (L.overflow) return;
     const int G = p.G, cb = s.qi.cell_bits, per = 16 / (cb / 8);  // cells per 16-byte unit
-    if (!L.overflow) {
-        if (threadIdx.x == 0) {
-            unsigned long long u = 0;
-            for (int g = 0; g < G; ++g) {
-                s.unit_prefix[g] = u;
-                u += skml_align16((unsigned long long)p.rows * L.col[g] * (cb / 8)) / 16;
-            }
-            s.unit_prefix[G] = u;
+    if (threadIdx.x == 0) {
+        unsigned long long u = 0;
+        for (int g = 0; g < G; ++g) {
+            s.unit_prefix[g] = u;
+            u += skml_align16((unsigned long long)p.rows * L.col[g] * (cb / 8)) / 16;
         }
-        __syncthreads();
-        const long long gsz = (long long)gridDim.x * blockDim.x, gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-        const long long units = (long long)s.unit_prefix[G];
-        const unsigned int zero = (unsigned int)s.qi.zero_idx;
-        for (long long u = gid; u < units; u += gsz) {
-            int g = 0;
-            while (g + 1 < G && (unsigned long long)u >= s.unit_prefix[g + 1]) ++g;
-            const long long j = u - (long long)s.unit_prefix[g];
-            const long long cells = (long long)p.rows * L.col[g];
-            const unsigned int* tab = p.tables + L.tab32_off[g];
-            unsigned int words[4] = {0, 0, 0, 0};
-            for (int t = 0; t < per; ++t) {
-                long long c = j * per + t;
-                unsigned int code = 0;
-                if (c < cells) {
-                    unsigned int cell = __ldcg(tab + c);
-                    code = cell == SKML_EMPTY_CELL ? zero : (cell & 0xFFFFu);
-                }
-                if (cb == 8) words[t >> 2] |= (code & 0xFFu) << (8 * (t & 3));
-                else words[t >> 1] |= (code & 0xFFFFu) << (16 * (t & 1));
-            }
-            uint4 v = make_uint4(words[0], words[1], words[2], words[3]);
-            const unsigned long long off = L.table_off[g] + 16ull * j;
-            st_v4(reinterpret_cast<uint4*>(p.payload + off), v);
-            for (unsigned int r = 0; r < p.world; ++r)
-                if (r != p.rank && p.peer_payload[r]) st_v4(reinterpret_cast<uint4*>(p.peer_payload[r] + off), v);
-        }
-        copy_range_to_peers(p, 0, L.off_tables);
-        copy_range_to_peers(p, L.off_deltas, L.total_bytes);
-    } else {
-        copy_range_to_peers(p, 0, SKML_HEADER_BYTES);
+        s.unit_prefix[G] = u;
     }
-    finish_publish(p);
+    __syncthreads();
+    const long long gsz = (long long)gridDim.x * blockDim.x, gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long units = (long long)s.unit_prefix[G];
+    const unsigned int zero = (unsigned int)s.qi.zero_idx;
+    for (long long u = gid; u < units; u += gsz) {
+        int g = 0;
+        while (g + 1 < G && (unsigned long long)u >= s.unit_prefix[g + 1]) ++g;
+        const long long j = u - (long long)s.unit_prefix[g];
+        const long long cells = (long long)p.rows * L.col[g];
+        const unsigned int* tab = p.tables + L.tab32_off[g];
+        unsigned int words[4] = {0, 0, 0, 0};
+        for (int t = 0; t < per; ++t) {
+            long long c = j * per + t;
+            unsigned int code = 0;
+            if (c < cells) {
+                unsigned int cell = __ldcg(tab + c);
+                code = cell == SKML_EMPTY_CELL ? zero : (cell & 0xFFFFu);
+            }
+            if (cb == 8) words[t >> 2] |= (code & 0xFFu) << (8 * (t & 3));
+            else words[t >> 1] |= (code & 0xFFFFu) << (16 * (t & 1));
+        }
+        uint4 v = make_uint4(words[0], words[1], words[2], words[3]);
+        const unsigned long long off = L.table_off[g] + 16ull * j;
+        st_v4(reinterpret_cast<uint4*>(p.payload + off), v);
+        for (unsigned int r = 0; r < p.world; ++r)
+            if (r != p.rank && p.peer_payload[r]) st_v4(reinterpret_cast<uint4*>(p.peer_payload[r] + off), v);
+    }
+}
+
+// Bytes [lo, hi) of the local payload -> the same bytes of every peer's slot, by this block alone:
+// 16-byte stores for the aligned interior, byte stores for a ragged head or tail (two blocks that
+// share a 16-byte unit each store only their own bytes of it).
+__device__ void push_bytes(const CP& p, unsigned long long lo, unsigned long long hi) {
+    if (p.world <= 1 || hi <= lo) return;
+    const unsigned long long a0 = (lo + 15ull) & ~15ull, a1 = hi & ~15ull;
+    if (a0 < a1) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.payload + a0);
+        for (unsigned long long i = threadIdx.x; i < (a1 - a0) / 16; i += blockDim.x) {
+            const uint4 v = ld_cg_v4(src + i);
+            for (unsigned int r = 0; r < p.world; ++r)
+                if (r != p.rank && p.peer_payload[r]) st_v4(reinterpret_cast<uint4*>(p.peer_payload[r] + a0) + i, v);
+        }
+    }
+    const unsigned long long head_end = a0 < hi ? a0 : hi, tail_begin = a1 > head_end ? a1 : head_end;
+    const unsigned long long ragged = (head_end - lo) + (hi - tail_begin);
+    for (unsigned long long i = threadIdx.x; i < ragged; i += blockDim.x) {
+        const unsigned long long a = i < head_end - lo ? lo + i : tail_begin + (i - (head_end - lo));
+        const unsigned char v = __ldcg(p.payload + a);
+        for (unsigned int r = 0; r < p.world; ++r)
+            if (r != p.rank && p.peer_payload[r]) p.peer_payload[r][a] = v;
+    }
+}
+
+// The flag bytes, restart points and delta bytes this block wrote for its chunks -> the peers' slots.
+__device__ void push_own_chunks(const CP& p, Smem& s, unsigned int my_begin, unsigned int my_end) {
+    const Layout& L = s.lay;
+    if (p.world <= 1 || L.overflow || my_begin >= my_end) return;
+    __syncthreads();  // this block's own stores are visible to all its threads
+    for (int g = 0; g < p.G; ++g) {
+        const unsigned int c0 = max(my_begin, L.chunk_prefix[g]), c1 = min(my_end, L.chunk_prefix[g + 1]);
+        if (c0 >= c1) continue;
+        const unsigned int ja = c0 - L.chunk_prefix[g], jb = c1 - L.chunk_prefix[g];
+        const bool last = c1 == L.chunk_prefix[g + 1];
+        const unsigned long long flag_bytes = skml_align16(8ull * ((2ull * L.n_g[g] + 63) / 64));
+        const unsigned long long f1 = min(flag_bytes, 256ull * jb);
+        push_bytes(p, L.flag_off[g] + 256ull * ja, L.flag_off[g] + (last ? flag_bytes : f1));
+        push_bytes(p, L.restart_off[g] + 16ull * ja, L.restart_off[g] + 16ull * jb);
+        unsigned long long d0 = s.pre_bytes[g], d1 = s.pre_bytes[g] + s.my_bytes[g];
+        if (last) d1 = skml_align16(8ull * ((d1 + 7) / 8));  // the zero padding written with the last chunk
+        push_bytes(p, L.delta_off[g] + d0, L.delta_off[g] + d1);
+    }
+}
+
+// Block 0 needs every block's byte counts for the header: bounded wait for their publications.
+__device__ bool wait_all_published(const CP& p, unsigned int epoch) {
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < gridDim.x) {
+        const long long t0 = clock64();
+        unsigned int ns = 20;
+        while (ld_acquire_gpu(&p.blk_flag[threadIdx.x]) != epoch) {
+            if (clock64() - t0 > p.budget) {
+                skml_set_status(p.status, SKML_TIMEOUT_BARRIER, 0x51u);
+                s_ok = 0;
+                break;
+            }
+            __nanosleep(ns);
+            if (ns < 400) ns *= 2;
+        }
+    }
+    __syncthreads();
+    return s_ok != 0;
 }
 
 // ---------------------------------------------------------------------------
@@ -1111,19 +1290,13 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_sparse_kernel(CP p, in
         n = 0;
     }
     if (n <= 0) {  // empty gradient: header-only payload
-        if (FUSED || stage == 4) {
+        if (FUSED || stage == 7) {
             if (threadIdx.x == 0) {
                 s.lay.overflow = 0;
                 s.qi.bin_num = 0;
             }
             __syncthreads();
-            write_header(p, s, 0, SKML_KIND_EMPTY);
-        }
-        if (FUSED) {
-            if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, 9)) return;
-        }
-        if (FUSED || stage == 5) {
-            copy_range_to_peers(p, 0, SKML_HEADER_BYTES);
+            write_header(p, s, 0, SKML_KIND_EMPTY);   // block 0 stores it locally and into the peers' slots
             finish_publish(p);
         }
         return;
@@ -1145,23 +1318,57 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_sparse_kernel(CP p, in
             if (threadIdx.x == 0) skml_set_status(p.status, SKML_BAD_INPUT, 0x32u);
             return;
         }
-        element_pass<false>(p, s, n);
+        stage_count(p, s, n);
     }
     STAGE_BARRIER(3)
     if (FUSED || stage == 4) {
         if (!FUSED) load_quantizer(p, s);
-        compute_layout(p, s, n);
-        write_header(p, s, n, SKML_KIND_SPARSE);
-        element_pass<true>(p, s, n);
+        layout_from_counts(p, s);
+        stage_scatter(p, s, n);
     }
     STAGE_BARRIER(4)
-    if (FUSED || stage == 5) {
+    // S5: key code and publication, with no grid barrier inside. In one cooperative launch a block waits
+    // only for the byte counts of the blocks before it (they are resident, and never wait for a later
+    // block), and block 0 for all of them before it writes the header; staged launches split the stage at
+    // those two points.
+    unsigned int my_begin = 0, my_end = 0;
+    if (FUSED || stage >= 5) {
         if (!FUSED) {
             load_quantizer(p, s);
-            compute_layout(p, s, n);
+            layout_from_counts(p, s);
         }
-        stage_push_sparse(p, s);
+        chunk_run(s.lay, p.G, my_begin, my_end);
+    }
+    if (FUSED || stage == 5) {
+        narrow_tables(p, s);   // the tables are complete since S4
+        pack_measure(p, s, my_begin, my_end);
+    }
+    unsigned int epoch = 0;
+    if (FUSED) {
+        // every block reads the same barrier generation here: it names this launch's publications
+        epoch = ld_acquire_gpu(&p.ctrl[1]) + 0x40000000u;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) st_release_gpu(&p.blk_flag[blockIdx.x], epoch);
+    }
+    if (FUSED || stage == 6) {
+        if (!FUSED) {  // the block's own counts again (shared memory does not survive a launch)
+            if (threadIdx.x < SKML_MAX_GROUPS) s.my_bytes[threadIdx.x] = p.blk_bytes[(long long)blockIdx.x * SKML_MAX_GROUPS + threadIdx.x];
+            __syncthreads();
+        }
+        pack_prefix(p, s, FUSED, epoch);
+        pack_write(p, s, my_begin, my_end);
+        push_own_chunks(p, s, my_begin, my_end);
         if (FUSED) stage_stamp(p.ctrl, 5);
+    }
+    if (FUSED || stage == 7) {
+        if (blockIdx.x == 0) {
+            if (FUSED && !wait_all_published(p, epoch)) return;
+            layout_finish(p, s);
+            write_header(p, s, n, SKML_KIND_SPARSE);
+        }
+        finish_publish(p);
+        if (FUSED) stage_stamp(p.ctrl, 6);
     }
 }
 
@@ -1212,10 +1419,7 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_dense_kernel(CP p, int
         }
     }
     STAGE_BARRIER(3)
-    if (FUSED || stage == 4) {
-        copy_range_to_peers(p, 0, SKML_HEADER_BYTES + skml_align16(4ull * p.q));
-        finish_publish(p);
-    }
+    if (FUSED || stage == 4) finish_publish(p);
 }
 
 // ---------------------------------------------------------------------------
@@ -1269,7 +1473,12 @@ static int fill_params(const SkmlCompressArgs* a, CP& p, int& grid) {
     p.run_cnt = reinterpret_cast<unsigned int*>(ws + L.run_cnt);
     p.run_w = reinterpret_cast<unsigned long long*>(ws + L.run_w);
     p.splits_raw = reinterpret_cast<unsigned int*>(ws + L.splits_raw);
-    p.stats = reinterpret_cast<CtaStat*>(ws + L.stats);
+    p.warp_cnt = reinterpret_cast<unsigned int*>(ws + L.warp_cnt);
+    p.blk_cnt = reinterpret_cast<unsigned int*>(ws + L.blk_cnt);
+    p.blk_bytes = reinterpret_cast<unsigned long long*>(ws + L.blk_bytes);
+    p.blk_flag = reinterpret_cast<unsigned int*>(ws + L.blk_flag);
+    p.chunk_off = reinterpret_cast<unsigned int*>(ws + L.chunk_off);
+    p.gkeys = reinterpret_cast<int*>(ws + L.gkeys);
     p.bins = reinterpret_cast<unsigned short*>(ws + L.bins);
     p.tables = reinterpret_cast<unsigned int*>(ws + L.tables);
     p.tables_cap = L.tables_cap;
@@ -1335,7 +1544,7 @@ extern "C" int skml_compress_sparse(const SkmlCompressArgs* a, void* stream) {
     int rc = fill_params(a, p, grid);
     if (rc) return rc;
     static LaunchCache cache;
-    return launch_stages(compress_sparse_kernel<true>, compress_sparse_kernel<false>, cache, p, grid, a->fused != 0, 5,
+    return launch_stages(compress_sparse_kernel<true>, compress_sparse_kernel<false>, cache, p, grid, a->fused != 0, 7,
                          (cudaStream_t)stream);
 }
 

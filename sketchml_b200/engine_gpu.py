@@ -103,7 +103,6 @@ class GpuEngine:
             self.xchg = PeerExchange(comm, self.comp.capacity, self.device)
             self._prepare_fast_step()
             self.depth = int(conf.pipeline_depth)
-            self._build_transposed_index()
             if self.depth == 1:
                 # gradient one step stale: batch t+1 is differentiated on its own stream while step t
                 # is still being compressed, exchanged and applied; the sparse-gradient buffers are doubled
@@ -124,6 +123,9 @@ class GpuEngine:
                 self.fp_codec = FixedPointCodec(bound, conf.fixed_point_bit_num, comm.world, self.device)
         else:
             self.dense_sum = torch.zeros(dim, dtype=torch.float32, device=self.device)
+        # the prepared gradient path serves every arm alike (the uncompressed baselines too)
+        self.depth = int(conf.pipeline_depth) if self.mode == "sketch" else 0
+        self._build_transposed_index()
 
     def _prepare_fast_step(self) -> None:
         """Argument blocks of the single-call step (`skml_train_step`), one per slot parity."""
@@ -159,20 +161,26 @@ class GpuEngine:
         """Column-major index of every minibatch, when the batches are fixed row slices (shard size a
         multiple of the batch size) and the index fits beside the data."""
         from .ops.transposed import build_batch_index
+        import time
         self.tindex = None
+        self.index_build_s, self.index_bytes = 0.0, 0   # what the one-time preparation cost (reported by the benchmarks)
         conf, csr, B = self.conf, self.csr, self.batch_rows
         if not conf.extras.get("transposed_index", True) or self.depth != 0 or B <= 0 or csr.rows % B != 0:
             return
-        need = csr.nnz * (8 if csr.values is not None else 4) * 1.5
+        need = csr.nnz * (8 if csr.values is not None else 4) * 1.1 + 16 * B * max(1, csr.max_row_nnz)
         free, _ = torch.cuda.mem_get_info(self.device)
-        if need > 0.5 * free:
+        if need > 0.8 * free:
             return
         idx = []
+        torch.cuda.synchronize(self.device)
+        t0 = time.perf_counter()
         for b in range(csr.rows // B):
             bi = build_batch_index(csr, b * B, (b + 1) * B)
             if bi.n_cols > self.st.dim * 2 // 3 or bi.n_cols > self.st.n_max:
                 return  # near-dense gradients take the dense kind: keep the scatter path
             idx.append(bi)
+        torch.cuda.synchronize(self.device)
+        self.index_build_s, self.index_bytes = time.perf_counter() - t0, sum(bi.nbytes() for bi in idx)
         self.tindex = idx
         self.coef = torch.zeros(B, dtype=torch.float32, device=self.device)
 
@@ -187,11 +195,7 @@ class GpuEngine:
             lo, hi = segs[i] if i < len(segs) else (0, 0)
             a.seg_lo[i], a.seg_cnt[i] = lo, hi - lo
         a.inv_batch = 1.0 / max(1, rows)
-        bi = None
-        if self.tindex is not None and csr is self.csr and len(segs) == 1:
-            lo, hi = segs[0]
-            if hi - lo == self.batch_rows and lo % self.batch_rows == 0:
-                bi = self.tindex[lo // self.batch_rows]
+        bi = self._index_of(csr, segs)
         if bi is not None:
             a.t_colptr, a.t_rowidx, a.t_vals, a.t_ucols = L.ptr(bi.colptr), L.ptr(bi.rowidx), L.ptr(bi.svals), L.ptr(bi.ucols)
             a.t_bins, a.t_long_col, a.t_long_e0, a.t_long_e1 = (L.ptr(bi.bins), L.ptr(bi.long_col), L.ptr(bi.long_e0),
@@ -278,11 +282,29 @@ class GpuEngine:
             m.optimizer.advance()
             return _BatchHandle(rows, self.batch_index), None, None
         st.partials.copy_(self.partials_template)
-        glm_grad(csr, segs, m.weights, st, m.loss.loss_id, rows, self.conf.hot_columns, self.conf.step_timeout_s)
-        compact_gradient(st, m.weights, lam)
+        bi = self._index_of(csr, segs)
+        if bi is not None:
+            # prepared batch: coefficients per row, then one gather-sum per distinct column; the keys are the index's
+            from .ops.transposed import glm_grad_transposed
+            glm_grad_transposed(csr, bi, m.weights, self.coef, st.vals, st.partials, st.status, m.loss.loss_id, lam,
+                                self.conf.step_timeout_s)
+            st.keys[:bi.n_cols].copy_(bi.ucols)
+            st.meta.copy_(bi.meta)
+        else:
+            glm_grad(csr, segs, m.weights, st, m.loss.loss_id, rows, self.conf.hot_columns, self.conf.step_timeout_s)
+            compact_gradient(st, m.weights, lam)
         m.optimizer.advance()
         h = _BatchHandle(rows, self.batch_index)
         return h, None, None
+
+    def _index_of(self, csr, segs):
+        """The prepared column index of the batch `segs` of the resident shard, if there is one."""
+        if getattr(self, "tindex", None) is None or csr is not self.csr or len(segs) != 1:
+            return None
+        lo, hi = segs[0]
+        if hi - lo != self.batch_rows or lo % self.batch_rows:
+            return None
+        return self.tindex[lo // self.batch_rows]
 
     def _fast_ok(self) -> bool:
         return (self.mode == "sketch" and getattr(self, "depth", 0) == 0 and bool(self.conf.extras.get("single_call_step", True)) and
@@ -471,19 +493,21 @@ class GpuEngine:
     def stage_times_us(self):
         """Durations of the stages of this rank's last fused compress and decode launches, from the
         `globaltimer` stamps the kernels leave in their workspaces (synchronises). Compress:
-        summary, split query, bucketize + statistics, pack + sketch insert, narrow + publish.
+        summary, split query, bucketize + count, scatter + sketch insert, key code, narrow + publish.
         Decode: prepare (including the wait for the peers' payloads), accumulate, claims."""
         if self.mode != "sketch":
             return None
         import numpy as np
         last = (self.t.step - 1) & 1  # the decode kernel keeps the stamps of even and odd steps apart
-        c = self.comp.workspace[:256].cpu().numpy().view(np.int64)[8:14]
+        c = self.comp.workspace[:256].cpu().numpy().view(np.int64)[8:15]
+        if int(self.st.meta[1]) != 1 or not all(0 <= int(c[i + 1] - c[i]) < 10**9 for i in range(6)):
+            return None   # dense-kind or empty step: the sparse compress kernel left no stamps
         dall = self.dec.workspace[:256].cpu().numpy().view(np.int64)
         d, dprev = dall[8 + 4 * last:12 + 4 * last], dall[8 + 4 * (1 - last):12 + 4 * (1 - last)]
-        return {"compress": [float(c[i + 1] - c[i]) / 1e3 for i in range(5)],
+        return {"compress": [float(c[i + 1] - c[i]) / 1e3 for i in range(6)],
                 "decode": [float(d[i + 1] - d[i]) / 1e3 for i in range(3)],
                 # idle time between the end of the compress kernel's last stage and the start of the decode kernel
-                "compress_to_decode_gap": float(d[0] - c[5]) / 1e3,
+                "compress_to_decode_gap": float(d[0] - c[6]) / 1e3,
                 # from the end of the previous step's decode kernel to the start of this step's compress kernel:
                 # the gradient kernels and the launch gaps around them
                 "prev_decode_to_compress": float(c[0] - dprev[3]) / 1e3 if dprev[3] else None,

@@ -64,8 +64,8 @@ class GpuCompressor:
                                                            group_num, row_num, self.col_ratio))
 
     def reset(self) -> None:
-        """Clears barrier words and counters (needed only after a kernel reported an error)."""
-        self.workspace[:256].zero_()
+        """Clears barrier words, counters and publication marks (needed only after a kernel reported an error)."""
+        self.workspace.zero_()
 
     def _args(self, keys, vals, meta, step, rank, world, payload_ptr, slot_capacity, peer_payload, peer_flag,
               status, loss_partials, given) -> L.CompressArgs:
@@ -100,7 +100,7 @@ class GpuCompressor:
         a = self._args(keys, vals, meta, step, rank, world, payload_ptr, slot_capacity, peer_payload, peer_flag,
                        status, loss_partials, given)
         L.check(self.lib.skml_compress_sparse(C.byref(a), L.stream()), "skml_compress_sparse")
-        L.count_launches(1 if self.fused else 5)
+        L.count_launches(1 if self.fused else 7)
         if dense_vals is not None:
             a.vals = L.ptr(dense_vals)
             L.check(self.lib.skml_compress_dense(C.byref(a), L.stream()), "skml_compress_dense")

@@ -19,7 +19,7 @@ def main():
     rank = int(os.environ["RANK"])
     kw = dict(algo="lr", format="synthetic", feature_num=300000, syn_rows=200000, syn_nnz_per_row=30, epoch_num=2,
               learn_rate=0.5, l2_reg=1e-4, valid_ratio=0.1, batch_sample_ratio=0.1, device="cuda", seed=5,
-              quant_bin_num=256, sketch_row_num=3, sketch_col_ratio=0.2, step_timeout_s=1.0,
+              quant_bin_num=256, sketch_group_num=16, sketch_row_num=3, sketch_col_ratio=0.5, step_timeout_s=1.0,
               extras={"heartbeat_timeout_s": 10.0, "check_status_every_step": scenario == "skip"})
     inj = None
     if scenario == "none":
@@ -30,6 +30,8 @@ def main():
         kw.update(optimizer="adam", learn_rate=0.01)
     elif scenario == "fixedpoint":
         kw.update(compressor="FixedPoint", fixed_point_bit_num=8)
+    elif scenario == "zip":
+        kw.update(compressor="Zip")
     elif scenario == "skip" and rank == 1:
         inj = FaultInjector(skip_publish_steps={3})
     res = {"rank": rank, "scenario": scenario}
