@@ -38,6 +38,8 @@
 #define MAX_LEVELS 24
 #define FP_SHIFT 20         // fixed-point fraction bits of sample weights
 #define MAX_SAMPLE 16        // largest sampling factor of the bottom-level sampler
+#define AP_STAGE_F 548       // staging words of one chunk's flag bits (<= 17 bits per key, plus a word of misalignment)
+#define AP_STAGE_D 1028      // the same for its delta bits (<= 32 bits per key)
 
 struct CP {
     const int* keys;
@@ -62,7 +64,12 @@ struct CP {
     unsigned int* blk_cnt;           // [grid][SKML_MAX_GROUPS]: the same per block
     unsigned long long* blk_bytes;   // [grid][SKML_MAX_GROUPS]: delta bytes of the chunks every block owns, per group
     unsigned int* blk_flag;          // [grid]: epoch in which blk_bytes was published
-    unsigned int* chunk_off;         // [chunks]: delta-byte offset of a chunk inside its owner's part of the group
+    unsigned int* chunk_off;         // [2 * chunks]: delta-byte offset of a chunk inside its owner's part of the group
+                                     // (delta_adaptive: flag-bit and delta-bit offsets)
+    unsigned long long* blk_bits;    // delta_adaptive: [grid][2 * SKML_MAX_GROUPS] flag bits / delta bits per block and group
+    unsigned int* blk_done;          // delta_adaptive: [grid] epoch in which the block finished writing its chunks
+    unsigned int* key_hist;          // delta_adaptive: [SKML_MAX_GROUPS][32] keys per delta width, zeroed in S1
+    int key_encoder;
     unsigned short* bins;
     int* gkeys;                      // keys, grouped: group g's list starts at Layout::goff[g]
     unsigned int* tables;
@@ -86,7 +93,10 @@ struct Layout {
     unsigned int goff[SKML_MAX_GROUPS];            // start of the group's staging list (a multiple of 4 entries)
     unsigned int chunk_prefix[SKML_MAX_GROUPS + 1]; // chunks of the groups before, group-major chunk numbering
     unsigned int base_rank[SKML_MAX_GROUPS];       // keys of the group in the blocks before this one
-    unsigned long long bytes_g[SKML_MAX_GROUPS];   // delta bytes of the group (known to every block from S6 on)
+    unsigned long long bytes_g[SKML_MAX_GROUPS];   // delta bytes of the group (block 0, for the header)
+    unsigned long long flag_bits[SKML_MAX_GROUPS], delta_bits[SKML_MAX_GROUPS];  // delta_adaptive: stream lengths
+    unsigned int num_iv[SKML_MAX_GROUPS], flag_kind[SKML_MAX_GROUPS];            // delta_adaptive: the groups' modes
+    unsigned long long off_keys;                   // delta_adaptive: start of the per-group [flags | deltas] sections
     unsigned long long table_off[SKML_MAX_GROUPS], flag_off[SKML_MAX_GROUPS], delta_off[SKML_MAX_GROUPS],
         restart_off[SKML_MAX_GROUPS], tab32_off[SKML_MAX_GROUPS];
     unsigned char hash_ids[SKML_MAX_GROUPS][8];
@@ -98,7 +108,7 @@ struct Layout {
 };
 
 struct WsLayout {
-    long long ctrl, run_vals, run_cnt, run_w, splits_raw, warp_cnt, blk_cnt, blk_bytes, blk_flag, chunk_off, bins, gkeys, tables,
+    long long ctrl, run_vals, run_cnt, run_w, splits_raw, warp_cnt, blk_cnt, blk_bytes, blk_flag, chunk_off, blk_bits, blk_done, key_hist, bins, gkeys, tables,
         total;
     long long tables_cap;
 };
@@ -117,7 +127,10 @@ static WsLayout ws_layout(long long n_max, long long q, long long G, long long r
     L.blk_cnt = o; o += al256(grid * SKML_MAX_GROUPS * 4);
     L.blk_bytes = o; o += al256(grid * SKML_MAX_GROUPS * 8);
     L.blk_flag = o; o += al256(grid * 4);
-    L.chunk_off = o; o += al256((n_max / SKML_RESTART_INTERVAL + SKML_MAX_GROUPS + 8) * 4);
+    L.chunk_off = o; o += al256((n_max / SKML_RESTART_INTERVAL + SKML_MAX_GROUPS + 8) * 8);
+    L.blk_bits = o; o += al256(grid * 2 * SKML_MAX_GROUPS * 8);
+    L.blk_done = o; o += al256(grid * 4);
+    L.key_hist = o; o += al256(SKML_MAX_GROUPS * 32 * 4);
     L.bins = o; o += al256(n_max * 2);
     L.gkeys = o; o += al256((n_max + 4 * SKML_MAX_GROUPS + 8) * 4);
     L.tables_cap = rows * ((long long)(col_ratio * (double)n_max) + 2 + G) + 64;
@@ -133,11 +146,11 @@ extern "C" long long skml_compress_workspace_bytes(long long n_max, long long bi
 }
 
 // Upper bound of the payload size for n_max non-zeros (sparse kind) or dim codes (dense kind).
-extern "C" long long skml_payload_capacity(long long n_max, long long dim, long long bin_num, long long group_num,
-                                           long long row_num, double col_ratio) {
+static __host__ __device__ inline long long payload_bound(long long n_max, long long dim, long long bin_num, long long group_num,
+                                                          long long row_num, double col_ratio) {
     long long G = group_num, R = SKML_RESTART_INTERVAL;
-    long long head = SKML_HEADER_BYTES + skml_align16(4 * bin_num) + SKML_GROUP_ENTRY_BYTES * G;
-    long long flags = n_max / 4 + 24 * G + 16;
+    long long head = SKML_HEADER_BYTES + (long long)skml_align16(4 * bin_num) + SKML_GROUP_ENTRY_BYTES * G;
+    long long flags = 17 * n_max / 8 + 24 * G + 16;   // delta_adaptive with unary flags: up to 17 flag bits per key
     long long restart = 16 * (n_max / R + G) + 16 * G;
     long long tables = 2 * row_num * ((long long)(col_ratio * (double)n_max) + 2) + 32 * G;
     long long deltas = 4 * n_max + 24 * G;
@@ -145,6 +158,11 @@ extern "C" long long skml_payload_capacity(long long n_max, long long dim, long 
     long long dense = head + 2 * dim + 64;
     long long cap = sparse > dense ? sparse : dense;
     return (cap + 255) & ~255ll;
+}
+
+extern "C" long long skml_payload_capacity(long long n_max, long long dim, long long bin_num, long long group_num,
+                                           long long row_num, double col_ratio) {
+    return payload_bound(n_max, dim, bin_num, group_num, row_num, col_ratio);
 }
 
 // ---------------------------------------------------------------------------
@@ -171,6 +189,9 @@ struct Smem {
     unsigned int wbase[SKML_WARPS][SKML_MAX_GROUPS];
     unsigned long long my_bytes[SKML_MAX_GROUPS];   // delta bytes of the chunks this block owns, per group
     unsigned long long pre_bytes[SKML_MAX_GROUPS];  // the same, summed over the blocks before this one
+    unsigned long long my_bits[2 * SKML_MAX_GROUPS], pre_bits[2 * SKML_MAX_GROUPS];  // delta_adaptive: flag / delta bits
+    unsigned int stage_f[4][AP_STAGE_F];            // delta_adaptive: one chunk's flag / delta bits per sub-block
+    unsigned int stage_d[4][AP_STAGE_D];
     unsigned int sub_part[4][8];                    // scan scratch of the four 256-thread sub-blocks
     unsigned int sub_total[4];
     unsigned long long unit_prefix[SKML_MAX_GROUPS + 1];
@@ -684,11 +705,12 @@ __device__ void layout_from_counts(const CP& p, Smem& s) {
         L.off_bv = SKML_HEADER_BYTES;
         L.off_gt = L.off_bv + skml_align16(4ull * p.q);
         L.off_flags = L.off_gt + (unsigned long long)SKML_GROUP_ENTRY_BYTES * G;
+        const bool adaptive = p.key_encoder == SKML_KEYS_DELTA_ADAPTIVE;
         unsigned long long o = L.off_flags;
         unsigned int go = 0, ch = 0;
         for (int g = 0; g < G; ++g) {
             L.flag_off[g] = o;
-            if (L.n_g[g]) o += skml_align16(8ull * ((2ull * L.n_g[g] + 63) / 64));
+            if (L.n_g[g] && !adaptive) o += skml_align16(8ull * ((2ull * L.n_g[g] + 63) / 64));
             L.goff[g] = go;
             go += (L.n_g[g] + 3u) & ~3u;
             L.chunk_prefix[g] = ch;
@@ -710,9 +732,12 @@ __device__ void layout_from_counts(const CP& p, Smem& s) {
             t32 += (unsigned long long)p.rows * col;
         }
         L.off_deltas = o;
-        // the key code adds at most four bytes per key: refuse now what cannot fit in the worst case
+        L.off_keys = o;  // delta_adaptive: both key sections of every group follow the tables
+        // the key code adds at most four bytes per key (delta_adaptive: 49 bits): refuse now what cannot
+        // fit in the worst case
         unsigned long long worst = o;
-        for (int g = 0; g < G; ++g) worst += skml_align16(4ull * L.n_g[g] + 8);
+        for (int g = 0; g < G; ++g)
+            worst += skml_align16(4ull * L.n_g[g] + 8) + (adaptive ? skml_align16(17ull * L.n_g[g] / 8 + 8) : 0ull);
         L.overflow = (worst > (unsigned long long)p.slot_capacity) || (t32 + 4 > (unsigned long long)p.tables_cap);
         if (L.overflow) skml_set_status(p.status, SKML_CAPACITY, 0x30u);
     }
@@ -993,6 +1018,331 @@ __device__ void pack_write(const CP& p, Smem& s, unsigned int my_begin, unsigned
     __syncthreads();
 }
 
+// ---------------------------------------------------------------------------
+// S5, DeltaAdaptive key code (the reference's live encoder, binary/DeltaAdaptiveEncoder.java:23-112).
+// Flags and deltas are bit streams: per group, every delta takes b * iv bits (b = 32 / m bits per
+// interval, iv = intervals needed) and a flag of log2(m) bits holding iv - 1, or iv one-bits and a
+// zero-bit ("unary" flags); m and the flag kind minimise the estimated bits per key over the group's
+// histogram of delta widths. Chunk starts are therefore bit positions, adjacent chunks share stream
+// words, and the sections' sizes depend on the data: the two sections of a group follow each other
+// at the end of the payload, and the (pre-zeroed) shared words are completed with atomic ORs.
+// ---------------------------------------------------------------------------
+__device__ void push_bytes(const CP& p, unsigned long long lo, unsigned long long hi);
+
+__device__ __forceinline__ int da_bits_needed(unsigned int d) { return d == 0u ? 1 : 32 - __clz(d); }
+
+// The reference's mode search in the same double arithmetic, operation by operation (explicit
+// round-to-nearest intrinsics keep the compiler from fusing multiply-adds); hist[k] = keys needing k bits.
+__device__ void da_choose(const unsigned int* hist, unsigned int n, unsigned int& num, unsigned int& kind) {
+    double prob[32];
+    const double dn = (double)(n > 0 ? n : 1);
+    for (int k = 0; k < 32; ++k) prob[k] = __ddiv_rn((double)hist[k], dn);
+    double best = 32.0;
+    num = 1;
+    kind = 0;
+    for (int m = 2, lg = 1; m <= 16; m *= 2, ++lg) {
+        const int b = 32 / m;
+        double sum = 0.0;
+        for (int i = 0; i < m; ++i) {
+            double ip = 0.0;
+            for (int j = 0; j < b; ++j) ip = __dadd_rn(ip, prob[i * b + j]);
+            sum = __dadd_rn(sum, __dmul_rn((double)(i + 1), ip));
+        }
+        const double t1 = __dadd_rn(__dmul_rn(sum, (double)b), (double)lg);
+        if (t1 < best) {
+            best = t1;
+            num = (unsigned int)m;
+            kind = 0;
+        }
+        const double t2 = __dadd_rn(__dmul_rn(sum, (double)(b + 1)), 1.0);
+        if (t2 < best) {
+            best = t2;
+            num = (unsigned int)m;
+            kind = 1;
+        }
+    }
+}
+
+// Pass 0: histogram of the delta widths of this block's chunks, per group, added to the global one.
+__device__ void apack_histogram(const CP& p, Smem& s, unsigned int my_begin, unsigned int my_end) {
+    const Layout& L = s.lay;
+    unsigned int* hist = s.stage_d[0];  // [G][32], the staging area is idle in this pass
+    for (int t = threadIdx.x; t < SKML_MAX_GROUPS * 32; t += blockDim.x) hist[t] = 0;
+    __syncthreads();
+    for (unsigned int c0 = my_begin; c0 < my_end; c0 += 4) {
+        ChunkWork c;
+        load_chunk(p, L, c0 + (threadIdx.x >> 8), my_end, p.G, c);
+        if (c.g >= 0) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (c.w[u]) atomicAdd(&hist[c.g * 32 + (da_bits_needed(c.d[u]) & 31)], 1u);
+        }
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < p.G * 32; t += blockDim.x)
+        if (hist[t]) atomicAdd(&p.key_hist[t], hist[t]);
+}
+
+__device__ __forceinline__ unsigned long long stream_bytes(unsigned long long bits) { return skml_align16(8ull * ((bits + 63) / 64)); }
+
+// Pass 1 prelude (every block): interval count and flag kind of every group from the complete
+// histogram. The histogram also gives the exact lengths of the two bit streams of every group, so the
+// whole layout of the key sections is known here, before a single key is coded.
+__device__ void apack_choose(const CP& p, Smem& s) {
+    Layout& L = s.lay;
+    if (threadIdx.x < p.G) {
+        const int g = threadIdx.x;
+        unsigned int h[32];
+        for (int k = 0; k < 32; ++k) h[k] = __ldcg(&p.key_hist[g * 32 + k]);
+        unsigned int num = 1, kind = 0;
+        da_choose(h, L.n_g[g], num, kind);
+        L.num_iv[g] = num;
+        L.flag_kind[g] = kind;
+        const unsigned int b = 32u / num, fb = 31u - (unsigned int)__clz(num);
+        unsigned long long fbits = 0, dbits = 0;
+        for (unsigned int k = 0; k < 32; ++k) {
+            const unsigned int need = k ? k : 32u;   // bin 0 holds the 32-bit deltas (need & 31)
+            const unsigned long long iv = (need + b - 1) / b;
+            fbits += (unsigned long long)h[k] * (kind ? iv + 1 : fb);
+            dbits += (unsigned long long)h[k] * b * iv;
+        }
+        L.flag_bits[g] = fbits;
+        L.delta_bits[g] = dbits;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long o = L.off_keys;
+        for (int g = 0; g < p.G; ++g) {
+            L.flag_off[g] = o;
+            if (L.n_g[g]) o += stream_bytes(L.flag_bits[g]);
+            L.delta_off[g] = o;
+            if (L.n_g[g]) o += stream_bytes(L.delta_bits[g]);
+        }
+        L.total_bytes = o;
+        if (o > (unsigned long long)p.slot_capacity) {
+            L.overflow = 1;
+            skml_set_status(p.status, SKML_CAPACITY, 0x37u);
+        }
+    }
+    __syncthreads();
+}
+
+struct KeyCode {
+    unsigned int fv, fw, dw;  // flag value / width, delta width (the delta value is the delta itself)
+};
+__device__ __forceinline__ KeyCode da_code(unsigned int d, unsigned int m, unsigned int kind) {
+    const int b = 32 / (int)m, fb = 31 - __clz(m);
+    const int iv = (da_bits_needed(d) + b - 1) / b;
+    KeyCode k;
+    k.fw = kind ? (unsigned int)(iv + 1) : (unsigned int)fb;
+    k.fv = kind ? ((1u << (iv + 1)) - 2u) : (unsigned int)(iv - 1);
+    k.dw = (unsigned int)(b * iv);
+    return k;
+}
+
+// Writes `nb` (<= 32) bits of `value`, most significant first, at bit offset `off` of a zeroed
+// shared-memory word array (stream bit p = bit (p & 31) of word p >> 5, as in java.util.BitSet).
+__device__ __forceinline__ void put_bits_shared(unsigned int* words, unsigned int off, unsigned int value, unsigned int nb) {
+    if (nb == 0) return;
+    const unsigned int rv = __brev(value) >> (32u - nb);
+    const unsigned int sh = off & 31u, w = off >> 5;
+    atomicOr(&words[w], rv << sh);
+    if (sh + nb > 32u) atomicOr(&words[w + 1], rv >> (32u - sh));
+}
+
+// Pass 1: flag and delta bits of this block's chunks -> chunk bit offsets inside the block's part of
+// each group, the block's bit totals per group (published for the blocks after it).
+__device__ void apack_measure(const CP& p, Smem& s, unsigned int my_begin, unsigned int my_end) {
+    const Layout& L = s.lay;
+    if (threadIdx.x < 2 * SKML_MAX_GROUPS) s.my_bits[threadIdx.x] = 0;
+    __syncthreads();
+    for (unsigned int c0 = my_begin; c0 < my_end; c0 += 4) {
+        ChunkWork c;
+        load_chunk(p, L, c0 + (threadIdx.x >> 8), my_end, p.G, c);
+        unsigned int packed = 0;  // flag bits (<= 17408 per chunk) in the low half, delta bits (<= 32768) above
+        if (c.g >= 0) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (c.w[u]) {
+                    const KeyCode k = da_code(c.d[u], L.num_iv[c.g], L.flag_kind[c.g]);
+                    packed += k.fw + (k.dw << 16);
+                }
+        }
+        unsigned int total;
+        sub_scan(s, packed, total);
+        if ((threadIdx.x & 255) == 0) s.sub_total[threadIdx.x >> 8] = total;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int q = 0; q < 4 && c0 + q < my_end; ++q) {
+                int g = 0;
+                while (g + 1 < p.G && c0 + q >= L.chunk_prefix[g + 1]) ++g;
+                p.chunk_off[2 * (c0 + q)] = (unsigned int)s.my_bits[2 * g];
+                p.chunk_off[2 * (c0 + q) + 1] = (unsigned int)s.my_bits[2 * g + 1];
+                s.my_bits[2 * g] += s.sub_total[q] & 0xFFFFu;
+                s.my_bits[2 * g + 1] += s.sub_total[q] >> 16;
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x < 2 * SKML_MAX_GROUPS) p.blk_bits[(long long)blockIdx.x * 2 * SKML_MAX_GROUPS + threadIdx.x] = s.my_bits[threadIdx.x];
+}
+
+// Bit totals of the blocks before this one -> this block's starting bit offsets inside the streams.
+__device__ void apack_prefix(const CP& p, Smem& s, bool wait, unsigned int epoch) {
+    if (threadIdx.x < 2 * SKML_MAX_GROUPS) s.pre_bits[threadIdx.x] = 0;
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < blockIdx.x) {
+        const unsigned int b = threadIdx.x;
+        bool ok = true;
+        if (wait) {
+            const long long t0 = clock64();
+            unsigned int ns = 20;
+            while (ld_acquire_gpu(&p.blk_flag[b]) != epoch) {
+                if (clock64() - t0 > p.budget) {
+                    skml_set_status(p.status, SKML_TIMEOUT_BARRIER, 0x52u);
+                    ok = false;
+                    break;
+                }
+                __nanosleep(ns);
+                if (ns < 400) ns *= 2;
+            }
+        }
+        if (ok) {
+            for (int g = 0; g < 2 * p.G; ++g) {
+                const unsigned long long v = __ldcg(&p.blk_bits[(long long)b * 2 * SKML_MAX_GROUPS + g]);
+                if (v) atomicAdd(&s.pre_bits[g], v);
+            }
+        } else {
+            s_ok = 0;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && !s_ok) s.lay.overflow = 1;
+    __syncthreads();
+}
+
+// One stream segment staged in shared memory -> the payload: whole words are stored, the first and
+// the last word may be shared with the neighbouring chunks and are completed with atomic ORs.
+__device__ __forceinline__ void flush_stream(unsigned int* dst_words, const unsigned int* stage, unsigned long long start_bit,
+                                             unsigned int nbits) {
+    if (nbits == 0) return;
+    const unsigned int sh = (unsigned int)(start_bit & 31ull);
+    const unsigned int nw = (sh + nbits + 31u) >> 5;
+    unsigned int* dst = dst_words + (start_bit >> 5);
+    for (unsigned int w = threadIdx.x & 255; w < nw; w += 256) {
+        const unsigned int v = stage[w];
+        const bool shared_word = (w == 0 && sh != 0) || (w == nw - 1 && ((sh + nbits) & 31u) != 0);
+        if (shared_word) {
+            if (v) atomicOr(dst + w, v);
+        } else {
+            dst[w] = v;
+        }
+    }
+}
+
+// Pass 2: the bit streams and restart points of this block's chunks.
+__device__ void apack_write(const CP& p, Smem& s, unsigned int my_begin, unsigned int my_end) {
+    const Layout& L = s.lay;
+    if (L.overflow) return;
+    const int t = threadIdx.x & 255, sb = threadIdx.x >> 8;
+    for (unsigned int c0 = my_begin; c0 < my_end; c0 += 4) {
+        ChunkWork c;
+        const unsigned int ch = c0 + sb;
+        load_chunk(p, L, ch, my_end, p.G, c);
+        KeyCode kc[4];
+        unsigned int packed = 0;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            kc[u].fv = kc[u].fw = kc[u].dw = 0;
+            if (c.g >= 0 && c.w[u]) {
+                kc[u] = da_code(c.d[u], L.num_iv[c.g], L.flag_kind[c.g]);
+                packed += kc[u].fw + (kc[u].dw << 16);
+            }
+        }
+        for (int i = t; i < AP_STAGE_F; i += 256) s.stage_f[sb][i] = 0;
+        for (int i = t; i < AP_STAGE_D; i += 256) s.stage_d[sb][i] = 0;
+        unsigned int total;
+        const unsigned int ex = sub_scan(s, packed, total);  // (its barriers also publish the cleared staging words)
+        unsigned long long fs = 0, ds = 0;
+        if (c.g >= 0) {
+            fs = s.pre_bits[2 * c.g] + __ldcg(&p.chunk_off[2 * ch]);
+            ds = s.pre_bits[2 * c.g + 1] + __ldcg(&p.chunk_off[2 * ch + 1]);
+            unsigned int fo = (unsigned int)(fs & 31ull) + (ex & 0xFFFFu), dof = (unsigned int)(ds & 31ull) + (ex >> 16);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                put_bits_shared(s.stage_f[sb], fo, kc[u].fv, kc[u].fw);
+                put_bits_shared(s.stage_d[sb], dof, c.d[u], kc[u].dw);
+                fo += kc[u].fw;
+                dof += kc[u].dw;
+            }
+        }
+        __syncthreads();
+        if (c.g >= 0) {
+            flush_stream(reinterpret_cast<unsigned int*>(p.payload + L.flag_off[c.g]), s.stage_f[sb], fs, total & 0xFFFFu);
+            flush_stream(reinterpret_cast<unsigned int*>(p.payload + L.delta_off[c.g]), s.stage_d[sb], ds, total >> 16);
+            if (t == 0) {
+                SkmlRestart r;
+                r.prev_key = (unsigned int)c.prev0;
+                r.flag_bit_off = (unsigned int)fs;
+                r.delta_bit_off = ds;
+                *reinterpret_cast<SkmlRestart*>(p.payload + L.restart_off[c.g] + (unsigned long long)c.j * sizeof(SkmlRestart)) = r;
+            }
+        }
+        __syncthreads();  // the staging words are cleared again by the next round
+    }
+}
+
+// The restart points and the 16-byte units of the two bit streams that hold bits of this block only
+// -> the peers' slots. Units that hold a block border are sent by block 0 once every block is done.
+__device__ void apush_own_chunks(const CP& p, Smem& s, unsigned int my_begin, unsigned int my_end) {
+    const Layout& L = s.lay;
+    if (p.world <= 1 || L.overflow || my_begin >= my_end) return;
+    __syncthreads();
+    for (int g = 0; g < p.G; ++g) {
+        const unsigned int c0 = max(my_begin, L.chunk_prefix[g]), c1 = min(my_end, L.chunk_prefix[g + 1]);
+        if (c0 >= c1) continue;
+        const bool last = c1 == L.chunk_prefix[g + 1];
+        push_bytes(p, L.restart_off[g] + 16ull * (c0 - L.chunk_prefix[g]), L.restart_off[g] + 16ull * (c1 - L.chunk_prefix[g]));
+        for (int k = 0; k < 2; ++k) {
+            const unsigned long long a = s.pre_bits[2 * g + k], b = a + s.my_bits[2 * g + k];
+            const unsigned long long lo = 16ull * ((a + 127) / 128), hi = last ? stream_bytes(k ? L.delta_bits[g] : L.flag_bits[g]) : 16ull * (b / 128);
+            const unsigned long long base = k ? L.delta_off[g] : L.flag_off[g];
+            if (hi > lo) push_bytes(p, base + lo, base + hi);
+        }
+    }
+}
+
+// Block 0, after every block has written its chunks: the stream units that hold a block border.
+__device__ void apush_borders(const CP& p, Smem& s) {
+    const Layout& L = s.lay;
+    if (p.world <= 1 || L.overflow) return;
+    const unsigned int total = L.chunk_prefix[p.G];
+    unsigned int per = (total + gridDim.x - 1) / gridDim.x;
+    per = (per + 3u) & ~3u;
+    const unsigned int b = threadIdx.x;
+    if (b >= 1 && b < gridDim.x && (unsigned long long)per * b < total) {
+        const unsigned int cs = per * b;
+        int g = 0;
+        while (g + 1 < p.G && cs >= L.chunk_prefix[g + 1]) ++g;
+        if (cs != L.chunk_prefix[g]) {  // the run of block b starts inside group g
+            unsigned long long a[2] = {0, 0};
+            for (unsigned int q = 0; q < b; ++q) {
+                a[0] += __ldcg(&p.blk_bits[(long long)q * 2 * SKML_MAX_GROUPS + 2 * g]);
+                a[1] += __ldcg(&p.blk_bits[(long long)q * 2 * SKML_MAX_GROUPS + 2 * g + 1]);
+            }
+            for (int k = 0; k < 2; ++k) {
+                if ((a[k] & 127ull) == 0) continue;
+                const unsigned long long off = (k ? L.delta_off[g] : L.flag_off[g]) + 16ull * (a[k] / 128);
+                const uint4 v = ld_cg_v4(reinterpret_cast<const uint4*>(p.payload + off));
+                for (unsigned int r = 0; r < p.world; ++r)
+                    if (r != p.rank && p.peer_payload[r]) st_v4(reinterpret_cast<uint4*>(p.peer_payload[r] + off), v);
+            }
+        }
+    }
+}
+
 __device__ __forceinline__ void chunk_run(const Layout& L, int G, unsigned int& my_begin, unsigned int& my_end) {
     const unsigned int total = L.chunk_prefix[G];
     unsigned int per = (total + gridDim.x - 1) / gridDim.x;
@@ -1036,6 +1386,15 @@ __device__ void stage_prepare(const CP& p, long long n) {
     uint4 ones = make_uint4(~0u, ~0u, ~0u, ~0u);
     uint4* t4 = reinterpret_cast<uint4*>(p.tables);
     for (long long i = gid; i < (cells + 3) / 4; i += gsz) t4[i] = ones;
+    if (p.key_encoder == SKML_KEYS_DELTA_ADAPTIVE) {
+        // the bit streams are completed with atomic ORs where chunks meet: they start from zero
+        long long bound = payload_bound(n, 0, p.q, p.G, p.rows, p.col_ratio);
+        if (bound > p.slot_capacity) bound = p.slot_capacity;
+        uint4 z = make_uint4(0, 0, 0, 0);
+        uint4* z4 = reinterpret_cast<uint4*>(p.payload);
+        for (long long i = gid + SKML_HEADER_BYTES / 16; i < bound / 16; i += gsz) z4[i] = z;
+        for (long long i = gid; i < SKML_MAX_GROUPS * 32; i += gsz) p.key_hist[i] = 0;
+    }
 }
 
 // Header, bucket values and group table (block 0), stored locally and into every peer's slot.
@@ -1063,6 +1422,12 @@ __device__ void write_header(const CP& p, Smem& s, long long n, int kind) {
             e.delta_off = L.n_g[g] ? L.delta_off[g] : 0;
             e.n_delta_words = (unsigned int)((L.bytes_g[g] + 7) / 8);
             e.flag_kind = 0;
+            if (p.key_encoder == SKML_KEYS_DELTA_ADAPTIVE) {
+                e.n_flag_words = (unsigned int)((L.flag_bits[g] + 63) / 64);
+                e.n_delta_words = (unsigned int)((L.delta_bits[g] + 63) / 64);
+                e.num_intervals = L.n_g[g] ? L.num_iv[g] : 0;
+                e.flag_kind = L.n_g[g] ? L.flag_kind[g] : 0;
+            }
             e.restart_off = L.n_g[g] ? L.restart_off[g] : 0;
             *reinterpret_cast<SkmlGroupEntry*>(p.payload + L.off_gt + (unsigned long long)g * sizeof(SkmlGroupEntry)) = e;
         }
@@ -1096,7 +1461,7 @@ __device__ void write_header(const CP& p, Smem& s, long long n, int kind) {
             h.group_num = (unsigned int)p.G;
             h.row_num = (unsigned int)p.rows;
             h.col_ratio = p.col_ratio;
-            h.key_encoder = SKML_KEYS_DELTA_BINARY;
+            h.key_encoder = (unsigned int)p.key_encoder;
             h.restart_interval = SKML_RESTART_INTERVAL;
             h.off_group_table = L.off_gt;
             h.off_key_flags = L.off_flags;
@@ -1247,14 +1612,14 @@ __device__ void push_own_chunks(const CP& p, Smem& s, unsigned int my_begin, uns
 }
 
 // Block 0 needs every block's byte counts for the header: bounded wait for their publications.
-__device__ bool wait_all_published(const CP& p, unsigned int epoch) {
+__device__ bool wait_all_published(const CP& p, const unsigned int* flags, unsigned int epoch) {
     __shared__ int s_ok;
     if (threadIdx.x == 0) s_ok = 1;
     __syncthreads();
     if (threadIdx.x < gridDim.x) {
         const long long t0 = clock64();
         unsigned int ns = 20;
-        while (ld_acquire_gpu(&p.blk_flag[threadIdx.x]) != epoch) {
+        while (ld_acquire_gpu(&flags[threadIdx.x]) != epoch) {
             if (clock64() - t0 > p.budget) {
                 skml_set_status(p.status, SKML_TIMEOUT_BARRIER, 0x51u);
                 s_ok = 0;
@@ -1290,7 +1655,7 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_sparse_kernel(CP p, in
         n = 0;
     }
     if (n <= 0) {  // empty gradient: header-only payload
-        if (FUSED || stage == 7) {
+        if (FUSED || stage == 8) {
             if (threadIdx.x == 0) {
                 s.lay.overflow = 0;
                 s.qi.bin_num = 0;
@@ -1327,11 +1692,12 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_sparse_kernel(CP p, in
         stage_scatter(p, s, n);
     }
     STAGE_BARRIER(4)
-    // S5: key code and publication, with no grid barrier inside. In one cooperative launch a block waits
-    // only for the byte counts of the blocks before it (they are resident, and never wait for a later
-    // block), and block 0 for all of them before it writes the header; staged launches split the stage at
-    // those two points.
+    // S5: key code and publication. In one cooperative launch a block waits only for the counts of the
+    // blocks before it (they are resident, and never wait for a later block), and block 0 for all of them
+    // before it writes the header; staged launches split the stage at those points. The delta_adaptive
+    // code needs the groups' complete histograms of delta widths first: one more grid barrier.
     unsigned int my_begin = 0, my_end = 0;
+    const bool adaptive = p.key_encoder == SKML_KEYS_DELTA_ADAPTIVE;
     if (FUSED || stage >= 5) {
         if (!FUSED) {
             load_quantizer(p, s);
@@ -1341,7 +1707,18 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_sparse_kernel(CP p, in
     }
     if (FUSED || stage == 5) {
         narrow_tables(p, s);   // the tables are complete since S4
-        pack_measure(p, s, my_begin, my_end);
+        if (adaptive && !s.lay.overflow) apack_histogram(p, s, my_begin, my_end);
+    }
+    if (FUSED && adaptive) {
+        if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, 0x15u)) return;
+    }
+    if (FUSED || stage == 6) {
+        if (adaptive) {
+            apack_choose(p, s);
+            apack_measure(p, s, my_begin, my_end);
+        } else {
+            pack_measure(p, s, my_begin, my_end);
+        }
     }
     unsigned int epoch = 0;
     if (FUSED) {
@@ -1351,20 +1728,38 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_sparse_kernel(CP p, in
         __syncthreads();
         if (threadIdx.x == 0) st_release_gpu(&p.blk_flag[blockIdx.x], epoch);
     }
-    if (FUSED || stage == 6) {
+    if (FUSED || stage == 7) {
         if (!FUSED) {  // the block's own counts again (shared memory does not survive a launch)
             if (threadIdx.x < SKML_MAX_GROUPS) s.my_bytes[threadIdx.x] = p.blk_bytes[(long long)blockIdx.x * SKML_MAX_GROUPS + threadIdx.x];
+            if (threadIdx.x < 2 * SKML_MAX_GROUPS) s.my_bits[threadIdx.x] = p.blk_bits[(long long)blockIdx.x * 2 * SKML_MAX_GROUPS + threadIdx.x];
             __syncthreads();
+            if (adaptive) apack_choose(p, s);
         }
-        pack_prefix(p, s, FUSED, epoch);
-        pack_write(p, s, my_begin, my_end);
-        push_own_chunks(p, s, my_begin, my_end);
+        if (adaptive) {
+            apack_prefix(p, s, FUSED, epoch);
+            apack_write(p, s, my_begin, my_end);
+            apush_own_chunks(p, s, my_begin, my_end);
+            if (FUSED) {
+                __threadfence();
+                __syncthreads();
+                if (threadIdx.x == 0) st_release_gpu(&p.blk_done[blockIdx.x], epoch);
+            }
+        } else {
+            pack_prefix(p, s, FUSED, epoch);
+            pack_write(p, s, my_begin, my_end);
+            push_own_chunks(p, s, my_begin, my_end);
+        }
         if (FUSED) stage_stamp(p.ctrl, 5);
     }
-    if (FUSED || stage == 7) {
+    if (FUSED || stage == 8) {
         if (blockIdx.x == 0) {
-            if (FUSED && !wait_all_published(p, epoch)) return;
-            layout_finish(p, s);
+            if (FUSED && !wait_all_published(p, adaptive ? p.blk_done : p.blk_flag, epoch)) return;
+            if (adaptive) {
+                if (!FUSED) apack_choose(p, s);
+                apush_borders(p, s);
+            } else {
+                layout_finish(p, s);
+            }
             write_header(p, s, n, SKML_KIND_SPARSE);
         }
         finish_publish(p);
@@ -1443,6 +1838,7 @@ static int fill_params(const SkmlCompressArgs* a, CP& p, int& grid) {
     if (a->row_num < 1 || a->row_num > SKML_MAX_ROWS) return (int)cudaErrorInvalidValue;
     if (a->world < 1 || a->world > SKML_MAX_PEERS || a->rank < 0 || a->rank >= a->world) return (int)cudaErrorInvalidValue;
     if (a->n_max >= (1ll << 31) || a->dim >= (1ll << 31)) return (int)cudaErrorInvalidValue;
+    if (a->key_encoder != SKML_KEYS_DELTA_BINARY && a->key_encoder != SKML_KEYS_DELTA_ADAPTIVE) return (int)cudaErrorInvalidValue;
     grid = a->grid > 0 ? (int)a->grid : device_sms();
     if (grid > MAX_GRID) grid = MAX_GRID;
     WsLayout L = ws_layout(a->n_max, a->bin_num, a->group_num, a->row_num, a->col_ratio, grid);
@@ -1478,6 +1874,10 @@ static int fill_params(const SkmlCompressArgs* a, CP& p, int& grid) {
     p.blk_bytes = reinterpret_cast<unsigned long long*>(ws + L.blk_bytes);
     p.blk_flag = reinterpret_cast<unsigned int*>(ws + L.blk_flag);
     p.chunk_off = reinterpret_cast<unsigned int*>(ws + L.chunk_off);
+    p.blk_bits = reinterpret_cast<unsigned long long*>(ws + L.blk_bits);
+    p.blk_done = reinterpret_cast<unsigned int*>(ws + L.blk_done);
+    p.key_hist = reinterpret_cast<unsigned int*>(ws + L.key_hist);
+    p.key_encoder = (int)a->key_encoder;
     p.gkeys = reinterpret_cast<int*>(ws + L.gkeys);
     p.bins = reinterpret_cast<unsigned short*>(ws + L.bins);
     p.tables = reinterpret_cast<unsigned int*>(ws + L.tables);
@@ -1544,7 +1944,7 @@ extern "C" int skml_compress_sparse(const SkmlCompressArgs* a, void* stream) {
     int rc = fill_params(a, p, grid);
     if (rc) return rc;
     static LaunchCache cache;
-    return launch_stages(compress_sparse_kernel<true>, compress_sparse_kernel<false>, cache, p, grid, a->fused != 0, 7,
+    return launch_stages(compress_sparse_kernel<true>, compress_sparse_kernel<false>, cache, p, grid, a->fused != 0, 8,
                          (cudaStream_t)stream);
 }
 

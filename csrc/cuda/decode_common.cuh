@@ -51,6 +51,7 @@ struct DecItem {  // one (rank, group) key stream
     unsigned long long off_bv;
     unsigned long long col_magic;
     int mixers;               // every row uses one of the three integer mixers (at most three rows)
+    unsigned int enc;         // key encoder of the item's payload (SkmlKeyEncoder)
 };
 
 
@@ -155,7 +156,8 @@ struct ChunkKeys {
 };
 
 __device__ __forceinline__ void decode_chunk(const DP& p, const DecItem& it, unsigned int j, const unsigned char* stab,
-                                             unsigned int* part_a, unsigned int* part_b, ChunkKeys& o) {
+                                             unsigned int* part_a, unsigned int* part_b, unsigned int* part_c,
+                                             unsigned short* s_pos, ChunkKeys& o) {
     const unsigned int first = j * SKML_RESTART_INTERVAL;
     const unsigned int cnt = min((unsigned int)SKML_RESTART_INTERVAL, it.e.n - first);
     const SkmlRestart rs = *reinterpret_cast<const SkmlRestart*>(it.base + it.e.restart_off + 16ull * j);
@@ -163,52 +165,133 @@ __device__ __forceinline__ void decode_chunk(const DP& p, const DecItem& it, uns
     o.i0 = i0;
     o.cnt = cnt;
     o.first = first;
-    unsigned int w[DEC_KPT];
-    unsigned int wsum = 0;
-#pragma unroll
-    for (int u = 0; u < DEC_KPT; ++u) w[u] = 0;
-    if (i0 < cnt) {
-        // the flags of DEC_KPT adjacent keys are 2 * DEC_KPT adjacent bits of one 32-bit word
-        const unsigned long long fb = (unsigned long long)rs.flag_bit_off + 2ull * i0;
-        const unsigned int word = __ldcg(reinterpret_cast<const unsigned int*>(it.base + it.e.flag_off) + (fb >> 5));
-        const unsigned int b = word >> (fb & 31);
-#pragma unroll
-        for (int u = 0; u < DEC_KPT; ++u) {
-            if (i0 + u < cnt) {
-                const unsigned int bb = (b >> (2 * u)) & 3u;
-                unsigned int wu = (((bb & 1u) << 1) | (bb >> 1)) + 1u;  // stream order is most significant bit first
-                if (wu == 3) wu = 4;                                     // flag value 2 is never written
-                w[u] = wu;
-                wsum += wu;
-            }
-        }
-    }
-    const unsigned int boff = dec_scan(wsum, part_a);
     unsigned int d[DEC_KPT];
 #pragma unroll
     for (int u = 0; u < DEC_KPT; ++u) d[u] = 0;
-    if (i0 < cnt) {
-        const unsigned long long byte0 = (rs.delta_bit_off >> 3) + boff;
-        if (byte0 + wsum <= 8ull * it.e.n_delta_words) {
-            // The thread's <= 4 * DEC_KPT delta bytes sit in at most DEC_KPT + 1 aligned words.
-            // Bit-reversing a little-endian word yields its four stream bytes in most-significant-
-            // first order (java.util.BitSet order), so a delta is a funnel shift away.
-            const unsigned int* src = reinterpret_cast<const unsigned int*>(it.base + it.e.delta_off);
-            const unsigned long long w0 = byte0 >> 2, wlim = 2ull * it.e.n_delta_words;
-            unsigned int W[DEC_KPT + 1];
+    if (it.enc == SKML_KEYS_DELTA_BINARY) {
+        unsigned int w[DEC_KPT];
+        unsigned int wsum = 0;
+    #pragma unroll
+        for (int u = 0; u < DEC_KPT; ++u) w[u] = 0;
+        if (i0 < cnt) {
+            // the flags of DEC_KPT adjacent keys are 2 * DEC_KPT adjacent bits of one 32-bit word
+            const unsigned long long fb = (unsigned long long)rs.flag_bit_off + 2ull * i0;
+            const unsigned int word = __ldcg(reinterpret_cast<const unsigned int*>(it.base + it.e.flag_off) + (fb >> 5));
+            const unsigned int b = word >> (fb & 31);
+    #pragma unroll
+            for (int u = 0; u < DEC_KPT; ++u) {
+                if (i0 + u < cnt) {
+                    const unsigned int bb = (b >> (2 * u)) & 3u;
+                    unsigned int wu = (((bb & 1u) << 1) | (bb >> 1)) + 1u;  // stream order is most significant bit first
+                    if (wu == 3) wu = 4;                                     // flag value 2 is never written
+                    w[u] = wu;
+                    wsum += wu;
+                }
+            }
+        }
+        const unsigned int boff = dec_scan(wsum, part_a);
+        if (i0 < cnt) {
+            const unsigned long long byte0 = (rs.delta_bit_off >> 3) + boff;
+            if (byte0 + wsum <= 8ull * it.e.n_delta_words) {
+                // The thread's <= 4 * DEC_KPT delta bytes sit in at most DEC_KPT + 1 aligned words.
+                // Bit-reversing a little-endian word yields its four stream bytes in most-significant-
+                // first order (java.util.BitSet order), so a delta is a funnel shift away.
+                const unsigned int* src = reinterpret_cast<const unsigned int*>(it.base + it.e.delta_off);
+                const unsigned long long w0 = byte0 >> 2, wlim = 2ull * it.e.n_delta_words;
+                unsigned int W[DEC_KPT + 1];
+    #pragma unroll
+                for (int t = 0; t <= DEC_KPT; ++t) W[t] = (w0 + t < wlim) ? __brev(__ldcg(src + w0 + t)) : 0u;
+                unsigned int start = (unsigned int)(byte0 & 3);
+    #pragma unroll
+                for (int u = 0; u < DEC_KPT; ++u) {
+                    const unsigned int wi = start >> 2, sh = 8u * (start & 3u);
+                    unsigned int hi = W[0], lo = W[1];
+    #pragma unroll
+                    for (int t = 1; t < DEC_KPT; ++t)
+                        if (wi == (unsigned int)t) { hi = W[t]; lo = W[t + 1]; }
+                    const unsigned int v = __funnelshift_l(lo, hi, sh);
+                    d[u] = w[u] ? v >> (32u - 8u * w[u]) : 0u;
+                    start += w[u];
+                }
+            }
+        }
+    } else {
+        // delta_adaptive (binary/DeltaAdaptiveEncoder.java:114-146): b = 32 / m bits per interval; the
+        // flag of a key gives its interval count iv, its delta takes b * iv bits, most significant first.
+        const unsigned int m = it.e.num_intervals, b = 32u / m, fbw = 31u - (unsigned int)__clz(m);
+        const unsigned int* fwords = reinterpret_cast<const unsigned int*>(it.base + it.e.flag_off);
+        const unsigned long long fw_lim = 2ull * it.e.n_flag_words;
+        unsigned int iv[DEC_KPT];
 #pragma unroll
-            for (int t = 0; t <= DEC_KPT; ++t) W[t] = (w0 + t < wlim) ? __brev(__ldcg(src + w0 + t)) : 0u;
-            unsigned int start = (unsigned int)(byte0 & 3);
+        for (int u = 0; u < DEC_KPT; ++u) iv[u] = 0;
+        if (!it.e.flag_kind) {
+            // fixed flags: iv - 1 in log2(m) bits per key (none when m = 1)
+            if (i0 < cnt) {
+                unsigned long long win = 0;
+                if (fbw) {
+                    const unsigned long long off = (unsigned long long)rs.flag_bit_off + (unsigned long long)fbw * i0;
+                    const unsigned long long w0 = off >> 5;
+                    const unsigned int lo = w0 < fw_lim ? __ldcg(fwords + w0) : 0u, hi = w0 + 1 < fw_lim ? __ldcg(fwords + w0 + 1) : 0u;
+                    win = ((unsigned long long)lo | ((unsigned long long)hi << 32)) >> (off & 31ull);
+                }
+#pragma unroll
+                for (int u = 0; u < DEC_KPT; ++u)
+                    if (i0 + u < cnt) {
+                        const unsigned int bits = fbw ? (unsigned int)(win >> (fbw * u)) & ((1u << fbw) - 1u) : 0u;
+                        iv[u] = (fbw ? (__brev(bits) >> (32u - fbw)) : 0u) + 1u;
+                    }
+            }
+        } else {
+            // unary flags: iv one-bits and a zero-bit per key. The thread that holds a stretch of the chunk's
+            // flag words ranks its zero bits (block scan of the counts) and notes where the key with that
+            // rank ends; zero bits beyond the chunk's keys (the next chunk, padding) are ignored.
+            const unsigned int sh = rs.flag_bit_off & 31u;
+            const unsigned long long wbase = (unsigned long long)(rs.flag_bit_off >> 5) + 3ull * threadIdx.x;
+            unsigned int zb[3], zsum = 0;
+#pragma unroll
+            for (int k = 0; k < 3; ++k) {
+                const unsigned int word = wbase + k < fw_lim ? __ldcg(fwords + wbase + k) : 0xFFFFFFFFu;
+                zb[k] = ~word;
+                if (threadIdx.x == 0 && k == 0) zb[k] &= ~((1u << sh) - 1u);  // bits of the chunk before
+                zsum += (unsigned int)__popc(zb[k]);
+            }
+            unsigned int r = dec_scan(zsum, part_c);
+#pragma unroll
+            for (int k = 0; k < 3; ++k) {
+                unsigned int z = zb[k];
+                while (z && r < cnt) {
+                    const int bit = __ffs(z) - 1;
+                    z &= z - 1;
+                    s_pos[r++] = (unsigned short)((3u * threadIdx.x + k) * 32u + (unsigned int)bit - sh);
+                }
+                r += (unsigned int)__popc(z);
+            }
+            __syncthreads();
+#pragma unroll
+            for (int u = 0; u < DEC_KPT; ++u)
+                if (i0 + u < cnt) {
+                    const unsigned int e = s_pos[i0 + u], st = (i0 + u) ? (unsigned int)s_pos[i0 + u - 1] + 1u : 0u;
+                    iv[u] = e - st;
+                }
+        }
+        unsigned int bsum = 0;
+#pragma unroll
+        for (int u = 0; u < DEC_KPT; ++u) bsum += b * iv[u];
+        const unsigned int bitoff = dec_scan(bsum, part_a);
+        if (i0 < cnt) {
+            const unsigned int* dwords = reinterpret_cast<const unsigned int*>(it.base + it.e.delta_off);
+            const unsigned long long dw_lim = 2ull * it.e.n_delta_words;
+            unsigned long long off = rs.delta_bit_off + bitoff;
 #pragma unroll
             for (int u = 0; u < DEC_KPT; ++u) {
-                const unsigned int wi = start >> 2, sh = 8u * (start & 3u);
-                unsigned int hi = W[0], lo = W[1];
-#pragma unroll
-                for (int t = 1; t < DEC_KPT; ++t)
-                    if (wi == (unsigned int)t) { hi = W[t]; lo = W[t + 1]; }
-                const unsigned int v = __funnelshift_l(lo, hi, sh);
-                d[u] = w[u] ? v >> (32u - 8u * w[u]) : 0u;
-                start += w[u];
+                const unsigned int dw = b * iv[u];
+                if (dw && dw <= 32u) {
+                    const unsigned long long w0 = off >> 5;
+                    const unsigned int lo = w0 < dw_lim ? __ldcg(dwords + w0) : 0u, hi = w0 + 1 < dw_lim ? __ldcg(dwords + w0 + 1) : 0u;
+                    const unsigned int x = __funnelshift_r(lo, hi, (unsigned int)(off & 31ull));
+                    d[u] = __brev(x << (32u - dw));
+                }
+                off += dw;
             }
         }
     }

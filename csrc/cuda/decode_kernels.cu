@@ -26,8 +26,15 @@
 //   ml/.../objective/GradientDescent.scala:89-117, Adam.scala:27-77 (updates).
 #include "decode_common.cuh"
 
+// The header fields that are needed after the work table is built.
+struct HdrLite {
+    unsigned int kind, cell_bits, bin_num, zero_idx;
+    unsigned long long off_dense_codes, off_bucket_values;
+    double loss_partials[4];
+};
+
 struct DecSmem {
-    SkmlHeader hdr[SKML_MAX_PEERS];
+    HdrLite hdr[SKML_MAX_PEERS];
     int nitems;
     unsigned long long total_chunks, total_keys;
     int any_dense;
@@ -47,6 +54,8 @@ struct DecSmem {
 
 // D0: wait, validate, build the work table (identically in every block).
 __device__ bool decode_prepare(const DP& p, DecSmem& s) {
+    // the full headers sit in the (still idle) table staging area while the work table is built
+    SkmlHeader* full = reinterpret_cast<SkmlHeader*>(reinterpret_cast<unsigned char*>(&s) + p.tab_off);
     if (threadIdx.x == 0) {
         s.ok = 1;
         for (int r = 0; r < p.world; ++r)
@@ -60,11 +69,11 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
     // headers -> shared memory (L2 loads: the bytes were written by other GPUs)
     for (int t = threadIdx.x; t < p.world * (SKML_HEADER_BYTES / 16); t += blockDim.x) {
         int r = t / (SKML_HEADER_BYTES / 16), i = t % (SKML_HEADER_BYTES / 16);
-        reinterpret_cast<uint4*>(&s.hdr[r])[i] = ld_cg_v4(reinterpret_cast<const uint4*>(p.payload[r]) + i);
+        reinterpret_cast<uint4*>(&full[r])[i] = ld_cg_v4(reinterpret_cast<const uint4*>(p.payload[r]) + i);
     }
     __syncthreads();
     if (threadIdx.x < p.world) {
-        const SkmlHeader& h = s.hdr[threadIdx.x];
+        const SkmlHeader& h = full[threadIdx.x];
         bool good = h.magic == SKML_MAGIC && h.version == SKML_VERSION && h.header_checksum == skml_header_checksum(&h) &&
                     h.step == p.step && h.rank == (unsigned int)threadIdx.x && h.dim == (unsigned long long)p.dim &&
                     h.total_bytes <= (unsigned long long)p.slot_capacity && h.dtype == SKML_F32 &&
@@ -72,13 +81,21 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
                     (h.kind != SKML_KIND_SPARSE || ((h.off_group_table & 15ull) == 0 &&
                                                     h.off_group_table + sizeof(SkmlGroupEntry) * h.group_num <= h.total_bytes)) &&
                     (h.kind == SKML_KIND_EMPTY || (h.bin_num >= 1 && h.bin_num <= SKML_GPU_MAX_BINS && h.zero_idx < h.bin_num)) &&
-                    (h.kind != SKML_KIND_SPARSE || (h.key_encoder == SKML_KEYS_DELTA_BINARY &&
+                    (h.kind != SKML_KIND_SPARSE || ((h.key_encoder == SKML_KEYS_DELTA_BINARY || h.key_encoder == SKML_KEYS_DELTA_ADAPTIVE) &&
                                                     h.restart_interval == SKML_RESTART_INTERVAL &&
                                                     (h.cell_bits == 8 || h.cell_bits == 16)));
         if (!good) {
             skml_set_status(p.status, SKML_BAD_HEADER, (unsigned int)threadIdx.x);
             s.ok = 0;
         }
+        HdrLite& l = s.hdr[threadIdx.x];
+        l.kind = h.kind;
+        l.cell_bits = h.cell_bits;
+        l.bin_num = h.bin_num;
+        l.zero_idx = h.zero_idx;
+        l.off_dense_codes = h.off_dense_codes;
+        l.off_bucket_values = h.off_bucket_values;
+        for (int i = 0; i < 4; ++i) l.loss_partials[i] = h.loss_partials[i];
     }
     __syncthreads();
     if (!s.ok) return false;
@@ -86,7 +103,7 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
     const int gcap = p.max_items / p.world;
     for (int t = threadIdx.x; t < p.world * gcap; t += blockDim.x) {
         const int r = t / gcap, g = t % gcap;
-        const SkmlHeader& h = s.hdr[r];
+        const SkmlHeader& h = full[r];
         DecItem& it = s.items[t];
         it.e.n = 0;
         if (h.kind == SKML_KIND_SPARSE && g < (int)h.group_num) {
@@ -104,7 +121,12 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
                                   it.e.table_off + (unsigned long long)h.row_num * it.e.col_num * (h.cell_bits / 8) <= lim &&
                                   it.e.flag_off + 8ull * it.e.n_flag_words <= lim && it.e.delta_off + 8ull * it.e.n_delta_words <= lim &&
                                   it.e.restart_off + 16ull * ((it.e.n + SKML_RESTART_INTERVAL - 1) / SKML_RESTART_INTERVAL) <= lim &&
-                                  2ull * it.e.n <= 64ull * it.e.n_flag_words;
+                                  (h.key_encoder == SKML_KEYS_DELTA_BINARY
+                                       ? 2ull * it.e.n <= 64ull * it.e.n_flag_words
+                                       : (it.e.flag_kind <= 1u && it.e.num_intervals >= 1u && it.e.num_intervals <= 16u &&
+                                          (it.e.num_intervals & (it.e.num_intervals - 1u)) == 0u &&
+                                          (it.e.num_intervals > 1u || it.e.flag_kind == 0u)));
+                it.enc = h.key_encoder;
                 it.base = p.payload[r];
                 it.zero = h.zero_idx;
                 it.cell_bits = h.cell_bits;
@@ -124,7 +146,7 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
         int dense = 0;
         double mx = 0.0;
         for (int r = 0; r < p.world; ++r) {
-            const SkmlHeader& h = s.hdr[r];
+            const SkmlHeader& h = full[r];
             s.rank_chunk_begin[r] = chunks;
             s.rank_key_begin[r] = keys;
             s.rank_item_begin[r] = ni;
@@ -196,7 +218,8 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
 // thread (256 threads), so that every thread has several independent load chains in flight and
 // several blocks share an SM.
 __device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch_begin, unsigned long long ch_end) {
-    __shared__ unsigned int s_part[4][DEC_THREADS / 32];  // [2 scans x chunk parity]
+    __shared__ unsigned int s_part[6][DEC_THREADS / 32];  // [3 scans x chunk parity]
+    __shared__ unsigned short s_pos[SKML_RESTART_INTERVAL];  // delta_adaptive with unary flags: where every key's flag ends
     int par = 0;
     // Every block takes a contiguous run of chunks, so that consecutive chunks belong to the same
     // (rank, group) list and its sketch table, when it fits, is staged in shared memory once and
@@ -215,7 +238,7 @@ __device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch
             stab = stage_table(it, tab_area);
         }
         ChunkKeys c;
-        decode_chunk(p, it, (unsigned int)(ch - it.chunk_prefix), stab, s_part[par], s_part[2 + par], c);
+        decode_chunk(p, it, (unsigned int)(ch - it.chunk_prefix), stab, s_part[par], s_part[2 + par], s_part[4 + par], s_pos, c);
         if (c.i0 < c.cnt) {
             int* ks = p.key_scratch + it.key_prefix + c.first;
             if (s.two_phase) {
@@ -372,7 +395,7 @@ __device__ void apply_owned(const DP& p, DecSmem& s) {
 __device__ void decode_accumulate_dense(const DP& p, DecSmem& s, int r_begin, int r_end) {
     const long long gsz = (long long)gridDim.x * blockDim.x, gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     for (int r = r_begin; r < r_end; ++r) {
-        const SkmlHeader& h = s.hdr[r];
+        const HdrLite& h = s.hdr[r];
         if (h.kind != SKML_KIND_DENSE) continue;
         const unsigned char* codes = p.payload[r] + h.off_dense_codes;
         const float* bv = reinterpret_cast<const float*>(p.payload[r] + h.off_bucket_values);

@@ -37,6 +37,7 @@ typedef struct SkmlCompressArgs {
     double given_min, given_max;
     long long fused;               // 1 = one cooperative launch, 0 = one launch per stage
     long long grid;                // 0 = one block per SM
+    long long key_encoder;         // 0 = delta_binary (byte-aligned deltas), 1 = delta_adaptive (the reference's live encoder)
 } SkmlCompressArgs;
 
 long long skml_compress_workspace_bytes(long long n_max, long long bin_num, long long group_num, long long row_num,

@@ -96,7 +96,8 @@ class GpuEngine:
         if self.mode == "sketch":
             self.comp = GpuCompressor(dim, bound, conf.quant_bin_num, conf.sketch_group_num, conf.sketch_row_num,
                                       conf.sketch_col_ratio, conf.seed, self.device,
-                                      fused=bool(conf.extras.get("fused", True)), budget_s=conf.step_timeout_s)
+                                      fused=bool(conf.extras.get("fused", True)), budget_s=conf.step_timeout_s,
+                                      key_encoder=conf.key_encoder)
             self.dec = GpuDecoder(dim, bound * comm.world, self.device, fused=bool(conf.extras.get("fused", True)),
                                   budget_s=conf.step_timeout_s, max_groups=conf.sketch_group_num)
             from .parallel.exchange import PeerExchange

@@ -47,13 +47,16 @@ class GpuCompressor:
 
     def __init__(self, dim: int, n_max: int, bin_num: int = 256, group_num: int = 8, row_num: int = 2,
                  col_ratio: float = 0.3, seed: int = 0, device="cuda", fused: bool = True, grid: int = 0,
-                 budget_s: float = 1.0):
+                 budget_s: float = 1.0, key_encoder: str = "delta_binary"):
         if bin_num > L.GPU_MAX_BINS:
             raise ValueError(f"the GPU compressor supports at most {L.GPU_MAX_BINS} buckets")
         self.lib = L.lib()
         self.dim, self.n_max = int(dim), int(max(n_max, 1))
         self.bin_num, self.group_num, self.row_num, self.col_ratio = bin_num, group_num, row_num, float(col_ratio)
         self.seed, self.fused, self.grid, self.budget_s = seed, fused, grid, budget_s
+        if key_encoder not in ("delta_binary", "delta_adaptive"):
+            raise ValueError(f"Unrecognizable key encoder: {key_encoder}")
+        self.key_encoder = 1 if key_encoder == "delta_adaptive" else 0
         self.device = torch.device(device)
         ws_n = max(self.n_max, 1)
         self.ws_bytes = int(self.lib.skml_compress_workspace_bytes(ws_n, bin_num, group_num, row_num, self.col_ratio, 0))
@@ -85,7 +88,7 @@ class GpuCompressor:
         if given is not None:
             splits, mn, mx = given
             a.given_splits, a.n_given, a.given_min, a.given_max = L.ptr(splits), splits.numel(), float(mn), float(mx)
-        a.fused, a.grid = int(self.fused), self.grid
+        a.fused, a.grid, a.key_encoder = int(self.fused), self.grid, self.key_encoder
         return a
 
     def make_args(self, *a, **k) -> L.CompressArgs:
@@ -100,7 +103,7 @@ class GpuCompressor:
         a = self._args(keys, vals, meta, step, rank, world, payload_ptr, slot_capacity, peer_payload, peer_flag,
                        status, loss_partials, given)
         L.check(self.lib.skml_compress_sparse(C.byref(a), L.stream()), "skml_compress_sparse")
-        L.count_launches(1 if self.fused else 7)
+        L.count_launches(1 if self.fused else 8)
         if dense_vals is not None:
             a.vals = L.ptr(dense_vals)
             L.check(self.lib.skml_compress_dense(C.byref(a), L.stream()), "skml_compress_dense")

@@ -28,6 +28,8 @@ def main():
         kw["compressor"] = "Float"
     elif scenario == "sketch_adam":
         kw.update(optimizer="adam", learn_rate=0.01)
+    elif scenario == "sketch_adaptive":
+        kw.update(key_encoder="delta_adaptive")
     elif scenario == "fixedpoint":
         kw.update(compressor="FixedPoint", fixed_point_bit_num=8)
     elif scenario == "zip":

@@ -24,25 +24,32 @@ def _sections(p):
     out = []
     for g in p["groups"]:
         out.append((g["n"], g["col_num"], tuple(g["hash_ids"]), g["table"].tolist() if g["n"] else None,
+                    (g["keys"]["num_intervals"], g["keys"]["flag_kind"]) if g["n"] else None,
                     g["keys"]["flag_words"].tolist() if g["n"] else None,
                     g["keys"]["delta_words"].tolist() if g["n"] else None,
                     g.get("restart_raw").tolist() if g["n"] else None))
     return out
 
 
+@pytest.mark.parametrize("encoder", ["delta_binary", "delta_adaptive"])
 @pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("n,dim,q,G,rows,ratio", [
     (5000, 200000, 256, 8, 2, 0.3), (1, 1000, 64, 8, 3, 0.2), (2049, 100000000, 128, 1, 3, 0.2),
-    (70000, 80000, 256, 8, 2, 0.3), (3000, 2 ** 31 - 2, 300, 4, 1, 0.5), (40000, 5000000, 64, 2, 8, 0.1)])
-def test_payload_bit_exact_with_given_splits(fused, n, dim, q, G, rows, ratio):
+    (70000, 80000, 256, 8, 2, 0.3), (3000, 2 ** 31 - 2, 300, 4, 1, 0.5), (40000, 5000000, 64, 2, 8, 0.1),
+    (300000, 3000000, 256, 8, 3, 0.2)])
+def test_payload_bit_exact_with_given_splits(encoder, fused, n, dim, q, G, rows, ratio):
+    """Everything downstream of the split points equals the CPU oracle bit for bit, with both key
+    encoders (delta_adaptive: the groups' interval counts and flag kinds, the two bit streams and
+    the restart points)."""
     from sketchml_b200.compress import oracle
     from sketchml_b200.ops import GpuCompressor
     keys, vals = _sparse_grad(n, dim, seed=n)
     qz = oracle.quantile_quantize(vals, q, 128, 1, 2, False)
     splits = qz["splits"].astype(np.float32)
-    opts = dict(bin_num=q, group_num=G, row_num=rows, col_ratio=ratio, seed=11, step=7, rank=2, world=4, tie_mode=1)
+    opts = dict(bin_num=q, group_num=G, row_num=rows, col_ratio=ratio, seed=11, step=7, rank=2, world=4, tie_mode=1,
+                key_encoder=1 if encoder == "delta_adaptive" else 0)
     ref = oracle.compress_sparse(keys, vals, dim, opts, splits, float(qz["min"]), float(qz["max"]))
-    comp = GpuCompressor(dim, n, q, G, rows, ratio, seed=11, fused=fused)
+    comp = GpuCompressor(dim, n, q, G, rows, ratio, seed=11, fused=fused, key_encoder=encoder)
     buf = comp.compress_local(torch.from_numpy(keys).cuda(), torch.from_numpy(vals).cuda(), step=7, rank=2, world=4,
                               given=(torch.from_numpy(splits).cuda(), qz["min"], qz["max"]))
     got = comp.payload_bytes(buf)
@@ -97,13 +104,14 @@ def test_quantile_splits_rank_error(fused, n):
 DECODE_MODES = {"staged": dict(fused=False), "fused": dict(fused=True)}
 
 
+@pytest.mark.parametrize("encoder", ["delta_binary", "delta_adaptive"])
 @pytest.mark.parametrize("mode", list(DECODE_MODES))
-def test_decode_sum_matches_oracle(mode):
+def test_decode_sum_matches_oracle(mode, encoder):
     from sketchml_b200.compress import oracle
     from sketchml_b200.ops import GpuCompressor, GpuDecoder
     dim, world = 300000, 3
     fused = mode != "staged"
-    comp = GpuCompressor(dim, 20000, 128, 8, 3, 0.2, seed=5, fused=fused)
+    comp = GpuCompressor(dim, 20000, 128, 8, 3, 0.2, seed=5, fused=fused, key_encoder=encoder)
     bufs, ref = [], np.zeros(dim)
     for r in range(world):
         keys, vals = _sparse_grad(15000 + 1000 * r, dim, seed=100 + r)
@@ -312,13 +320,14 @@ def test_several_overlapping_payloads_sgd_and_adam(mode):
     assert torch.equal(w, w2) and torch.equal(m, m2) and torch.equal(vv, v2)
 
 
-def test_decode_skewed_keys_many_ranks():
+@pytest.mark.parametrize("encoder", ["delta_binary", "delta_adaptive"])
+def test_decode_skewed_keys_many_ranks(encoder):
     """Eight payloads with Zipf-like keys (many shared coordinates, one nearly empty payload): the fused
     launch must give the bits of the staged launches, which apply the ranks in the same order per
     coordinate, for SGD and for lazy Adam, and the same bits on every repetition."""
     from sketchml_b200.ops import GpuCompressor, GpuDecoder
     dim, P, n = 3_000_000, 8, 40000
-    comp = GpuCompressor(dim, n, 256, 8, 3, 0.2, seed=9)
+    comp = GpuCompressor(dim, n, 256, 8, 3, 0.2, seed=9, key_encoder=encoder)
     rng = np.random.default_rng(5)
     bufs = []
     for r in range(P):

@@ -64,9 +64,12 @@ def test_fused_exchange_matches_nccl_baselines(tmp_path, world):
     validation loss stays within 1 % of the uncompressed run's at equal epochs."""
     _need(world)
     sk, un, kv = _run("sketch", tmp_path, world), _run("none", tmp_path, world), _run("kv", tmp_path, world)
-    for name, res in (("sketch", sk), ("none", un), ("kv", kv)):
+    ad = _run("sketch_adaptive", tmp_path, world)
+    for name, res in (("sketch", sk), ("sketch_adaptive", ad), ("none", un), ("kv", kv)):
         _check_replicas(res)
         print(name, world, "train", res[0]["train_loss"], "valid", res[0]["valid_loss"])
+    # the key encoder is lossless: the reference's delta_adaptive keys give the very same weights
+    assert ad[0]["hash"] == sk[0]["hash"], "delta_adaptive and delta_binary keys decoded differently"
     assert abs(un[0]["valid_loss"][-1] - kv[0]["valid_loss"][-1]) < 1e-4, (un[0]["valid_loss"], kv[0]["valid_loss"])
     gap = abs(sk[0]["valid_loss"][-1] - un[0]["valid_loss"][-1]) / un[0]["valid_loss"][-1]
     print("sketch vs uncompressed validation-loss gap", world, gap)
