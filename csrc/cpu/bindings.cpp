@@ -39,6 +39,7 @@ static SketchOptions options_from(const py::dict& d) {
     geti("key_encoder", o.key_encoder);
     geti("cell_bits", o.cell_bits);
     geti("sketch_k", o.sketch_k);
+    geti("threads", o.threads);
     geti("seed", o.seed);
     geti("step", o.step);
     geti("rank", o.rank);
@@ -465,16 +466,16 @@ PYBIND11_MODULE(_oracle, m) {
         .def_property_readonly("retained", [](PySketch<double>& s) { return s.s.retained(); });
 
     m.def("quantile_quantize",
-          [](py::array v, int bins, int k, uint64_t seed, int offset_mode, bool jmax) -> py::dict {
+          [](py::array v, int bins, int k, uint64_t seed, int offset_mode, bool jmax, int threads) -> py::dict {
               if (is_f32(v)) {
                   F32Array a(v);
-                  return quantizer_dict(quantile_quantize<float>(a.data(), a.size(), bins, k, seed, offset_mode, jmax));
+                  return quantizer_dict(quantile_quantize_parallel<float>(a.data(), a.size(), bins, k, seed, offset_mode, jmax, threads));
               }
               F64Array a(v);
-              return quantizer_dict(quantile_quantize<double>(a.data(), a.size(), bins, k, seed, offset_mode, jmax));
+              return quantizer_dict(quantile_quantize_parallel<double>(a.data(), a.size(), bins, k, seed, offset_mode, jmax, threads));
           },
           py::arg("values"), py::arg("bin_num") = 256, py::arg("k") = 128, py::arg("seed") = 0,
-          py::arg("offset_mode") = 2, py::arg("java_compat_max") = false);
+          py::arg("offset_mode") = 2, py::arg("java_compat_max") = false, py::arg("threads") = 1);
     m.def("uniform_quantize", [](F64Array v, int bins) {
         return quantizer_dict(uniform_quantize<double>(v.data(), v.size(), bins));
     });

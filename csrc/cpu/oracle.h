@@ -24,6 +24,7 @@
 #include <queue>
 #include <stdexcept>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "../common/skml_common.h"
@@ -335,6 +336,72 @@ Quantizer<T> quantile_quantize(const T* v, size_t n, int bin_num, int k, uint64_
     QuantileSketch<T> sk(k, seed, offset_mode, java_compat_max);
     for (size_t i = 0; i < n; ++i) sk.update(v[i]);
     return quantizer_from_splits<T>(sk.quantiles(bin_num), sk.min_value(), sk.max_value(), v, n);
+}
+
+// Runs fn(t) for t in [0, threads) on `threads` std::threads (the calling thread takes t = 0) and
+// rethrows the first exception. The reference keeps one process-wide thread pool of this size
+// (common/Constants.java:19-24).
+template <class F>
+void run_parallel(int threads, F fn) {
+    if (threads <= 1) {
+        fn(0);
+        return;
+    }
+    std::vector<std::thread> pool;
+    std::vector<std::string> errors(threads);
+    for (int t = 1; t < threads; ++t)
+        pool.emplace_back([&, t] {
+            try {
+                fn(t);
+            } catch (const std::exception& e) {
+                errors[t] = e.what();
+                if (errors[t].empty()) errors[t] = "worker thread failed";
+            }
+        });
+    try {
+        fn(0);
+    } catch (const std::exception& e) {
+        errors[0] = e.what();
+        if (errors[0].empty()) errors[0] = "worker thread failed";
+    }
+    for (auto& th : pool) th.join();
+    for (auto& e : errors)
+        if (!e.empty()) throw Error(e);
+}
+
+// quantization/QuantileQuantizer.java:53-92 (parallelQuantize): every thread summarises a contiguous
+// slice of the values in its own sketch, the sketches are merged into the first one, the splits are
+// queried from the merged summary (and, unlike the reference, de-duplicated as in the serial path),
+// and the bucket of every value is looked up slice by slice in parallel.
+template <class T>
+Quantizer<T> quantile_quantize_parallel(const T* v, size_t n, int bin_num, int k, uint64_t seed, int offset_mode,
+                                        bool java_compat_max, int threads) {
+    if (n == 0) throw Error("cannot quantize an empty vector");
+    if (threads < 1) throw Error("parallelism must be positive");
+    threads = (int)std::min<size_t>((size_t)threads, std::max<size_t>(1, n / 256));
+    if (threads == 1) return quantile_quantize<T>(v, n, bin_num, k, seed, offset_mode, java_compat_max);
+    std::vector<QuantileSketch<T>> parts;
+    parts.reserve(threads);
+    for (int t = 0; t < threads; ++t) parts.emplace_back(k, seed + 0x9E3779B97F4A7C15ull * (uint64_t)t, offset_mode, java_compat_max);
+    auto slice = [&](int t, size_t& lo, size_t& hi) {
+        lo = n * (size_t)t / (size_t)threads;
+        hi = n * (size_t)(t + 1) / (size_t)threads;
+    };
+    run_parallel(threads, [&](int t) {
+        size_t lo, hi;
+        slice(t, lo, hi);
+        for (size_t i = lo; i < hi; ++i) parts[t].update(v[i]);
+    });
+    for (int t = 1; t < threads; ++t) parts[0].merge(parts[t]);
+    Quantizer<T> q = quantizer_from_splits<T>(parts[0].quantiles(bin_num), parts[0].min_value(), parts[0].max_value(),
+                                              (const T*)nullptr, 0);
+    q.bins.resize(n);
+    run_parallel(threads, [&](int t) {
+        size_t lo, hi;
+        slice(t, lo, hi);
+        for (size_t i = lo; i < hi; ++i) q.bins[i] = q.index_of(v[i]);
+    });
+    return q;
 }
 
 template <class T>
@@ -698,6 +765,7 @@ struct SketchOptions {
     int key_encoder = SKML_KEYS_DELTA_BINARY;
     int cell_bits = -1;  // -1 = 8 if bin_num <= 256 else 16; 32 = raw; 0 = Huffman
     int sketch_k = 128;
+    int threads = 1;   // intra-worker parallelism of the CPU library (common/Constants.java:19-24)
     uint64_t seed = 0, step = 0;
     uint32_t rank = 0, world = 1;
     int offset_mode = 2;
@@ -726,9 +794,9 @@ struct GroupedSketch {
         }
         sketches.assign(group_num, MinMaxSketch());
         keys.assign(group_num, EncodedKeys());
-        for (int g = 0; g < group_num; ++g) {
+        auto build_group = [&](int g) {
             size_t sz = gk[g].size();
-            if (sz == 0) continue;
+            if (sz == 0) return;
             int cols = (int)std::ceil((double)sz * col_ratio);
             if (cols < 1) cols = 1;
             uint8_t ids[8];
@@ -737,7 +805,13 @@ struct GroupedSketch {
             for (size_t j = 0; j < sz; ++j) sketches[g].insert(gk[g][j], gb[g][j]);
             keys[g] = key_encoder == SKML_KEYS_DELTA_BINARY ? delta_binary_encode(gk[g].data(), sz)
                                                             : delta_adaptive_encode(gk[g].data(), sz);
-        }
+        };
+        // sketch/frequency/GroupedMinMaxSketch.java:72-101 (parallelCreate): the groups are independent,
+        // so with several threads every thread builds the sketches and key codes of its share of groups
+        const int threads = std::max(1, std::min(o.threads, group_num));
+        run_parallel(threads, [&](int t) {
+            for (int g = t; g < group_num; g += threads) build_group(g);
+        });
     }
     void restore(std::vector<int32_t>& k_out, std::vector<int32_t>& b_out) const {
         std::vector<std::vector<int32_t>> ks, bs;
@@ -1073,9 +1147,9 @@ std::vector<uint8_t> compress_sparse(const int32_t* keys, const T* vals, size_t 
     }
     Quantizer<T> q = given_splits
                          ? quantizer_from_splits<T>(*given_splits, given_min, given_max, vals, n)
-                         : quantile_quantize<T>(vals, n, o.bin_num, o.sketch_k,
-                                                skml_rand(o.seed, o.step, o.rank, 0x9u), o.offset_mode,
-                                                o.java_compat_max);
+                         : quantile_quantize_parallel<T>(vals, n, o.bin_num, o.sketch_k,
+                                                         skml_rand(o.seed, o.step, o.rank, 0x9u), o.offset_mode,
+                                                         o.java_compat_max, o.threads);
     return skml_serialize(sketch_from_quantizer<T>(q, keys, n, dim, o), o);
 }
 
@@ -1087,9 +1161,9 @@ std::vector<uint8_t> compress_dense(const T* vals, size_t dim, const SketchOptio
     if (dim == 0) return empty_payload<T>(0, o);
     Quantizer<T> q = given_splits
                          ? quantizer_from_splits<T>(*given_splits, given_min, given_max, vals, dim)
-                         : quantile_quantize<T>(vals, dim, o.bin_num, o.sketch_k,
-                                                skml_rand(o.seed, o.step, o.rank, 0x9u), o.offset_mode,
-                                                o.java_compat_max);
+                         : quantile_quantize_parallel<T>(vals, dim, o.bin_num, o.sketch_k,
+                                                         skml_rand(o.seed, o.step, o.rank, 0x9u), o.offset_mode,
+                                                         o.java_compat_max, o.threads);
     SketchGradient<T> g;
     g.h.kind = SKML_KIND_DENSE;
     g.h.step = o.step;

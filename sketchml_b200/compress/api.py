@@ -26,9 +26,12 @@ def sizeof(obj) -> int:
 
 
 class Parallel:
-    """Process-wide parallelism knob (common/Constants.java:9-42). The oracle is
-    single-threaded; on a GPU the parallel decomposition is the kernel grid, so this
-    only records the request for API parity."""
+    """Process-wide parallelism of the CPU library (common/Constants.java:9-42): the number of
+    threads the ``parallel_*`` methods hand to the C++ library, which then summarises the values in
+    per-thread quantile sketches that are merged (quantization/QuantileQuantizer.java:53-92), looks
+    the buckets up slice by slice, and builds the groups' sketches and key codes on a thread per
+    share of groups (sketch/frequency/GroupedMinMaxSketch.java:72-101). On a GPU the parallel
+    decomposition is the kernel grid instead."""
     _parallelism = 1
 
     @classmethod
@@ -126,6 +129,14 @@ class QuantileQuantizer(Quantizer):
         self._source = v
         self._take(oracle.quantile_quantize(v, self.bin_num, self.k, self.seed, self.offset_mode,
                                             self.java_compat_max), len(v))
+
+    def parallel_quantize(self, values) -> None:
+        """One sketch per thread over a slice of the values, merged before the splits are queried;
+        the buckets are looked up in parallel (QuantileQuantizer.java:53-92)."""
+        v = np.ascontiguousarray(values)
+        self._source = v
+        self._take(oracle.quantile_quantize(v, self.bin_num, self.k, self.seed, self.offset_mode,
+                                            self.java_compat_max, Parallel.get_parallelism()), len(v))
 
 
 class UniformQuantizer(Quantizer):
@@ -258,7 +269,7 @@ class GroupedMinMaxSketch:
         self.bin_num, self.zero_value = bin_num, zero_value
         self.payload = None
 
-    def create(self, keys, bins) -> None:
+    def create(self, keys, bins, threads: int = 1) -> None:
         """Builds the per-group sketches and key codes from (key, bucket) pairs. The
         buckets are passed through a quantizer whose splits are the integers
         0.5, 1.5, ... so that bucket b decodes to b."""
@@ -266,16 +277,20 @@ class GroupedMinMaxSketch:
         bins = np.asarray(bins, np.float64)
         splits = np.arange(self.bin_num - 1, dtype=np.float64) + 0.5
         self._splits = splits
-        self.payload = self._build(keys, bins, splits)
+        self.payload = self._build(keys, bins, splits, threads)
 
-    def _build(self, keys, bins, splits):
+    def _build(self, keys, bins, splits, threads: int = 1):
         # zero_idx is derived from the splits by the oracle: shift so that bucket
         # `zero_value` is the first with split >= 0.
         shift = self.zero_value
-        return oracle.compress_sparse(keys, bins - shift, int(keys.max()) + 1 if len(keys) else 1, self.opts,
+        return oracle.compress_sparse(keys, bins - shift, int(keys.max()) + 1 if len(keys) else 1,
+                                      dict(self.opts, threads=int(threads)),
                                       splits - shift, float(-shift - 0.5), float(self.bin_num - shift - 0.5))
 
-    parallel_create = create
+    def parallel_create(self, keys, bins) -> None:
+        """The same payload, with the groups' sketches and key codes built on `Parallel.get_parallelism()`
+        threads (GroupedMinMaxSketch.java:72-101)."""
+        self.create(keys, bins, threads=Parallel.get_parallelism())
 
     def restore(self):
         p = oracle.parse(self.payload)
@@ -351,7 +366,22 @@ class SparseVectorCompressor(VectorCompressor):
                 f"Lengths of key array and value array do not match: {len(keys)}, {len(values)}")
         self._size = len(keys)
         dim = int(keys.max()) + 1 if len(keys) else 1
-        self.payload = oracle.compress_sparse(keys, values, dim, self.opts)
+        self.payload = oracle.compress_sparse(keys, values, dim, dict(self.opts, threads=self._threads))
+
+    _threads = 1
+
+    def parallel_compress_sparse(self, keys, values) -> None:
+        """Per-thread quantile sketches merged into one, buckets looked up in parallel, one thread per
+        share of bucket groups (sample/SparseVectorCompressor.java parallelCompressSparse)."""
+        self._threads = Parallel.get_parallelism()
+        try:
+            self.compress_sparse(keys, values)
+        finally:
+            self._threads = 1
+
+    def parallel_compress_dense(self, values) -> None:
+        values = np.asarray(values, self.dtype)
+        self.parallel_compress_sparse(np.arange(len(values), dtype=np.int32), values)
 
     def compress_dense(self, values) -> None:
         values = np.asarray(values, self.dtype)
@@ -384,13 +414,23 @@ class DenseVectorCompressor(VectorCompressor):
         self._size = 0
         self._keys = None
 
-    def compress_dense(self, values) -> None:
+    def compress_dense(self, values, parallel: bool = False) -> None:
         self.q = Quantizer.new_quantizer(self.quant_type, self.bin_num)
         if isinstance(self.q, QuantileQuantizer):
             self.q.seed = self.seed
-        self.q.quantize(np.asarray(values, np.float64))
+        (self.q.parallel_quantize if parallel else self.q.quantize)(np.asarray(values, np.float64))
         self._size = len(values)
         self._keys = None
+
+    def parallel_compress_dense(self, values) -> None:
+        """sample/DenseVectorCompressor.java parallelCompressDense: the quantizer's parallel form."""
+        self.compress_dense(values, parallel=True)
+
+    def parallel_compress_sparse(self, keys, values) -> None:
+        keys = np.asarray(keys, np.int32)
+        dense = np.zeros(int(keys.max()) + 1 if len(keys) else 0)
+        dense[keys] = values
+        self.compress_dense(dense, parallel=True)
 
     def compress_sparse(self, keys, values) -> None:
         keys = np.asarray(keys, np.int32)

@@ -476,7 +476,14 @@ class GpuEngine:
         m = self.t.model
         if self.valid_csr is None or self.valid_csr.rows == 0:
             return [0.0, 0, 0, 0, 0, 0]
-        acc = glm_validate(self.valid_csr, m.weights, m.loss.loss_id, self.st.status, budget_s=self.conf.step_timeout_s)
+        margins = None
+        if self.conf.extras.get("auc"):
+            margins = torch.empty(self.valid_csr.rows, dtype=torch.float32, device=self.device)
+        acc = glm_validate(self.valid_csr, m.weights, m.loss.loss_id, self.st.status, margins=margins,
+                           budget_s=self.conf.step_timeout_s)
+        if margins is not None:
+            from .utils import rank_sum_auc
+            self.last_auc = rank_sum_auc(margins, self.valid_csr.labels)
         return acc.cpu().tolist()
 
     def payload_stats(self, step: int):

@@ -29,7 +29,8 @@ from .data import CSRMatrix, DataSet, SyntheticSpec, generate_cpu, load_data, sh
 from .gradient import kinds as G
 from .models import build_model
 from .parallel import FaultInjector, Heartbeat, LocalComm, PayloadError, make_comm, validate_payload
-from .utils import MetricsLogger, PhaseTimer, export_model, get_logger, load_checkpoint, save_checkpoint, weights_hash
+from .utils import (MetricsLogger, PhaseTimer, export_model, get_logger, load_checkpoint, rank_sum_auc, save_checkpoint,
+                    weights_hash)
 
 logger = get_logger()
 
@@ -110,6 +111,8 @@ class HostEngine:
             return [0.0, 0, 0, 0, 0, 0]
         b = t.valid_data.matrix.to("cpu")
         pre = t.model.loss.predict(t.model.weights.double().cpu(), b)
+        if t.conf.extras.get("auc"):
+            self.last_auc = rank_sum_auc(pre, b.labels)
         return validation_counts(pre, b.labels.double(), t.model.loss)
 
     def sync(self):
@@ -300,6 +303,9 @@ class Trainer:
         out = {"valid_loss": s[0] / n, "precision": (s[1] + s[2]) / n,
                "true_recall": s[1] / max(s[1] + s[4], 1.0), "false_recall": s[2] / max(s[2] + s[3], 1.0),
                "valid_num": int(s[5])}
+        if self.conf.extras.get("auc"):
+            # as in the reference (ValidationUtil.scala:43-92) every worker ranks its own validation rows
+            out["auc"] = float(getattr(self.engine, "last_auc", float("nan")))
         logger.info("Epoch[%d] validation cost %.0f ms, valid size=%d, loss=%.6f, precision=%.6f, "
                     "trueRecall=%.6f, falseRecall=%.6f", epoch, (time.perf_counter() - t0) * 1e3, out["valid_num"],
                     out["valid_loss"], out["precision"], out["true_recall"], out["false_recall"])

@@ -50,3 +50,20 @@ class MetricsLogger:
         if self._f:
             self._f.close()
             self._f = None
+
+
+def rank_sum_auc(scores, labels, java_compat: bool = False) -> float:
+    """Area under the ROC curve by the rank-sum formula over the scores sorted ascending
+    (ml/util/ValidationUtil.scala:69-82): with M positives (label 1) and N others,
+    AUC = (sum of the positives' ranks - M (M + 1) / 2) / (M N). The reference adds up 0-based positions
+    instead of ranks, which lowers its figure by 1 / N; ``java_compat`` reproduces that. Works on torch
+    tensors of any device (one sort)."""
+    import torch
+    s = torch.as_tensor(scores).double().flatten()
+    y = torch.as_tensor(labels).to(s.device).flatten()
+    pos = (y == 1)[torch.argsort(s, stable=True)]
+    m, n = int(pos.sum()), int((~pos).sum())
+    if m == 0 or n == 0:
+        return float("nan")
+    ranks = torch.arange(0 if java_compat else 1, s.numel() + (0 if java_compat else 1), device=s.device, dtype=torch.float64)
+    return float((ranks[pos].sum() - m * (m + 1) / 2.0) / m / n)

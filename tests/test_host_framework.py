@@ -293,3 +293,30 @@ def test_checkpoint_resume_and_export(tmp_path):
         load_checkpoint(str(bad))
     from sketchml_b200 import cli
     assert cli.main(["export", str(ck), str(tmp_path / "m2.txt")]) == 0 and os.path.exists(tmp_path / "m2.txt.pt")
+
+
+def test_rank_sum_auc_matches_pair_counting():
+    """The rank-sum AUC (ValidationUtil.scala:69-82) against the definition: the fraction of
+    (positive, negative) pairs ranked correctly; the reference's 0-based variant is 1 / N lower."""
+    import numpy as np
+    from sketchml_b200.utils import rank_sum_auc
+    rng = np.random.default_rng(0)
+    y = np.where(rng.random(400) < 0.3, 1.0, -1.0)
+    s = rng.normal(size=400) + 0.8 * (y == 1)
+    pos, neg = s[y == 1], s[y != 1]
+    want = (pos[:, None] > neg[None, :]).mean()
+    assert abs(rank_sum_auc(s, y) - want) < 1e-12
+    assert abs(rank_sum_auc(s, y, java_compat=True) - (want - 1.0 / len(neg))) < 1e-12
+
+
+def test_trainer_reports_auc_when_asked():
+    from sketchml_b200.config import MLConf
+    from sketchml_b200.trainer import Trainer
+    conf = MLConf(algo="lr", format="synthetic", feature_num=2000, syn_rows=4000, syn_nnz_per_row=10, epoch_num=2,
+                  batch_sample_ratio=0.25, learn_rate=0.5, l2_reg=1e-5, valid_ratio=0.25, device="cpu", dtype="float64",
+                  compressor="None", extras={"auc": True})
+    t = Trainer(conf)
+    t.load_data()
+    t.train()
+    v = t.validate(99)
+    assert 0.5 < v["auc"] <= 1.0

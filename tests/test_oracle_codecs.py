@@ -410,3 +410,34 @@ def test_pack_varnibbles_roundtrip():
             widths += (v >> (4 * k)) != 0
         assert d["block_offsets"][-1] == widths.sum()
         assert np.array_equal(o.unpack_varnibbles(d["flags"], d["words"], n), v)
+
+
+def test_parallel_quantize_and_create_use_threads():
+    """The `parallel_*` forms run on `Parallel.get_parallelism()` threads of the C++ library: per-thread
+    quantile sketches merged into one keep the rank error of a k = 128 summary, the buckets equal the
+    serial lookup for the same splits, and the thread-per-group sketch build gives the serial payload."""
+    from sketchml_b200.compress import GroupedMinMaxSketch, Parallel, QuantileQuantizer, SparseVectorCompressor
+    rng = np.random.default_rng(3)
+    v = rng.laplace(0, 1e-2, 400_000)
+    Parallel.set_parallelism(4)
+    try:
+        q = QuantileQuantizer(256, seed=7)
+        q.parallel_quantize(v)
+        s = np.sort(v)
+        ranks = np.searchsorted(s, q.splits) / len(v)
+        assert np.abs(np.diff(np.concatenate([[0.0], ranks, [1.0]]))).max() < 1.0 / 256 + 0.03
+        assert np.array_equal(q.get_bins(), np.searchsorted(q.splits, v, side="right"))
+        assert q.min == v.min() and q.max == v.max()
+        keys = np.sort(rng.choice(5_000_000, 60_000, replace=False)).astype(np.int32)
+        bins = rng.integers(0, 256, len(keys))
+        a, b = GroupedMinMaxSketch(8, 2, 0.3, 256, 128, seed=5), GroupedMinMaxSketch(8, 2, 0.3, 256, 128, seed=5)
+        a.create(keys, bins)
+        b.parallel_create(keys, bins)
+        assert a.payload == b.payload
+        c = SparseVectorCompressor(seed=2)
+        c.parallel_compress_sparse(keys, v[: len(keys)])
+        k2, v2 = c.decompress_sparse()
+        assert np.array_equal(k2, keys)
+        assert np.all(np.sign(v2) == np.sign(v[: len(keys)])) or (np.sign(v2) != np.sign(v[: len(keys)])).mean() < 0.06
+    finally:
+        Parallel.shutdown()
