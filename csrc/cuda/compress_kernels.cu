@@ -38,6 +38,8 @@
 #define MAX_LEVELS 24
 #define FP_SHIFT 20         // fixed-point fraction bits of sample weights
 #define MAX_SAMPLE 16        // largest sampling factor of the bottom-level sampler
+#define HUF_MAX_SYMS 512     // symbols per bucket group the device Huffman coder accepts
+#define HUF_RESTART 128      // cells between two restart offsets of a Huffman-coded table
 #define AP_STAGE_F 548       // staging words of one chunk's flag bits (<= 17 bits per key, plus a word of misalignment)
 #define AP_STAGE_D 1028      // the same for its delta bits (<= 32 bits per key)
 
@@ -70,6 +72,10 @@ struct CP {
     unsigned int* blk_done;          // delta_adaptive: [grid] epoch in which the block finished writing its chunks
     unsigned int* key_hist;          // delta_adaptive: [SKML_MAX_GROUPS][32] keys per delta width, zeroed in S1
     int key_encoder;
+    int huffman;                     // sketch tables travel Huffman-coded (cell_bits = 0)
+    unsigned int* cell_hist;         // Huffman: [bin_num + groups] cells per symbol, zeroed in S1
+    unsigned long long* blk_tbits;   // Huffman: [grid][SKML_MAX_GROUPS] code bits per block and group
+    unsigned int* tchunk_off;        // Huffman: [table chunks] bit offset of a chunk inside its owner's part of the stream
     unsigned short* bins;
     int* gkeys;                      // keys, grouped: group g's list starts at Layout::goff[g]
     unsigned int* tables;
@@ -97,6 +103,10 @@ struct Layout {
     unsigned long long flag_bits[SKML_MAX_GROUPS], delta_bits[SKML_MAX_GROUPS];  // delta_adaptive: stream lengths
     unsigned int num_iv[SKML_MAX_GROUPS], flag_kind[SKML_MAX_GROUPS];            // delta_adaptive: the groups' modes
     unsigned long long off_keys;                   // delta_adaptive: start of the per-group [flags | deltas] sections
+    // Huffman-coded tables: symbol range, cells, present symbols, code bits, chunk numbering, stream / restart starts
+    unsigned int sym_lo[SKML_MAX_GROUPS], nsym[SKML_MAX_GROUPS], cells[SKML_MAX_GROUPS], items[SKML_MAX_GROUPS];
+    unsigned int tchunk_prefix[SKML_MAX_GROUPS + 1];
+    unsigned long long tbits[SKML_MAX_GROUPS], tstream_off[SKML_MAX_GROUPS], trestart_off[SKML_MAX_GROUPS];
     unsigned long long table_off[SKML_MAX_GROUPS], flag_off[SKML_MAX_GROUPS], delta_off[SKML_MAX_GROUPS],
         restart_off[SKML_MAX_GROUPS], tab32_off[SKML_MAX_GROUPS];
     unsigned char hash_ids[SKML_MAX_GROUPS][8];
@@ -108,7 +118,7 @@ struct Layout {
 };
 
 struct WsLayout {
-    long long ctrl, run_vals, run_cnt, run_w, splits_raw, warp_cnt, blk_cnt, blk_bytes, blk_flag, chunk_off, blk_bits, blk_done, key_hist, bins, gkeys, tables,
+    long long ctrl, run_vals, run_cnt, run_w, splits_raw, warp_cnt, blk_cnt, blk_bytes, blk_flag, chunk_off, blk_bits, blk_done, key_hist, cell_hist, blk_tbits, tchunk_off, bins, gkeys, tables,
         total;
     long long tables_cap;
 };
@@ -131,6 +141,9 @@ static WsLayout ws_layout(long long n_max, long long q, long long G, long long r
     L.blk_bits = o; o += al256(grid * 2 * SKML_MAX_GROUPS * 8);
     L.blk_done = o; o += al256(grid * 4);
     L.key_hist = o; o += al256(SKML_MAX_GROUPS * 32 * 4);
+    L.cell_hist = o; o += al256((SKML_GPU_MAX_BINS + SKML_MAX_GROUPS) * 4);
+    L.blk_tbits = o; o += al256(grid * SKML_MAX_GROUPS * 8);
+    L.tchunk_off = o; o += al256(((rows * ((long long)(col_ratio * (double)n_max) + 2 + G) + 64) / 1024 + SKML_MAX_GROUPS + 8) * 4);
     L.bins = o; o += al256(n_max * 2);
     L.gkeys = o; o += al256((n_max + 4 * SKML_MAX_GROUPS + 8) * 4);
     L.tables_cap = rows * ((long long)(col_ratio * (double)n_max) + 2 + G) + 64;
@@ -152,7 +165,10 @@ static __host__ __device__ inline long long payload_bound(long long n_max, long 
     long long head = SKML_HEADER_BYTES + (long long)skml_align16(4 * bin_num) + SKML_GROUP_ENTRY_BYTES * G;
     long long flags = 17 * n_max / 8 + 24 * G + 16;   // delta_adaptive with unary flags: up to 17 flag bits per key
     long long restart = 16 * (n_max / R + G) + 16 * G;
-    long long tables = 2 * row_num * ((long long)(col_ratio * (double)n_max) + 2) + 32 * G;
+    long long cells = row_num * ((long long)(col_ratio * (double)n_max) + 2 * G);
+    // two bytes per cell cover 8/16-bit codes and any Huffman stream (at most 10 bits per cell); the
+    // Huffman sections add their code books (12 bytes per symbol) and one restart offset per 128 cells
+    long long tables = 2 * cells + 32 * G + 12 * (bin_num + G) + cells / 32 + 96 * G;
     long long deltas = 4 * n_max + 24 * G;
     long long sparse = head + flags + restart + tables + deltas + 64;
     long long dense = head + 2 * dim + 64;
@@ -192,12 +208,17 @@ struct Smem {
     unsigned long long my_bits[2 * SKML_MAX_GROUPS], pre_bits[2 * SKML_MAX_GROUPS];  // delta_adaptive: flag / delta bits
     unsigned int stage_f[4][AP_STAGE_F];            // delta_adaptive: one chunk's flag / delta bits per sub-block
     unsigned int stage_d[4][AP_STAGE_D];
+    unsigned char huf_len[SKML_GPU_MAX_BINS + SKML_MAX_GROUPS];   // Huffman: code length / code word per symbol slot
+    unsigned int huf_code[SKML_GPU_MAX_BINS + SKML_MAX_GROUPS];
+    unsigned long long my_tbits[SKML_MAX_GROUPS], pre_tbits[SKML_MAX_GROUPS];
     unsigned int sub_part[4][8];                    // scan scratch of the four 256-thread sub-blocks
     unsigned int sub_total[4];
     unsigned long long unit_prefix[SKML_MAX_GROUPS + 1];
     int flag;
 };
 
+
+static_assert(sizeof(Smem) <= 227 * 1024, "the compress kernels' shared memory must fit one SM");
 
 __device__ __forceinline__ unsigned int lanemask_lt() {
     unsigned int m;
@@ -1343,6 +1364,405 @@ __device__ void apush_borders(const CP& p, Smem& s) {
     }
 }
 
+// ---------------------------------------------------------------------------
+// S5, Huffman-coded sketch tables (cell_bits = 0; the reference codes every table this way when it
+// serialises a sketch: sketch/frequency/MinMaxSketch.java:88-97, binary/HuffmanEncoder.java:88-124).
+// Section of one group: u32 {items, 64-bit words, cells, restart interval}; items x {i32 value,
+// i32 code, i32 code length}, ascending by value; the code stream (most significant bit first in
+// java.util.BitSet order); then, 16-byte aligned, one u32 stream offset per 128 cells (not in the
+// reference: it lets a decoder start anywhere). The symbols of a group are the buckets of its range
+// plus the "never written" cell (Integer.MAX_VALUE), at most HUF_MAX_SYMS of them. Any prefix code is
+// valid on the wire (the items carry the codes); the coder builds an optimal one from the cell
+// histogram and assigns canonical code words.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ unsigned int huf_slot(const Layout& L, int g, unsigned int cell) {
+    const unsigned int sidx = cell == SKML_EMPTY_CELL ? L.nsym[g] - 1u : (cell & 0xFFFFu) - L.sym_lo[g];
+    return L.sym_lo[g] + (unsigned int)g + (sidx < L.nsym[g] ? sidx : L.nsym[g] - 1u);
+}
+
+// Table chunks (1024 cells of one group's table, group-major) of this block: a contiguous run.
+__device__ __forceinline__ void tchunk_run(const Layout& L, int G, unsigned int& t_begin, unsigned int& t_end) {
+    const unsigned int total = L.tchunk_prefix[G];
+    unsigned int per = (total + gridDim.x - 1) / gridDim.x;
+    per = (per + 3u) & ~3u;
+    t_begin = min(total, per * blockIdx.x);
+    t_end = min(total, t_begin + per);
+}
+
+struct CellWork {
+    int g;
+    unsigned int j, cnt;      // chunk index inside the group's table, cells in the chunk
+    unsigned int cell[4];     // this thread's cells (32-bit working form)
+};
+
+__device__ __forceinline__ void load_cells(const CP& p, const Layout& L, unsigned int ch, unsigned int ch_end, int G, CellWork& c) {
+    const unsigned int t = threadIdx.x & 255;
+    c.g = -1;
+    c.cnt = 0;
+    c.j = 0;
+    if (ch >= ch_end) return;
+    int g = 0;
+    while (g + 1 < G && ch >= L.tchunk_prefix[g + 1]) ++g;
+    c.g = g;
+    c.j = ch - L.tchunk_prefix[g];
+    const unsigned int first = c.j * 1024u;
+    c.cnt = min(1024u, L.cells[g] - first);
+    const unsigned int* tab = p.tables + L.tab32_off[g] + first;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) c.cell[u] = 4u * t + u < c.cnt ? __ldcg(tab + 4u * t + u) : SKML_EMPTY_CELL;
+}
+
+// Symbol ranges, cell counts and table chunks of the groups (every block, thread 0).
+__device__ void huf_ranges(const CP& p, Smem& s) {
+    Layout& L = s.lay;
+    if (threadIdx.x == 0) {
+        unsigned int ch = 0;
+        for (int g = 0; g < p.G; ++g) {
+            const int lo = g ? s.qi.edges[g - 1] : 0, hi = s.qi.edges[g];
+            L.sym_lo[g] = (unsigned int)lo;
+            L.nsym[g] = (unsigned int)(hi > lo ? hi - lo : 0) + 1u;
+            L.cells[g] = (unsigned int)p.rows * L.col[g];
+            L.tchunk_prefix[g] = ch;
+            ch += (L.cells[g] + 1023u) / 1024u;
+            if (L.n_g[g] && L.nsym[g] > HUF_MAX_SYMS) {
+                L.overflow = 1;
+                skml_set_status(p.status, SKML_BAD_INPUT, 0x38u);
+            }
+        }
+        L.tchunk_prefix[p.G] = ch;
+    }
+    __syncthreads();
+}
+
+// Pass 0: histogram of the cell symbols of this block's table chunks, added to the global one.
+__device__ void huf_histogram(const CP& p, Smem& s, unsigned int t_begin, unsigned int t_end) {
+    const Layout& L = s.lay;
+    unsigned int* hist = s.huf_code;  // idle until the codes are built
+    for (int t = threadIdx.x; t < SKML_GPU_MAX_BINS + SKML_MAX_GROUPS; t += blockDim.x) hist[t] = 0;
+    __syncthreads();
+    for (unsigned int c0 = t_begin; c0 < t_end; c0 += 4) {
+        CellWork c;
+        load_cells(p, L, c0 + (threadIdx.x >> 8), t_end, p.G, c);
+        if (c.g >= 0) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (4u * (threadIdx.x & 255) + u < c.cnt) atomicAdd(&hist[huf_slot(L, c.g, c.cell[u])], 1u);
+        }
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < s.qi.bin_num + p.G; t += blockDim.x)
+        if (hist[t]) atomicAdd(&p.cell_hist[t], hist[t]);
+    __syncthreads();
+}
+
+// Per-warp scratch of the code construction (in the shared memory the quantile stages no longer need).
+struct HufScratch {
+    unsigned int w[HUF_MAX_SYMS];         // leaf weights, ascending
+    unsigned int iw[HUF_MAX_SYMS];        // weights of the internal nodes, in creation order (ascending)
+    unsigned short ord[HUF_MAX_SYMS];     // symbol of the i-th lightest leaf
+    unsigned short pl[HUF_MAX_SYMS];      // parent (internal node) of every leaf
+    unsigned short pi[HUF_MAX_SYMS];      // parent of every internal node
+    unsigned char di[HUF_MAX_SYMS];       // depth of every internal node
+};
+
+// Optimal prefix code of every group from the complete histogram (every block; one warp per group,
+// eight groups at a time), canonical code words, section sizes and the layout that follows the tables.
+__device__ void huf_build(const CP& p, Smem& s) {
+    Layout& L = s.lay;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    HufScratch* scratch = reinterpret_cast<HufScratch*>(s.runs_all);
+    for (int t = threadIdx.x; t < SKML_GPU_MAX_BINS + SKML_MAX_GROUPS; t += blockDim.x) {
+        s.huf_len[t] = 0;
+        s.huf_code[t] = 0;
+    }
+    __syncthreads();
+    if (warp < 8 && !L.overflow) {
+        HufScratch& h = scratch[warp];
+        for (int g = warp; g < p.G; g += 8) {
+            const unsigned int n = L.nsym[g], base = L.sym_lo[g] + (unsigned int)g;
+            if (L.n_g[g] == 0) {
+                if (lane == 0) {
+                    L.items[g] = 0;
+                    L.tbits[g] = 0;
+                }
+                continue;
+            }
+            // rank sort of the present symbols by (count, symbol): every lane ranks its symbols
+            unsigned int m = 0;
+            for (unsigned int a = lane; a < n; a += 32) m += __ldcg(&p.cell_hist[base + a]) ? 1u : 0u;
+            m = warp_sum(m);
+            for (unsigned int a = lane; a < n; a += 32) {
+                const unsigned int ca = __ldcg(&p.cell_hist[base + a]);
+                if (!ca) continue;
+                unsigned int r = 0;
+                for (unsigned int b = 0; b < n; ++b) {
+                    const unsigned int cb = __ldcg(&p.cell_hist[base + b]);
+                    if (cb && (cb < ca || (cb == ca && b < a))) ++r;
+                }
+                h.ord[r] = (unsigned short)a;
+                h.w[r] = ca;
+            }
+            __syncwarp();
+            if (lane == 0) {
+                unsigned long long bits = 0;
+                if (m == 1) {
+                    s.huf_len[base + h.ord[0]] = 1;   // a single symbol gets the one-bit code 0
+                    s.huf_code[base + h.ord[0]] = 0;
+                    bits = h.w[0];
+                } else {
+                    // two-queue construction: leaves and internal nodes are both consumed in ascending weight
+                    unsigned int li = 0, ii = 0, ni = 0;
+                    while (ni + 1 < m) {
+                        unsigned int wsum = 0;
+                        for (int k = 0; k < 2; ++k) {
+                            const bool take_leaf = li < m && (ii >= ni || h.w[li] <= h.iw[ii]);
+                            if (take_leaf) {
+                                wsum += h.w[li];
+                                h.pl[li++] = (unsigned short)ni;
+                            } else {
+                                wsum += h.iw[ii];
+                                h.pi[ii++] = (unsigned short)ni;
+                            }
+                        }
+                        h.iw[ni++] = wsum;
+                    }
+                    h.di[ni - 1] = 0;  // the root
+                    for (int j = (int)ni - 2; j >= 0; --j) h.di[j] = (unsigned char)(h.di[h.pi[j]] + 1);
+                    unsigned int per_len[33];
+                    for (int k = 0; k < 33; ++k) per_len[k] = 0;
+                    unsigned int longest = 0;
+                    for (unsigned int i = 0; i < m; ++i) {
+                        const unsigned int len = (unsigned int)h.di[h.pl[i]] + 1u;
+                        s.huf_len[base + h.ord[i]] = (unsigned char)(len < 32 ? len : 32);
+                        if (len < 33) ++per_len[len];
+                        longest = max(longest, len);
+                        bits += (unsigned long long)h.w[i] * len;
+                    }
+                    if (longest > 31) {
+                        L.overflow = 1;
+                        skml_set_status(p.status, SKML_BAD_INPUT, 0x39u);
+                    }
+                    // canonical code words: lengths ascending, symbols ascending inside a length
+                    unsigned int next[33], code = 0;
+                    for (int k = 1; k < 33; ++k) {
+                        next[k] = code;
+                        code = (code + per_len[k]) << 1;
+                    }
+                    for (unsigned int a = 0; a < n; ++a) {
+                        const unsigned int len = s.huf_len[base + a];
+                        if (len && len < 32) s.huf_code[base + a] = next[len]++;
+                    }
+                }
+                L.items[g] = m;
+                L.tbits[g] = bits;
+            }
+            __syncwarp();
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long o = L.off_tables;
+        for (int g = 0; g < p.G; ++g) {
+            L.table_off[g] = o;
+            if (L.n_g[g]) {
+                const unsigned long long stream = o + 16ull + 12ull * L.items[g];
+                L.tstream_off[g] = stream;
+                L.trestart_off[g] = skml_align16(stream + 8ull * ((L.tbits[g] + 63) / 64));
+                o = skml_align16(L.trestart_off[g] + 4ull * ((L.cells[g] + HUF_RESTART - 1) / HUF_RESTART));
+            }
+        }
+        L.off_deltas = o;
+        L.off_keys = o;
+        unsigned long long worst = o;
+        const bool adaptive = p.key_encoder == SKML_KEYS_DELTA_ADAPTIVE;
+        for (int g = 0; g < p.G; ++g)
+            worst += skml_align16(4ull * L.n_g[g] + 8) + (adaptive ? skml_align16(17ull * L.n_g[g] / 8 + 8) : 0ull);
+        if (worst > (unsigned long long)p.slot_capacity && !L.overflow) {
+            L.overflow = 1;
+            skml_set_status(p.status, SKML_CAPACITY, 0x3Au);
+        }
+    }
+    __syncthreads();
+}
+
+// Pass 1: code bits of this block's table chunks -> chunk offsets inside the block's part of each
+// group's stream, the block's bit totals per group (published with the key counts).
+__device__ void huf_measure(const CP& p, Smem& s, unsigned int t_begin, unsigned int t_end) {
+    const Layout& L = s.lay;
+    if (threadIdx.x < SKML_MAX_GROUPS) s.my_tbits[threadIdx.x] = 0;
+    __syncthreads();
+    for (unsigned int c0 = t_begin; c0 < t_end; c0 += 4) {
+        CellWork c;
+        load_cells(p, L, c0 + (threadIdx.x >> 8), t_end, p.G, c);
+        unsigned int bits = 0;
+        if (c.g >= 0) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (4u * (threadIdx.x & 255) + u < c.cnt) bits += s.huf_len[huf_slot(L, c.g, c.cell[u])];
+        }
+        unsigned int total;
+        sub_scan(s, bits, total);
+        if ((threadIdx.x & 255) == 0) s.sub_total[threadIdx.x >> 8] = total;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int q = 0; q < 4 && c0 + q < t_end; ++q) {
+                int g = 0;
+                while (g + 1 < p.G && c0 + q >= L.tchunk_prefix[g + 1]) ++g;
+                p.tchunk_off[c0 + q] = (unsigned int)s.my_tbits[g];
+                s.my_tbits[g] += s.sub_total[q];
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x < SKML_MAX_GROUPS) p.blk_tbits[(long long)blockIdx.x * SKML_MAX_GROUPS + threadIdx.x] = s.my_tbits[threadIdx.x];
+}
+
+// Table bits of the blocks before this one (the caller has waited for their publications).
+__device__ void huf_prefix(const CP& p, Smem& s) {
+    if (threadIdx.x < SKML_MAX_GROUPS) s.pre_tbits[threadIdx.x] = 0;
+    __syncthreads();
+    if (threadIdx.x < blockIdx.x) {
+        for (int g = 0; g < p.G; ++g) {
+            const unsigned long long v = __ldcg(&p.blk_tbits[(long long)threadIdx.x * SKML_MAX_GROUPS + g]);
+            if (v) atomicAdd(&s.pre_tbits[g], v);
+        }
+    }
+    __syncthreads();
+}
+
+// Pass 2: code streams and restart offsets of this block's table chunks; section head and items by
+// the block that owns a group's first chunk.
+__device__ void huf_write(const CP& p, Smem& s, unsigned int t_begin, unsigned int t_end) {
+    const Layout& L = s.lay;
+    if (L.overflow) return;
+    const int t = threadIdx.x & 255, sb = threadIdx.x >> 8;
+    for (unsigned int c0 = t_begin; c0 < t_end; c0 += 4) {
+        CellWork c;
+        const unsigned int ch = c0 + sb;
+        load_cells(p, L, ch, t_end, p.G, c);
+        unsigned int len[4], code[4], bits = 0;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            len[u] = code[u] = 0;
+            if (c.g >= 0 && 4u * t + u < c.cnt) {
+                const unsigned int slot = huf_slot(L, c.g, c.cell[u]);
+                len[u] = s.huf_len[slot];
+                code[u] = s.huf_code[slot];
+                bits += len[u];
+            }
+        }
+        for (int i = t; i < AP_STAGE_D; i += 256) s.stage_d[sb][i] = 0;
+        unsigned int total;
+        const unsigned int ex = sub_scan(s, bits, total);
+        unsigned long long start = 0;
+        if (c.g >= 0) {
+            start = s.pre_tbits[c.g] + __ldcg(&p.tchunk_off[ch]);
+            unsigned int off = (unsigned int)(start & 31ull) + ex;
+            if (4u * t < c.cnt && ((c.j * 1024u + 4u * t) % HUF_RESTART) == 0)
+                reinterpret_cast<unsigned int*>(p.payload + L.trestart_off[c.g])[(c.j * 1024u + 4u * t) / HUF_RESTART] =
+                    (unsigned int)(start + ex);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                put_bits_shared(s.stage_d[sb], off, code[u], len[u]);
+                off += len[u];
+            }
+        }
+        __syncthreads();
+        if (c.g >= 0) {
+            flush_stream(reinterpret_cast<unsigned int*>(p.payload + L.tstream_off[c.g]), s.stage_d[sb], start, total);
+            if (c.j == 0) {
+                // this sub-block owns the group's first chunk: section head and items (ascending by value)
+                const int g = c.g;
+                unsigned int* head = reinterpret_cast<unsigned int*>(p.payload + L.table_off[g]);
+                if (t == 0) {
+                    head[0] = L.items[g];
+                    head[1] = (unsigned int)((L.tbits[g] + 63) / 64);
+                    head[2] = L.cells[g];
+                    head[3] = HUF_RESTART;
+                }
+                if (t < 32) {
+                    const unsigned int base = L.sym_lo[g] + (unsigned int)g, n = L.nsym[g];
+                    unsigned int seen = 0;
+                    for (unsigned int a0 = 0; a0 < n; a0 += 32) {
+                        const unsigned int a = a0 + t;
+                        const unsigned int ln = a < n ? s.huf_len[base + a] : 0u;
+                        const unsigned int present = __ballot_sync(0xFFFFFFFFu, ln != 0);
+                        if (ln) {
+                            int* rec = reinterpret_cast<int*>(head + 4) + 3 * (seen + __popc(present & ((1u << t) - 1u)));
+                            rec[0] = a + 1 == n ? 0x7FFFFFFF : (int)(L.sym_lo[g] + a);
+                            rec[1] = (int)s.huf_code[base + a];
+                            rec[2] = (int)ln;
+                        }
+                        seen += __popc(present);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// Absolute byte range of the 16-byte units that hold only bits [a, b) of a stream starting at byte
+// `base` (4-byte aligned): from the first unit boundary at or after bit a to the last one at or before b.
+__device__ __forceinline__ void own_units(unsigned long long base, unsigned long long a, unsigned long long b,
+                                          unsigned long long& lo, unsigned long long& hi) {
+    lo = 16ull * ((8ull * base + a + 127ull) / 128ull);
+    hi = 16ull * ((8ull * base + b) / 128ull);
+}
+
+// The parts of the coded tables this block wrote -> the peers' slots (units that hold a block border
+// are sent by block 0 once every block is done).
+__device__ void huf_push_own(const CP& p, Smem& s, unsigned int t_begin, unsigned int t_end) {
+    const Layout& L = s.lay;
+    if (p.world <= 1 || L.overflow || t_begin >= t_end) return;
+    __syncthreads();
+    for (int g = 0; g < p.G; ++g) {
+        const unsigned int c0 = max(t_begin, L.tchunk_prefix[g]), c1 = min(t_end, L.tchunk_prefix[g + 1]);
+        if (c0 >= c1) continue;
+        const bool first = c0 == L.tchunk_prefix[g], last = c1 == L.tchunk_prefix[g + 1];
+        const unsigned long long a = s.pre_tbits[g], b = a + s.my_tbits[g];
+        unsigned long long lo, hi;
+        own_units(L.tstream_off[g], a, b, lo, hi);
+        if (first) lo = L.table_off[g];          // head, items and the stream's first bits
+        if (last) hi = L.trestart_off[g];        // the stream's padding up to the restart offsets
+        if (hi > lo) push_bytes(p, lo, hi);
+        // restart offsets of the block's chunks (1024 / HUF_RESTART per chunk)
+        const unsigned int e0 = (c0 - L.tchunk_prefix[g]) * (1024u / HUF_RESTART);
+        unsigned int e1 = (c1 - L.tchunk_prefix[g]) * (1024u / HUF_RESTART);
+        const unsigned int ne = (L.cells[g] + HUF_RESTART - 1) / HUF_RESTART;
+        unsigned long long r1 = L.trestart_off[g] + 4ull * min(e1, ne);
+        if (last) r1 = skml_align16(r1);
+        push_bytes(p, L.trestart_off[g] + 4ull * e0, r1);
+        (void)e1;
+    }
+}
+
+// Block 0, after every block has written: the units of the table streams that hold a block border.
+__device__ void huf_push_borders(const CP& p, Smem& s) {
+    const Layout& L = s.lay;
+    if (p.world <= 1 || L.overflow) return;
+    const unsigned int total = L.tchunk_prefix[p.G];
+    unsigned int per = (total + gridDim.x - 1) / gridDim.x;
+    per = (per + 3u) & ~3u;
+    const unsigned int b = threadIdx.x;
+    if (b >= 1 && b < gridDim.x && (unsigned long long)per * b < total) {
+        const unsigned int cs = per * b;
+        int g = 0;
+        while (g + 1 < p.G && cs >= L.tchunk_prefix[g + 1]) ++g;
+        if (cs != L.tchunk_prefix[g]) {
+            unsigned long long a = 0;
+            for (unsigned int q = 0; q < b; ++q) a += __ldcg(&p.blk_tbits[(long long)q * SKML_MAX_GROUPS + g]);
+            const unsigned long long bit = 8ull * L.tstream_off[g] + a;
+            if (bit & 127ull) {
+                const unsigned long long off = 16ull * (bit / 128ull);
+                const uint4 v = ld_cg_v4(reinterpret_cast<const uint4*>(p.payload + off));
+                for (unsigned int r = 0; r < p.world; ++r)
+                    if (r != p.rank && p.peer_payload[r]) st_v4(reinterpret_cast<uint4*>(p.peer_payload[r] + off), v);
+            }
+        }
+    }
+}
+
 __device__ __forceinline__ void chunk_run(const Layout& L, int G, unsigned int& my_begin, unsigned int& my_end) {
     const unsigned int total = L.chunk_prefix[G];
     unsigned int per = (total + gridDim.x - 1) / gridDim.x;
@@ -1386,7 +1806,7 @@ __device__ void stage_prepare(const CP& p, long long n) {
     uint4 ones = make_uint4(~0u, ~0u, ~0u, ~0u);
     uint4* t4 = reinterpret_cast<uint4*>(p.tables);
     for (long long i = gid; i < (cells + 3) / 4; i += gsz) t4[i] = ones;
-    if (p.key_encoder == SKML_KEYS_DELTA_ADAPTIVE) {
+    if (p.key_encoder == SKML_KEYS_DELTA_ADAPTIVE || p.huffman) {
         // the bit streams are completed with atomic ORs where chunks meet: they start from zero
         long long bound = payload_bound(n, 0, p.q, p.G, p.rows, p.col_ratio);
         if (bound > p.slot_capacity) bound = p.slot_capacity;
@@ -1394,6 +1814,7 @@ __device__ void stage_prepare(const CP& p, long long n) {
         uint4* z4 = reinterpret_cast<uint4*>(p.payload);
         for (long long i = gid + SKML_HEADER_BYTES / 16; i < bound / 16; i += gsz) z4[i] = z;
         for (long long i = gid; i < SKML_MAX_GROUPS * 32; i += gsz) p.key_hist[i] = 0;
+        for (long long i = gid; i < SKML_GPU_MAX_BINS + SKML_MAX_GROUPS; i += gsz) p.cell_hist[i] = 0;
     }
 }
 
@@ -1452,7 +1873,7 @@ __device__ void write_header(const CP& p, Smem& s, long long n, int kind) {
             h.nnz = (unsigned long long)n;
             h.bin_num = (unsigned int)q.bin_num;
             h.zero_idx = (unsigned int)q.zero_idx;
-            h.cell_bits = (unsigned int)q.cell_bits;
+            h.cell_bits = (kind == SKML_KIND_SPARSE && p.huffman) ? 0u : (unsigned int)q.cell_bits;
             h.min_value = (double)q.minv;
             h.max_value = (double)q.maxv;
             h.off_bucket_values = SKML_HEADER_BYTES;
@@ -1696,29 +2117,39 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_sparse_kernel(CP p, in
     // blocks before it (they are resident, and never wait for a later block), and block 0 for all of them
     // before it writes the header; staged launches split the stage at those points. The delta_adaptive
     // code needs the groups' complete histograms of delta widths first: one more grid barrier.
-    unsigned int my_begin = 0, my_end = 0;
-    const bool adaptive = p.key_encoder == SKML_KEYS_DELTA_ADAPTIVE;
+    unsigned int my_begin = 0, my_end = 0, t_begin = 0, t_end = 0;
+    const bool adaptive = p.key_encoder == SKML_KEYS_DELTA_ADAPTIVE, huffman = p.huffman != 0;
     if (FUSED || stage >= 5) {
         if (!FUSED) {
             load_quantizer(p, s);
             layout_from_counts(p, s);
         }
         chunk_run(s.lay, p.G, my_begin, my_end);
+        if (huffman) {
+            huf_ranges(p, s);
+            tchunk_run(s.lay, p.G, t_begin, t_end);
+        }
     }
     if (FUSED || stage == 5) {
-        narrow_tables(p, s);   // the tables are complete since S4
+        if (huffman) {
+            if (!s.lay.overflow) huf_histogram(p, s, t_begin, t_end);
+        } else {
+            narrow_tables(p, s);   // the tables are complete since S4
+        }
         if (adaptive && !s.lay.overflow) apack_histogram(p, s, my_begin, my_end);
     }
-    if (FUSED && adaptive) {
+    if (FUSED && (adaptive || huffman)) {
         if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, 0x15u)) return;
     }
+    if (FUSED || stage >= 6) {
+        // code tables and the layout behind the tables (every block; staged launches repeat it per stage)
+        if (huffman && (FUSED || stage >= 6)) huf_build(p, s);
+        if (adaptive) apack_choose(p, s);
+    }
     if (FUSED || stage == 6) {
-        if (adaptive) {
-            apack_choose(p, s);
-            apack_measure(p, s, my_begin, my_end);
-        } else {
-            pack_measure(p, s, my_begin, my_end);
-        }
+        if (adaptive) apack_measure(p, s, my_begin, my_end);
+        else pack_measure(p, s, my_begin, my_end);
+        if (huffman) huf_measure(p, s, t_begin, t_end);
     }
     unsigned int epoch = 0;
     if (FUSED) {
@@ -1728,38 +2159,43 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_sparse_kernel(CP p, in
         __syncthreads();
         if (threadIdx.x == 0) st_release_gpu(&p.blk_flag[blockIdx.x], epoch);
     }
+    const bool borders = adaptive || huffman;  // stream words shared by two blocks are sent by block 0 at the end
     if (FUSED || stage == 7) {
         if (!FUSED) {  // the block's own counts again (shared memory does not survive a launch)
-            if (threadIdx.x < SKML_MAX_GROUPS) s.my_bytes[threadIdx.x] = p.blk_bytes[(long long)blockIdx.x * SKML_MAX_GROUPS + threadIdx.x];
+            if (threadIdx.x < SKML_MAX_GROUPS) {
+                s.my_bytes[threadIdx.x] = p.blk_bytes[(long long)blockIdx.x * SKML_MAX_GROUPS + threadIdx.x];
+                s.my_tbits[threadIdx.x] = p.blk_tbits[(long long)blockIdx.x * SKML_MAX_GROUPS + threadIdx.x];
+            }
             if (threadIdx.x < 2 * SKML_MAX_GROUPS) s.my_bits[threadIdx.x] = p.blk_bits[(long long)blockIdx.x * 2 * SKML_MAX_GROUPS + threadIdx.x];
             __syncthreads();
-            if (adaptive) apack_choose(p, s);
         }
         if (adaptive) {
             apack_prefix(p, s, FUSED, epoch);
             apack_write(p, s, my_begin, my_end);
             apush_own_chunks(p, s, my_begin, my_end);
-            if (FUSED) {
-                __threadfence();
-                __syncthreads();
-                if (threadIdx.x == 0) st_release_gpu(&p.blk_done[blockIdx.x], epoch);
-            }
         } else {
             pack_prefix(p, s, FUSED, epoch);
             pack_write(p, s, my_begin, my_end);
             push_own_chunks(p, s, my_begin, my_end);
         }
+        if (huffman) {
+            huf_prefix(p, s);   // (the key prefix above has waited for the blocks before this one)
+            huf_write(p, s, t_begin, t_end);
+            huf_push_own(p, s, t_begin, t_end);
+        }
+        if (FUSED && borders) {
+            __threadfence();
+            __syncthreads();
+            if (threadIdx.x == 0) st_release_gpu(&p.blk_done[blockIdx.x], epoch);
+        }
         if (FUSED) stage_stamp(p.ctrl, 5);
     }
     if (FUSED || stage == 8) {
         if (blockIdx.x == 0) {
-            if (FUSED && !wait_all_published(p, adaptive ? p.blk_done : p.blk_flag, epoch)) return;
-            if (adaptive) {
-                if (!FUSED) apack_choose(p, s);
-                apush_borders(p, s);
-            } else {
-                layout_finish(p, s);
-            }
+            if (FUSED && !wait_all_published(p, borders ? p.blk_done : p.blk_flag, epoch)) return;
+            if (adaptive) apush_borders(p, s);
+            else layout_finish(p, s);
+            if (huffman) huf_push_borders(p, s);
             write_header(p, s, n, SKML_KIND_SPARSE);
         }
         finish_publish(p);
@@ -1878,6 +2314,10 @@ static int fill_params(const SkmlCompressArgs* a, CP& p, int& grid) {
     p.blk_done = reinterpret_cast<unsigned int*>(ws + L.blk_done);
     p.key_hist = reinterpret_cast<unsigned int*>(ws + L.key_hist);
     p.key_encoder = (int)a->key_encoder;
+    p.huffman = a->cell_bits == 0 ? 1 : 0;
+    p.cell_hist = reinterpret_cast<unsigned int*>(ws + L.cell_hist);
+    p.blk_tbits = reinterpret_cast<unsigned long long*>(ws + L.blk_tbits);
+    p.tchunk_off = reinterpret_cast<unsigned int*>(ws + L.tchunk_off);
     p.gkeys = reinterpret_cast<int*>(ws + L.gkeys);
     p.bins = reinterpret_cast<unsigned short*>(ws + L.bins);
     p.tables = reinterpret_cast<unsigned int*>(ws + L.tables);

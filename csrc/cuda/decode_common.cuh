@@ -16,6 +16,7 @@
 #define DEC_KPT 4        // keys of a 1024-key chunk per thread
 #define DEC_THREADS (SKML_RESTART_INTERVAL / DEC_KPT)
 #define DEC_BLOCKS_PER_SM 4
+#define DEC_HUF_MAX_ITEMS 513  // code words of one Huffman-coded table the expander accepts
 #define DEC_TAB_SMEM 36864   // bytes of shared memory per block for a staged sketch table
 
 struct DP {
@@ -40,6 +41,8 @@ struct DP {
     long long budget;
     int max_items;
     int tab_off;     // byte offset of the staged-table area inside the dynamic shared memory (0 = none)
+    unsigned char* tab_scratch;   // expanded Huffman-coded tables (null: such payloads are refused)
+    long long tab_capacity;
 };
 
 struct DecItem {  // one (rank, group) key stream
@@ -52,6 +55,8 @@ struct DecItem {  // one (rank, group) key stream
     unsigned long long col_magic;
     int mixers;               // every row uses one of the three integer mixers (at most three rows)
     unsigned int enc;         // key encoder of the item's payload (SkmlKeyEncoder)
+    const unsigned char* tab; // the sketch table as 8/16-bit bucket codes: inside the payload, or expanded from its Huffman form
+    unsigned int huffman;     // the payload carries the table Huffman-coded (expanded into the scratch before the decode)
 };
 
 
@@ -97,9 +102,9 @@ __device__ __forceinline__ float query_one(const DP& p, const DecItem& it, unsig
                 if (it.cell_bits == 8) cells[r] = stab[c];
                 else cells[r] = reinterpret_cast<const unsigned short*>(stab)[c];
             } else if (it.cell_bits == 8) {
-                cells[r] = __ldcg(it.base + it.e.table_off + c);
+                cells[r] = __ldcg(it.tab + c);
             } else {
-                cells[r] = __ldcg(reinterpret_cast<const unsigned short*>(it.base + it.e.table_off) + c);
+                cells[r] = __ldcg(reinterpret_cast<const unsigned short*>(it.tab) + c);
             }
         }
     }
@@ -335,7 +340,7 @@ __device__ __forceinline__ const unsigned char* stage_table(const DecItem& it, u
     const unsigned long long tbytes = (unsigned long long)it.rows * it.e.col_num * (it.cell_bits / 8);
     if (!tab_area || tbytes > DEC_TAB_SMEM) return nullptr;
     __syncthreads();  // the previous table's readers are done
-    const uint4* src = reinterpret_cast<const uint4*>(it.base + it.e.table_off);
+    const uint4* src = reinterpret_cast<const uint4*>(it.tab);
     uint4* dst = reinterpret_cast<uint4*>(tab_area);
     const int nv = (int)((tbytes + 15) / 16);  // table sections are padded to 16 bytes
     for (int t = threadIdx.x; t < nv; t += blockDim.x) dst[t] = ld_cg_v4(src + t);

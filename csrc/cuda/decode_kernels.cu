@@ -49,6 +49,7 @@ struct DecSmem {
     double inv_world;
     int ok;
     int max_items;
+    int nhuf;        // items whose table arrives Huffman-coded
     DecItem items[1];  // max_items entries (dynamic shared memory)
 };
 
@@ -83,7 +84,7 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
                     (h.kind == SKML_KIND_EMPTY || (h.bin_num >= 1 && h.bin_num <= SKML_GPU_MAX_BINS && h.zero_idx < h.bin_num)) &&
                     (h.kind != SKML_KIND_SPARSE || ((h.key_encoder == SKML_KEYS_DELTA_BINARY || h.key_encoder == SKML_KEYS_DELTA_ADAPTIVE) &&
                                                     h.restart_interval == SKML_RESTART_INTERVAL &&
-                                                    (h.cell_bits == 8 || h.cell_bits == 16)));
+                                                    (h.cell_bits == 8 || h.cell_bits == 16 || (h.cell_bits == 0 && p.tab_scratch))));
         if (!good) {
             skml_set_status(p.status, SKML_BAD_HEADER, (unsigned int)threadIdx.x);
             s.ok = 0;
@@ -118,7 +119,7 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
             if (it.e.n) {
                 const unsigned long long lim = h.total_bytes;
                 const bool good = it.e.col_num > 0 && (unsigned long long)h.row_num * it.e.col_num < (1ull << 31) &&
-                                  it.e.table_off + (unsigned long long)h.row_num * it.e.col_num * (h.cell_bits / 8) <= lim &&
+                                  it.e.table_off + (h.cell_bits ? (unsigned long long)h.row_num * it.e.col_num * (h.cell_bits / 8) : 16ull) <= lim &&
                                   it.e.flag_off + 8ull * it.e.n_flag_words <= lim && it.e.delta_off + 8ull * it.e.n_delta_words <= lim &&
                                   it.e.restart_off + 16ull * ((it.e.n + SKML_RESTART_INTERVAL - 1) / SKML_RESTART_INTERVAL) <= lim &&
                                   (h.key_encoder == SKML_KEYS_DELTA_BINARY
@@ -128,8 +129,10 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
                                           (it.e.num_intervals > 1u || it.e.flag_kind == 0u)));
                 it.enc = h.key_encoder;
                 it.base = p.payload[r];
+                it.tab = it.base + it.e.table_off;
+                it.huffman = h.cell_bits == 0 ? 1u : 0u;
+                it.cell_bits = it.huffman ? (h.bin_num <= 256 ? 8u : 16u) : h.cell_bits;  // Huffman: width of the expanded table
                 it.zero = h.zero_idx;
-                it.cell_bits = h.cell_bits;
                 it.rows = h.row_num;
                 it.off_bv = h.off_bucket_values;
                 it.col_magic = good ? skml_fastmod_magic(it.e.col_num) : 0ull;
@@ -141,8 +144,8 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        int ni = 0;
-        unsigned long long chunks = 0, keys = 0;
+        int ni = 0, nhuf = 0;
+        unsigned long long chunks = 0, keys = 0, tab_used = 0;
         int dense = 0;
         double mx = 0.0;
         for (int r = 0; r < p.world; ++r) {
@@ -173,6 +176,17 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
                 DecItem& it = s.items[ni];
                 it.chunk_prefix = chunks;
                 it.key_prefix = keys;
+                if (it.huffman) {
+                    const unsigned long long bytes = skml_align16((unsigned long long)it.rows * it.e.col_num * (it.cell_bits / 8));
+                    if (tab_used + bytes > (unsigned long long)p.tab_capacity) {
+                        skml_set_status(p.status, SKML_CAPACITY, 0x41u);
+                        s.ok = 0;
+                        break;
+                    }
+                    it.tab = p.tab_scratch + tab_used;
+                    tab_used += bytes;
+                    ++nhuf;
+                }
                 chunks += (it.e.n + SKML_RESTART_INTERVAL - 1) / SKML_RESTART_INTERVAL;
                 keys += it.e.n;
                 ++ni;
@@ -193,6 +207,7 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
             if (s.items[i].e.n > s.items[ref].e.n) ref = i;
         s.ref_item = ref;
         s.nitems = ni;
+        s.nhuf = nhuf;
         s.total_chunks = chunks;
         s.total_keys = keys;
         s.any_dense = dense;
@@ -212,6 +227,104 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
     }
     __syncthreads();
     return s.ok != 0;
+}
+
+// Huffman-coded sketch tables -> 8/16-bit bucket codes in the scratch, before any key is decoded
+// (binary/HuffmanEncoder.java:126-166 decodes by walking a tree; here the code words, left-aligned and
+// sorted, are searched with the next 32 stream bits: in a prefix code the word that matches is the
+// largest one not above them). A block works on one item at a time; its threads each decode a stretch
+// of cells from a restart offset (every `head[3]` cells; a table without restart offsets is decoded by
+// one thread). Never-written cells (Integer.MAX_VALUE) become the zero bucket, as in the narrow form.
+__device__ void expand_tables(const DP& p, DecSmem& s) {
+    if (s.nhuf == 0) return;
+    unsigned char* area = reinterpret_cast<unsigned char*>(&s) + p.tab_off;
+    unsigned int* la = reinterpret_cast<unsigned int*>(area);                       // left-aligned code words, ascending
+    unsigned short* sym = reinterpret_cast<unsigned short*>(la + DEC_HUF_MAX_ITEMS);  // their symbols (0xFFFF = never written)
+    unsigned char* len = reinterpret_cast<unsigned char*>(sym + DEC_HUF_MAX_ITEMS);
+    __shared__ unsigned int s_head[4];
+    __shared__ int s_bad;
+    // blocks are dealt to the Huffman items round-robin; the blocks of one item share its stretches
+    const int H = s.nhuf, B = (int)gridDim.x;
+    int seen = 0;
+    for (int i = 0; i < s.nitems; ++i) {
+        const DecItem& it = s.items[i];
+        if (!it.huffman) continue;
+        const int mine = seen++;
+        int helper = 0, nhelp = 1;
+        if (H <= B) {
+            if ((int)blockIdx.x % H != mine) continue;
+            helper = (int)blockIdx.x / H;
+            nhelp = (B - mine + H - 1) / H;
+        } else if (mine % B != (int)blockIdx.x) {
+            continue;
+        }
+        const unsigned char* sec = it.base + it.e.table_off;
+        __syncthreads();
+        if (threadIdx.x < 4) s_head[threadIdx.x] = __ldcg(reinterpret_cast<const unsigned int*>(sec) + threadIdx.x);
+        if (threadIdx.x == 0) s_bad = 0;
+        __syncthreads();
+        const unsigned int nitems = s_head[0], nwords = s_head[1], cells = s_head[2], interval = s_head[3];
+        const unsigned long long lim = reinterpret_cast<const SkmlHeader*>(it.base)->total_bytes;
+        const unsigned int want = it.rows * it.e.col_num;
+        const unsigned long long stream_off = it.e.table_off + 16ull + 12ull * nitems;
+        const unsigned long long restart_off = skml_align16(stream_off + 8ull * nwords);
+        const unsigned int nseg = interval ? (cells + interval - 1) / interval : 1u;
+        if (nitems == 0 || nitems > DEC_HUF_MAX_ITEMS || cells != want || stream_off + 8ull * nwords > lim ||
+            (interval && restart_off + 4ull * nseg > lim)) {
+            if (threadIdx.x == 0) skml_set_status(p.status, SKML_BAD_HEADER, 0x600u | (unsigned int)(i & 0xFF));
+            continue;
+        }
+        // code words: rank sort by the left-aligned word
+        for (unsigned int a = threadIdx.x; a < nitems; a += blockDim.x) {
+            const int* rec = reinterpret_cast<const int*>(sec + 16) + 3 * a;
+            const int value = __ldcg(rec), bits = __ldcg(rec + 1), nb = __ldcg(rec + 2);
+            if (nb < 1 || nb > 32) {
+                s_bad = 1;
+                continue;
+            }
+            const unsigned int mine_la = (unsigned int)bits << (32 - nb);
+            unsigned int r = 0;
+            for (unsigned int b = 0; b < nitems; ++b) {
+                const int* rb = reinterpret_cast<const int*>(sec + 16) + 3 * b;
+                const int nbb = __ldcg(rb + 2);
+                const unsigned int other = (nbb >= 1 && nbb <= 32) ? (unsigned int)__ldcg(rb + 1) << (32 - nbb) : 0u;
+                if (other < mine_la || (other == mine_la && b < a)) ++r;
+            }
+            la[r] = mine_la;
+            len[r] = (unsigned char)nb;
+            sym[r] = value == 0x7FFFFFFF ? (unsigned short)0xFFFFu : (unsigned short)value;
+        }
+        __syncthreads();
+        if (s_bad) {
+            if (threadIdx.x == 0) skml_set_status(p.status, SKML_BAD_HEADER, 0x700u | (unsigned int)(i & 0xFF));
+            continue;
+        }
+        const unsigned int* words = reinterpret_cast<const unsigned int*>(it.base + stream_off);
+        const unsigned long long wlim = 2ull * nwords;
+        const unsigned int* restart = reinterpret_cast<const unsigned int*>(it.base + restart_off);
+        unsigned char* out = const_cast<unsigned char*>(it.tab);
+        const unsigned int zero = it.zero;
+        for (unsigned int sg = (unsigned int)helper * blockDim.x + threadIdx.x; sg < nseg; sg += (unsigned int)nhelp * blockDim.x) {
+            unsigned long long pos = interval ? __ldcg(restart + sg) : 0ull;
+            const unsigned int c0 = interval ? sg * interval : 0u, c1 = interval ? min(cells, c0 + interval) : cells;
+            for (unsigned int c = c0; c < c1; ++c) {
+                const unsigned long long w0 = pos >> 5;
+                const unsigned int lo = w0 < wlim ? __ldcg(words + w0) : 0u, hi = w0 + 1 < wlim ? __ldcg(words + w0 + 1) : 0u;
+                const unsigned int x = __brev(__funnelshift_r(lo, hi, (unsigned int)(pos & 31ull)));
+                unsigned int a = 0, b = nitems;   // largest word <= x
+                while (b - a > 1) {
+                    const unsigned int mid = (a + b) >> 1;
+                    if (la[mid] <= x) a = mid;
+                    else b = mid;
+                }
+                unsigned int v = sym[a] == 0xFFFFu ? zero : sym[a];
+                if (it.cell_bits == 8) out[c] = (unsigned char)v;
+                else reinterpret_cast<unsigned short*>(out)[c] = (unsigned short)v;
+                pos += len[a];
+            }
+        }
+    }
+    __syncthreads();
 }
 
 // D1 for sparse payloads: one 1024-key chunk per block iteration, DEC_KPT adjacent keys per
@@ -458,6 +571,13 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_BLOCKS_PER_SM) decode_update_
         reinterpret_cast<unsigned long long*>(p.ctrl)[8 + 4 * (int)(p.step & 1)] = t;
     }
     if (!decode_prepare(p, s)) return;
+    if (s.nhuf) {  // tables that arrived Huffman-coded become plain bucket codes first
+        if (FUSED || stage == 0) expand_tables(p, s);
+        if (FUSED) {
+            if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, 0x2Eu)) return;
+        }
+    }
+    if (!FUSED && stage == 0) return;
     if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -576,6 +696,8 @@ extern "C" int skml_decode_update(const SkmlDecodeArgs* a, void* stream_) {
     p.acc = a->acc;
     p.key_scratch = a->key_scratch;
     p.val_scratch = a->val_scratch;
+    p.tab_scratch = a->table_scratch;
+    p.tab_capacity = a->table_capacity;
     p.key_capacity = a->key_capacity;
     p.loss_out = a->loss_out;
     p.out_sum = a->out_sum;
@@ -626,7 +748,7 @@ extern "C" int skml_decode_update(const SkmlDecodeArgs* a, void* stream_) {
     // stages: Adam = accumulate + claims; SGD over several payloads with a value scratch = decode +
     // one apply pass per rank; otherwise one pass per rank
     const int nst = a->adam_v ? 2 : ((a->world > 1 && a->val_scratch) ? (int)a->world + 1 : (int)a->world);
-    for (int st = 1; st <= nst; ++st) {
+    for (int st = a->table_scratch ? 0 : 1; st <= nst; ++st) {
         decode_update_kernel<false><<<grid, DEC_THREADS, smem, stream>>>(p, st);
         e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;

@@ -38,6 +38,7 @@ typedef struct SkmlCompressArgs {
     long long fused;               // 1 = one cooperative launch, 0 = one launch per stage
     long long grid;                // 0 = one block per SM
     long long key_encoder;         // 0 = delta_binary (byte-aligned deltas), 1 = delta_adaptive (the reference's live encoder)
+    long long cell_bits;           // sketch tables on the wire: -1 = 8/16-bit bucket codes, 0 = Huffman-coded (the reference's form)
 } SkmlCompressArgs;
 
 long long skml_compress_workspace_bytes(long long n_max, long long bin_num, long long group_num, long long row_num,
@@ -73,6 +74,8 @@ typedef struct SkmlDecodeArgs {
     long long grid;
     long long max_groups;      // upper bound of the payloads' group count (0 = 32): sizes the work table
     float* val_scratch;        // decoded values, capacity key_capacity (null: SGD applies payload by payload)
+    unsigned char* table_scratch;  // room for the sketch tables of payloads that carry them Huffman-coded (null: refused)
+    long long table_capacity;      // its size in bytes
 } SkmlDecodeArgs;
 
 long long skml_decode_workspace_bytes(long long world, long long group_num);

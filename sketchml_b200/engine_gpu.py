@@ -97,9 +97,10 @@ class GpuEngine:
             self.comp = GpuCompressor(dim, bound, conf.quant_bin_num, conf.sketch_group_num, conf.sketch_row_num,
                                       conf.sketch_col_ratio, conf.seed, self.device,
                                       fused=bool(conf.extras.get("fused", True)), budget_s=conf.step_timeout_s,
-                                      key_encoder=conf.key_encoder)
+                                      key_encoder=conf.key_encoder, cell_bits=0 if conf.cell_bits == 0 else -1)
             self.dec = GpuDecoder(dim, bound * comm.world, self.device, fused=bool(conf.extras.get("fused", True)),
-                                  budget_s=conf.step_timeout_s, max_groups=conf.sketch_group_num)
+                                  budget_s=conf.step_timeout_s, max_groups=conf.sketch_group_num,
+                                  table_capacity=self._table_scratch_bytes(conf, bound, comm.world))
             from .parallel.exchange import PeerExchange
             self.xchg = PeerExchange(comm, self.comp.capacity, self.device)
             self._prepare_fast_step()
@@ -297,6 +298,15 @@ class GpuEngine:
         m.optimizer.advance()
         h = _BatchHandle(rows, self.batch_index)
         return h, None, None
+
+    @staticmethod
+    def _table_scratch_bytes(conf, bound, world):
+        """Scratch for the sketch tables of Huffman-coded payloads, expanded to two-byte bucket codes:
+        rows x ceil(col_ratio x keys) cells per group, every rank's payload at once."""
+        if conf.cell_bits != 0:
+            return 0
+        cells = conf.sketch_row_num * (conf.sketch_col_ratio * bound + 16 * conf.sketch_group_num)
+        return int(2 * world * cells) + 4096
 
     def _index_of(self, csr, segs):
         """The prepared column index of the batch `segs` of the resident shard, if there is one."""

@@ -47,7 +47,7 @@ class GpuCompressor:
 
     def __init__(self, dim: int, n_max: int, bin_num: int = 256, group_num: int = 8, row_num: int = 2,
                  col_ratio: float = 0.3, seed: int = 0, device="cuda", fused: bool = True, grid: int = 0,
-                 budget_s: float = 1.0, key_encoder: str = "delta_binary"):
+                 budget_s: float = 1.0, key_encoder: str = "delta_binary", cell_bits: int = -1):
         if bin_num > L.GPU_MAX_BINS:
             raise ValueError(f"the GPU compressor supports at most {L.GPU_MAX_BINS} buckets")
         self.lib = L.lib()
@@ -57,6 +57,9 @@ class GpuCompressor:
         if key_encoder not in ("delta_binary", "delta_adaptive"):
             raise ValueError(f"Unrecognizable key encoder: {key_encoder}")
         self.key_encoder = 1 if key_encoder == "delta_adaptive" else 0
+        if cell_bits not in (-1, 0, 8, 16):
+            raise ValueError("cell_bits: -1 (8/16-bit codes by bucket count) or 0 (Huffman-coded tables)")
+        self.cell_bits = 0 if cell_bits == 0 else -1
         self.device = torch.device(device)
         ws_n = max(self.n_max, 1)
         self.ws_bytes = int(self.lib.skml_compress_workspace_bytes(ws_n, bin_num, group_num, row_num, self.col_ratio, 0))
@@ -88,7 +91,7 @@ class GpuCompressor:
         if given is not None:
             splits, mn, mx = given
             a.given_splits, a.n_given, a.given_min, a.given_max = L.ptr(splits), splits.numel(), float(mn), float(mx)
-        a.fused, a.grid, a.key_encoder = int(self.fused), self.grid, self.key_encoder
+        a.fused, a.grid, a.key_encoder, a.cell_bits = int(self.fused), self.grid, self.key_encoder, self.cell_bits
         return a
 
     def make_args(self, *a, **k) -> L.CompressArgs:
@@ -156,7 +159,10 @@ class GpuDecoder:
     """Owns the scratch memory of the fused decode + aggregate + update kernel."""
 
     def __init__(self, dim: int, key_capacity: int, device="cuda", fused: bool = True, grid: int = 0,
-                 budget_s: float = 1.0, max_groups: int = 32):
+                 budget_s: float = 1.0, max_groups: int = 32, table_capacity: int = 0):
+        """``table_capacity``: bytes of scratch for the sketch tables of payloads that carry them
+        Huffman-coded (they are expanded to bucket codes before the keys are decoded); 0 = two bytes per
+        decoded key."""
         self.lib = L.lib()
         self.max_groups = int(max_groups)
         self.dim, self.key_capacity = int(dim), int(max(key_capacity, 1))
@@ -166,6 +172,8 @@ class GpuDecoder:
         self.key_scratch = torch.zeros(self.key_capacity, dtype=torch.int32, device=self.device)
         self.val_scratch = torch.zeros(self.key_capacity, dtype=torch.float32, device=self.device)
         self.workspace = torch.zeros(256, dtype=torch.uint8, device=self.device)
+        self.table_capacity = int(table_capacity) if table_capacity > 0 else 2 * self.key_capacity + 4096
+        self.table_scratch = torch.zeros(self.table_capacity, dtype=torch.uint8, device=self.device)
 
     def reset(self) -> None:
         self.workspace.zero_()
@@ -190,6 +198,7 @@ class GpuDecoder:
         a.budget_cycles = L.budget_cycles(self.budget_s)
         a.fused, a.grid, a.max_groups = int(self.fused), self.grid, self.max_groups
         a.val_scratch = L.ptr(self.val_scratch)
+        a.table_scratch, a.table_capacity = L.ptr(self.table_scratch), self.table_capacity
         return a
 
     def decode_update(self, payload_ptrs: Sequence[int], flag_ptrs: Sequence[Optional[int]], slot_capacity: int,

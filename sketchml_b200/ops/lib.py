@@ -35,7 +35,7 @@ class CompressArgs(C.Structure):
         ("payload", c_vp), ("slot_capacity", c_ll), ("peer_payload", c_vp * MAX_PEERS),
         ("peer_flag", c_vp * MAX_PEERS), ("workspace", c_vp), ("workspace_bytes", c_ll), ("status", c_vp),
         ("budget_cycles", c_ll), ("given_splits", c_vp), ("n_given", c_ll), ("given_min", c_d),
-        ("given_max", c_d), ("fused", c_ll), ("grid", c_ll), ("key_encoder", c_ll),
+        ("given_max", c_d), ("fused", c_ll), ("grid", c_ll), ("key_encoder", c_ll), ("cell_bits", c_ll),
     ]
 
 
@@ -45,7 +45,7 @@ class DecodeArgs(C.Structure):
         ("step", c_ull), ("dim", c_ll), ("w", c_vp), ("adam_m", c_vp), ("adam_v", c_vp), ("lr", c_d),
         ("adam_scale", c_d), ("acc", c_vp), ("key_scratch", c_vp), ("key_capacity", c_ll), ("loss_out", c_vp),
         ("out_sum", c_vp), ("workspace", c_vp), ("status", c_vp), ("budget_cycles", c_ll), ("fused", c_ll),
-        ("grid", c_ll), ("max_groups", c_ll), ("val_scratch", c_vp),
+        ("grid", c_ll), ("max_groups", c_ll), ("val_scratch", c_vp), ("table_scratch", c_vp), ("table_capacity", c_ll),
     ]
 
 

@@ -67,6 +67,54 @@ def test_payload_bit_exact_with_given_splits(encoder, fused, n, dim, q, G, rows,
     assert np.array_equal(k2, keys) and np.array_equal(v2, v3)
 
 
+@pytest.mark.parametrize("encoder", ["delta_binary", "delta_adaptive"])
+@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("n,dim,q,G,rows,ratio", [
+    (5000, 200000, 256, 8, 2, 0.3), (1, 1000, 64, 8, 3, 0.2), (2049, 100000000, 128, 1, 3, 0.2),
+    (3000, 2 ** 31 - 2, 300, 4, 1, 0.5), (300000, 3000000, 256, 8, 3, 0.2)])
+def test_huffman_coded_tables(encoder, fused, n, dim, q, G, rows, ratio):
+    """cell_bits = 0: the tables travel Huffman-coded. The device's code is canonical and carries restart
+    offsets, so its bytes differ from the CPU oracle's tree-walk code; the decoded tables, every other
+    section and the decoded gradient are the oracle's bit for bit. The GPU decoder reads both forms."""
+    from sketchml_b200.compress import oracle
+    from sketchml_b200.ops import GpuCompressor, GpuDecoder
+    keys, vals = _sparse_grad(n, dim, seed=n + 3)
+    qz = oracle.quantile_quantize(vals, q, 128, 1, 2, False)
+    splits = qz["splits"].astype(np.float32)
+    opts = dict(bin_num=q, group_num=G, row_num=rows, col_ratio=ratio, seed=11, step=7, rank=0, world=1, tie_mode=1,
+                key_encoder=1 if encoder == "delta_adaptive" else 0, cell_bits=0)
+    ref = oracle.compress_sparse(keys, vals, dim, opts, splits, float(qz["min"]), float(qz["max"]))
+    comp = GpuCompressor(dim, n, q, G, rows, ratio, seed=11, fused=fused, key_encoder=encoder, cell_bits=0)
+    buf = comp.compress_local(torch.from_numpy(keys).cuda(), torch.from_numpy(vals).cuda(), step=7, rank=0, world=1,
+                              given=(torch.from_numpy(splits).cuda(), qz["min"], qz["max"]))
+    got = comp.payload_bytes(buf)
+    pg, pr = oracle.parse(got), oracle.parse(ref)
+    assert pg["cell_bits"] == pr["cell_bits"] == 0
+    for gi, (a, b) in enumerate(zip(_sections(pg), _sections(pr))):
+        for fi, (x, y) in enumerate(zip(a, b)):
+            assert x == y, f"group {gi} field {fi} differs"
+    _, k2, v2 = oracle.decompress(got)
+    _, k3, v3 = oracle.decompress(ref)
+    assert np.array_equal(k2, keys) and np.array_equal(v2, v3)
+    # with enough cells per group to pay for the code books, the Huffman-coded payload is the smaller one
+    plain = GpuCompressor(dim, n, q, G, rows, ratio, seed=11, fused=fused, key_encoder=encoder)
+    pb = plain.compress_local(torch.from_numpy(keys).cuda(), torch.from_numpy(vals).cuda(), step=7, rank=0, world=1,
+                              given=(torch.from_numpy(splits).cuda(), qz["min"], qz["max"]))
+    if n >= 100000:
+        assert len(got) < len(plain.payload_bytes(pb))
+    # both the device-made and the oracle-made payload decode on the GPU to the oracle's values
+    want = np.zeros(dim if dim <= 10 ** 8 else 1)
+    if dim <= 10 ** 8:
+        want[k3] = v3
+        dec = GpuDecoder(dim, n, fused=fused)
+        out = dec.decode_sum([buf], step=7).cpu().numpy()
+        assert np.array_equal(out[k3], v3.astype(np.float32)) and np.count_nonzero(out) <= n
+        rb = torch.zeros(max(buf.numel(), len(ref) + 256), dtype=torch.uint8, device="cuda")
+        rb[:len(ref)] = torch.frombuffer(bytearray(ref), dtype=torch.uint8).cuda()
+        out2 = dec.decode_sum([rb], step=7).cpu().numpy()
+        assert np.array_equal(out2, out)
+
+
 @pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("n", [100, 255, 256, 257, 2047, 2048, 2049, 30000, 1000003])
 def test_quantile_splits_rank_error(fused, n):
@@ -104,14 +152,15 @@ def test_quantile_splits_rank_error(fused, n):
 DECODE_MODES = {"staged": dict(fused=False), "fused": dict(fused=True)}
 
 
+@pytest.mark.parametrize("cell_bits", [-1, 0])
 @pytest.mark.parametrize("encoder", ["delta_binary", "delta_adaptive"])
 @pytest.mark.parametrize("mode", list(DECODE_MODES))
-def test_decode_sum_matches_oracle(mode, encoder):
+def test_decode_sum_matches_oracle(mode, encoder, cell_bits):
     from sketchml_b200.compress import oracle
     from sketchml_b200.ops import GpuCompressor, GpuDecoder
     dim, world = 300000, 3
     fused = mode != "staged"
-    comp = GpuCompressor(dim, 20000, 128, 8, 3, 0.2, seed=5, fused=fused, key_encoder=encoder)
+    comp = GpuCompressor(dim, 20000, 128, 8, 3, 0.2, seed=5, fused=fused, key_encoder=encoder, cell_bits=cell_bits)
     bufs, ref = [], np.zeros(dim)
     for r in range(world):
         keys, vals = _sparse_grad(15000 + 1000 * r, dim, seed=100 + r)

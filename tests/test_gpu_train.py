@@ -45,6 +45,31 @@ def test_sketch_training_tracks_uncompressed(algo, opt):
     assert gap < 0.3, (h_s, h_n)
 
 
+def test_wire_codecs_are_lossless_and_shrink_the_payload():
+    """The key encoder (delta_binary / the reference's delta_adaptive) and the table coder (8/16-bit
+    cells / Huffman, the reference's wire form) only change the bytes: the trained weights are
+    bit-identical for the four combinations, and every reference codec makes the payload smaller."""
+    sizes, weights = {}, {}
+    for enc in ("delta_binary", "delta_adaptive"):
+        for cb in (-1, 0):
+            from sketchml_b200.trainer import Trainer
+            t = Trainer(_conf(compressor="Sketch", key_encoder=enc, cell_bits=cb, feature_num=400000, syn_rows=60000,
+                              syn_nnz_per_row=30, epoch_num=1, quant_bin_num=256, valid_ratio=0.0))
+            t.load_data()
+            t.train()
+            nnz, nbytes = t.engine.payload_stats(t.step - 1)
+            sizes[(enc, cb)] = nbytes / nnz
+            weights[(enc, cb)] = t.model.weights.detach().cpu().clone()
+            t.close()
+    print("payload bytes per non-zero", sizes)
+    ref = weights[("delta_binary", -1)]
+    differ = [k for k, w in weights.items() if not torch.equal(w, ref)]
+    assert not differ, f"weights differ from the delta_binary / plain-table run for {differ}"
+    assert sizes[("delta_adaptive", -1)] < sizes[("delta_binary", -1)]
+    assert sizes[("delta_binary", 0)] < sizes[("delta_binary", -1)]
+    assert sizes[("delta_adaptive", 0)] == min(sizes.values())
+
+
 def test_gpu_uncompressed_matches_host_engine():
     from sketchml_b200.data import SyntheticSpec, generate_cpu
     spec = SyntheticSpec(6000, 8000, 15, 1.1, "binary", "logistic", 0.1, 0.0, 3)
