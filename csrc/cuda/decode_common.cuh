@@ -43,6 +43,9 @@ struct DP {
     int tab_off;     // byte offset of the staged-table area inside the dynamic shared memory (0 = none)
     unsigned char* tab_scratch;   // expanded Huffman-coded tables (null: such payloads are refused)
     long long tab_capacity;
+    double* wsq;       // running sum of squares of the weights (null: not kept)
+    double* reg_out;   // receives reg_lambda * sqrt(*wsq) when the launch ends
+    double reg_lambda;
 };
 
 struct DecItem {  // one (rank, group) key stream
@@ -63,24 +66,37 @@ struct DecItem {  // one (rank, group) key stream
 __device__ __forceinline__ long long to_fixed(double v, int shift) { return __double2ll_rn(ldexp(v, shift)); }
 __device__ __forceinline__ double from_fixed(long long a, int shift) { return ldexp((double)a, -shift); }
 
-__device__ __forceinline__ void apply_one(const DP& p, long long k, float g) {
+// Both return new^2 - old^2 of the weight they changed (0 when they write the plain sum instead): the
+// callers add these up so that the squared norm of the model is kept current without a pass over it.
+__device__ __forceinline__ float apply_one(const DP& p, long long k, float g) {
     if (p.out_sum) {
         p.out_sum[k] = g;
-    } else if (!p.adam_v) {
-        p.w[k] -= p.lr * g;
+        return 0.f;
+    }
+    const float old = p.w[k];
+    float nw;
+    if (!p.adam_v) {
+        nw = old - p.lr * g;
     } else {
         float mt = 0.9f * p.adam_m[k] + 0.1f * g;
         float vt = 0.999f * p.adam_v[k] + 0.001f * g * g;
-        p.w[k] -= p.lr * p.adam_scale * mt / (sqrtf(vt) + 1e-8f);
+        nw = old - p.lr * p.adam_scale * mt / (sqrtf(vt) + 1e-8f);
         p.adam_m[k] = mt;
         p.adam_v[k] = vt;
     }
+    p.w[k] = nw;
+    return (nw - old) * (nw + old);
 }
 
 // Linear modes: SGD step on w, or accumulation of the plain mean into out_sum.
-__device__ __forceinline__ void apply_direct(const DP& p, long long k, float g) {
-    if (p.out_sum) p.out_sum[k] += g;
-    else p.w[k] -= p.lr * g;
+__device__ __forceinline__ float apply_direct(const DP& p, long long k, float g) {
+    if (p.out_sum) {
+        p.out_sum[k] += g;
+        return 0.f;
+    }
+    const float old = p.w[k], nw = old - p.lr * g;
+    p.w[k] = nw;
+    return (nw - old) * (nw + old);
 }
 
 // Query of one key in its group's sketch: the bucket value of the cell farthest from the zero bucket.

@@ -330,7 +330,7 @@ __device__ void expand_tables(const DP& p, DecSmem& s) {
 // D1 for sparse payloads: one 1024-key chunk per block iteration, DEC_KPT adjacent keys per
 // thread (256 threads), so that every thread has several independent load chains in flight and
 // several blocks share an SM.
-__device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch_begin, unsigned long long ch_end) {
+__device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch_begin, unsigned long long ch_end, float& dsq) {
     __shared__ unsigned int s_part[6][DEC_THREADS / 32];  // [3 scans x chunk parity]
     __shared__ unsigned short s_pos[SKML_RESTART_INTERVAL];  // delta_adaptive with unary flags: where every key's flag ends
     int par = 0;
@@ -366,11 +366,11 @@ __device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch
             } else if (s.direct) {  // single payload: keys are unique inside it, plain read-modify-write
 #pragma unroll
                 for (int u = 0; u < DEC_KPT; ++u)
-                    if (c.live[u]) apply_direct(p, c.keys[u], c.bv[u] * (float)s.inv_world);
+                    if (c.live[u]) dsq += apply_direct(p, c.keys[u], c.bv[u] * (float)s.inv_world);
             } else if (s.adam_plain) {  // single payload: the decoded value is the whole gradient of its key
 #pragma unroll
                 for (int u = 0; u < DEC_KPT; ++u)
-                    if (c.live[u] && c.bv[u] != 0.f) apply_one(p, c.keys[u], c.bv[u] * (float)s.inv_world);
+                    if (c.live[u] && c.bv[u] != 0.f) dsq += apply_one(p, c.keys[u], c.bv[u] * (float)s.inv_world);
             } else {
 #pragma unroll
                 for (int u = 0; u < DEC_KPT; ++u) {
@@ -387,7 +387,7 @@ __device__ void decode_accumulate(const DP& p, DecSmem& s, unsigned long long ch
 
 // Ordered apply of one rank's stashed (key, value) pairs: keys are unique inside a payload, so the
 // plain read-modify-write needs no atomics; four independent pairs per thread and iteration.
-__device__ void apply_stashed(const DP& p, unsigned long long begin, unsigned long long end) {
+__device__ void apply_stashed(const DP& p, unsigned long long begin, unsigned long long end, float& dsq) {
     const unsigned long long gsz = (unsigned long long)gridDim.x * blockDim.x;
     for (unsigned long long t = begin + (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; t < end; t += 4 * gsz) {
         unsigned int k[4];
@@ -408,7 +408,11 @@ __device__ void apply_stashed(const DP& p, unsigned long long begin, unsigned lo
         for (int u = 0; u < 4; ++u)
             if (k[u] < (unsigned long long)p.dim) {
                 if (p.out_sum) p.out_sum[k[u]] = old[u] + v[u];
-                else p.w[k[u]] = old[u] - p.lr * v[u];
+                else {
+                    const float nw = old[u] - p.lr * v[u];
+                    p.w[k[u]] = nw;
+                    dsq += (nw - old[u]) * (nw + old[u]);
+                }
             }
     }
 }
@@ -419,7 +423,7 @@ __device__ void apply_stashed(const DP& p, unsigned long long begin, unsigned lo
 // four independent entries per thread and iteration; a block barrier ends the pass.
 template <int OP>
 __device__ __forceinline__ void owned_pass(const DP& p, DecSmem& s, const unsigned long long* seg_b,
-                                           const unsigned long long* seg_e, int r) {
+                                           const unsigned long long* seg_e, int r, float& dsq) {
     const int i0 = s.rank_item_begin[r], i1 = s.rank_item_begin[r + 1];
     float* dst = OP == 0 ? (p.out_sum ? p.out_sum : p.w) : reinterpret_cast<float*>(p.acc);
     unsigned int total = 0;
@@ -450,11 +454,14 @@ __device__ __forceinline__ void owned_pass(const DP& p, DecSmem& s, const unsign
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             if (k[u] >= (unsigned long long)p.dim) continue;
-            if (OP == 0) dst[k[u]] = p.out_sum ? old[u] + v[u] : old[u] - p.lr * v[u];
-            else if (OP == 1) dst[k[u]] = old[u] + v[u];
+            if (OP == 0) {
+                const float nw = p.out_sum ? old[u] + v[u] : old[u] - p.lr * v[u];
+                dst[k[u]] = nw;
+                if (!p.out_sum) dsq += (nw - old[u]) * (nw + old[u]);
+            } else if (OP == 1) dst[k[u]] = old[u] + v[u];
             else if (old[u] != 0.f) {
                 dst[k[u]] = 0.f;
-                apply_one(p, k[u], old[u]);
+                dsq += apply_one(p, k[u], old[u]);
             }
         }
     }
@@ -465,7 +472,7 @@ __device__ __forceinline__ void owned_pass(const DP& p, DecSmem& s, const unsign
 // list), finds its slice of every (rank, group) list by binary search in the stashed keys, and applies
 // the slices rank by rank with only a block barrier in between: all updates of one coordinate
 // happen in one block, in rank order, so replicas stay bit-identical.
-__device__ void apply_owned(const DP& p, DecSmem& s) {
+__device__ void apply_owned(const DP& p, DecSmem& s, float& dsq) {
     if (s.nitems == 0) return;
     unsigned long long* seg_b = reinterpret_cast<unsigned long long*>(&s.items[p.max_items]);
     unsigned long long* seg_e = seg_b + p.max_items;
@@ -497,15 +504,15 @@ __device__ void apply_owned(const DP& p, DecSmem& s) {
         // Adam: sum the ranks' values per coordinate in rank order (plain floats in the zeroed
         // accumulator array), then let the first rank that holds a coordinate apply the update
         // and clear the sum.
-        for (int r = 0; r < p.world; ++r) owned_pass<1>(p, s, seg_b, seg_e, r);
-        for (int r = 0; r < p.world; ++r) owned_pass<2>(p, s, seg_b, seg_e, r);
+        for (int r = 0; r < p.world; ++r) owned_pass<1>(p, s, seg_b, seg_e, r, dsq);
+        for (int r = 0; r < p.world; ++r) owned_pass<2>(p, s, seg_b, seg_e, r, dsq);
     } else {
-        for (int r = 0; r < p.world; ++r) owned_pass<0>(p, s, seg_b, seg_e, r);
+        for (int r = 0; r < p.world; ++r) owned_pass<0>(p, s, seg_b, seg_e, r, dsq);
     }
 }
 
 // D1 for dense payloads: every coordinate carries a bucket code.
-__device__ void decode_accumulate_dense(const DP& p, DecSmem& s, int r_begin, int r_end) {
+__device__ void decode_accumulate_dense(const DP& p, DecSmem& s, int r_begin, int r_end, float& dsq) {
     const long long gsz = (long long)gridDim.x * blockDim.x, gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     for (int r = r_begin; r < r_end; ++r) {
         const HdrLite& h = s.hdr[r];
@@ -516,7 +523,7 @@ __device__ void decode_accumulate_dense(const DP& p, DecSmem& s, int r_begin, in
             unsigned int code = h.cell_bits == 8 ? __ldcg(codes + i) : __ldcg(reinterpret_cast<const unsigned short*>(codes) + i);
             if (code >= h.bin_num) code = h.zero_idx;
             if (s.direct) {
-                apply_direct(p, i, __ldcg(bv + code) * (float)s.inv_world);
+                dsq += apply_direct(p, i, __ldcg(bv + code) * (float)s.inv_world);
                 continue;
             }
             const long long fx = to_fixed((double)__ldcg(bv + code) * s.inv_world, s.shift);
@@ -526,14 +533,14 @@ __device__ void decode_accumulate_dense(const DP& p, DecSmem& s, int r_begin, in
 }
 
 // D2: claim and update.
-__device__ void decode_update(const DP& p, DecSmem& s) {
+__device__ void decode_update(const DP& p, DecSmem& s, float& dsq) {
     const long long gsz = (long long)gridDim.x * blockDim.x, gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (s.any_dense) {
         for (long long i = gid; i < p.dim; i += gsz) {
             long long a = p.acc[i];
             if (a) {
                 p.acc[i] = 0;
-                apply_one(p, i, (float)from_fixed(a, s.shift));
+                dsq += apply_one(p, i, (float)from_fixed(a, s.shift));
             }
         }
     } else {
@@ -550,7 +557,7 @@ __device__ void decode_update(const DP& p, DecSmem& s) {
                 a[u] = k[u] < p.dim ? (long long)atomicExch(reinterpret_cast<unsigned long long*>(p.acc + k[u]), 0ull) : 0ll;
 #pragma unroll
             for (int u = 0; u < 4; ++u)
-                if (a[u]) apply_one(p, k[u], (float)from_fixed(a[u], s.shift));
+                if (a[u]) dsq += apply_one(p, k[u], (float)from_fixed(a[u], s.shift));
         }
     }
     if (blockIdx.x == 0 && threadIdx.x == 0 && p.loss_out) {
@@ -561,10 +568,37 @@ __device__ void decode_update(const DP& p, DecSmem& s) {
     }
 }
 
+// Adds the launch's change of the squared weight norm to the running sum; the last block to arrive
+// turns the sum into the regularisation loss of the next batch (lambda * ||w||_2, un-squared as in
+// ml/objective/Loss.scala:48-53) so that no step passes over the whole model for it.
+__device__ void finish_norm(const DP& p, float dsq) {
+    if (!p.wsq) return;
+    __shared__ double s_red[DEC_THREADS / 32];
+    double d = (double)dsq;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) d += __shfl_down_sync(0xFFFFFFFFu, d, o);
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = d;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int w = 0; w < DEC_THREADS / 32; ++w) t += s_red[w];
+        if (t != 0.0) atomicAdd(p.wsq, t);
+        __threadfence();
+        const unsigned int prev = atomicAdd(&p.ctrl[3], 1u);
+        if (prev == gridDim.x - 1) {
+            p.ctrl[3] = 0;
+            __threadfence();
+            const double w2 = *reinterpret_cast<volatile double*>(p.wsq);
+            if (p.reg_out) p.reg_out[0] = p.reg_lambda * sqrt(w2 > 0.0 ? w2 : 0.0);
+        }
+    }
+}
+
 template <bool FUSED>
 __global__ void __launch_bounds__(DEC_THREADS, DEC_BLOCKS_PER_SM) decode_update_kernel(DP p, int stage) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     DecSmem& s = *reinterpret_cast<DecSmem*>(smem_raw);
+    float dsq = 0.f;  // this thread's share of the change of ||w||^2
     if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -586,7 +620,7 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_BLOCKS_PER_SM) decode_update_
     if (s.direct || s.adam_plain) {
         if (s.two_phase) {
             // Phase 1 (un-fused: stage 1): every payload's keys and values, no ordering needed.
-            if (FUSED || stage == 1) decode_accumulate(p, s, 0, s.total_chunks);
+            if (FUSED || stage == 1) decode_accumulate(p, s, 0, s.total_chunks, dsq);
             if (FUSED) {
                 if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, 0x2Fu)) return;
                 if (blockIdx.x == 0 && threadIdx.x == 0) {
@@ -597,13 +631,13 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_BLOCKS_PER_SM) decode_update_
             }
             // Phase 2 without dense payloads (un-fused: stage 2): key-range-owned apply, no grid barrier.
             if (!s.any_dense) {
-                if (FUSED || stage == 2) apply_owned(p, s);
+                if (FUSED || stage == 2) apply_owned(p, s, dsq);
             } else
             // Phase 2 with dense payloads (un-fused: stage r + 2): one apply pass per rank, in rank order.
             for (int r = 0; r < p.world; ++r) {
                 if (FUSED || stage == r + 2) {
-                    apply_stashed(p, s.rank_key_begin[r], s.rank_key_begin[r + 1]);
-                    if (s.any_dense) decode_accumulate_dense(p, s, r, r + 1);
+                    apply_stashed(p, s.rank_key_begin[r], s.rank_key_begin[r + 1], dsq);
+                    if (s.any_dense) decode_accumulate_dense(p, s, r, r + 1, dsq);
                 }
                 if (FUSED && r + 1 < p.world) {
                     if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, 0x30u + r)) return;
@@ -613,8 +647,8 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_BLOCKS_PER_SM) decode_update_
             // one pass per rank; un-fused launches run pass `stage - 1` each
             for (int r = 0; r < p.world; ++r) {
                 if (FUSED || stage == r + 1) {
-                    decode_accumulate(p, s, s.rank_chunk_begin[r], s.rank_chunk_begin[r + 1]);
-                    if (s.any_dense) decode_accumulate_dense(p, s, r, r + 1);
+                    decode_accumulate(p, s, s.rank_chunk_begin[r], s.rank_chunk_begin[r + 1], dsq);
+                    if (s.any_dense) decode_accumulate_dense(p, s, r, r + 1, dsq);
                 }
                 if (FUSED && r + 1 < p.world) {
                     if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, 0x30u + r)) return;
@@ -633,6 +667,7 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_BLOCKS_PER_SM) decode_update_
             if (!s.two_phase) reinterpret_cast<unsigned long long*>(p.ctrl)[10 + 4 * (int)(p.step & 1)] = t;
             reinterpret_cast<unsigned long long*>(p.ctrl)[11 + 4 * (int)(p.step & 1)] = t;
         }
+        finish_norm(p, dsq);
         if (FUSED) {
             // the last block to finish leaves the kernel's true end time (block 0's stamp above is its own)
             __syncthreads();
@@ -649,8 +684,8 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_BLOCKS_PER_SM) decode_update_
         return;
     }
     if (FUSED || stage == 1) {
-        decode_accumulate(p, s, 0, s.total_chunks);
-        if (s.any_dense) decode_accumulate_dense(p, s, 0, p.world);
+        decode_accumulate(p, s, 0, s.total_chunks, dsq);
+        if (s.any_dense) decode_accumulate_dense(p, s, 0, p.world, dsq);
     }
     if (FUSED) {
         if (!skml_grid_barrier(p.ctrl, gridDim.x, p.status, p.budget, 0x21u)) return;
@@ -660,12 +695,13 @@ __global__ void __launch_bounds__(DEC_THREADS, DEC_BLOCKS_PER_SM) decode_update_
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
         reinterpret_cast<unsigned long long*>(p.ctrl)[10 + 4 * (int)(p.step & 1)] = t;
     }
-    if (FUSED || stage == 2) decode_update(p, s);
+    if (FUSED || stage == 2) decode_update(p, s, dsq);
     if (FUSED && blockIdx.x == 0 && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
         reinterpret_cast<unsigned long long*>(p.ctrl)[11 + 4 * (int)(p.step & 1)] = t;
     }
+    finish_norm(p, dsq);
 }
 
 extern "C" long long skml_decode_workspace_bytes(long long world, long long group_num) {
@@ -698,6 +734,9 @@ extern "C" int skml_decode_update(const SkmlDecodeArgs* a, void* stream_) {
     p.val_scratch = a->val_scratch;
     p.tab_scratch = a->table_scratch;
     p.tab_capacity = a->table_capacity;
+    p.wsq = a->out_sum ? nullptr : a->weight_sumsq;
+    p.reg_out = a->reg_out;
+    p.reg_lambda = a->reg_lambda;
     p.key_capacity = a->key_capacity;
     p.loss_out = a->loss_out;
     p.out_sum = a->out_sum;

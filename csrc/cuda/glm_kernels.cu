@@ -672,6 +672,97 @@ extern "C" int skml_update_sparse(float* w, float* m, float* v, const int* keys,
     return (int)cudaGetLastError();
 }
 
+// Sum of squares of the model in one launch: a contiguous slice per block, the partial sums added in
+// block order by the last block to finish (so the result does not depend on the schedule).
+constexpr int NORM_BLOCKS = 592;
+
+__global__ void __launch_bounds__(256) weight_norm_kernel(const float* __restrict__ w, long long dim, double lambda,
+                                                          double* __restrict__ sumsq_out, double* __restrict__ reg_out,
+                                                          double* __restrict__ partials, unsigned int* __restrict__ counter) {
+    const long long per = ((dim + gridDim.x - 1) / gridDim.x + 3) & ~3ll;
+    const long long lo = per * blockIdx.x, hi = lo + per < dim ? lo + per : dim;
+    double acc = 0.0;
+    for (long long i = lo + 4ll * threadIdx.x; i < hi; i += 4ll * blockDim.x) {
+        if (i + 4 <= hi) {
+            const float4 v = *reinterpret_cast<const float4*>(w + i);  // lo is a multiple of 4: 16-byte aligned
+            acc += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
+        } else {
+            for (long long j = i; j < hi; ++j) acc += (double)w[j] * w[j];
+        }
+    }
+    __shared__ double sh[256];
+    __shared__ bool last;
+    sh[threadIdx.x] = acc;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if (threadIdx.x < o) sh[threadIdx.x] += sh[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        partials[blockIdx.x] = sh[0];
+        __threadfence();
+        last = atomicAdd(counter, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    double t = 0.0;
+    for (int b = threadIdx.x; b < (int)gridDim.x; b += 256) t += __ldcg(partials + b);
+    sh[threadIdx.x] = t;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if (threadIdx.x < o) sh[threadIdx.x] += sh[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        *counter = 0;
+        if (sumsq_out) sumsq_out[0] = sh[0];
+        if (reg_out) reg_out[0] = lambda * sqrt(sh[0]);
+    }
+}
+
+extern "C" long long skml_weight_norm_scratch_bytes() { return (NORM_BLOCKS + 2) * 8; }
+
+extern "C" int skml_weight_norm(const float* w, long long dim, double lambda, double* sumsq_out, double* reg_out,
+                                void* scratch, void* stream) {
+    if (!w || !scratch || dim < 0) return (int)cudaErrorInvalidValue;
+    double* partials = reinterpret_cast<double*>(scratch);
+    unsigned int* counter = reinterpret_cast<unsigned int*>(partials + NORM_BLOCKS);
+    weight_norm_kernel<<<NORM_BLOCKS, 256, 0, (cudaStream_t)stream>>>(w, dim, lambda, sumsq_out, reg_out, partials, counter);
+    return (int)cudaGetLastError();
+}
+
+// Update from a dense accumulator on exactly the coordinates of the gathered key lists, clearing the
+// accumulator on the way: the work is proportional to the number of gathered keys, not to the model
+// dimension. One launch per list (keys are distinct inside a list, so a launch touches every word at
+// most once); a coordinate shared by several lists is updated by the first one and found cleared
+// (exactly zero, skipped) by the later ones. A sum that is exactly zero is a no-op, as in the
+// `sparse_only` dense update.
+__global__ void update_gathered_kernel(float* w, float* m, float* v, float* acc, const int* keys, const long long* count,
+                                       long long stride, float scale, int adam, float lr, float adam_scale) {
+    long long n = *count;
+    if (n > stride) n = stride;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const int k = keys[i];
+        const float g = acc[k];
+        if (g == 0.f) continue;
+        acc[k] = 0.f;
+        apply_update(w, m, v, k, g * scale, adam, lr, adam_scale);
+    }
+}
+
+extern "C" int skml_update_gathered(float* w, float* m, float* v, float* acc, const int* keys, const long long* counts,
+                                    long long stride, int lists, float scale, int adam, float lr, float adam_scale,
+                                    void* stream) {
+    for (int l = 0; l < lists; ++l) {
+        update_gathered_kernel<<<sm_count() * 8, 256, 0, (cudaStream_t)stream>>>(w, m, v, acc, keys + (long long)l * stride,
+                                                                                 counts + l, stride, scale, adam, lr, adam_scale);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
+}
+
 // Scatter-add of (key, value) lists into a dense accumulator (raw key/value all-gather
 // baseline: local sum of the gathered lists).
 __global__ void scatter_kv_kernel(float* acc, const int* keys, const float* vals, const long long* counts,

@@ -76,6 +76,9 @@ typedef struct SkmlDecodeArgs {
     float* val_scratch;        // decoded values, capacity key_capacity (null: SGD applies payload by payload)
     unsigned char* table_scratch;  // room for the sketch tables of payloads that carry them Huffman-coded (null: refused)
     long long table_capacity;      // its size in bytes
+    double* weight_sumsq;          // optional device double: sum of w^2, kept current by the update (see skml_weight_norm)
+    double* reg_out;               // optional device double: receives reg_lambda * sqrt(*weight_sumsq) when the launch ends
+    double reg_lambda;
 } SkmlDecodeArgs;
 
 long long skml_decode_workspace_bytes(long long world, long long group_num);
@@ -97,6 +100,15 @@ int skml_update_dense(float* w, float* m, float* v, const float* g, long long di
                       float adam_scale, int sparse_only, void* stream);
 int skml_update_sparse(float* w, float* m, float* v, const int* keys, const float* vals, const long long* n_ptr,
                        long long n_max, float scale, int adam, float lr, float adam_scale, void* stream);
+// Applies acc[key] * scale to the model on the coordinates of `lists` gathered key lists (list l at
+// keys + l * stride, counts[l] entries) and clears those accumulator words.
+int skml_update_gathered(float* w, float* m, float* v, float* acc, const int* keys, const long long* counts,
+                         long long stride, int lists, float scale, int adam, float lr, float adam_scale, void* stream);
+// sumsq_out[0] = sum of w^2 (double, fixed summation order), reg_out[0] = lambda * sqrt of it; one
+// launch, `scratch` holds skml_weight_norm_scratch_bytes() bytes that are zero before the first call.
+long long skml_weight_norm_scratch_bytes();
+int skml_weight_norm(const float* w, long long dim, double lambda, double* sumsq_out, double* reg_out, void* scratch,
+                     void* stream);
 int skml_scatter_kv(float* acc, const int* keys, const float* vals, const long long* counts, long long stride,
                     int lists, void* stream);
 int skml_gen_wstar(float* w, long long dim, double density, unsigned long long seed, void* stream);
@@ -165,6 +177,23 @@ int skml_fixedpoint_pack(const float* vals, const long long* n_ptr, long long n_
 int skml_fixedpoint_unpack_scatter(float* acc, const int* keys, const unsigned char* codes, const double* norms,
                                    const long long* counts, long long key_stride, long long code_stride, int lists,
                                    int bits, float* vals_out, void* stream);
+
+// Zip baseline compressor: ZipML split search on the device (no value is read back to the host), one
+// bucket code per value (skml_zipml_code_bytes(bin_num) bytes each) and a table of
+// skml_zipml_table_len(bin_num) bucket midpoints per list. `scratch`: skml_zipml_scratch_bytes(n_max)
+// bytes; meta: buckets, zero bucket, halving rounds; range: min, max. 2 <= bin_num <= 8190.
+long long skml_zipml_scratch_bytes(long long n_max);
+int skml_zipml_code_bytes(int bin_num);
+int skml_zipml_table_len(int bin_num);
+int skml_zipml_pack(const float* vals, const long long* n_ptr, long long n_max, int bin_num, void* scratch,
+                    long long scratch_bytes, float* splits, float* mids, int* meta, float* range, unsigned char* codes,
+                    void* stream);
+// Decodes `lists` code arrays (list l at codes + l * code_stride, keys + l * key_stride, its table at
+// mids + l * table_len, counts[l] entries); adds into acc[key] when acc is given, stores the values to
+// vals_out[l * key_stride + i] when vals_out is given (keys may then be null).
+int skml_zipml_unpack_scatter(float* acc, const int* keys, const unsigned char* codes, const float* mids,
+                              const long long* counts, long long key_stride, long long code_stride, int lists,
+                              int bin_num, float* vals_out, void* stream);
 
 // Peer memory (one process per GPU): CUDA IPC handles of a cudaMalloc'ed region.
 int skml_ipc_get_handle(void* dev_ptr, unsigned char* handle64);

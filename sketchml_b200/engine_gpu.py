@@ -23,7 +23,8 @@ from .data import SyntheticSpec
 from .ops import lib as L
 from .ops.codec import GpuCompressor, GpuDecoder, read_status
 from .ops.datagen import generate_gpu
-from .ops.glm import DeviceCSR, GlmState, compact_gradient, glm_grad, glm_validate, update_dense, update_sparse
+from .ops.glm import (DeviceCSR, GlmState, compact_gradient, glm_grad, glm_validate, update_dense, update_gathered,
+                      update_sparse)
 from .parallel.failure import check_status
 
 
@@ -93,6 +94,13 @@ class GpuEngine:
         m = self.t.model
         self.reg_every_step = bool(conf.extras.get("reg_loss_every_step", dim <= (1 << 22)))
         self.adam = conf.optimizer == "adam"
+        # regularisation loss lambda * ||w||_2 of every batch: one launch of a norm kernel per step for the
+        # baseline arms; the sketch arm's decode kernel keeps the sum of squares current as it updates, so
+        # its steps pass over the model only once per epoch (to shed the rounding of the running sum)
+        self.wsq = torch.zeros(1, dtype=torch.float64, device=self.device)
+        self.norm_scratch = torch.zeros(int(L.lib().skml_weight_norm_scratch_bytes()) // 8, dtype=torch.float64,
+                                        device=self.device)
+        self._norm_seeded = False
         if self.mode == "sketch":
             self.comp = GpuCompressor(dim, bound, conf.quant_bin_num, conf.sketch_group_num, conf.sketch_row_num,
                                       conf.sketch_col_ratio, conf.seed, self.device,
@@ -101,6 +109,8 @@ class GpuEngine:
             self.dec = GpuDecoder(dim, bound * comm.world, self.device, fused=bool(conf.extras.get("fused", True)),
                                   budget_s=conf.step_timeout_s, max_groups=conf.sketch_group_num,
                                   table_capacity=self._table_scratch_bytes(conf, bound, comm.world))
+            if self.reg_every_step and m.loss.is_l2_reg and conf.extras.get("track_norm", True):
+                self.dec.track_norm(self.wsq, self.partials_template[2:3], m.loss.lam)
             from .parallel.exchange import PeerExchange
             self.xchg = PeerExchange(comm, self.comp.capacity, self.device)
             self._prepare_fast_step()
@@ -119,10 +129,13 @@ class GpuEngine:
             self.kv_vals = torch.zeros((comm.world, bound), dtype=torch.float32, device=self.device)
             self.kv_counts = torch.zeros(comm.world, dtype=torch.int64, device=self.device)
             self.kv_acc = torch.zeros(dim, dtype=torch.float32, device=self.device)
-            self.fp_codec = None
+            self.fp_codec = self.zip_codec = None
             if self.value_quant == C.COMPRESSOR_FIXED_POINT:
                 from .ops.baseline_quant import FixedPointCodec
                 self.fp_codec = FixedPointCodec(bound, conf.fixed_point_bit_num, comm.world, self.device)
+            elif self.value_quant == C.COMPRESSOR_ZIP:
+                from .ops.baseline_quant import ZipCodec
+                self.zip_codec = ZipCodec(bound, conf.quant_bin_num, comm.world, self.device)
         else:
             self.dense_sum = torch.zeros(dim, dtype=torch.float32, device=self.device)
         # the prepared gradient path serves every arm alike (the uncompressed baselines too)
@@ -255,8 +268,7 @@ class GpuEngine:
             if rows != self._template_rows:
                 self.partials_template[0] = float(rows)
                 self._template_rows = rows
-            if self.reg_every_step and m.loss.is_l2_reg:
-                self.partials_template[2:3].copy_(torch.linalg.vector_norm(m.weights).double() * m.loss.lam)
+            self._refresh_reg_loss()
             self._pending = (csr, segs, rows, done_event)
             self.deferred_release = done_event is not None
             m.optimizer.advance()
@@ -266,10 +278,7 @@ class GpuEngine:
         if rows != self._template_rows:
             self.partials_template[0] = float(rows)
             self._template_rows = rows
-        if self.reg_every_step and m.loss.is_l2_reg:
-            # reg loss = lambda * ||w||_2 (un-squared, ml/objective/Loss.scala:48-53); an O(dim) pass,
-            # so large models refresh it once per epoch instead
-            self.partials_template[2:3].copy_(torch.linalg.vector_norm(m.weights).double() * m.loss.lam)
+        self._refresh_reg_loss()
         lam = m.loss.get_reg_param() if m.loss.is_l2_reg else 0.0
         if getattr(self, "depth", 0) == 1 and self.mode == "sketch":
             par = self.batch_index & 1
@@ -298,6 +307,22 @@ class GpuEngine:
         m.optimizer.advance()
         h = _BatchHandle(rows, self.batch_index)
         return h, None, None
+
+    def _refresh_reg_loss(self, force: bool = False) -> None:
+        """Leaves lambda * ||w||_2 (un-squared, ml/objective/Loss.scala:48-53) of the current model in the
+        loss template. Models above 4M coordinates skip the per-batch term (`resolve_losses` adds one
+        value per epoch) unless ``extras["reg_loss_every_step"]`` asks for it."""
+        m = self.t.model
+        if not (self.reg_every_step and m.loss.is_l2_reg):
+            return
+        tracked = self.mode == "sketch" and self.dec.norm_track is not None
+        if tracked and self._norm_seeded and not force and self.batch_index % max(self.conf.batch_num, 1):
+            return  # the decode kernel of the previous step left the value
+        L.check(L.lib().skml_weight_norm(L.ptr(m.weights), m.weights.numel(), float(m.loss.lam), L.ptr(self.wsq),
+                                         L.ptr(self.partials_template[2:3]), L.ptr(self.norm_scratch), L.stream()),
+                "skml_weight_norm")
+        L.count_launches(1)
+        self._norm_seeded = True
 
     @staticmethod
     def _table_scratch_bytes(conf, bound, world):
@@ -361,8 +386,8 @@ class GpuEngine:
                 self._maybe_shadow(step, st, None)
         if self.mode != "sketch" and self.value_quant:
             self._quantize_values(step)
-        if self.mode == "nccl_kv" and self.fp_codec is not None:
-            self._exchange_fixed_point(step, lr, am, av, adam_scale, ring)
+        if self.mode == "nccl_kv" and (self.fp_codec is not None or self.zip_codec is not None):
+            self._exchange_coded(step, lr, am, av, adam_scale, ring)
             self.batch_index += 1
             return
         if self.mode == "sketch":
@@ -384,8 +409,9 @@ class GpuEngine:
                 dist.all_reduce(st.partials)
                 L.check(L.lib().skml_scatter_kv(L.ptr(self.kv_acc), L.ptr(self.kv_keys), L.ptr(self.kv_vals),
                                                 L.ptr(self.kv_counts), self.n_max, comm.world, L.stream()), "scatter_kv")
-                update_dense(m.weights, self.kv_acc, 1.0 / comm.world, lr, am, av, adam_scale, sparse_only=True)
-                self.kv_acc.zero_()
+                # update and clear on the gathered coordinates only: nothing here is proportional to dim
+                update_gathered(m.weights, self.kv_acc, self.kv_keys, self.kv_counts, self.n_max, comm.world,
+                                1.0 / comm.world, lr, am, av, adam_scale)
             else:
                 update_sparse(m.weights, st.keys, st.vals, st.meta, self.n_max, 1.0, lr, am, av, adam_scale)
             ring.copy_(st.partials)
@@ -413,21 +439,29 @@ class GpuEngine:
                       conf.sketch_group_num, conf.sketch_row_num, conf.sketch_col_ratio, self.comp.seed)
         self.shadow_checks = getattr(self, "shadow_checks", 0) + 1
 
-    def _exchange_fixed_point(self, step, lr, am, av, adam_scale, ring) -> None:
-        """FixedPoint baseline: packed b-bit codes and raw keys are what crosses NVLink."""
-        st, comm, m, fp = self.st, self.t.comm, self.t.model, self.fp_codec
-        fp.pack(st.vals, st.meta[:1], self._fp_seed(step))
+    def _exchange_coded(self, step, lr, am, av, adam_scale, ring) -> None:
+        """FixedPoint / Zip baselines: packed codes (plus the norm or the midpoint table) and raw keys are
+        what crosses NVLink."""
+        st, comm, m = self.st, self.t.comm, self.t.model
+        fp, zp = self.fp_codec, self.zip_codec
+        if fp is not None:
+            fp.pack(st.vals, st.meta[:1], self._fp_seed(step))
+            codes, side, all_codes, all_side = fp.codes, fp.norm, getattr(fp, "all_codes", None), getattr(fp, "all_norms", None)
+        else:
+            zp.pack(st.vals, st.meta[:1])
+            codes, side, all_codes, all_side = zp.codes, zp.mids, getattr(zp, "all_codes", None), getattr(zp, "all_mids", None)
+        codec = fp if fp is not None else zp
         if comm.world > 1:
             dist.all_gather_into_tensor(self.kv_keys.view(-1), st.keys)
-            dist.all_gather_into_tensor(fp.all_codes.view(-1), fp.codes)
+            dist.all_gather_into_tensor(all_codes.view(-1), codes)
             dist.all_gather_into_tensor(self.kv_counts, st.meta[:1])
-            dist.all_gather_into_tensor(fp.all_norms, fp.norm)
+            dist.all_gather_into_tensor(all_side.view(-1), side)
             dist.all_reduce(st.partials)
-            fp.unpack(self.kv_keys, fp.all_codes, fp.all_norms, self.kv_counts, comm.world, acc=self.kv_acc)
-            update_dense(m.weights, self.kv_acc, 1.0 / comm.world, lr, am, av, adam_scale, sparse_only=True)
-            self.kv_acc.zero_()
+            codec.unpack(self.kv_keys, all_codes, all_side, self.kv_counts, comm.world, acc=self.kv_acc)
+            update_gathered(m.weights, self.kv_acc, self.kv_keys, self.kv_counts, self.n_max, comm.world,
+                            1.0 / comm.world, lr, am, av, adam_scale)
         else:
-            fp.unpack(st.keys, fp.codes, fp.norm, st.meta[:1], 1, vals_out=st.vals)
+            codec.unpack(st.keys, codes, side, st.meta[:1], 1, vals_out=st.vals)
             update_sparse(m.weights, st.keys, st.vals, st.meta, self.n_max, 1.0, lr, am, av, adam_scale)
         ring.copy_(st.partials)
 
@@ -435,11 +469,13 @@ class GpuEngine:
         return self.conf.seed * 1315423911 + step * 8191 + self.t.comm.rank
 
     def _quantize_values(self, step: int) -> None:
-        from .ops.baseline_quant import fixed_point_roundtrip, zipml_roundtrip
+        """Dense gradient kind (and the dense all-reduce arm) under a value quantizer: the values are
+        replaced in place by what the quantizer would decode to."""
+        from .ops.baseline_quant import ZipCodec, fixed_point_roundtrip
         st, conf = self.st, self.conf
-        if getattr(self, "fp_codec", None) is not None:
-            return  # sparse lists are quantized by the pack kernel
-        targets = [(st.vals, st.meta[0])]
+        targets = []
+        if getattr(self, "fp_codec", None) is None and getattr(self, "zip_codec", None) is None:
+            targets.append((st.vals, st.meta[0]))   # sparse lists are otherwise coded by the pack kernels
         if st.dense_vals is not None:
             targets.append((st.dense_vals, torch.where(st.meta[1] == 2, st.meta[0] * 0 + st.dim, st.meta[0] * 0)))
         for vals, n in targets:
@@ -447,7 +483,11 @@ class GpuEngine:
                 fixed_point_roundtrip(vals, n, conf.fixed_point_bit_num,
                                       conf.seed * 1315423911 + step * 8191 + self.t.comm.rank)
             else:
-                zipml_roundtrip(vals, n, conf.quant_bin_num)
+                cache = self.__dict__.setdefault("_zip_roundtrip", {})
+                zc = cache.get(vals.numel())
+                if zc is None:
+                    zc = cache[vals.numel()] = ZipCodec(vals.numel(), conf.quant_bin_num, 1, self.device)
+                zc.roundtrip(vals, n.reshape(1))
 
     def _densify(self) -> None:
         st = self.st
@@ -456,6 +496,10 @@ class GpuEngine:
                                         1, L.stream()), "scatter_kv")
         if st.dense_vals is not None:  # dense kind: the compaction wrote every coordinate instead of a list
             self.dense_sum.copy_(torch.where(st.meta[1] == 2, st.dense_vals, self.dense_sum))
+
+    def after_resume(self) -> None:
+        """The weights were replaced from outside (checkpoint): the running sum of squares is stale."""
+        self._norm_seeded = False
 
     def check(self) -> None:
         """Reads the status word (synchronises) and raises on a kernel-reported error."""

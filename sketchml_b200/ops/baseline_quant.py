@@ -5,10 +5,9 @@ the b-bit codes are what travels between ranks (4 + b/8 bytes per non-zero), key
 the reference (ml/gradient/FixedPointGradient.scala:27-30). `fixed_point_roundtrip` is the
 same arithmetic in torch ops, kept for the dense gradient kind.
 
-Zip: `zipml_roundtrip` (torch ops) turns the values into the values the reference's ZipML
-compressor would decode to (keys raw, ml/gradient/ZipGradient.scala:27-30); the values are
-exchanged dequantized (fp32) through the raw key/value all-gather path, so the byte saving of
-its packed codes is not realised on the wire.
+Zip: `ZipCodec` wraps the ZipML kernels (csrc/cuda/zipml_kernels.cu): split search, one bucket
+code per value and the table of bucket midpoints; codes, table and raw keys are what travels
+(keys raw as in the reference, ml/gradient/ZipGradient.scala:27-30).
 
 Reference: ml/gradient/FixedPointGradient.scala:39-75 (sign + (b-1)-bit magnitude of
 floor(|v| / ||v||_2 * max) + Bernoulli(1/2)), ml/gradient/ZipGradient.scala:70-129 (sorted
@@ -74,45 +73,51 @@ def fixed_point_roundtrip(vals: torch.Tensor, n: torch.Tensor, num_bits: int, se
     vals.copy_(torch.where(live, out.float(), vals))
 
 
-def zipml_roundtrip(vals: torch.Tensor, n: torch.Tensor, bin_num: int) -> None:
-    """In place on vals[:n]: every value is replaced by the midpoint of its ZipML bucket."""
-    cnt = int(n.item())  # the halving loop is data dependent: this baseline synchronises
-    if cnt == 0:
-        return
-    v = vals[:cnt].double()
-    s, _ = torch.sort(v)
-    r = torch.cumsum(s, 0)
-    t = torch.cumsum(s * s, 0)
-    idx = torch.arange(cnt, device=v.device)
-    split_num = cnt
-    while split_num > bin_num:
-        pairs = split_num // 2
-        L = idx[0:2 * pairs:2]
-        nxt = torch.cat([idx[2:2 * pairs:2], idx.new_tensor([cnt])]) if 2 * pairs >= split_num else idx[2:2 * pairs + 1:2]
-        R = nxt[:pairs] - 1
-        rl = torch.where(L > 0, r[(L - 1).clamp_min(0)], torch.zeros_like(r[L]))
-        tl = torch.where(L > 0, t[(L - 1).clamp_min(0)], torch.zeros_like(t[L]))
-        l1, l2 = r[R] - rl, t[R] - tl
-        m = (R - L + 1).double()
-        mean = l1 / m
-        err = l2 + mean * mean * m - 2 * mean * l1
-        odd = split_num % 2
-        thr_num = min(max(1, bin_num // 2 - odd), pairs)
-        thr = torch.topk(err, thr_num).values[-1]
-        keep_second = err >= thr
-        # keep at most thr_num second halves (ties at the threshold are cut in index order)
-        over = torch.cumsum(keep_second.long(), 0) > thr_num
-        keep_second = keep_second & ~over
-        firsts = idx[0:2 * pairs:2]
-        seconds = idx[1:2 * pairs:2][keep_second]
-        new = torch.sort(torch.cat([firsts, seconds] + ([idx[split_num - 1:split_num]] if odd else []))).values
-        if new.numel() >= split_num:
-            break
-        idx = torch.cat([new, idx[new.numel():]])
-        split_num = new.numel()
-    splits = torch.unique_consecutive(s[idx[1:split_num]]) if split_num > 1 else s[:1]
-    lo, hi = s[0], s[-1]
-    edges = torch.cat([lo.view(1), splits, hi.view(1)])
-    mids = 0.5 * (edges[:-1] + edges[1:])
-    bins = torch.searchsorted(splits, v, right=True)
-    vals[:cnt] = mids[bins].float()
+class ZipCodec:
+    """ZipML quantizer on the device for up to ``n_max`` values: ``pack`` leaves one bucket code per value
+    (``code_bytes`` each) and the table of bucket midpoints; these and the raw keys are what travels
+    between ranks. No step of it reads anything back to the host."""
+
+    def __init__(self, n_max: int, bin_num: int, world: int, device):
+        self.lib = L.lib()
+        self.n_max, self.bin_num, self.world = int(n_max), int(bin_num), int(world)
+        if not 2 <= self.bin_num <= 8190:
+            raise ValueError(f"Zip compressor: bin number out of range: {bin_num}")
+        self.code_bytes = int(self.lib.skml_zipml_code_bytes(self.bin_num))
+        self.table_len = int(self.lib.skml_zipml_table_len(self.bin_num))
+        self.code_stride = (self.n_max * self.code_bytes + 15) // 16 * 16
+        self.scratch_bytes = int(self.lib.skml_zipml_scratch_bytes(self.n_max))
+        if self.scratch_bytes <= 0:
+            raise ValueError(f"Zip compressor: cannot size the scratch for {n_max} values")
+        self.scratch = torch.zeros(self.scratch_bytes, dtype=torch.uint8, device=device)
+        self.codes = torch.zeros(self.code_stride, dtype=torch.uint8, device=device)
+        self.splits = torch.zeros(self.table_len, dtype=torch.float32, device=device)
+        self.mids = torch.zeros(self.table_len, dtype=torch.float32, device=device)
+        self.meta = torch.zeros(4, dtype=torch.int32, device=device)
+        self.range = torch.zeros(2, dtype=torch.float32, device=device)
+        if world > 1:
+            self.all_codes = torch.zeros((world, self.code_stride), dtype=torch.uint8, device=device)
+            self.all_mids = torch.zeros((world, self.table_len), dtype=torch.float32, device=device)
+
+    def pack(self, vals: torch.Tensor, n: torch.Tensor) -> None:
+        """vals[:n] -> self.codes, self.mids, self.meta (n: device int64 scalar / 1-element view)."""
+        L.check(self.lib.skml_zipml_pack(L.ptr(vals), L.ptr(n), self.n_max, self.bin_num, L.ptr(self.scratch),
+                                         self.scratch_bytes, L.ptr(self.splits), L.ptr(self.mids), L.ptr(self.meta),
+                                         L.ptr(self.range), L.ptr(self.codes), L.stream()), "skml_zipml_pack")
+        L.count_launches(4)
+
+    def unpack(self, keys, codes: torch.Tensor, mids: torch.Tensor, counts: torch.Tensor, lists: int,
+               acc: torch.Tensor = None, vals_out: torch.Tensor = None) -> None:
+        L.check(self.lib.skml_zipml_unpack_scatter(L.ptr(acc), L.ptr(keys), L.ptr(codes), L.ptr(mids), L.ptr(counts),
+                                                   self.n_max, self.code_stride, lists, self.bin_num, L.ptr(vals_out),
+                                                   L.stream()), "skml_zipml_unpack_scatter")
+        L.count_launches(lists)
+
+    def roundtrip(self, vals: torch.Tensor, n: torch.Tensor) -> None:
+        """In place on vals[:n]: every value is replaced by the midpoint of its bucket."""
+        self.pack(vals, n)
+        self.unpack(None, self.codes, self.mids, n, 1, vals_out=vals)
+
+    def wire_bytes(self, n: int) -> int:
+        """Bytes one rank contributes for n non-zeros: raw keys, codes, the midpoint table and the count."""
+        return 4 * n + n * self.code_bytes + 4 * self.table_len + 8

@@ -174,6 +174,12 @@ class GpuDecoder:
         self.workspace = torch.zeros(256, dtype=torch.uint8, device=self.device)
         self.table_capacity = int(table_capacity) if table_capacity > 0 else 2 * self.key_capacity + 4096
         self.table_scratch = torch.zeros(self.table_capacity, dtype=torch.uint8, device=self.device)
+        self.norm_track = None  # (sum of w^2, where lambda * ||w|| goes, lambda): see track_norm
+
+    def track_norm(self, sumsq: torch.Tensor, reg_out: torch.Tensor, lam: float) -> None:
+        """From now on every update keeps ``sumsq`` (device double, the caller seeds it with the model's sum
+        of squares) current and leaves ``lam * sqrt(sumsq)`` in ``reg_out`` (device double) at its end."""
+        self.norm_track = (sumsq, reg_out, float(lam))
 
     def reset(self) -> None:
         self.workspace.zero_()
@@ -199,6 +205,8 @@ class GpuDecoder:
         a.fused, a.grid, a.max_groups = int(self.fused), self.grid, self.max_groups
         a.val_scratch = L.ptr(self.val_scratch)
         a.table_scratch, a.table_capacity = L.ptr(self.table_scratch), self.table_capacity
+        if self.norm_track is not None and w is not None:
+            a.weight_sumsq, a.reg_out, a.reg_lambda = L.ptr(self.norm_track[0]), L.ptr(self.norm_track[1]), self.norm_track[2]
         return a
 
     def decode_update(self, payload_ptrs: Sequence[int], flag_ptrs: Sequence[Optional[int]], slot_capacity: int,

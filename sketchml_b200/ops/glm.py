@@ -119,6 +119,15 @@ def update_dense(w, g, scale: float, lr: float, m=None, v=None, adam_scale: floa
                                       adam_scale, int(sparse_only), L.stream()), "skml_update_dense")
 
 
+def update_gathered(w, acc, keys, counts, stride: int, lists: int, scale: float, lr: float, m=None, v=None,
+                    adam_scale: float = 1.0):
+    """Applies ``acc[key] * scale`` on the coordinates of the gathered key lists and clears them."""
+    L.check(L.lib().skml_update_gathered(L.ptr(w), L.ptr(m), L.ptr(v), L.ptr(acc), L.ptr(keys), L.ptr(counts), stride,
+                                         lists, scale, int(v is not None), lr, adam_scale, L.stream()),
+            "skml_update_gathered")
+    L.count_launches(lists)
+
+
 def update_sparse(w, keys, vals, n_ptr: Optional[torch.Tensor], n_max: int, scale: float, lr: float, m=None, v=None,
                   adam_scale: float = 1.0):
     L.check(L.lib().skml_update_sparse(L.ptr(w), L.ptr(m), L.ptr(v), L.ptr(keys), L.ptr(vals), L.ptr(n_ptr), n_max,

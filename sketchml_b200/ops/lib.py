@@ -46,6 +46,7 @@ class DecodeArgs(C.Structure):
         ("adam_scale", c_d), ("acc", c_vp), ("key_scratch", c_vp), ("key_capacity", c_ll), ("loss_out", c_vp),
         ("out_sum", c_vp), ("workspace", c_vp), ("status", c_vp), ("budget_cycles", c_ll), ("fused", c_ll),
         ("grid", c_ll), ("max_groups", c_ll), ("val_scratch", c_vp), ("table_scratch", c_vp), ("table_capacity", c_ll),
+        ("weight_sumsq", c_vp), ("reg_out", c_vp), ("reg_lambda", c_d),
     ]
 
 
@@ -82,6 +83,9 @@ _SIGS = {
     "skml_update_dense": (c_int, [c_vp, c_vp, c_vp, c_vp, c_ll, c_f, c_int, c_f, c_f, c_int, c_vp]),
     "skml_update_sparse": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_ll, c_f, c_int, c_f, c_f, c_vp]),
     "skml_scatter_kv": (c_int, [c_vp, c_vp, c_vp, c_vp, c_ll, c_int, c_vp]),
+    "skml_weight_norm_scratch_bytes": (c_ll, []),
+    "skml_weight_norm": (c_int, [c_vp, c_ll, c_d, c_vp, c_vp, c_vp, c_vp]),
+    "skml_update_gathered": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_ll, c_int, c_f, c_int, c_f, c_f, c_vp]),
     "skml_gen_wstar": (c_int, [c_vp, c_ll, c_d, c_ull, c_vp]),
     "skml_gen_rows": (c_int, [c_vp, c_vp, c_vp, c_ll, c_ll, c_int, c_int, c_d, c_int, c_int, c_f, c_vp, c_ull, c_vp]),
     "skml_glm_coef": (c_int, [c_vp, c_vp, c_vp, c_vp, c_ll, c_ll, c_ll, c_d, c_vp, c_int, c_f, c_vp, c_vp, c_vp, c_ll, c_vp]),
@@ -101,6 +105,11 @@ _SIGS = {
     "skml_fixedpoint_scratch_bytes": (c_ll, []),
     "skml_fixedpoint_code_bytes": (c_ll, [c_ll, c_int]),
     "skml_fixedpoint_pack": (c_int, [c_vp, c_vp, c_ll, c_int, c_ull, c_vp, c_vp, c_vp, c_vp]),
+    "skml_zipml_scratch_bytes": (c_ll, [c_ll]),
+    "skml_zipml_code_bytes": (c_int, [c_int]),
+    "skml_zipml_table_len": (c_int, [c_int]),
+    "skml_zipml_pack": (c_int, [c_vp, c_vp, c_ll, c_int, c_vp, c_ll, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "skml_zipml_unpack_scatter": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_ll, c_ll, c_int, c_int, c_vp, c_vp]),
     "skml_fixedpoint_unpack_scatter": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_ll, c_ll, c_int, c_int, c_vp, c_vp]),
     "skml_train_step": (c_int, [C.POINTER(StepArgs), c_vp]),
     "skml_ipc_get_handle": (c_int, [c_vp, c_vp]),

@@ -442,3 +442,60 @@ def test_delta_adaptive_device_codec_rejects_unsorted_keys():
     from sketchml_b200.ops import keys as K
     with pytest.raises(ValueError):
         K.encode(torch.tensor([1, 5, 5, 9], dtype=torch.int32, device="cuda"))
+
+
+def _zip_pack(vals, bins):
+    from sketchml_b200.ops.baseline_quant import ZipCodec
+    n = len(vals)
+    zc = ZipCodec(max(n, 1) + 37, bins, 1, "cuda")   # a capacity above n: the padding must not disturb the search
+    v = torch.zeros(zc.n_max, device="cuda")
+    v[:n] = torch.from_numpy(vals).cuda()
+    cnt = torch.tensor([n], dtype=torch.int64, device="cuda")
+    zc.pack(v, cnt)
+    nb, zero, rounds = (int(x) for x in zc.meta[:3].cpu())
+    codes = zc.codes.cpu().numpy()
+    codes = codes[:n] if zc.code_bytes == 1 else codes[:2 * n].view(np.uint16)
+    return zc, v, cnt, nb, zero, rounds, zc.splits[:max(nb - 1, 0)].cpu().numpy(), zc.mids[:nb].cpu().numpy(), codes.astype(np.int64)
+
+
+@pytest.mark.parametrize("n,bins", [(1, 16), (2, 2), (3, 2), (77, 8), (1000, 256), (4097, 33), (50001, 256), (300000, 300)])
+def test_zipml_device_quantizer_equals_oracle_on_exact_sums(n, bins):
+    """Values on a dyadic grid make every prefix sum exact in double, whatever the order of the adds,
+    so the device search must pick the very split points of the CPU oracle, round by round."""
+    from sketchml_b200.compress import oracle
+    rng = np.random.default_rng(n + bins)
+    vals = (rng.integers(-2000, 2000, n) / 1024.0).astype(np.float32)
+    ref = oracle.zipml_quantize(vals.astype(np.float64), bins)
+    zc, v, cnt, nb, zero, rounds, splits, mids, codes = _zip_pack(vals, bins)
+    assert nb == ref["bin_num"] and zero == ref["zero_idx"]
+    assert np.array_equal(splits.astype(np.float64), ref["splits"])
+    assert np.array_equal(mids, ref["values"].astype(np.float32))
+    assert np.array_equal(codes, ref["bins"])
+    # decode: every value becomes its bucket's midpoint; the accumulating form adds them at the keys
+    out = torch.zeros_like(v)
+    zc.unpack(None, zc.codes, zc.mids, cnt, 1, vals_out=out)
+    assert np.array_equal(out[:n].cpu().numpy(), ref["values"].astype(np.float32)[ref["bins"]])
+    keys = torch.from_numpy(np.sort(rng.choice(4 * n + 8, n, replace=False)).astype(np.int32)).cuda()
+    kfull = torch.zeros(zc.n_max, dtype=torch.int32, device="cuda")
+    kfull[:n] = keys
+    acc = torch.zeros(4 * n + 8, device="cuda")
+    zc.unpack(kfull, zc.codes, zc.mids, cnt, 1, acc=acc)
+    assert torch.equal(acc[keys.long()], out[:n]) and int(torch.count_nonzero(acc)) <= n
+
+
+@pytest.mark.parametrize("bins", [16, 256])
+def test_zipml_device_quantizer_quality_and_empty_input(bins):
+    """Real-valued input: the order of the prefix-sum adds differs from the sequential oracle, so near
+    ties may fall the other way; the quantization error must still match the oracle's closely."""
+    from sketchml_b200.compress import oracle
+    _, vals = _sparse_grad(120000, 10 ** 6, seed=5)
+    ref = oracle.zipml_quantize(vals.astype(np.float64), bins)
+    zc, v, cnt, nb, zero, rounds, splits, mids, codes = _zip_pack(vals, bins)
+    assert 2 <= nb <= bins and rounds >= 8 and np.all(np.diff(splits) > 0)
+    err_dev = np.mean((mids[codes].astype(np.float64) - vals) ** 2)
+    err_ref = np.mean((ref["values"][ref["bins"]] - vals) ** 2)
+    assert err_dev <= err_ref * 1.02 + 1e-18, (err_dev, err_ref)
+    assert np.all(vals >= np.concatenate([[vals.min()], splits])[codes]) and np.all(vals <= np.concatenate([splits, [vals.max()]])[codes])
+    cnt.zero_()
+    zc.pack(v, cnt)
+    assert int(zc.meta[0]) == 0

@@ -70,6 +70,29 @@ def test_wire_codecs_are_lossless_and_shrink_the_payload():
     assert sizes[("delta_adaptive", 0)] == min(sizes.values())
 
 
+@pytest.mark.parametrize("opt", ["sgd", "adam"])
+def test_running_weight_norm_matches_a_pass_over_the_model(opt):
+    """The decode kernel keeps sum(w^2) current while it updates (no pass over the model per step): the
+    per-epoch losses equal those of a run that recomputes the norm every step, and the running sum
+    equals the model's at the end."""
+    from sketchml_b200.trainer import Trainer
+    kw = dict(compressor="Sketch", optimizer=opt, learn_rate=0.5 if opt == "sgd" else 0.01, l2_reg=1e-2, valid_ratio=0.0,
+              epoch_num=2)
+    res = {}
+    for track in (True, False):
+        t = Trainer(_conf(extras={"track_norm": track}, **kw))
+        t.load_data()
+        h = t.train()
+        w = t.model.weights.detach().double()
+        res[track] = (h["train_loss"], w.clone(), float(t.engine.wsq.item()))
+        assert (t.engine.dec.norm_track is not None) == track
+        t.close()
+    assert torch.equal(res[True][1], res[False][1])
+    assert np.allclose(res[True][0], res[False][0], rtol=1e-6, atol=0)
+    true_sq = float((res[True][1] ** 2).sum())
+    assert abs(res[True][2] - true_sq) <= 1e-5 * true_sq, (res[True][2], true_sq)
+
+
 def test_gpu_uncompressed_matches_host_engine():
     from sketchml_b200.data import SyntheticSpec, generate_cpu
     spec = SyntheticSpec(6000, 8000, 15, 1.1, "binary", "logistic", 0.1, 0.0, 3)
