@@ -184,18 +184,43 @@ extern "C" long long skml_payload_capacity(long long n_max, long long dim, long 
 // ---------------------------------------------------------------------------
 // shared memory carve-up (dynamic, one block per SM)
 // ---------------------------------------------------------------------------
-struct Smem {
-    // stage S1
+// Per-warp scratch of the Huffman code construction.
+struct HufScratch {
+    unsigned int w[HUF_MAX_SYMS];         // leaf weights, ascending
+    unsigned int iw[HUF_MAX_SYMS];        // weights of the internal nodes, in creation order (ascending)
+    unsigned short ord[HUF_MAX_SYMS];     // symbol of the i-th lightest leaf
+    unsigned short pl[HUF_MAX_SYMS];      // parent (internal node) of every leaf
+    unsigned short pi[HUF_MAX_SYMS];      // parent of every internal node
+    unsigned char di[HUF_MAX_SYMS];       // depth of every internal node
+};
+
+// The quantile stages (S1, S2) and the coding stage (S5) never hold data at the same time, so their
+// arrays share one region: the smaller the block's shared memory, the more of the SM's 256 KB is left
+// as L1 for the scatter and coding passes, which keep many loads in flight.
+struct SmemQuantile {
     unsigned int tile[TILE];
     unsigned int levels[MAX_LEVELS][SK_K];
     unsigned int run[SK_K];
     unsigned int merge[2 * SK_K];
     unsigned int tail[SK_K];
     unsigned long long e_acc[SK_K];
-    // stage S2 (all blocks' runs)
-    unsigned int runs_all[MAX_GRID * SK_K];
+    unsigned int runs_all[MAX_GRID * SK_K];   // S2: all blocks' runs
     unsigned int runs_cnt[MAX_GRID];
     unsigned long long runs_w[MAX_GRID];
+};
+struct SmemCoding {
+    unsigned int stage_f[4][AP_STAGE_F];            // delta_adaptive: one chunk's flag / delta bits per sub-block
+    unsigned int stage_d[4][AP_STAGE_D];            // (also the staging of the Huffman table streams)
+    unsigned char huf_len[SKML_GPU_MAX_BINS + SKML_MAX_GROUPS];   // Huffman: code length / code word per symbol slot
+    unsigned int huf_code[SKML_GPU_MAX_BINS + SKML_MAX_GROUPS];
+    HufScratch huf_scratch[8];
+};
+
+struct Smem {
+    union {
+        SmemQuantile qs;
+        SmemCoding cs;
+    };
     // stages S3..S6
     float splits[SKML_GPU_MAX_BINS];
     unsigned char grp_lut[SKML_GPU_MAX_BINS];      // bucket -> group
@@ -206,10 +231,6 @@ struct Smem {
     unsigned long long my_bytes[SKML_MAX_GROUPS];   // delta bytes of the chunks this block owns, per group
     unsigned long long pre_bytes[SKML_MAX_GROUPS];  // the same, summed over the blocks before this one
     unsigned long long my_bits[2 * SKML_MAX_GROUPS], pre_bits[2 * SKML_MAX_GROUPS];  // delta_adaptive: flag / delta bits
-    unsigned int stage_f[4][AP_STAGE_F];            // delta_adaptive: one chunk's flag / delta bits per sub-block
-    unsigned int stage_d[4][AP_STAGE_D];
-    unsigned char huf_len[SKML_GPU_MAX_BINS + SKML_MAX_GROUPS];   // Huffman: code length / code word per symbol slot
-    unsigned int huf_code[SKML_GPU_MAX_BINS + SKML_MAX_GROUPS];
     unsigned long long my_tbits[SKML_MAX_GROUPS], pre_tbits[SKML_MAX_GROUPS];
     unsigned int sub_part[4][8];                    // scan scratch of the four 256-thread sub-blocks
     unsigned int sub_total[4];
@@ -218,7 +239,10 @@ struct Smem {
 };
 
 
-static_assert(sizeof(Smem) <= 227 * 1024, "the compress kernels' shared memory must fit one SM");
+// 164 KB is a shared-memory carve-out step of the SM: staying under it (with the block's static shared
+// memory and the 1 KB the system reserves) leaves 92 KB of L1; measured, the scatter + insert stage of
+// 2.3M keys takes 69 us with that L1 and 120 us with the 28 KB that the next step (228 KB) leaves.
+static_assert(sizeof(Smem) <= 162 * 1024, "the compress kernels' shared memory must stay below the 164 KB carve-out");
 
 __device__ __forceinline__ unsigned int lanemask_lt() {
     unsigned int m;
@@ -239,39 +263,39 @@ __device__ __forceinline__ void stage_stamp(unsigned int* ctrl, int i) {
 // ---------------------------------------------------------------------------
 // S1: quantile summary
 // ---------------------------------------------------------------------------
-// Merge the sorted runs a[128] and b[128] into s.merge (ascending) with a bitonic merge.
+// Merge the sorted runs a[128] and b[128] into s.qs.merge (ascending) with a bitonic merge.
 __device__ __forceinline__ void merge_runs(Smem& s, const unsigned int* a, const unsigned int* b) {
     for (int t = threadIdx.x; t < SK_K; t += blockDim.x) {
-        s.merge[t] = a[t];
-        s.merge[2 * SK_K - 1 - t] = b[t];
+        s.qs.merge[t] = a[t];
+        s.qs.merge[2 * SK_K - 1 - t] = b[t];
     }
     __syncthreads();
     for (int j = SK_K; j > 0; j >>= 1) {
         for (int t = threadIdx.x; t < SK_K; t += blockDim.x) {
             int i = ((t & ~(j - 1)) << 1) | (t & (j - 1));
-            unsigned int x = s.merge[i], y = s.merge[i | j];
+            unsigned int x = s.qs.merge[i], y = s.qs.merge[i | j];
             if (x > y) {
-                s.merge[i] = y;
-                s.merge[i | j] = x;
+                s.qs.merge[i] = y;
+                s.qs.merge[i | j] = x;
             }
         }
         __syncthreads();
     }
 }
 
-// Carry s.run (weight TILE_W << level0) up the level chain.
+// Carry s.qs.run (weight TILE_W << level0) up the level chain.
 __device__ __forceinline__ void carry_run(Smem& s, unsigned int& occupied, int level, const CP& p, unsigned long long salt) {
     while (true) {
         if (!(occupied & (1u << level))) {
-            for (int t = threadIdx.x; t < SK_K; t += blockDim.x) s.levels[level][t] = s.run[t];
+            for (int t = threadIdx.x; t < SK_K; t += blockDim.x) s.qs.levels[level][t] = s.qs.run[t];
             occupied |= 1u << level;
             __syncthreads();
             return;
         }
-        merge_runs(s, s.levels[level], s.run);
+        merge_runs(s, s.qs.levels[level], s.qs.run);
         unsigned int off = (unsigned int)(skml_rand(p.seed, p.step, ((unsigned long long)p.rank << 32) | blockIdx.x,
                                                     salt * 64 + level) & 1u);
-        for (int t = threadIdx.x; t < SK_K; t += blockDim.x) s.run[t] = s.merge[2 * t + off];
+        for (int t = threadIdx.x; t < SK_K; t += blockDim.x) s.qs.run[t] = s.qs.merge[2 * t + off];
         occupied &= ~(1u << level);
         __syncthreads();
         ++level;
@@ -279,7 +303,11 @@ __device__ __forceinline__ void carry_run(Smem& s, unsigned int& occupied, int l
     }
 }
 
-__device__ void stage_summary(const CP& p, Smem& s, const float* __restrict__ vals, long long n) {
+// The block's share of the values -> one run of at most SK_K samples in s.qs.tile[0, cnt) with weight w.
+__device__ void summarize_slice(const CP& p, Smem& s, const float* __restrict__ vals, long long n, unsigned int& run_cnt,
+                                unsigned long long& run_w) {
+    run_cnt = 0;
+    run_w = 0;
     // Bottom-level sampler (as in KLL sketches): of every f consecutive values one is kept at random
     // with weight f, so one 2048-sort covers f * 2048 values and enters the level chain as one run
     // of weight 16 f. f is the smallest power of two (<= MAX_SAMPLE) for which every block has one
@@ -293,13 +321,7 @@ __device__ void stage_summary(const CP& p, Smem& s, const float* __restrict__ va
     const long long ST = (long long)f * TILE;
     const long long nst = (n + ST - 1) / ST;
     const long long t0 = blockIdx.x;  // super tiles are dealt round-robin: t0, t0 + grid, ...
-    if (t0 >= nst || n <= 0) {
-        if (threadIdx.x == 0) {
-            p.run_cnt[blockIdx.x] = 0;
-            p.run_w[blockIdx.x] = 0;
-        }
-        return;
-    }
+    if (t0 >= nst || n <= 0) return;
     unsigned int occupied = 0;
     int tail_cnt = 0;
     unsigned long long tail_w = 0;
@@ -335,15 +357,15 @@ __device__ void stage_summary(const CP& p, Smem& s, const float* __restrict__ va
                         }
                     }
                 }
-                s.tile[t] = chosen;
+                s.qs.tile[t] = chosen;
             }
             __syncthreads();
             if (st == t0) stage_stamp(p.ctrl, 10);
-            block_sort_2048(s.tile);
+            block_sort_2048(s.qs.tile);
             if (st == t0) stage_stamp(p.ctrl, 11);
             const unsigned int off = (unsigned int)(skml_rand(p.seed, p.step, ((unsigned long long)p.rank << 32) | blockIdx.x,
                                                               0x7200u + (unsigned long long)((st - t0) / gridDim.x)) & (TILE_W - 1));
-            for (int t = threadIdx.x; t < SK_K; t += blockDim.x) s.run[t] = s.tile[t * TILE_W + off];
+            for (int t = threadIdx.x; t < SK_K; t += blockDim.x) s.qs.run[t] = s.qs.tile[t * TILE_W + off];
             __syncthreads();
             carry_run(s, occupied, lf, p, (unsigned long long)((st - t0) / gridDim.x) + 1);
             continue;
@@ -363,10 +385,10 @@ __device__ void stage_summary(const CP& p, Smem& s, const float* __restrict__ va
                     if ((unsigned int)j == pick) chosen = k;
                 }
             }
-            s.tile[t] = chosen;
+            s.qs.tile[t] = chosen;
         }
         __syncthreads();
-        block_sort_2048(s.tile);
+        block_sort_2048(s.qs.tile);
         int stride = 1;
         while ((ms + stride - 1) / stride > SK_K) stride <<= 1;
         tail_cnt = (ms + stride - 1) / stride;
@@ -374,7 +396,7 @@ __device__ void stage_summary(const CP& p, Smem& s, const float* __restrict__ va
         for (int t = threadIdx.x; t < tail_cnt; t += blockDim.x) {
             int idx = t * stride + (int)off;
             if (idx > ms - 1) idx = ms - 1;
-            s.tail[t] = s.tile[idx];
+            s.qs.tail[t] = s.qs.tile[idx];
         }
         tail_w = (((unsigned long long)m) << FP_SHIFT) / (unsigned long long)tail_cnt;
         __syncthreads();
@@ -410,24 +432,22 @@ __device__ void stage_summary(const CP& p, Smem& s, const float* __restrict__ va
         }
     }
     stage_stamp(p.ctrl, 13);
-    // collapse the levels (+ tail) into one published run
+    // collapse the levels (+ tail) into one run (the sort buffer is free now)
     int nruns = __popc(occupied) + (tail_cnt > 0 ? 1 : 0);
-    unsigned int* out = p.run_vals + (long long)blockIdx.x * SK_K;
+    unsigned int* out = s.qs.tile;
     if (nruns == 1) {
         const unsigned int* src;
         int cnt;
         unsigned long long w;
         if (tail_cnt > 0) {
-            src = s.tail; cnt = tail_cnt; w = tail_w;
+            src = s.qs.tail; cnt = tail_cnt; w = tail_w;
         } else {
             int lv = __ffs(occupied) - 1;
-            src = s.levels[lv]; cnt = SK_K; w = ((unsigned long long)TILE_W << lv) << FP_SHIFT;
+            src = s.qs.levels[lv]; cnt = SK_K; w = ((unsigned long long)TILE_W << lv) << FP_SHIFT;
         }
         for (int t = threadIdx.x; t < cnt; t += blockDim.x) out[t] = src[t];
-        if (threadIdx.x == 0) {
-            p.run_cnt[blockIdx.x] = (unsigned int)cnt;
-            p.run_w[blockIdx.x] = w;
-        }
+        run_cnt = (unsigned int)cnt;
+        run_w = w;
         return;
     }
     // several runs: exclusive cumulative weight of every sample, then 128 mid-rank samples
@@ -445,17 +465,17 @@ __device__ void stage_summary(const CP& p, Smem& s, const float* __restrict__ va
             i -= SK_K;
             ++seen;
         }
-        const unsigned int value = a >= 0 ? s.levels[a][i] : s.tail[i];
+        const unsigned int value = a >= 0 ? s.qs.levels[a][i] : s.qs.tail[i];
         const unsigned long long wa = a >= 0 ? (((unsigned long long)TILE_W << a) << FP_SHIFT) : tail_w;
         unsigned long long e = (unsigned long long)i * wa;
         for (int lv = 0; lv < MAX_LEVELS; ++lv) {
             if (!(occupied & (1u << lv)) || lv == a) continue;
             unsigned long long wl = ((unsigned long long)TILE_W << lv) << FP_SHIFT;
             bool before = a < 0 || lv < a;  // runs earlier in the order win ties
-            int c = before ? upper_bound_u(s.levels[lv], SK_K, value) : lower_bound_u(s.levels[lv], SK_K, value);
+            int c = before ? upper_bound_u(s.qs.levels[lv], SK_K, value) : lower_bound_u(s.qs.levels[lv], SK_K, value);
             e += (unsigned long long)c * wl;
         }
-        if (tail_cnt > 0 && a >= 0) e += (unsigned long long)lower_bound_u(s.tail, tail_cnt, value) * tail_w;
+        if (tail_cnt > 0 && a >= 0) e += (unsigned long long)lower_bound_u(s.qs.tail, tail_cnt, value) * tail_w;
         // targets t_j = (2j+1) * Wc / 256, j = 0..127, covered iff e <= t_j < e + wa
         long long j = (long long)((e << 7) / Wc) - 1;
         if (j < 0) j = 0;
@@ -467,9 +487,119 @@ __device__ void stage_summary(const CP& p, Smem& s, const float* __restrict__ va
         }
         (void)seen;
     }
+    run_cnt = SK_K;
+    run_w = Wc / SK_K;
+}
+
+// --- thread-block cluster primitives (distributed shared memory) ---
+__device__ __forceinline__ unsigned int cluster_ctarank() {
+    unsigned int r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ unsigned int cluster_nctarank() {
+    unsigned int r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+// hardware barrier of the cluster's blocks (blocks that have exited count as arrived)
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared-memory address of `ptr` (a location in this block's shared memory) in block `rank` of the cluster
+__device__ __forceinline__ unsigned int dsmem_addr(const void* ptr, unsigned int rank) {
+    const unsigned int a = (unsigned int)__cvta_generic_to_shared(ptr);
+    unsigned int r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ unsigned int ld_dsmem_u32(unsigned int addr) {
+    unsigned int v;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long ld_dsmem_u64(unsigned int addr) {
+    unsigned long long v;
+    asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(addr) : "memory");
+    return v;
+}
+
+// Two weighted runs a (s.qs.tile[0, ca), weight wa) and b (s.qs.tile[SK_K, SK_K + cb), weight wb) -> SK_K samples
+// at the mid ranks (2j + 1) / (2 SK_K) of their union, left in s.qs.tile[0, SK_K); returns the new weight.
+__device__ unsigned long long merge_two_runs(Smem& s, unsigned int ca, unsigned long long wa, unsigned int cb,
+                                             unsigned long long wb) {
+    const unsigned int* a = s.qs.tile;
+    const unsigned int* b = s.qs.tile + SK_K;
+    const unsigned long long Wc = (unsigned long long)ca * wa + (unsigned long long)cb * wb;
+    for (unsigned int sidx = threadIdx.x; sidx < ca + cb; sidx += blockDim.x) {
+        const bool from_a = sidx < ca;
+        const unsigned int i = from_a ? sidx : sidx - ca;
+        const unsigned int value = from_a ? a[i] : b[i];
+        const unsigned long long w = from_a ? wa : wb;
+        // weight in front of the sample; run a wins ties
+        const unsigned long long e = (unsigned long long)i * w +
+            (from_a ? (unsigned long long)lower_bound_u(b, (int)cb, value) * wb : (unsigned long long)upper_bound_u(a, (int)ca, value) * wa);
+        long long j = (long long)((e << 7) / Wc) - 1;
+        if (j < 0) j = 0;
+        for (; j < SK_K; ++j) {
+            const unsigned long long tj = (unsigned long long)(2 * j + 1) * (Wc >> 8);
+            if (tj < e) continue;
+            if (tj >= e + w) break;
+            s.qs.merge[j] = value;
+        }
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < SK_K; t += blockDim.x) s.qs.tile[t] = s.qs.merge[t];
+    __syncthreads();
+    return Wc / SK_K;
+}
+
+// S1: every block summarises its share of the values; the blocks of a thread-block cluster then merge
+// their runs in shared memory (the cluster's first block reads the others' runs through distributed
+// shared memory) and only the merged run goes to global memory, so S2 has 1 / cluster-size as many runs
+// to load and to rank against. Launched without clusters the cluster is the block itself.
+__device__ void stage_summary(const CP& p, Smem& s, const float* __restrict__ vals, long long n) {
+    __shared__ unsigned int s_pub_cnt;
+    __shared__ unsigned long long s_pub_w;
+    unsigned int cnt;
+    unsigned long long w;
+    summarize_slice(p, s, vals, n, cnt, w);
+    const unsigned int cs = cluster_nctarank(), cr = cluster_ctarank();
     if (threadIdx.x == 0) {
-        p.run_cnt[blockIdx.x] = SK_K;
-        p.run_w[blockIdx.x] = Wc / SK_K;
+        s_pub_cnt = cnt;
+        s_pub_w = w;
+    }
+    __syncthreads();
+    if (cs > 1) {
+        cluster_sync_all();   // every block's run, count and weight are in its shared memory
+        if (cr == 0) {
+            for (unsigned int r = 1; r < cs; ++r) {
+                const unsigned int cb = ld_dsmem_u32(dsmem_addr(&s_pub_cnt, r));
+                const unsigned long long wb = ld_dsmem_u64(dsmem_addr(&s_pub_w, r));
+                if (cb == 0 || cb > SK_K) continue;   // uniform over the block
+                const unsigned int src = dsmem_addr(s.qs.tile, r);
+                unsigned int* dst = cnt ? s.qs.tile + SK_K : s.qs.tile;
+                for (unsigned int t = threadIdx.x; t < cb; t += blockDim.x) dst[t] = ld_dsmem_u32(src + 4u * t);
+                __syncthreads();
+                if (cnt == 0) {
+                    cnt = cb;
+                    w = wb;
+                } else {
+                    w = merge_two_runs(s, cnt, w, cb, wb);
+                    cnt = SK_K;
+                }
+            }
+        } else {
+            cnt = 0;   // this block's samples travel in the first block's run
+            w = 0;
+        }
+        cluster_sync_all();   // nobody reads the others' shared memory any more
+    }
+    unsigned int* out = p.run_vals + (long long)blockIdx.x * SK_K;
+    for (unsigned int t = threadIdx.x; t < cnt; t += blockDim.x) out[t] = s.qs.tile[t];
+    if (threadIdx.x == 0) {
+        p.run_cnt[blockIdx.x] = cnt;
+        p.run_w[blockIdx.x] = w;
     }
 }
 
@@ -486,8 +616,8 @@ __device__ void stage_query(const CP& p, Smem& s, long long n) {
     if (n <= 0) return;
     const int nb = gridDim.x;
     for (int t = threadIdx.x; t < nb; t += blockDim.x) {
-        s.runs_cnt[t] = p.run_cnt[t];
-        s.runs_w[t] = p.run_w[t];
+        s.qs.runs_cnt[t] = p.run_cnt[t];
+        s.qs.runs_w[t] = p.run_w[t];
     }
     __syncthreads();
     {
@@ -499,51 +629,52 @@ __device__ void stage_query(const CP& p, Smem& s, long long n) {
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int t = t0 + u * blockDim.x;
-                v[u] = t < nv ? ld_cg_v4(src + t) : make_uint4(0, 0, 0, 0);
+                // runs that a cluster merged away are empty: nothing to fetch
+                v[u] = (t < nv && (4 * t) % SK_K < (int)s.qs.runs_cnt[(4 * t) / SK_K]) ? ld_cg_v4(src + t) : make_uint4(0, 0, 0, 0);
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int t = t0 + u * blockDim.x;
                 if (t >= nv) continue;
-                const int c = (4 * t) / SK_K, i = (4 * t) % SK_K, cnt = (int)s.runs_cnt[c];
-                s.runs_all[4 * t] = i < cnt ? v[u].x : 0xFFFFFFFFu;
-                s.runs_all[4 * t + 1] = i + 1 < cnt ? v[u].y : 0xFFFFFFFFu;
-                s.runs_all[4 * t + 2] = i + 2 < cnt ? v[u].z : 0xFFFFFFFFu;
-                s.runs_all[4 * t + 3] = i + 3 < cnt ? v[u].w : 0xFFFFFFFFu;
+                const int c = (4 * t) / SK_K, i = (4 * t) % SK_K, cnt = (int)s.qs.runs_cnt[c];
+                s.qs.runs_all[4 * t] = i < cnt ? v[u].x : 0xFFFFFFFFu;
+                s.qs.runs_all[4 * t + 1] = i + 1 < cnt ? v[u].y : 0xFFFFFFFFu;
+                s.qs.runs_all[4 * t + 2] = i + 2 < cnt ? v[u].z : 0xFFFFFFFFu;
+                s.qs.runs_all[4 * t + 3] = i + 3 < cnt ? v[u].w : 0xFFFFFFFFu;
             }
         }
     }
     __syncthreads();
     // total weight: every warp sums a strided share, lanes combine by shuffle (all threads need it)
     unsigned long long Wtot = 0;
-    for (int c = threadIdx.x & 31; c < nb; c += 32) Wtot += (unsigned long long)s.runs_cnt[c] * s.runs_w[c];
+    for (int c = threadIdx.x & 31; c < nb; c += 32) Wtot += (unsigned long long)s.qs.runs_cnt[c] * s.qs.runs_w[c];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) Wtot += __shfl_xor_sync(0xFFFFFFFFu, Wtot, o);
     const double inv_q = 1.0 / (double)p.q;
     const int i = threadIdx.x & (SK_K - 1), part = threadIdx.x / SK_K, parts = blockDim.x / SK_K;
     for (int c = blockIdx.x; c < nb; c += gridDim.x) {
-        const int cnt = (int)s.runs_cnt[c];
+        const int cnt = (int)s.qs.runs_cnt[c];
         if (cnt == 0) continue;  // uniform over the block
-        if (threadIdx.x < SK_K) s.e_acc[threadIdx.x] = 0ull;
+        if (threadIdx.x < SK_K) s.qs.e_acc[threadIdx.x] = 0ull;
         __syncthreads();
         if (i < cnt) {
-            const unsigned int value = s.runs_all[c * SK_K + i];
+            const unsigned int value = s.qs.runs_all[c * SK_K + i];
             unsigned long long e = 0;
             for (int c2 = part; c2 < nb; c2 += parts) {
-                int cnt2 = (int)s.runs_cnt[c2];
+                int cnt2 = (int)s.qs.runs_cnt[c2];
                 if (cnt2 == 0) continue;
                 int k;
                 if (c2 == c) k = i;
-                else if (c2 < c) k = upper_bound_u(s.runs_all + c2 * SK_K, cnt2, value);
-                else k = lower_bound_u(s.runs_all + c2 * SK_K, cnt2, value);
-                e += (unsigned long long)k * s.runs_w[c2];
+                else if (c2 < c) k = upper_bound_u(s.qs.runs_all + c2 * SK_K, cnt2, value);
+                else k = lower_bound_u(s.qs.runs_all + c2 * SK_K, cnt2, value);
+                e += (unsigned long long)k * s.qs.runs_w[c2];
             }
-            atomicAdd(&s.e_acc[i], e);
+            atomicAdd(&s.qs.e_acc[i], e);
         }
         __syncthreads();
         if (threadIdx.x < cnt) {
-            const unsigned int value = s.runs_all[c * SK_K + threadIdx.x];
-            const unsigned long long e = s.e_acc[threadIdx.x], w = s.runs_w[c];
+            const unsigned int value = s.qs.runs_all[c * SK_K + threadIdx.x];
+            const unsigned long long e = s.qs.e_acc[threadIdx.x], w = s.qs.runs_w[c];
             const bool last = e + w >= Wtot;
             // smallest t with target >= e
             int lo = 0, hi = p.q - 1;
@@ -1087,7 +1218,7 @@ __device__ void da_choose(const unsigned int* hist, unsigned int n, unsigned int
 // Pass 0: histogram of the delta widths of this block's chunks, per group, added to the global one.
 __device__ void apack_histogram(const CP& p, Smem& s, unsigned int my_begin, unsigned int my_end) {
     const Layout& L = s.lay;
-    unsigned int* hist = s.stage_d[0];  // [G][32], the staging area is idle in this pass
+    unsigned int* hist = s.cs.stage_d[0];  // [G][32], the staging area is idle in this pass
     for (int t = threadIdx.x; t < SKML_MAX_GROUPS * 32; t += blockDim.x) hist[t] = 0;
     __syncthreads();
     for (unsigned int c0 = my_begin; c0 < my_end; c0 += 4) {
@@ -1282,8 +1413,8 @@ __device__ void apack_write(const CP& p, Smem& s, unsigned int my_begin, unsigne
                 packed += kc[u].fw + (kc[u].dw << 16);
             }
         }
-        for (int i = t; i < AP_STAGE_F; i += 256) s.stage_f[sb][i] = 0;
-        for (int i = t; i < AP_STAGE_D; i += 256) s.stage_d[sb][i] = 0;
+        for (int i = t; i < AP_STAGE_F; i += 256) s.cs.stage_f[sb][i] = 0;
+        for (int i = t; i < AP_STAGE_D; i += 256) s.cs.stage_d[sb][i] = 0;
         unsigned int total;
         const unsigned int ex = sub_scan(s, packed, total);  // (its barriers also publish the cleared staging words)
         unsigned long long fs = 0, ds = 0;
@@ -1293,16 +1424,16 @@ __device__ void apack_write(const CP& p, Smem& s, unsigned int my_begin, unsigne
             unsigned int fo = (unsigned int)(fs & 31ull) + (ex & 0xFFFFu), dof = (unsigned int)(ds & 31ull) + (ex >> 16);
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                put_bits_shared(s.stage_f[sb], fo, kc[u].fv, kc[u].fw);
-                put_bits_shared(s.stage_d[sb], dof, c.d[u], kc[u].dw);
+                put_bits_shared(s.cs.stage_f[sb], fo, kc[u].fv, kc[u].fw);
+                put_bits_shared(s.cs.stage_d[sb], dof, c.d[u], kc[u].dw);
                 fo += kc[u].fw;
                 dof += kc[u].dw;
             }
         }
         __syncthreads();
         if (c.g >= 0) {
-            flush_stream(reinterpret_cast<unsigned int*>(p.payload + L.flag_off[c.g]), s.stage_f[sb], fs, total & 0xFFFFu);
-            flush_stream(reinterpret_cast<unsigned int*>(p.payload + L.delta_off[c.g]), s.stage_d[sb], ds, total >> 16);
+            flush_stream(reinterpret_cast<unsigned int*>(p.payload + L.flag_off[c.g]), s.cs.stage_f[sb], fs, total & 0xFFFFu);
+            flush_stream(reinterpret_cast<unsigned int*>(p.payload + L.delta_off[c.g]), s.cs.stage_d[sb], ds, total >> 16);
             if (t == 0) {
                 SkmlRestart r;
                 r.prev_key = (unsigned int)c.prev0;
@@ -1437,7 +1568,7 @@ __device__ void huf_ranges(const CP& p, Smem& s) {
 // Pass 0: histogram of the cell symbols of this block's table chunks, added to the global one.
 __device__ void huf_histogram(const CP& p, Smem& s, unsigned int t_begin, unsigned int t_end) {
     const Layout& L = s.lay;
-    unsigned int* hist = s.huf_code;  // idle until the codes are built
+    unsigned int* hist = s.cs.huf_code;  // idle until the codes are built
     for (int t = threadIdx.x; t < SKML_GPU_MAX_BINS + SKML_MAX_GROUPS; t += blockDim.x) hist[t] = 0;
     __syncthreads();
     for (unsigned int c0 = t_begin; c0 < t_end; c0 += 4) {
@@ -1455,25 +1586,15 @@ __device__ void huf_histogram(const CP& p, Smem& s, unsigned int t_begin, unsign
     __syncthreads();
 }
 
-// Per-warp scratch of the code construction (in the shared memory the quantile stages no longer need).
-struct HufScratch {
-    unsigned int w[HUF_MAX_SYMS];         // leaf weights, ascending
-    unsigned int iw[HUF_MAX_SYMS];        // weights of the internal nodes, in creation order (ascending)
-    unsigned short ord[HUF_MAX_SYMS];     // symbol of the i-th lightest leaf
-    unsigned short pl[HUF_MAX_SYMS];      // parent (internal node) of every leaf
-    unsigned short pi[HUF_MAX_SYMS];      // parent of every internal node
-    unsigned char di[HUF_MAX_SYMS];       // depth of every internal node
-};
-
 // Optimal prefix code of every group from the complete histogram (every block; one warp per group,
 // eight groups at a time), canonical code words, section sizes and the layout that follows the tables.
 __device__ void huf_build(const CP& p, Smem& s) {
     Layout& L = s.lay;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    HufScratch* scratch = reinterpret_cast<HufScratch*>(s.runs_all);
+    HufScratch* scratch = s.cs.huf_scratch;
     for (int t = threadIdx.x; t < SKML_GPU_MAX_BINS + SKML_MAX_GROUPS; t += blockDim.x) {
-        s.huf_len[t] = 0;
-        s.huf_code[t] = 0;
+        s.cs.huf_len[t] = 0;
+        s.cs.huf_code[t] = 0;
     }
     __syncthreads();
     if (warp < 8 && !L.overflow) {
@@ -1506,8 +1627,8 @@ __device__ void huf_build(const CP& p, Smem& s) {
             if (lane == 0) {
                 unsigned long long bits = 0;
                 if (m == 1) {
-                    s.huf_len[base + h.ord[0]] = 1;   // a single symbol gets the one-bit code 0
-                    s.huf_code[base + h.ord[0]] = 0;
+                    s.cs.huf_len[base + h.ord[0]] = 1;   // a single symbol gets the one-bit code 0
+                    s.cs.huf_code[base + h.ord[0]] = 0;
                     bits = h.w[0];
                 } else {
                     // two-queue construction: leaves and internal nodes are both consumed in ascending weight
@@ -1533,7 +1654,7 @@ __device__ void huf_build(const CP& p, Smem& s) {
                     unsigned int longest = 0;
                     for (unsigned int i = 0; i < m; ++i) {
                         const unsigned int len = (unsigned int)h.di[h.pl[i]] + 1u;
-                        s.huf_len[base + h.ord[i]] = (unsigned char)(len < 32 ? len : 32);
+                        s.cs.huf_len[base + h.ord[i]] = (unsigned char)(len < 32 ? len : 32);
                         if (len < 33) ++per_len[len];
                         longest = max(longest, len);
                         bits += (unsigned long long)h.w[i] * len;
@@ -1549,8 +1670,8 @@ __device__ void huf_build(const CP& p, Smem& s) {
                         code = (code + per_len[k]) << 1;
                     }
                     for (unsigned int a = 0; a < n; ++a) {
-                        const unsigned int len = s.huf_len[base + a];
-                        if (len && len < 32) s.huf_code[base + a] = next[len]++;
+                        const unsigned int len = s.cs.huf_len[base + a];
+                        if (len && len < 32) s.cs.huf_code[base + a] = next[len]++;
                     }
                 }
                 L.items[g] = m;
@@ -1598,7 +1719,7 @@ __device__ void huf_measure(const CP& p, Smem& s, unsigned int t_begin, unsigned
         if (c.g >= 0) {
 #pragma unroll
             for (int u = 0; u < 4; ++u)
-                if (4u * (threadIdx.x & 255) + u < c.cnt) bits += s.huf_len[huf_slot(L, c.g, c.cell[u])];
+                if (4u * (threadIdx.x & 255) + u < c.cnt) bits += s.cs.huf_len[huf_slot(L, c.g, c.cell[u])];
         }
         unsigned int total;
         sub_scan(s, bits, total);
@@ -1646,12 +1767,12 @@ __device__ void huf_write(const CP& p, Smem& s, unsigned int t_begin, unsigned i
             len[u] = code[u] = 0;
             if (c.g >= 0 && 4u * t + u < c.cnt) {
                 const unsigned int slot = huf_slot(L, c.g, c.cell[u]);
-                len[u] = s.huf_len[slot];
-                code[u] = s.huf_code[slot];
+                len[u] = s.cs.huf_len[slot];
+                code[u] = s.cs.huf_code[slot];
                 bits += len[u];
             }
         }
-        for (int i = t; i < AP_STAGE_D; i += 256) s.stage_d[sb][i] = 0;
+        for (int i = t; i < AP_STAGE_D; i += 256) s.cs.stage_d[sb][i] = 0;
         unsigned int total;
         const unsigned int ex = sub_scan(s, bits, total);
         unsigned long long start = 0;
@@ -1663,13 +1784,13 @@ __device__ void huf_write(const CP& p, Smem& s, unsigned int t_begin, unsigned i
                     (unsigned int)(start + ex);
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                put_bits_shared(s.stage_d[sb], off, code[u], len[u]);
+                put_bits_shared(s.cs.stage_d[sb], off, code[u], len[u]);
                 off += len[u];
             }
         }
         __syncthreads();
         if (c.g >= 0) {
-            flush_stream(reinterpret_cast<unsigned int*>(p.payload + L.tstream_off[c.g]), s.stage_d[sb], start, total);
+            flush_stream(reinterpret_cast<unsigned int*>(p.payload + L.tstream_off[c.g]), s.cs.stage_d[sb], start, total);
             if (c.j == 0) {
                 // this sub-block owns the group's first chunk: section head and items (ascending by value)
                 const int g = c.g;
@@ -1685,12 +1806,12 @@ __device__ void huf_write(const CP& p, Smem& s, unsigned int t_begin, unsigned i
                     unsigned int seen = 0;
                     for (unsigned int a0 = 0; a0 < n; a0 += 32) {
                         const unsigned int a = a0 + t;
-                        const unsigned int ln = a < n ? s.huf_len[base + a] : 0u;
+                        const unsigned int ln = a < n ? s.cs.huf_len[base + a] : 0u;
                         const unsigned int present = __ballot_sync(0xFFFFFFFFu, ln != 0);
                         if (ln) {
                             int* rec = reinterpret_cast<int*>(head + 4) + 3 * (seen + __popc(present & ((1u << t) - 1u)));
                             rec[0] = a + 1 == n ? 0x7FFFFFFF : (int)(L.sym_lo[g] + a);
-                            rec[1] = (int)s.huf_code[base + a];
+                            rec[1] = (int)s.cs.huf_code[base + a];
                             rec[2] = (int)ln;
                         }
                         seen += __popc(present);
@@ -2064,7 +2185,9 @@ __device__ bool wait_all_published(const CP& p, const unsigned int* flags, unsig
     }
 
 // STAGE < 0: all stages in one cooperative launch; otherwise only that stage.
-template <bool FUSED>
+// ADAPTIVE / HUFFMAN: the key encoder and the table coder are compile-time choices, so that the default
+// path (delta_binary keys, plain tables) carries none of the other coders' registers.
+template <bool FUSED, bool ADAPTIVE, bool HUFFMAN>
 __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_sparse_kernel(CP p, int stage) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     Smem& s = *reinterpret_cast<Smem*>(smem_raw);
@@ -2118,7 +2241,7 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_sparse_kernel(CP p, in
     // before it writes the header; staged launches split the stage at those points. The delta_adaptive
     // code needs the groups' complete histograms of delta widths first: one more grid barrier.
     unsigned int my_begin = 0, my_end = 0, t_begin = 0, t_end = 0;
-    const bool adaptive = p.key_encoder == SKML_KEYS_DELTA_ADAPTIVE, huffman = p.huffman != 0;
+    constexpr bool adaptive = ADAPTIVE, huffman = HUFFMAN;
     if (FUSED || stage >= 5) {
         if (!FUSED) {
             load_quantizer(p, s);
@@ -2346,7 +2469,35 @@ extern "C" long long skml_compress_splits_offset(long long n_max, long long bin_
 struct LaunchCache {
     bool ready = false;
     int max_grid = 0;
+    int cluster = 1;   // blocks per thread-block cluster (2 where that many clusters fit the device at once)
 };
+
+// One launch through the extensible API: cooperative when `coop`, in clusters of `cluster` blocks.
+template <class K>
+static cudaError_t launch_ex(K kernel, int grid, int cluster, bool coop, const CP& p, int stage, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(SKML_BLOCK);
+    cfg.dynamicSmemBytes = sizeof(Smem);
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    unsigned int na = 0;
+    if (coop) {
+        attrs[na].id = cudaLaunchAttributeCooperative;
+        attrs[na].val.cooperative = 1;
+        ++na;
+    }
+    if (cluster > 1) {
+        attrs[na].id = cudaLaunchAttributeClusterDimension;
+        attrs[na].val.clusterDim.x = (unsigned int)cluster;
+        attrs[na].val.clusterDim.y = 1;
+        attrs[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = na;
+    return cudaLaunchKernelEx(&cfg, kernel, p, stage);
+}
 
 template <class K>
 static int launch_stages(K fused_kernel, K staged_kernel, LaunchCache& cache, CP& p, int grid, bool fused, int nstages,
@@ -2361,18 +2512,45 @@ static int launch_stages(K fused_kernel, K staged_kernel, LaunchCache& cache, CP
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_kernel, SKML_BLOCK, sizeof(Smem));
         if (per_sm < 1) return (int)cudaErrorLaunchOutOfResources;
         cache.max_grid = per_sm * device_sms();
+        // pairs of blocks as clusters when the whole grid still fits the device at once that way
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(cache.max_grid & ~1);
+        cfg.blockDim = dim3(SKML_BLOCK);
+        cfg.dynamicSmemBytes = sizeof(Smem);
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int nclusters = 0;
+        const char* knob = getenv("SKML_COMPRESS_CLUSTER");   // "1": plain blocks, no clusters
+        if (knob && knob[0] == '1' && knob[1] == 0) {
+            cache.cluster = 1;
+        } else if (cudaOccupancyMaxActiveClusters(&nclusters, fused_kernel, &cfg) == cudaSuccess && 2 * nclusters >= (cache.max_grid & ~1) &&
+            cache.max_grid >= 2)
+            cache.cluster = 2;
+        else
+            cudaGetLastError();  // a refused query is not an error of the caller
         cache.ready = true;
     }
+    if (grid > cache.max_grid) grid = cache.max_grid;
+    int cluster = cache.cluster;
+    if (grid < 2 * cluster) cluster = 1;   // tiny grids (tests) keep plain blocks
+    if (cluster > 1) grid -= grid % cluster;
     if (fused) {
-        if (grid > cache.max_grid) grid = cache.max_grid;
-        int stage = -1;
-        void* args[] = {&p, &stage};
-        e = cudaLaunchCooperativeKernel((const void*)fused_kernel, dim3(grid), dim3(SKML_BLOCK), args, sizeof(Smem), stream);
+        e = launch_ex(fused_kernel, grid, cluster, true, p, -1, stream);
+        if (e != cudaSuccess && cluster > 1) {
+            // the device refuses cooperative clusters of this shape: plain blocks from now on
+            cudaGetLastError();
+            cache.cluster = 1;
+            e = launch_ex(fused_kernel, grid, 1, true, p, -1, stream);
+        }
         return (int)e;
     }
     for (int st = 1; st <= nstages; ++st) {
-        staged_kernel<<<grid, SKML_BLOCK, sizeof(Smem), stream>>>(p, st);
-        e = cudaGetLastError();
+        e = launch_ex(staged_kernel, grid, st == 1 ? cluster : 1, false, p, st, stream);
         if (e != cudaSuccess) return (int)e;
     }
     return 0;
@@ -2383,9 +2561,17 @@ extern "C" int skml_compress_sparse(const SkmlCompressArgs* a, void* stream) {
     int grid = 0;
     int rc = fill_params(a, p, grid);
     if (rc) return rc;
-    static LaunchCache cache;
-    return launch_stages(compress_sparse_kernel<true>, compress_sparse_kernel<false>, cache, p, grid, a->fused != 0, 8,
-                         (cudaStream_t)stream);
+    static LaunchCache cache[4];
+    const bool adaptive = p.key_encoder == SKML_KEYS_DELTA_ADAPTIVE, huffman = p.huffman != 0;
+    const bool fused = a->fused != 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (adaptive && huffman)
+        return launch_stages(compress_sparse_kernel<true, true, true>, compress_sparse_kernel<false, true, true>, cache[3], p, grid, fused, 8, st);
+    if (adaptive)
+        return launch_stages(compress_sparse_kernel<true, true, false>, compress_sparse_kernel<false, true, false>, cache[2], p, grid, fused, 8, st);
+    if (huffman)
+        return launch_stages(compress_sparse_kernel<true, false, true>, compress_sparse_kernel<false, false, true>, cache[1], p, grid, fused, 8, st);
+    return launch_stages(compress_sparse_kernel<true, false, false>, compress_sparse_kernel<false, false, false>, cache[0], p, grid, fused, 8, st);
 }
 
 extern "C" int skml_compress_dense(const SkmlCompressArgs* a, void* stream) {

@@ -814,6 +814,17 @@ extern "C" int skml_ipc_open_handle(const unsigned char* handle64, void** dev_pt
 
 extern "C" int skml_ipc_close(void* dev_ptr) { return (int)cudaIpcCloseMemHandle(dev_ptr); }
 
+// A zeroed device allocation of its own (cudaMalloc): the IPC handle of a receive region then names
+// exactly that region, whatever a caching allocator does with the rest of the memory.
+extern "C" int skml_region_alloc(long long bytes, void** dev_ptr) {
+    if (bytes <= 0 || !dev_ptr) return (int)cudaErrorInvalidValue;
+    cudaError_t e = cudaMalloc(dev_ptr, (size_t)bytes);
+    if (e != cudaSuccess) return (int)e;
+    return (int)cudaMemset(*dev_ptr, 0, (size_t)bytes);
+}
+
+extern "C" int skml_region_free(void* dev_ptr) { return (int)cudaFree(dev_ptr); }
+
 extern "C" int skml_enable_peer_access(int peer_device) {
     cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
     if (e == cudaErrorPeerAccessAlreadyEnabled) {

@@ -199,6 +199,9 @@ int skml_zipml_unpack_scatter(float* acc, const int* keys, const unsigned char* 
 int skml_ipc_get_handle(void* dev_ptr, unsigned char* handle64);
 int skml_ipc_open_handle(const unsigned char* handle64, void** dev_ptr);
 int skml_ipc_close(void* dev_ptr);
+// A zeroed cudaMalloc allocation of its own for a receive region, and its release.
+int skml_region_alloc(long long bytes, void** dev_ptr);
+int skml_region_free(void* dev_ptr);
 int skml_enable_peer_access(int peer_device);
 
 #ifdef __cplusplus

@@ -1,10 +1,14 @@
-"""DeltaAdaptive key encoder on the device.
+"""DeltaAdaptive key codec on the device as a stand-alone call.
 
 The reference's live key encoder (binary/DeltaAdaptiveEncoder.java:23-146): an adaptive
-variable-width bit code for sorted keys. The fused exchange uses the byte-aligned DeltaBinary
-form; this stand-alone codec produces and reads the reference's own format on the GPU, bit for
-bit equal to the CPU oracle (`oracle.delta_adaptive_encode`). The kernels are maps over keys or
-words (csrc/cuda/keys_kernels.cu); the prefix sums between them are `torch.cumsum` calls.
+variable-width bit code for sorted keys. The training step does not come through here: with
+``key_encoder="delta_adaptive"`` the fused compress and decode kernels write and read this format
+themselves, chunk by chunk, without leaving the device (csrc/cuda/compress_kernels.cu,
+decode_common.cuh). This module is the library form of the codec, `encode(keys) -> AdaptiveKeys`
+and back, bit for bit equal to the CPU oracle (`oracle.delta_adaptive_encode`). It returns tensors
+of exactly the encoded size, which depends on the data, so `encode` reads the two bit counts back
+to the host once; the kernels are maps over keys or words (csrc/cuda/keys_kernels.cu) with
+`torch.cumsum` between them.
 """
 from __future__ import annotations
 

@@ -115,6 +115,8 @@ _SIGS = {
     "skml_ipc_get_handle": (c_int, [c_vp, c_vp]),
     "skml_ipc_open_handle": (c_int, [c_vp, C.POINTER(c_vp)]),
     "skml_ipc_close": (c_int, [c_vp]),
+    "skml_region_alloc": (c_int, [c_ll, c_vp]),
+    "skml_region_free": (c_int, [c_vp]),
     "skml_enable_peer_access": (c_int, [c_int]),
 }
 

@@ -25,6 +25,13 @@ from ..ops import lib as L
 from ..ops.codec import FLAG_BYTES, ExchangeRegionView
 
 
+class _RawDeviceBytes:
+    """CUDA array interface over a raw device pointer, so that torch can view the bytes without owning them."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1", "data": (int(ptr), False), "version": 2}
+
+
 class PeerExchange:
     def __init__(self, comm, slot_capacity: int, device: torch.device):
         self.comm = comm
@@ -34,8 +41,12 @@ class PeerExchange:
         self.device = device
         self.slot_capacity = int((slot_capacity + 255) // 256 * 256)
         nbytes = ExchangeRegionView.region_bytes(self.world, self.slot_capacity)
-        # a dedicated allocation: the IPC handle covers exactly this buffer
-        self.region = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        # an allocation of its own, outside the caching allocator: the IPC handle names exactly this buffer
+        raw = C.c_void_p()
+        with torch.cuda.device(device):
+            L.check(L.lib().skml_region_alloc(nbytes, C.byref(raw)), "cudaMalloc(receive region)")
+        self._raw = raw.value
+        self.region = torch.as_tensor(_RawDeviceBytes(self._raw, nbytes), device=device)
         self._opened: List[int] = []
         self.views: List[ExchangeRegionView] = [None] * self.world
         self.views[self.rank] = ExchangeRegionView(self.region.data_ptr(), self.world, self.slot_capacity)
@@ -47,8 +58,7 @@ class PeerExchange:
         handle = (C.c_ubyte * 64)()
         # the handle names the allocation that contains the pointer; send the offset too
         L.check(lib.skml_ipc_get_handle(self.region.data_ptr(), C.addressof(handle)), "cudaIpcGetMemHandle")
-        base = self._allocation_base()
-        blob = bytes(handle) + int(self.region.data_ptr() - base).to_bytes(8, "little")
+        blob = bytes(handle) + int(0).to_bytes(8, "little")  # the region starts its allocation
         blobs = self.comm.all_gather_bytes(blob)
         for r, b in enumerate(blobs):
             if r == self.rank:
@@ -60,19 +70,6 @@ class PeerExchange:
             self._opened.append(p.value)
             self.views[r] = ExchangeRegionView(p.value + off, self.world, self.slot_capacity)
         self.comm.barrier()
-
-    def _allocation_base(self) -> int:
-        """Start of the driver allocation holding ``self.region`` (the caching allocator may
-        place the tensor inside a larger segment)."""
-        ptr = self.region.data_ptr()
-        try:
-            for seg in torch.cuda.memory_snapshot():
-                a = seg["address"]
-                if a <= ptr < a + seg["total_size"]:
-                    return a
-        except Exception:
-            pass
-        return ptr
 
     # --- pointers for one step -------------------------------------------------
     def send_ptrs(self, step: int):
@@ -96,3 +93,10 @@ class PeerExchange:
         for p in self._opened:
             lib.skml_ipc_close(p)
         self._opened.clear()
+        if getattr(self, "_raw", None):
+            # peers store into this region only for a step whose decode this rank has already finished
+            # (the decode needs every peer's payload), so nothing of theirs is in flight here any more
+            torch.cuda.synchronize(self.device)
+            self.region = None
+            lib.skml_region_free(self._raw)
+            self._raw = None
