@@ -15,9 +15,17 @@
 #define DEC_MAX_ITEMS (SKML_MAX_PEERS * SKML_MAX_GROUPS)
 #define DEC_KPT 4        // keys of a 1024-key chunk per thread
 #define DEC_THREADS (SKML_RESTART_INTERVAL / DEC_KPT)
-#define DEC_BLOCKS_PER_SM 4
+// Blocks per SM: three blocks of 256 threads with a 36 KB table area each keep the SM's shared-memory
+// carve-out at 164 KB, which leaves 92 KB of L1. The apply passes are random read-modify-writes whose
+// number in flight grows with the L1 (every miss holds a line): measured on eight payloads of 433k keys,
+// four blocks (28 KB of L1) took 218 us per launch, three blocks 175 us; lazy Adam 624 -> 445 us.
+#ifndef DEC_BLOCKS_PER_SM
+#define DEC_BLOCKS_PER_SM 3
+#endif
 #define DEC_HUF_MAX_ITEMS 513  // code words of one Huffman-coded table the expander accepts
+#ifndef DEC_TAB_SMEM
 #define DEC_TAB_SMEM 36864   // bytes of shared memory per block for a staged sketch table
+#endif
 
 struct DP {
     const unsigned char* payload[SKML_MAX_PEERS];
