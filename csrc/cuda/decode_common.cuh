@@ -23,6 +23,13 @@
 #define DEC_BLOCKS_PER_SM 3
 #endif
 #define DEC_HUF_MAX_ITEMS 513  // code words of one Huffman-coded table the expander accepts
+// Key ranges per block in the key-range-owned apply, dealt in snake order. Two ranges per block even out
+// the blocks' finishing times (last block 38 us -> 7 us after the first at eight payloads of 433k keys)
+// but not the launch time (175 us either way: the apply is bound by the random DRAM sectors in total,
+// not by the slowest block); lazy Adam gains 4 % with two, SGD loses 2 %, so the default stays one.
+#ifndef DEC_OWN_RANGES
+#define DEC_OWN_RANGES 1
+#endif
 #ifndef DEC_TAB_SMEM
 #define DEC_TAB_SMEM 36864   // bytes of shared memory per block for a staged sketch table
 #endif

@@ -468,28 +468,34 @@ __device__ __forceinline__ void owned_pass(const DP& p, DecSmem& s, const unsign
     __syncthreads();
 }
 
-// Barrier-free ordered apply. Every block owns a key range (bounds = quantiles of the longest key
-// list), finds its slice of every (rank, group) list by binary search in the stashed keys, and applies
-// the slices rank by rank with only a block barrier in between: all updates of one coordinate
-// happen in one block, in rank order, so replicas stay bit-identical.
+// Barrier-free ordered apply. The key space is cut into DEC_OWN_RANGES x blocks ranges at the quantiles
+// of the longest key list; a block owns one range per round, dealt in snake order (round 0: range b,
+// round 1: range 2B - 1 - b, ...). Low keys are the frequent ones and sit in L2 while the high ones
+// miss to DRAM, so a block's ranges cost about the same in sum although single ranges differ several
+// times. For each of its ranges the block finds its slice of every (rank, group) list by binary search
+// in the stashed keys and applies the slices rank by rank with only a block barrier in between: all
+// updates of one coordinate happen in one block, in rank order, so replicas stay bit-identical.
 __device__ void apply_owned(const DP& p, DecSmem& s, float& dsq) {
     if (s.nitems == 0) return;
-    unsigned long long* seg_b = reinterpret_cast<unsigned long long*>(&s.items[p.max_items]);
-    unsigned long long* seg_e = seg_b + p.max_items;
-    __shared__ unsigned long long s_bound[2];
-    if (threadIdx.x < 2) {
+    unsigned long long* seg = reinterpret_cast<unsigned long long*>(&s.items[p.max_items]);  // [2 * DEC_OWN_RANGES][max_items]
+    __shared__ unsigned long long s_bound[2 * DEC_OWN_RANGES];
+    if (threadIdx.x < 2 * DEC_OWN_RANGES) {
         const DecItem& ref = s.items[s.ref_item];
-        const unsigned long long b = blockIdx.x + threadIdx.x, B = gridDim.x;
+        const unsigned long long B = gridDim.x, total = (unsigned long long)DEC_OWN_RANGES * B;
+        const unsigned long long round = threadIdx.x >> 1;
+        const unsigned long long range = (round & 1ull) ? (round + 1ull) * B - 1ull - blockIdx.x : round * B + blockIdx.x;
+        const unsigned long long j = range + (threadIdx.x & 1);   // lower / upper bound of the range
         unsigned long long v;
-        if (b == 0) v = 0ull;
-        else if (b >= B) v = 1ull << 32;
-        else v = (unsigned long long)(unsigned int)__ldcg(p.key_scratch + ref.key_prefix + b * (unsigned long long)ref.e.n / B);
+        if (j == 0) v = 0ull;
+        else if (j >= total) v = 1ull << 32;
+        else v = (unsigned long long)(unsigned int)__ldcg(p.key_scratch + ref.key_prefix + j * (unsigned long long)ref.e.n / total);
         s_bound[threadIdx.x] = v;
     }
     __syncthreads();
-    for (int t = threadIdx.x; t < 2 * s.nitems; t += blockDim.x) {
-        const DecItem& it = s.items[t >> 1];
-        const unsigned long long bound = s_bound[t & 1];
+    for (int t = threadIdx.x; t < 2 * DEC_OWN_RANGES * s.nitems; t += blockDim.x) {
+        const int item = t / (2 * DEC_OWN_RANGES), which = t % (2 * DEC_OWN_RANGES);
+        const DecItem& it = s.items[item];
+        const unsigned long long bound = s_bound[which];
         const int* list = p.key_scratch + it.key_prefix;
         unsigned int lo = 0, hi = it.e.n;
         while (lo < hi) {  // first position whose key is >= bound
@@ -497,17 +503,21 @@ __device__ void apply_owned(const DP& p, DecSmem& s, float& dsq) {
             if ((unsigned long long)(unsigned int)__ldcg(list + mid) < bound) lo = mid + 1;
             else hi = mid;
         }
-        ((t & 1) ? seg_e : seg_b)[t >> 1] = it.key_prefix + lo;
+        seg[(size_t)which * p.max_items + item] = it.key_prefix + lo;
     }
     __syncthreads();
-    if (p.adam_v) {
-        // Adam: sum the ranks' values per coordinate in rank order (plain floats in the zeroed
-        // accumulator array), then let the first rank that holds a coordinate apply the update
-        // and clear the sum.
-        for (int r = 0; r < p.world; ++r) owned_pass<1>(p, s, seg_b, seg_e, r, dsq);
-        for (int r = 0; r < p.world; ++r) owned_pass<2>(p, s, seg_b, seg_e, r, dsq);
-    } else {
-        for (int r = 0; r < p.world; ++r) owned_pass<0>(p, s, seg_b, seg_e, r, dsq);
+    for (int round = 0; round < DEC_OWN_RANGES; ++round) {
+        const unsigned long long* seg_b = seg + (size_t)(2 * round) * p.max_items;
+        const unsigned long long* seg_e = seg_b + p.max_items;
+        if (p.adam_v) {
+            // Adam: sum the ranks' values per coordinate in rank order (plain floats in the zeroed
+            // accumulator array), then let the first rank that holds a coordinate apply the update
+            // and clear the sum.
+            for (int r = 0; r < p.world; ++r) owned_pass<1>(p, s, seg_b, seg_e, r, dsq);
+            for (int r = 0; r < p.world; ++r) owned_pass<2>(p, s, seg_b, seg_e, r, dsq);
+        } else {
+            for (int r = 0; r < p.world; ++r) owned_pass<0>(p, s, seg_b, seg_e, r, dsq);
+        }
     }
 }
 
@@ -748,7 +758,7 @@ extern "C" int skml_decode_update(const SkmlDecodeArgs* a, void* stream_) {
     if (groups > SKML_MAX_GROUPS) groups = SKML_MAX_GROUPS;
     p.max_items = (int)(a->world * groups);
     // dynamic shared memory: work table, two slice bounds per entry, then the staged-table area
-    const size_t smem_items = (sizeof(DecSmem) + (size_t)p.max_items * (sizeof(DecItem) + 16) + 15) & ~(size_t)15;
+    const size_t smem_items = (sizeof(DecSmem) + (size_t)p.max_items * (sizeof(DecItem) + 16 * DEC_OWN_RANGES) + 15) & ~(size_t)15;
     p.tab_off = (int)smem_items;
     const size_t smem = smem_items + DEC_TAB_SMEM;
     static int sms = 0;
@@ -759,7 +769,7 @@ extern "C" int skml_decode_update(const SkmlDecodeArgs* a, void* stream_) {
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
-        const int cap = (int)(sizeof(DecSmem) + (size_t)DEC_MAX_ITEMS * (sizeof(DecItem) + 16) + 16 + DEC_TAB_SMEM);
+        const int cap = (int)(sizeof(DecSmem) + (size_t)DEC_MAX_ITEMS * (sizeof(DecItem) + 16 * DEC_OWN_RANGES) + 16 + DEC_TAB_SMEM);
         cudaError_t e0 = cudaFuncSetAttribute(decode_update_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);
         if (e0 == cudaSuccess)
             e0 = cudaFuncSetAttribute(decode_update_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap);

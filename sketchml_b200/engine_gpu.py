@@ -562,7 +562,8 @@ class GpuEngine:
         import numpy as np
         last = (self.t.step - 1) & 1  # the decode kernel keeps the stamps of even and odd steps apart
         c = self.comp.workspace[:256].cpu().numpy().view(np.int64)[8:15]
-        if int(self.st.meta[1]) != 1 or not all(0 <= int(c[i + 1] - c[i]) < 10**9 for i in range(6)):
+        kind = 1 if getattr(self, "_last_index", None) is not None else int(self.st.meta[1])  # index batches are sparse
+        if kind != 1 or not all(0 <= int(c[i + 1] - c[i]) < 10**9 for i in range(6)):
             return None   # dense-kind or empty step: the sparse compress kernel left no stamps
         dall = self.dec.workspace[:256].cpu().numpy().view(np.int64)
         d, dprev = dall[8 + 4 * last:12 + 4 * last], dall[8 + 4 * (1 - last):12 + 4 * (1 - last)]
