@@ -35,6 +35,8 @@ def main():
     ap.add_argument("--dim", type=int, default=50_000_000)
     ap.add_argument("--nnz-per-row", type=int, default=30)
     ap.add_argument("--adam", action="store_true")
+    ap.add_argument("--plain-adam-state", action="store_true",
+                    help="two plain moment arrays instead of the engine's packed {m, v, sum, -} quads")
     ap.add_argument("--iters", type=int, default=8)
     args = ap.parse_args()
     P, dim = args.ranks, args.dim
@@ -56,7 +58,11 @@ def main():
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     m = v = None
     if args.adam:
-        m, v = torch.zeros(dim, device="cuda"), torch.zeros(dim, device="cuda")
+        if args.plain_adam_state:
+            m, v = torch.zeros(dim, device="cuda"), torch.zeros(dim, device="cuda")
+        else:
+            quad = torch.zeros((dim, 4), device="cuda")
+            m, v = quad[:, 0], quad[:, 1]
     tc, td = [], []
     for it in range(args.iters):
         for r in range(P):

@@ -23,12 +23,12 @@
 #define DEC_BLOCKS_PER_SM 3
 #endif
 #define DEC_HUF_MAX_ITEMS 513  // code words of one Huffman-coded table the expander accepts
-// Key ranges per block in the key-range-owned apply, dealt in snake order. Two ranges per block even out
-// the blocks' finishing times (last block 38 us -> 7 us after the first at eight payloads of 433k keys)
-// but not the launch time (175 us either way: the apply is bound by the random DRAM sectors in total,
-// not by the slowest block); lazy Adam gains 4 % with two, SGD loses 2 %, so the default stays one.
+// Most key ranges a block takes in the key-range-owned apply (dealt in snake order; sizes the slice
+// table in shared memory). Measured at eight payloads of 433k keys: two ranges per block even out the
+// blocks' finishing times (last block 38 us -> 7 us after the first) but not the SGD launch (175 us either
+// way), so SGD takes one; lazy Adam, which sweeps its range 2 x ranks times, takes two (-4 %).
 #ifndef DEC_OWN_RANGES
-#define DEC_OWN_RANGES 1
+#define DEC_OWN_RANGES 2
 #endif
 #ifndef DEC_TAB_SMEM
 #define DEC_TAB_SMEM 36864   // bytes of shared memory per block for a staged sketch table
@@ -44,6 +44,9 @@ struct DP {
     float* w;
     float* adam_m;
     float* adam_v;
+    long long adam_stride;  // elements between the moments of neighbouring coordinates (4: packed {m, v, sum, -} quads)
+    float* fsum;            // lazy Adam: float sum of the ranks' values per coordinate, all zero between calls
+    long long fsum_stride;
     float lr, adam_scale;
     long long* acc;
     int* key_scratch;
@@ -93,11 +96,12 @@ __device__ __forceinline__ float apply_one(const DP& p, long long k, float g) {
     if (!p.adam_v) {
         nw = old - p.lr * g;
     } else {
-        float mt = 0.9f * p.adam_m[k] + 0.1f * g;
-        float vt = 0.999f * p.adam_v[k] + 0.001f * g * g;
+        const long long q = k * p.adam_stride;
+        float mt = 0.9f * p.adam_m[q] + 0.1f * g;
+        float vt = 0.999f * p.adam_v[q] + 0.001f * g * g;
         nw = old - p.lr * p.adam_scale * mt / (sqrtf(vt) + 1e-8f);
-        p.adam_m[k] = mt;
-        p.adam_v[k] = vt;
+        p.adam_m[q] = mt;
+        p.adam_v[q] = vt;
     }
     p.w[k] = nw;
     return (nw - old) * (nw + old);

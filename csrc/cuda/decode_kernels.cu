@@ -425,7 +425,8 @@ template <int OP>
 __device__ __forceinline__ void owned_pass(const DP& p, DecSmem& s, const unsigned long long* seg_b,
                                            const unsigned long long* seg_e, int r, float& dsq) {
     const int i0 = s.rank_item_begin[r], i1 = s.rank_item_begin[r + 1];
-    float* dst = OP == 0 ? (p.out_sum ? p.out_sum : p.w) : reinterpret_cast<float*>(p.acc);
+    float* dst = OP == 0 ? (p.out_sum ? p.out_sum : p.w) : p.fsum;
+    const long long ds = OP == 0 ? 1ll : p.fsum_stride;
     unsigned int total = 0;
     for (int i = i0; i < i1; ++i) total += (unsigned int)(seg_e[i] - seg_b[i]);
     for (unsigned int q = threadIdx.x; q < total; q += 4 * blockDim.x) {
@@ -450,7 +451,7 @@ __device__ __forceinline__ void owned_pass(const DP& p, DecSmem& s, const unsign
             }
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) old[u] = k[u] < (unsigned long long)p.dim ? dst[k[u]] : 0.f;
+        for (int u = 0; u < 4; ++u) old[u] = k[u] < (unsigned long long)p.dim ? dst[k[u] * ds] : 0.f;
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             if (k[u] >= (unsigned long long)p.dim) continue;
@@ -458,9 +459,9 @@ __device__ __forceinline__ void owned_pass(const DP& p, DecSmem& s, const unsign
                 const float nw = p.out_sum ? old[u] + v[u] : old[u] - p.lr * v[u];
                 dst[k[u]] = nw;
                 if (!p.out_sum) dsq += (nw - old[u]) * (nw + old[u]);
-            } else if (OP == 1) dst[k[u]] = old[u] + v[u];
+            } else if (OP == 1) dst[k[u] * ds] = old[u] + v[u];
             else if (old[u] != 0.f) {
-                dst[k[u]] = 0.f;
+                dst[k[u] * ds] = 0.f;
                 dsq += apply_one(p, k[u], old[u]);
             }
         }
@@ -479,9 +480,13 @@ __device__ void apply_owned(const DP& p, DecSmem& s, float& dsq) {
     if (s.nitems == 0) return;
     unsigned long long* seg = reinterpret_cast<unsigned long long*>(&s.items[p.max_items]);  // [2 * DEC_OWN_RANGES][max_items]
     __shared__ unsigned long long s_bound[2 * DEC_OWN_RANGES];
-    if (threadIdx.x < 2 * DEC_OWN_RANGES) {
+    // SGD: one range per block (more ranges even out the blocks but do not shorten the launch: the random
+    // DRAM sectors bound it in total); lazy Adam sweeps a range 2 x ranks times, and smaller ranges keep
+    // its sectors in L2 between the sweeps
+    const int rounds = p.adam_v ? DEC_OWN_RANGES : 1;
+    if (threadIdx.x < 2 * rounds) {
         const DecItem& ref = s.items[s.ref_item];
-        const unsigned long long B = gridDim.x, total = (unsigned long long)DEC_OWN_RANGES * B;
+        const unsigned long long B = gridDim.x, total = (unsigned long long)rounds * B;
         const unsigned long long round = threadIdx.x >> 1;
         const unsigned long long range = (round & 1ull) ? (round + 1ull) * B - 1ull - blockIdx.x : round * B + blockIdx.x;
         const unsigned long long j = range + (threadIdx.x & 1);   // lower / upper bound of the range
@@ -492,8 +497,8 @@ __device__ void apply_owned(const DP& p, DecSmem& s, float& dsq) {
         s_bound[threadIdx.x] = v;
     }
     __syncthreads();
-    for (int t = threadIdx.x; t < 2 * DEC_OWN_RANGES * s.nitems; t += blockDim.x) {
-        const int item = t / (2 * DEC_OWN_RANGES), which = t % (2 * DEC_OWN_RANGES);
+    for (int t = threadIdx.x; t < 2 * rounds * s.nitems; t += blockDim.x) {
+        const int item = t / (2 * rounds), which = t % (2 * rounds);
         const DecItem& it = s.items[item];
         const unsigned long long bound = s_bound[which];
         const int* list = p.key_scratch + it.key_prefix;
@@ -506,13 +511,12 @@ __device__ void apply_owned(const DP& p, DecSmem& s, float& dsq) {
         seg[(size_t)which * p.max_items + item] = it.key_prefix + lo;
     }
     __syncthreads();
-    for (int round = 0; round < DEC_OWN_RANGES; ++round) {
+    for (int round = 0; round < rounds; ++round) {
         const unsigned long long* seg_b = seg + (size_t)(2 * round) * p.max_items;
         const unsigned long long* seg_e = seg_b + p.max_items;
         if (p.adam_v) {
             // Adam: sum the ranks' values per coordinate in rank order (plain floats in the zeroed
-            // accumulator array), then let the first rank that holds a coordinate apply the update
-            // and clear the sum.
+            // sums), then let the first rank that holds a coordinate apply the update and clear the sum.
             for (int r = 0; r < p.world; ++r) owned_pass<1>(p, s, seg_b, seg_e, r, dsq);
             for (int r = 0; r < p.world; ++r) owned_pass<2>(p, s, seg_b, seg_e, r, dsq);
         } else {
@@ -737,6 +741,14 @@ extern "C" int skml_decode_update(const SkmlDecodeArgs* a, void* stream_) {
     p.w = a->w;
     p.adam_m = a->adam_m;
     p.adam_v = a->adam_v;
+    p.adam_stride = a->adam_stride > 1 ? a->adam_stride : 1;
+    if (p.adam_stride == 4 && a->adam_m) {
+        p.fsum = a->adam_m + 2;   // packed quads {m, v, sum, -}: the three words of a coordinate share a sector
+        p.fsum_stride = 4;
+    } else {
+        p.fsum = reinterpret_cast<float*>(a->acc);
+        p.fsum_stride = 1;
+    }
     p.lr = (float)a->lr;
     p.adam_scale = (float)a->adam_scale;
     p.acc = a->acc;

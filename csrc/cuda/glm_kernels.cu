@@ -624,51 +624,54 @@ extern "C" long long skml_compact_blocks(int dim) {
 // fused decode kernel).
 // opt[0] = lr, opt[1] = sqrt(1 - beta2^t) / (1 - beta1^t) for Adam.
 // ---------------------------------------------------------------------------
+// ms: elements between the moments of neighbouring coordinates (1: plain arrays; 4: m and v point into
+// one array of per-coordinate quads, so both moments of a coordinate come with one memory sector).
 __device__ __forceinline__ void apply_update(float* w, float* m, float* v, long long k, float gval, int adam,
-                                             float lr, float adam_scale) {
+                                             float lr, float adam_scale, long long ms) {
     if (!adam) {
         w[k] -= lr * gval;
     } else {
-        float mt = 0.9f * m[k] + 0.1f * gval;
-        float vt = 0.999f * v[k] + 0.001f * gval * gval;
+        const long long q = k * ms;
+        float mt = 0.9f * m[q] + 0.1f * gval;
+        float vt = 0.999f * v[q] + 0.001f * gval * gval;
         w[k] -= lr * adam_scale * mt / (sqrtf(vt) + 1e-8f);
-        m[k] = mt;
-        v[k] = vt;
+        m[q] = mt;
+        v[q] = vt;
     }
 }
 
 __global__ void update_dense_kernel(float* w, float* m, float* v, const float* g, long long dim, float scale,
-                                    int adam, float lr, float adam_scale, int sparse_only) {
+                                    int adam, float lr, float adam_scale, int sparse_only, long long ms) {
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < dim; i += (long long)gridDim.x * blockDim.x) {
         float gv = g[i] * scale;
         if (sparse_only && gv == 0.f) continue;
-        apply_update(w, m, v, i, gv, adam, lr, adam_scale);
+        apply_update(w, m, v, i, gv, adam, lr, adam_scale, ms);
     }
 }
 
 __global__ void update_sparse_kernel(float* w, float* m, float* v, const int* keys, const float* vals,
                                      const long long* n_ptr, long long n_max, float scale, int adam, float lr,
-                                     float adam_scale) {
+                                     float adam_scale, long long ms) {
     long long n = n_ptr ? *n_ptr : n_max;
     if (n > n_max) n = n_max;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
-        apply_update(w, m, v, keys[i], vals[i] * scale, adam, lr, adam_scale);
+        apply_update(w, m, v, keys[i], vals[i] * scale, adam, lr, adam_scale, ms);
 }
 
 extern "C" int skml_update_dense(float* w, float* m, float* v, const float* g, long long dim, float scale, int adam,
-                                 float lr, float adam_scale, int sparse_only, void* stream) {
+                                 float lr, float adam_scale, int sparse_only, int adam_stride, void* stream) {
     int grid = sm_count() * 8;
     update_dense_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(w, m, v, g, dim, scale, adam, lr, adam_scale,
-                                                                sparse_only);
+                                                                sparse_only, adam_stride > 1 ? adam_stride : 1);
     return (int)cudaGetLastError();
 }
 
 extern "C" int skml_update_sparse(float* w, float* m, float* v, const int* keys, const float* vals,
                                   const long long* n_ptr, long long n_max, float scale, int adam, float lr,
-                                  float adam_scale, void* stream) {
+                                  float adam_scale, int adam_stride, void* stream) {
     int grid = sm_count() * 8;
     update_sparse_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(w, m, v, keys, vals, n_ptr, n_max, scale, adam, lr,
-                                                                 adam_scale);
+                                                                 adam_scale, adam_stride > 1 ? adam_stride : 1);
     return (int)cudaGetLastError();
 }
 
@@ -739,7 +742,7 @@ extern "C" int skml_weight_norm(const float* w, long long dim, double lambda, do
 // (exactly zero, skipped) by the later ones. A sum that is exactly zero is a no-op, as in the
 // `sparse_only` dense update.
 __global__ void update_gathered_kernel(float* w, float* m, float* v, float* acc, const int* keys, const long long* count,
-                                       long long stride, float scale, int adam, float lr, float adam_scale) {
+                                       long long stride, float scale, int adam, float lr, float adam_scale, long long ms) {
     long long n = *count;
     if (n > stride) n = stride;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
@@ -747,16 +750,17 @@ __global__ void update_gathered_kernel(float* w, float* m, float* v, float* acc,
         const float g = acc[k];
         if (g == 0.f) continue;
         acc[k] = 0.f;
-        apply_update(w, m, v, k, g * scale, adam, lr, adam_scale);
+        apply_update(w, m, v, k, g * scale, adam, lr, adam_scale, ms);
     }
 }
 
 extern "C" int skml_update_gathered(float* w, float* m, float* v, float* acc, const int* keys, const long long* counts,
                                     long long stride, int lists, float scale, int adam, float lr, float adam_scale,
-                                    void* stream) {
+                                    int adam_stride, void* stream) {
     for (int l = 0; l < lists; ++l) {
         update_gathered_kernel<<<sm_count() * 8, 256, 0, (cudaStream_t)stream>>>(w, m, v, acc, keys + (long long)l * stride,
-                                                                                 counts + l, stride, scale, adam, lr, adam_scale);
+                                                                                 counts + l, stride, scale, adam, lr, adam_scale,
+                                                                                 adam_stride > 1 ? adam_stride : 1);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;
     }

@@ -79,6 +79,9 @@ typedef struct SkmlDecodeArgs {
     double* weight_sumsq;          // optional device double: sum of w^2, kept current by the update (see skml_weight_norm)
     double* reg_out;               // optional device double: receives reg_lambda * sqrt(*weight_sumsq) when the launch ends
     double reg_lambda;
+    long long adam_stride;         // 0 / 1: adam_m and adam_v are plain arrays; 4: both point into one array of
+                                   // {m, v, sum, unused} quads (adam_v = adam_m + 1), whose third word the kernel
+                                   // uses for the per-coordinate sums of lazy Adam (zero between calls)
 } SkmlDecodeArgs;
 
 long long skml_decode_workspace_bytes(long long world, long long group_num);
@@ -96,14 +99,17 @@ int skml_compact(float* g, const float* w, unsigned int* bitmap, int dim, float 
                  long long* meta, int* keys, float* vals, float* dense_vals, long long capacity, unsigned int* status,
                  void* stream);
 long long skml_compact_blocks(int dim);
+// The update entry points take `adam_stride`: elements between the moments of neighbouring coordinates (1: plain
+// arrays, 4: packed quads, see SkmlDecodeArgs).
 int skml_update_dense(float* w, float* m, float* v, const float* g, long long dim, float scale, int adam, float lr,
-                      float adam_scale, int sparse_only, void* stream);
+                      float adam_scale, int sparse_only, int adam_stride, void* stream);
 int skml_update_sparse(float* w, float* m, float* v, const int* keys, const float* vals, const long long* n_ptr,
-                       long long n_max, float scale, int adam, float lr, float adam_scale, void* stream);
+                       long long n_max, float scale, int adam, float lr, float adam_scale, int adam_stride, void* stream);
 // Applies acc[key] * scale to the model on the coordinates of `lists` gathered key lists (list l at
 // keys + l * stride, counts[l] entries) and clears those accumulator words.
 int skml_update_gathered(float* w, float* m, float* v, float* acc, const int* keys, const long long* counts,
-                         long long stride, int lists, float scale, int adam, float lr, float adam_scale, void* stream);
+                         long long stride, int lists, float scale, int adam, float lr, float adam_scale, int adam_stride,
+                         void* stream);
 // sumsq_out[0] = sum of w^2 (double, fixed summation order), reg_out[0] = lambda * sqrt of it; one
 // launch, `scratch` holds skml_weight_norm_scratch_bytes() bytes that are zero before the first call.
 long long skml_weight_norm_scratch_bytes();

@@ -94,6 +94,16 @@ class GpuEngine:
         m = self.t.model
         self.reg_every_step = bool(conf.extras.get("reg_loss_every_step", dim <= (1 << 22)))
         self.adam = conf.optimizer == "adam"
+        if self.adam and conf.extras.get("packed_adam_state", True):
+            # both moments (and, in the fused decode kernel, the per-coordinate sum of the ranks' values) of a
+            # coordinate in one 16-byte quad: a lazy Adam step touches one memory sector of state per
+            # coordinate instead of three
+            opt = m.optimizer
+            quad = torch.zeros((dim, 4), dtype=torch.float32, device=self.device)
+            quad[:, 0].copy_(opt.m)
+            quad[:, 1].copy_(opt.v)
+            self.adam_quad = quad
+            opt.m, opt.v = quad[:, 0], quad[:, 1]
         # regularisation loss lambda * ||w||_2 of every batch: one launch of a norm kernel per step for the
         # baseline arms; the sketch arm's decode kernel keeps the sum of squares current as it updates, so
         # its steps pass over the model only once per epoch (to shed the rounding of the running sum)
@@ -510,6 +520,8 @@ class GpuEngine:
             if self.mode == "sketch":
                 self.comp.reset()
                 self.dec.reset()
+                if getattr(self, "adam_quad", None) is not None:
+                    self.adam_quad[:, 2].zero_()   # the per-coordinate sums of an interrupted lazy-Adam step
             check_status(s, f"at step {self.t.step} on rank {self.t.comm.rank}")
 
     def resolve_losses(self, handles) -> List[float]:

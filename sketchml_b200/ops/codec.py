@@ -198,6 +198,9 @@ class GpuDecoder:
         a.world, a.slot_capacity, a.step, a.dim = world, slot_capacity, step, self.dim
         a.w, a.adam_m, a.adam_v = L.ptr(w), L.ptr(adam_m), L.ptr(adam_v)
         a.lr, a.adam_scale = float(lr), float(adam_scale)
+        if adam_m is not None and adam_v is not None:
+            from .glm import moment_stride
+            a.adam_stride = moment_stride(adam_m, adam_v)
         a.acc, a.key_scratch, a.key_capacity = L.ptr(self.acc), L.ptr(self.key_scratch), self.key_capacity
         a.loss_out, a.out_sum = L.ptr(loss_out), L.ptr(out_sum)
         a.workspace, a.status = L.ptr(self.workspace), L.ptr(status)

@@ -114,16 +114,27 @@ def compact_gradient(st: GlmState, w: torch.Tensor, lam: float) -> None:
     L.count_launches(3)
 
 
+def moment_stride(m, v) -> int:
+    """Elements between the Adam moments of neighbouring coordinates: 1 for plain arrays, 4 when m and v are
+    columns 0 and 1 of one [dim, 4] array (both moments of a coordinate then share a memory sector)."""
+    if m is None or v is None:
+        return 1
+    sm, sv = int(m.stride(0)), int(v.stride(0))
+    if sm != sv or sm not in (1, 4) or (sm == 4 and v.data_ptr() != m.data_ptr() + 4):
+        raise ValueError("Adam moments must be two plain arrays or columns 0 and 1 of one [dim, 4] float32 array")
+    return sm
+
+
 def update_dense(w, g, scale: float, lr: float, m=None, v=None, adam_scale: float = 1.0, sparse_only: bool = False):
     L.check(L.lib().skml_update_dense(L.ptr(w), L.ptr(m), L.ptr(v), L.ptr(g), w.numel(), scale, int(v is not None), lr,
-                                      adam_scale, int(sparse_only), L.stream()), "skml_update_dense")
+                                      adam_scale, int(sparse_only), moment_stride(m, v), L.stream()), "skml_update_dense")
 
 
 def update_gathered(w, acc, keys, counts, stride: int, lists: int, scale: float, lr: float, m=None, v=None,
                     adam_scale: float = 1.0):
     """Applies ``acc[key] * scale`` on the coordinates of the gathered key lists and clears them."""
     L.check(L.lib().skml_update_gathered(L.ptr(w), L.ptr(m), L.ptr(v), L.ptr(acc), L.ptr(keys), L.ptr(counts), stride,
-                                         lists, scale, int(v is not None), lr, adam_scale, L.stream()),
+                                         lists, scale, int(v is not None), lr, adam_scale, moment_stride(m, v), L.stream()),
             "skml_update_gathered")
     L.count_launches(lists)
 
@@ -131,4 +142,5 @@ def update_gathered(w, acc, keys, counts, stride: int, lists: int, scale: float,
 def update_sparse(w, keys, vals, n_ptr: Optional[torch.Tensor], n_max: int, scale: float, lr: float, m=None, v=None,
                   adam_scale: float = 1.0):
     L.check(L.lib().skml_update_sparse(L.ptr(w), L.ptr(m), L.ptr(v), L.ptr(keys), L.ptr(vals), L.ptr(n_ptr), n_max,
-                                       scale, int(v is not None), lr, adam_scale, L.stream()), "skml_update_sparse")
+                                       scale, int(v is not None), lr, adam_scale, moment_stride(m, v), L.stream()),
+            "skml_update_sparse")

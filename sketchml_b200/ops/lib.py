@@ -46,7 +46,7 @@ class DecodeArgs(C.Structure):
         ("adam_scale", c_d), ("acc", c_vp), ("key_scratch", c_vp), ("key_capacity", c_ll), ("loss_out", c_vp),
         ("out_sum", c_vp), ("workspace", c_vp), ("status", c_vp), ("budget_cycles", c_ll), ("fused", c_ll),
         ("grid", c_ll), ("max_groups", c_ll), ("val_scratch", c_vp), ("table_scratch", c_vp), ("table_capacity", c_ll),
-        ("weight_sumsq", c_vp), ("reg_out", c_vp), ("reg_lambda", c_d),
+        ("weight_sumsq", c_vp), ("reg_out", c_vp), ("reg_lambda", c_d), ("adam_stride", c_ll),
     ]
 
 
@@ -80,12 +80,12 @@ _SIGS = {
                                   c_ll, c_vp]),
     "skml_compact": (c_int, [c_vp, c_vp, c_vp, c_int, c_f, c_vp, c_vp, c_vp, c_vp, c_vp, c_ll, c_vp, c_vp]),
     "skml_compact_blocks": (c_ll, [c_int]),
-    "skml_update_dense": (c_int, [c_vp, c_vp, c_vp, c_vp, c_ll, c_f, c_int, c_f, c_f, c_int, c_vp]),
-    "skml_update_sparse": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_ll, c_f, c_int, c_f, c_f, c_vp]),
+    "skml_update_dense": (c_int, [c_vp, c_vp, c_vp, c_vp, c_ll, c_f, c_int, c_f, c_f, c_int, c_int, c_vp]),
+    "skml_update_sparse": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_ll, c_f, c_int, c_f, c_f, c_int, c_vp]),
     "skml_scatter_kv": (c_int, [c_vp, c_vp, c_vp, c_vp, c_ll, c_int, c_vp]),
     "skml_weight_norm_scratch_bytes": (c_ll, []),
     "skml_weight_norm": (c_int, [c_vp, c_ll, c_d, c_vp, c_vp, c_vp, c_vp]),
-    "skml_update_gathered": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_ll, c_int, c_f, c_int, c_f, c_f, c_vp]),
+    "skml_update_gathered": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_ll, c_int, c_f, c_int, c_f, c_f, c_int, c_vp]),
     "skml_gen_wstar": (c_int, [c_vp, c_ll, c_d, c_ull, c_vp]),
     "skml_gen_rows": (c_int, [c_vp, c_vp, c_vp, c_ll, c_ll, c_int, c_int, c_d, c_int, c_int, c_f, c_vp, c_ull, c_vp]),
     "skml_glm_coef": (c_int, [c_vp, c_vp, c_vp, c_vp, c_ll, c_ll, c_ll, c_d, c_vp, c_int, c_f, c_vp, c_vp, c_vp, c_ll, c_vp]),

@@ -367,6 +367,13 @@ def test_several_overlapping_payloads_sgd_and_adam(mode):
     v2 = torch.zeros(dim, device="cuda")
     dec.decode_update(ptrs, [None] * P, cap, 7, status, w=w2, lr=0.1, adam_m=m2, adam_v=v2, adam_scale=scale)
     assert torch.equal(w, w2) and torch.equal(m, m2) and torch.equal(vv, v2)
+    # the packed state layout ({m, v, sum, -} per coordinate) gives the same bits and leaves its sums clean
+    quad = torch.zeros((dim, 4), device="cuda")
+    w3 = torch.ones(dim, device="cuda")
+    dec.decode_update(ptrs, [None] * P, cap, 7, status, w=w3, lr=0.1, adam_m=quad[:, 0], adam_v=quad[:, 1], adam_scale=scale)
+    assert int(status.item()) == 0
+    assert torch.equal(w, w3) and torch.equal(m, quad[:, 0]) and torch.equal(vv, quad[:, 1])
+    assert float(quad[:, 2:].abs().max()) == 0 and float(dec.acc.abs().max()) == 0
 
 
 @pytest.mark.parametrize("encoder", ["delta_binary", "delta_adaptive"])
@@ -406,6 +413,13 @@ def test_decode_skewed_keys_many_ranks(encoder):
         return w, m, v
     for a, b in zip(adam(dec), adam(ref_dec)):
         assert torch.equal(a, b)
+    quad = torch.zeros((dim, 4), device="cuda")
+    wq = torch.ones(dim, device="cuda")
+    dec.decode_update(ptrs, [None] * P, cap, 3, status, w=wq, lr=0.1, adam_m=quad[:, 0], adam_v=quad[:, 1], adam_scale=0.3)
+    assert int(status.item()) == 0
+    for a, b in zip((wq, quad[:, 0], quad[:, 1]), adam(ref_dec)):
+        assert torch.equal(a, b)
+    assert float(quad[:, 2].abs().max()) == 0
     assert float(dec.acc.abs().max()) == 0
 
 
