@@ -67,6 +67,9 @@ def parse():
     p.add_argument("--no-baselines", action="store_true")
     p.add_argument("--unfused", action="store_true")
     p.add_argument("--pipeline-depth", type=int, default=0, choices=[0, 1])
+    p.add_argument("--exchange-sms", type=int, default=0,
+                   help="SMs given to the cooperative compress / decode kernels (0 = all); with --pipeline-depth 1 the "
+                        "rest runs the next batch's gradient")
     p.add_argument("--min-seconds", type=float, default=0.5, help="timed segments are repeated until this much time is covered")
     return p.parse_args()
 
@@ -167,6 +170,8 @@ class Bench:
         from sketchml_b200.config import MLConf
         c, a = self.c, self.args
         ex = {"fused": not a.unfused, "heartbeat": False}
+        if a.exchange_sms:
+            ex["exchange_sms"] = a.exchange_sms
         ex.update(extras)
         return MLConf(algo=c["algo"], format="synthetic", feature_num=c["dim"], worker_num=self.world, valid_ratio=0.0,
                       epoch_num=1, batch_sample_ratio=c["batch"], learn_rate=c["lr"], learn_decay=0.9, l2_reg=c["l2"],
@@ -360,7 +365,8 @@ def main():
                        "l2_policy": "inputs larger than L2: every step reads a fresh batch slice (and its prepared "
                                     "column index when `index_bytes` > 0) plus random words of the weight array, "
                                     "together several times the 126 MB of L2",
-                       "fused": not args.unfused, "pipeline_depth": args.pipeline_depth},
+                       "fused": not args.unfused, "pipeline_depth": args.pipeline_depth,
+                       "exchange_sms": args.exchange_sms or "all"},
             "segments": {"count": len(seg), "steps_each": args.steps, "ms_min": min(seg), "ms_median": statistics.median(seg),
                          "ms_max": max(seg)},
             "clocks": res["clocks"], "gpu_launches": res["launches"],

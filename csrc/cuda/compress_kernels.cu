@@ -2052,18 +2052,24 @@ __device__ void copy_range_to_peers(const CP& p, unsigned long long lo, unsigned
 }
 
 __device__ void finish_publish(const CP& p) {
+    __shared__ int s_last;
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
         unsigned int prev = atomicAdd(&p.ctrl[2], 1u);
-        if (prev == gridDim.x - 1) {
+        s_last = prev == gridDim.x - 1;
+        if (s_last) {
             p.ctrl[2] = 0;
             p.ctrl[4] = 0;  // the summary's min / max words go back to "nothing yet"
             p.ctrl[5] = 0;
-            __threadfence_system();
-            for (unsigned int r = 0; r < p.world; ++r)
-                if (p.peer_flag[r]) st_release_sys(p.peer_flag[r], p.step + 1);
         }
+    }
+    __syncthreads();
+    // the last block to arrive raises the arrival flags, one thread per rank so that the releases (each
+    // orders this GPU's earlier peer stores before its flag) run side by side instead of one after another
+    if (s_last && threadIdx.x < p.world && p.peer_flag[threadIdx.x]) {
+        __threadfence_system();
+        st_release_sys(p.peer_flag[threadIdx.x], p.step + 1);
     }
 }
 

@@ -57,14 +57,12 @@ struct DecSmem {
 __device__ bool decode_prepare(const DP& p, DecSmem& s) {
     // the full headers sit in the (still idle) table staging area while the work table is built
     SkmlHeader* full = reinterpret_cast<SkmlHeader*>(reinterpret_cast<unsigned char*>(&s) + p.tab_off);
-    if (threadIdx.x == 0) {
-        s.ok = 1;
-        for (int r = 0; r < p.world; ++r)
-            if (p.flag[r] && !skml_wait_flag(p.flag[r], p.step + 1, p.status, p.budget, (unsigned int)r)) {
-                s.ok = 0;
-                break;
-            }
-    }
+    if (threadIdx.x == 0) s.ok = 1;
+    __syncthreads();
+    // one thread per rank polls that rank's arrival flag (bounded), so the waits overlap
+    if (threadIdx.x < p.world && p.flag[threadIdx.x] &&
+        !skml_wait_flag(p.flag[threadIdx.x], p.step + 1, p.status, p.budget, (unsigned int)threadIdx.x))
+        s.ok = 0;
     __syncthreads();
     if (!s.ok) return false;
     // headers -> shared memory (L2 loads: the bytes were written by other GPUs)

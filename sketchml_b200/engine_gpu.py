@@ -112,11 +112,14 @@ class GpuEngine:
                                         device=self.device)
         self._norm_seeded = False
         if self.mode == "sketch":
+            # extras["exchange_sms"]: SMs the two cooperative kernels take (default: all). With pipeline_depth=1
+            # the rest is left to the next batch's gradient kernels on their own stream.
+            xsms = int(conf.extras.get("exchange_sms", 0) or 0)
             self.comp = GpuCompressor(dim, bound, conf.quant_bin_num, conf.sketch_group_num, conf.sketch_row_num,
-                                      conf.sketch_col_ratio, conf.seed, self.device,
+                                      conf.sketch_col_ratio, conf.seed, self.device, grid=xsms,
                                       fused=bool(conf.extras.get("fused", True)), budget_s=conf.step_timeout_s,
                                       key_encoder=conf.key_encoder, cell_bits=0 if conf.cell_bits == 0 else -1)
-            self.dec = GpuDecoder(dim, bound * comm.world, self.device, fused=bool(conf.extras.get("fused", True)),
+            self.dec = GpuDecoder(dim, bound * comm.world, self.device, fused=bool(conf.extras.get("fused", True)), grid=3 * xsms,
                                   budget_s=conf.step_timeout_s, max_groups=conf.sketch_group_num,
                                   table_capacity=self._table_scratch_bytes(conf, bound, comm.world))
             if self.reg_every_step and m.loss.is_l2_reg and conf.extras.get("track_norm", True):
@@ -297,8 +300,16 @@ class GpuEngine:
                 # the buffers of this parity were last read by step t-2's compress kernel
                 self.stream_g.wait_event(self.ev_applied[par])
                 st.partials.copy_(self.partials_template)
-                glm_grad(csr, segs, m.weights, st, m.loss.loss_id, rows, self.conf.hot_columns, self.conf.step_timeout_s)
-                compact_gradient(st, m.weights, lam)
+                bi = self._index_of(csr, segs)
+                if bi is not None:
+                    from .ops.transposed import glm_grad_transposed
+                    glm_grad_transposed(csr, bi, m.weights, self.coef, st.vals, st.partials, st.status, m.loss.loss_id, lam,
+                                        self.conf.step_timeout_s)
+                    st.keys[:bi.n_cols].copy_(bi.ucols)
+                    st.meta.copy_(bi.meta)
+                else:
+                    glm_grad(csr, segs, m.weights, st, m.loss.loss_id, rows, self.conf.hot_columns, self.conf.step_timeout_s)
+                    compact_gradient(st, m.weights, lam)
                 self.ev_grad[par].record()
             m.optimizer.advance()
             return _BatchHandle(rows, self.batch_index), None, None
