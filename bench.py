@@ -67,6 +67,9 @@ def parse():
     p.add_argument("--no-baselines", action="store_true")
     p.add_argument("--unfused", action="store_true")
     p.add_argument("--pipeline-depth", type=int, default=0, choices=[0, 1])
+    p.add_argument("--index-form", default="columns", choices=["tiled", "columns"],
+                   help="prepared batch index: plain per-column lists, or row-tiled (coefficient tiles in shared memory, no "
+                        "atomics; slower on the named configurations)")
     p.add_argument("--exchange-sms", type=int, default=0,
                    help="SMs given to the cooperative compress / decode kernels (0 = all); with --pipeline-depth 1 the "
                         "rest runs the next batch's gradient")
@@ -172,6 +175,7 @@ class Bench:
         ex = {"fused": not a.unfused, "heartbeat": False}
         if a.exchange_sms:
             ex["exchange_sms"] = a.exchange_sms
+        ex["tiled_index"] = a.index_form == "tiled"
         ex.update(extras)
         return MLConf(algo=c["algo"], format="synthetic", feature_num=c["dim"], worker_num=self.world, valid_ratio=0.0,
                       epoch_num=1, batch_sample_ratio=c["batch"], learn_rate=c["lr"], learn_decay=0.9, l2_reg=c["l2"],

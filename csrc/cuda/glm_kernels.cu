@@ -1083,6 +1083,153 @@ extern "C" int skml_colsum_ex(const int* colptr, const int* rowidx, const float*
 }
 
 // ---------------------------------------------------------------------------
+// Row-tiled form of the transposed index. The per-column gather of `coef[row]` above costs one random
+// 32-byte L2 sector per batch entry. Here the batch rows are cut into tiles of `tile_rows` rows whose
+// coefficients fit in shared memory (196 KB for 49,152 rows), the index is ordered by (tile, column,
+// row) with 16-bit tile-local rows, and a block that owns (a share of) a tile gathers from shared
+// memory. One partial sum per (tile, column) pair goes to `partial[pair_dst[p]]`, a position in
+// (column, tile) order, so the second kernel adds a column's partial sums from consecutive words, in
+// tile order: no atomics anywhere, the result is bit-reproducible.
+// ---------------------------------------------------------------------------
+constexpr int CT_SHORT = 8;   // pairs of up to this many entries are summed by one lane
+
+template <bool HAS_VALS>
+__global__ void __launch_bounds__(1024, 1)
+coltile_partial_kernel(const float* __restrict__ coef, int rows, int tile_rows, const int* __restrict__ tile_pair_ptr,
+                       int blocks_per_tile, const int* __restrict__ pair_ptr, const unsigned short* __restrict__ lrow,
+                       const float* __restrict__ svals, const int* __restrict__ pair_dst, float* __restrict__ partial) {
+    extern __shared__ __align__(16) float s_coef[];
+    const int tile = blockIdx.x / blocks_per_tile, sub = blockIdx.x % blocks_per_tile;
+    const int r0 = tile * tile_rows, nr = min(tile_rows, rows - r0);
+    {   // the tile's coefficients (r0 is a multiple of 4 floats: 16-byte aligned rows)
+        const float4* src = reinterpret_cast<const float4*>(coef + r0);
+        float4* dst = reinterpret_cast<float4*>(s_coef);
+        const int nv = nr / 4;
+        for (int i = threadIdx.x; i < nv; i += blockDim.x) dst[i] = __ldg(src + i);
+        for (int i = 4 * nv + threadIdx.x; i < nr; i += blockDim.x) s_coef[i] = __ldg(coef + r0 + i);
+    }
+    __syncthreads();
+    // this block's share of the tile's pairs: cut by entries (pairs are not split), found by binary search
+    const int p0 = tile_pair_ptr[tile], p1 = tile_pair_ptr[tile + 1];
+    __shared__ int s_my[2];
+    if (threadIdx.x < 2) {
+        const long long e0 = pair_ptr[p0], e1 = pair_ptr[p1];
+        const int which = sub + threadIdx.x;
+        int pos;
+        if (which == 0) pos = p0;
+        else if (which >= blocks_per_tile) pos = p1;
+        else {
+            const long long target = e0 + (e1 - e0) * which / blocks_per_tile;
+            int lo = p0, hi = p1;
+            while (lo < hi) {   // first pair that starts at or after the target entry
+                const int mid = (lo + hi) >> 1;
+                if ((long long)pair_ptr[mid] < target) lo = mid + 1;
+                else hi = mid;
+            }
+            pos = lo;
+        }
+        s_my[threadIdx.x] = pos;
+    }
+    __syncthreads();
+    const int my0 = s_my[0], my1 = s_my[1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    // the warps share the block's pairs by entries too (a warp that drew the frequent columns' pairs would
+    // otherwise have many times the work of the others)
+    int w0 = my0, w1 = my1;
+    if (lane < 2 && my1 > my0) {
+        const long long e0 = pair_ptr[my0], e1 = pair_ptr[my1];
+        const int which = warp + lane;
+        int pos;
+        if (which == 0) pos = my0;
+        else if (which >= nwarps) pos = my1;
+        else {
+            const long long target = e0 + (e1 - e0) * which / nwarps;
+            int lo = my0, hi = my1;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if ((long long)pair_ptr[mid] < target) lo = mid + 1;
+                else hi = mid;
+            }
+            pos = lo;
+        }
+        if (lane == 0) w0 = pos;
+        else w1 = pos;
+    }
+    w0 = __shfl_sync(0xFFFFFFFFu, w0, 0);
+    w1 = __shfl_sync(0xFFFFFFFFu, w1, 1);
+    for (int base = w0; base < w1; base += 32) {
+        const int p = base + lane;
+        const bool valid = p < w1;
+        const int e0 = valid ? __ldg(pair_ptr + p) : 0, e1 = valid ? __ldg(pair_ptr + p + 1) : 0;
+        const int len = e1 - e0;
+        float acc = 0.f;
+        if (valid && len <= CT_SHORT) {
+            for (int e = e0; e < e1; ++e) acc = fmaf(s_coef[lrow[e]], HAS_VALS ? svals[e] : 1.f, acc);
+        }
+        unsigned int longs = __ballot_sync(0xFFFFFFFFu, valid && len > CT_SHORT);
+        while (longs) {   // the warp sums one long pair at a time (fixed order: lane stride, shuffle tree)
+            const int src = __ffs(longs) - 1;
+            longs &= longs - 1;
+            const int se0 = __shfl_sync(0xFFFFFFFFu, e0, src), se1 = __shfl_sync(0xFFFFFFFFu, e1, src);
+            float part = 0.f, part2 = 0.f;   // two independent chains: the loads of a round overlap
+            int e = se0 + lane;
+            for (; e + 32 < se1; e += 64) {
+                const unsigned short r0 = lrow[e], r1 = lrow[e + 32];
+                part = fmaf(s_coef[r0], HAS_VALS ? svals[e] : 1.f, part);
+                part2 = fmaf(s_coef[r1], HAS_VALS ? svals[e + 32] : 1.f, part2);
+            }
+            if (e < se1) part = fmaf(s_coef[lrow[e]], HAS_VALS ? svals[e] : 1.f, part);
+            part = warp_sum(part + part2);
+            if (lane == src) acc = part;
+        }
+        if (valid) partial[__ldg(pair_dst + p)] = acc;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+colsum_combine_kernel(const int* __restrict__ col_pair_ptr, const float* __restrict__ partial, const int* __restrict__ ucols,
+                      const float* __restrict__ w, float lambda, int n_cols, float* __restrict__ out) {
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < n_cols; c += gridDim.x * blockDim.x) {
+        const int q0 = col_pair_ptr[c], q1 = col_pair_ptr[c + 1];
+        float v = 0.f;
+        for (int q = q0; q < q1; ++q) v += partial[q];   // tile order
+        out[c] = v + lambda * __ldg(w + ucols[c]);
+    }
+}
+
+extern "C" int skml_colsum_tiled(const int* tile_pair_ptr, const int* pair_ptr, const unsigned short* lrow, const float* svals,
+                                 const int* pair_dst, const int* col_pair_ptr, const int* ucols, int rows, int tile_rows,
+                                 int n_tiles, int n_cols, const float* coef, const float* w, float lambda, float* partial,
+                                 float* out, void* stream_) {
+    if (n_cols <= 0 || n_tiles <= 0) return 0;
+    if (tile_rows <= 0 || tile_rows > 65536 || (tile_rows & 3) || (long long)n_tiles * tile_rows < rows) return (int)cudaErrorInvalidValue;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    static bool ready = false;
+    if (!ready) {
+        cudaError_t e = cudaFuncSetAttribute(coltile_partial_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 * 4 - 40 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(coltile_partial_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 * 4 - 40 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        ready = true;
+    }
+    const int tr = tile_rows < rows ? tile_rows : ((rows + 3) & ~3);
+    const size_t smem = (size_t)tr * sizeof(float);
+    if (smem > 65536 * 4 - 40 * 1024) return (int)cudaErrorInvalidValue;
+    int bpt = sm_count() / n_tiles;
+    if (bpt < 1) bpt = 1;
+    const unsigned grid = (unsigned)(n_tiles * bpt);
+    if (svals)
+        coltile_partial_kernel<true><<<grid, 1024, smem, stream>>>(coef, rows, tile_rows, tile_pair_ptr, bpt, pair_ptr, lrow, svals,
+                                                                  pair_dst, partial);
+    else
+        coltile_partial_kernel<false><<<grid, 1024, smem, stream>>>(coef, rows, tile_rows, tile_pair_ptr, bpt, pair_ptr, lrow, svals,
+                                                                   pair_dst, partial);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    colsum_combine_kernel<<<sm_count() * 8, 256, 0, stream>>>(col_pair_ptr, partial, ucols, w, lambda, n_cols, out);
+    return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
 // skml_compact_noalloc: the compaction above for callers that must not allocate.
 // (Declared and documented in skml_noalloc.h; it has no counterpart in the reference.)
 //

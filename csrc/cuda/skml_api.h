@@ -115,6 +115,11 @@ int skml_update_gathered(float* w, float* m, float* v, float* acc, const int* ke
 long long skml_weight_norm_scratch_bytes();
 int skml_weight_norm(const float* w, long long dim, double lambda, double* sumsq_out, double* reg_out, void* scratch,
                      void* stream);
+// Column sums over the row-tiled transposed index (see SkmlStepArgs.tt_*): out[c] = sum over the batch entries of
+// column c of coef[row] * value + lambda * w[ucols[c]], bit-reproducible. `partial`: scratch of one float per pair.
+int skml_colsum_tiled(const int* tile_pair_ptr, const int* pair_ptr, const unsigned short* lrow, const float* svals,
+                      const int* pair_dst, const int* col_pair_ptr, const int* ucols, int rows, int tile_rows, int n_tiles,
+                      int n_cols, const float* coef, const float* w, float lambda, float* partial, float* out, void* stream);
 int skml_scatter_kv(float* acc, const int* keys, const float* vals, const long long* counts, long long stride,
                     int lists, void* stream);
 int skml_gen_wstar(float* w, long long dim, double density, unsigned long long seed, void* stream);
@@ -269,6 +274,15 @@ typedef struct SkmlStepArgs {
     float* wc;                         // device scratch [>= l_ncols]: weights of the batch's columns
     float* gc;                         // device scratch [>= l_ncols], all zero between steps: compact gradient
     void* grad_done_event;             // optional cudaEvent_t, recorded after the last kernel that reads the batch
+    // row-tiled form of the transposed index (tt_pair_ptr null = the per-column form above); t_vals, t_ucols,
+    // t_cols, t_meta and coef are shared with it, t_vals being in (tile, column, row) order
+    const int* tt_tile_pair_ptr;       // [tt_tiles + 1] pair ranges of the row tiles
+    const int* tt_pair_ptr;            // [pairs + 1] entry ranges of the (tile, column) pairs
+    const unsigned short* tt_lrow;     // tile-local row of every entry
+    const int* tt_pair_dst;            // [pairs] position of a pair's partial sum in (column, tile) order
+    const int* tt_col_pair_ptr;        // [t_cols + 1] partial-sum ranges of the columns
+    float* tt_partial;                 // device scratch [>= pairs]
+    long long tt_tiles, tt_tile_rows, tt_rows;
 } SkmlStepArgs;
 
 int skml_train_step(SkmlStepArgs* args, void* stream);

@@ -17,17 +17,23 @@ static int batch_consumed(const SkmlStepArgs* a, cudaStream_t stream) {
 extern "C" int skml_train_step(SkmlStepArgs* a, void* stream_) {
     if (!a || !a->compress || !a->decode) return (int)cudaErrorInvalidValue;
     cudaStream_t stream = (cudaStream_t)stream_;
-    if (a->t_colptr) {
+    if (a->t_colptr || a->tt_pair_ptr) {
         // transposed index: coefficients per row, then one gather-sum per distinct column
-        int rc = skml_step_prep(a->partials, a->partials_template, a->gvals, a->t_long_col, (int)a->t_long, stream_);
+        const bool tiled = a->tt_pair_ptr != nullptr;
+        int rc = skml_step_prep(a->partials, a->partials_template, a->gvals, a->t_long_col, tiled ? 0 : (int)a->t_long, stream_);
         if (rc) return rc;
         rc = skml_glm_coef(a->rowptr, a->cols, a->vals, a->labels, a->seg_lo[0], a->seg_cnt[0], a->nnz_padded,
                                a->avg_nnz, a->w, (int)a->loss_id, (float)a->inv_batch, a->partials + 1, a->coef,
                                a->status, a->budget_cycles, stream_);
         if (rc) return rc;
-        rc = skml_colsum_ex(a->t_colptr, a->t_rowidx, a->t_vals, a->t_ucols, a->t_bins, a->t_long_col, a->t_long_e0,
-                            a->t_long_e1, (int)a->t_short, (int)a->t_medium, (int)a->t_long, (int)a->t_cols, a->coef, a->w,
-                            (float)a->lambda, a->gvals, 1, stream_);
+        if (tiled)
+            rc = skml_colsum_tiled(a->tt_tile_pair_ptr, a->tt_pair_ptr, a->tt_lrow, a->t_vals, a->tt_pair_dst, a->tt_col_pair_ptr,
+                                   a->t_ucols, (int)a->tt_rows, (int)a->tt_tile_rows, (int)a->tt_tiles, (int)a->t_cols, a->coef,
+                                   a->w, (float)a->lambda, a->tt_partial, a->gvals, stream_);
+        else
+            rc = skml_colsum_ex(a->t_colptr, a->t_rowidx, a->t_vals, a->t_ucols, a->t_bins, a->t_long_col, a->t_long_e0,
+                                a->t_long_e1, (int)a->t_short, (int)a->t_medium, (int)a->t_long, (int)a->t_cols, a->coef, a->w,
+                                (float)a->lambda, a->gvals, 1, stream_);
         if (rc) return rc;
         rc = batch_consumed(a, stream);
         if (rc) return rc;

@@ -202,15 +202,27 @@ class GpuEngine:
         idx = []
         torch.cuda.synchronize(self.device)
         t0 = time.perf_counter()
+        # extras["tiled_index"]: the row-tiled form (a row tile's coefficients in shared memory, no atomics at all,
+        # strictly bit-reproducible). Off by default: measured on the headline batch it is slower (partial sums
+        # 176 us + combine 92 us against 103 us), because the frequent columns, which hold most entries, already
+        # gather near-sequential coefficients in the per-column form, and a 192 KB tile allows one block per SM.
+        tiled = bool(conf.extras.get("tiled_index", False))
         for b in range(csr.rows // B):
-            bi = build_batch_index(csr, b * B, (b + 1) * B)
+            bi = build_batch_index(csr, b * B, (b + 1) * B, tiled=tiled)
             if bi.n_cols > self.st.dim * 2 // 3 or bi.n_cols > self.st.n_max:
                 return  # near-dense gradients take the dense kind: keep the scatter path
             idx.append(bi)
+        if tiled:
+            # one scratch for the partial sums of all batches (a step uses one batch's index at a time)
+            shared = torch.zeros(max([bi.tiled.n_pairs for bi in idx if bi.tiled is not None] + [1]), dtype=torch.float32,
+                                 device=self.device)
+            for bi in idx:
+                if bi.tiled is not None:
+                    bi.tiled.partial = shared
         torch.cuda.synchronize(self.device)
         self.index_build_s, self.index_bytes = time.perf_counter() - t0, sum(bi.nbytes() for bi in idx)
         self.tindex = idx
-        self.coef = torch.zeros(B, dtype=torch.float32, device=self.device)
+        self.coef = torch.zeros((B + 3) // 4 * 4, dtype=torch.float32, device=self.device)
 
     def _launch_fast_step(self, step: int, lr: float, adam_scale: float, ring_ptr: int) -> None:
         csr, segs, rows, done_event = self._pending
@@ -224,14 +236,23 @@ class GpuEngine:
             a.seg_lo[i], a.seg_cnt[i] = lo, hi - lo
         a.inv_batch = 1.0 / max(1, rows)
         bi = self._index_of(csr, segs)
-        if bi is not None:
+        if bi is not None and bi.tiled is not None:
+            tp = bi.tiled
+            a.t_colptr, a.t_vals, a.t_ucols, a.t_cols = None, L.ptr(bi.svals), L.ptr(bi.ucols), bi.n_cols
+            a.t_long_col, a.t_long = None, 0
+            a.tt_tile_pair_ptr, a.tt_pair_ptr, a.tt_lrow = L.ptr(tp.tile_pair_ptr), L.ptr(tp.pair_ptr), L.ptr(tp.lrow)
+            a.tt_pair_dst, a.tt_col_pair_ptr, a.tt_partial = L.ptr(tp.pair_dst), L.ptr(tp.col_pair_ptr), L.ptr(tp.partial)
+            a.tt_tiles, a.tt_tile_rows, a.tt_rows = tp.n_tiles, tp.tile_rows, bi.rows
+            a.t_meta, a.coef = L.ptr(bi.meta), L.ptr(self.coef)
+        elif bi is not None:
+            a.tt_pair_ptr = None
             a.t_colptr, a.t_rowidx, a.t_vals, a.t_ucols = L.ptr(bi.colptr), L.ptr(bi.rowidx), L.ptr(bi.svals), L.ptr(bi.ucols)
             a.t_bins, a.t_long_col, a.t_long_e0, a.t_long_e1 = (L.ptr(bi.bins), L.ptr(bi.long_col), L.ptr(bi.long_e0),
                                                                 L.ptr(bi.long_e1))
             a.t_short, a.t_medium, a.t_long, a.t_cols = bi.n_short, bi.n_medium, bi.n_long, bi.n_cols
             a.t_meta, a.coef = L.ptr(bi.meta), L.ptr(self.coef)
         else:
-            a.t_colptr = None
+            a.t_colptr = a.tt_pair_ptr = None
         lid = getattr(csr, "lid", None) if bi is None else None
         if lid is not None:
             ucols, n_cols, meta_ptr = lid

@@ -63,6 +63,8 @@ class StepArgs(C.Structure):
         ("t_long", c_ll), ("t_cols", c_ll), ("t_meta", c_vp), ("coef", c_vp),
         ("l_ucols", c_vp), ("l_meta", c_vp), ("l_ncols", c_ll), ("wc", c_vp), ("gc", c_vp),
         ("grad_done_event", c_vp),
+        ("tt_tile_pair_ptr", c_vp), ("tt_pair_ptr", c_vp), ("tt_lrow", c_vp), ("tt_pair_dst", c_vp),
+        ("tt_col_pair_ptr", c_vp), ("tt_partial", c_vp), ("tt_tiles", c_ll), ("tt_tile_rows", c_ll), ("tt_rows", c_ll),
     ]
 
 
@@ -85,6 +87,8 @@ _SIGS = {
     "skml_scatter_kv": (c_int, [c_vp, c_vp, c_vp, c_vp, c_ll, c_int, c_vp]),
     "skml_weight_norm_scratch_bytes": (c_ll, []),
     "skml_weight_norm": (c_int, [c_vp, c_ll, c_d, c_vp, c_vp, c_vp, c_vp]),
+    "skml_colsum_tiled": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_vp, c_vp, c_f,
+                                  c_vp, c_vp, c_vp]),
     "skml_update_gathered": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_ll, c_int, c_f, c_int, c_f, c_f, c_int, c_vp]),
     "skml_gen_wstar": (c_int, [c_vp, c_ll, c_d, c_ull, c_vp]),
     "skml_gen_rows": (c_int, [c_vp, c_vp, c_vp, c_ll, c_ll, c_int, c_int, c_d, c_int, c_int, c_f, c_vp, c_ull, c_vp]),

@@ -182,3 +182,38 @@ def test_transposed_index_gradient_matches_scatter_path(binary):
     assert abs(float(st.partials[1]) - ref_loss) < 1e-3 * abs(ref_loss)
     assert abs(bi.n_cols - n) <= 3          # the scatter path drops |v| <= 1e-8, this one keeps them
     assert float((got - ref).abs().max()) < 2e-6 * max(1.0, float(ref.abs().max())) + 2e-8
+
+
+@pytest.mark.parametrize("binary", [True, False])
+@pytest.mark.parametrize("tile_rows_max,rows", [(49152, 2000), (512, 2000), (1000, 5003), (49152, 60000)])
+def test_row_tiled_index_matches_the_per_column_form(binary, tile_rows_max, rows, monkeypatch):
+    """The row-tiled index (tile coefficients in shared memory, partial sums per (tile, column) pair added in
+    tile order) gives the gradient of the per-column form up to the order of the float adds, the same keys,
+    and the same bits on every repetition."""
+    from sketchml_b200.models.loss import L2LogLoss
+    from sketchml_b200.ops import DeviceCSR, GlmState
+    from sketchml_b200.ops import transposed as T
+    monkeypatch.setattr(T, "TILE_ROWS_MAX", tile_rows_max)
+    dev = torch.device("cuda")
+    loss = L2LogLoss(1e-3)
+    dim = 30000
+    m = _random_csr(rows + 500, dim, 1, 40, seed=33, binary=binary)
+    csr = DeviceCSR(m, dev)
+    w = (torch.randn(dim) * 0.3).float().to(dev)
+    st = GlmState.create(dim, dim, dev)
+    lo, hi = 250, 250 + rows
+    plain, tiled = T.build_batch_index(csr, lo, hi), T.build_batch_index(csr, lo, hi, tiled=True)
+    assert tiled.tiled is not None and tiled.tiled.n_tiles == -(-rows // tile_rows_max)
+    assert torch.equal(plain.ucols, tiled.ucols) and int(tiled.tiled.pair_ptr[-1]) == int(csr.rowptr[hi] - csr.rowptr[lo])
+    assert int(tiled.tiled.col_pair_ptr[-1]) == tiled.tiled.n_pairs
+    coef = torch.zeros((rows + 3) // 4 * 4, device=dev)
+    outs = []
+    for bi in (plain, tiled, tiled):
+        out = torch.full((dim,), 7.0, device=dev)
+        st.partials.zero_()
+        T.glm_grad_transposed(csr, bi, w, coef, out, st.partials, st.status, loss.loss_id, loss.lam)
+        assert int(st.status.item()) == 0
+        outs.append(out[:bi.n_cols].clone())
+    assert torch.equal(outs[1], outs[2])
+    assert float((outs[0].double() - outs[1].double()).abs().max()) < 2e-6 * max(1.0, float(outs[0].abs().max()))
+
