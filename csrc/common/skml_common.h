@@ -10,6 +10,7 @@
 //   sketch/.../sketch/frequency/GroupedMinMaxSketch.java:148-158,
 //   MinMaxSketch.java:88-97, DeltaBinaryEncoder.java:67-87 -> field lists of the container
 #pragma once
+#include <stddef.h>
 #include <stdint.h>
 
 #if defined(__CUDACC__)
@@ -55,7 +56,7 @@ struct SkmlHeader {
     uint64_t total_bytes;
     uint64_t off_bucket_values, off_group_table, off_tables, off_key_flags, off_key_deltas,
         off_restart, off_dense_codes;
-    uint64_t header_checksum;  // FNV-1a 64 over all bytes before this field
+    uint64_t header_checksum;  // FNV-1a 64 recurrence over the 64-bit words before this field
     uint8_t pad[SKML_HEADER_BYTES - 216];
 };
 static_assert(sizeof(SkmlHeader) == SKML_HEADER_BYTES, "SkmlHeader must be 256 bytes");
@@ -96,10 +97,19 @@ SKML_HD uint64_t skml_fnv1a(const uint8_t* p, uint32_t n) {
     return h;
 }
 
+// Header checksum: the FNV-1a recurrence over the header's 64-bit little-endian words (not its bytes: the
+// fused kernels compute it on their critical path, one dependent multiply per step, 18 steps instead of 144).
 SKML_HD uint64_t skml_header_checksum(const SkmlHeader* h) {
-    return skml_fnv1a(reinterpret_cast<const uint8_t*>(h),
-                      (uint32_t)((const uint8_t*)&h->header_checksum - (const uint8_t*)h));
+    const uint64_t* w = reinterpret_cast<const uint64_t*>(h);
+    const uint32_t n = (uint32_t)(((const uint8_t*)&h->header_checksum - (const uint8_t*)h) / 8);
+    uint64_t x = 1469598103934665603ull;
+    for (uint32_t i = 0; i < n; ++i) {
+        x ^= w[i];
+        x *= 1099511628211ull;
+    }
+    return x;
 }
+static_assert(offsetof(SkmlHeader, header_checksum) % 8 == 0, "the checksum covers whole 64-bit words");
 
 // ---------------------------------------------------------------------------
 // Integer hashes with Java int semantics: adds, multiplies and left shifts wrap
