@@ -144,7 +144,8 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
     if (threadIdx.x == 0) {
         int ni = 0, nhuf = 0;
         unsigned long long chunks = 0, keys = 0, tab_used = 0;
-        int dense = 0;
+        int dense = 0, ref = 0;
+        unsigned int ref_n = 0;
         double mx = 0.0;
         for (int r = 0; r < p.world; ++r) {
             const SkmlHeader& h = full[r];
@@ -185,8 +186,13 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
                     tab_used += bytes;
                     ++nhuf;
                 }
-                chunks += (it.e.n + SKML_RESTART_INTERVAL - 1) / SKML_RESTART_INTERVAL;
-                keys += it.e.n;
+                const unsigned int n_it = it.e.n;
+                chunks += (n_it + SKML_RESTART_INTERVAL - 1) / SKML_RESTART_INTERVAL;
+                keys += n_it;
+                if (n_it > ref_n) {   // the longest list (the first of equals) gives the apply its range bounds
+                    ref_n = n_it;
+                    ref = ni;
+                }
                 ++ni;
             }
             if (!s.ok) break;
@@ -200,9 +206,6 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
             s.rank_key_begin[r] = keys;
             s.rank_item_begin[r] = ni;
         }
-        int ref = 0;
-        for (int i = 1; i < ni; ++i)
-            if (s.items[i].e.n > s.items[ref].e.n) ref = i;
         s.ref_item = ref;
         s.nitems = ni;
         s.nhuf = nhuf;
