@@ -6,9 +6,9 @@ variable-width bit code for sorted keys. The training step does not come through
 themselves, chunk by chunk, without leaving the device (csrc/cuda/compress_kernels.cu,
 decode_common.cuh). This module is the library form of the codec, `encode(keys) -> AdaptiveKeys`
 and back, bit for bit equal to the CPU oracle (`oracle.delta_adaptive_encode`). It returns tensors
-of exactly the encoded size, which depends on the data, so `encode` reads the two bit counts back
-to the host once; the kernels are maps over keys or words (csrc/cuda/keys_kernels.cu) with
-`torch.cumsum` between them.
+of exactly the encoded size, which depends on the data, so `encode` reads the status, the chosen
+mode and the two bit counts back to the host in one copy; the kernels are maps over keys or words
+(csrc/cuda/keys_kernels.cu) with `torch.cumsum` between them.
 """
 from __future__ import annotations
 
@@ -60,11 +60,12 @@ def encode(keys: torch.Tensor) -> AdaptiveKeys:
     L.check(lib.skml_da_widths(L.ptr(keys), n, L.ptr(params), L.ptr(flag_w), L.ptr(delta_w), L.stream()), "skml_da_widths")
     flag_incl = torch.cumsum(flag_w[:n], 0, dtype=torch.int64) if n else torch.zeros(0, dtype=torch.int64, device=dev)
     delta_incl = torch.cumsum(delta_w[:n], 0, dtype=torch.int64) if n else torch.zeros(0, dtype=torch.int64, device=dev)
-    if int(status.item()) & 1:
+    # the one read-back of the call: status, mode and the two stream lengths together
+    zero = torch.zeros(1, dtype=torch.int64, device=dev)
+    st, m, kind, flag_bits, delta_bits = (int(x) for x in torch.cat(
+        [status.long(), params.long(), flag_incl[-1:] if n else zero, delta_incl[-1:] if n else zero]).tolist())
+    if st & 1:
         raise ValueError("keys must be non-negative and strictly increasing")
-    m, kind = (int(x) for x in params.tolist())
-    flag_bits = int(flag_incl[-1]) if n else 0
-    delta_bits = int(delta_incl[-1]) if n else 0
     fw, dw = _words(flag_bits, dev), _words(delta_bits, dev)
     L.check(lib.skml_da_pack(L.ptr(keys), n, L.ptr(params), L.ptr(flag_incl), L.ptr(delta_incl), L.ptr(fw), L.ptr(dw),
                              L.stream()), "skml_da_pack")
