@@ -73,6 +73,7 @@ struct CP {
     unsigned int* key_hist;          // delta_adaptive: [SKML_MAX_GROUPS][32] keys per delta width, zeroed in S1
     int key_encoder;
     int huffman;                     // sketch tables travel Huffman-coded (cell_bits = 0)
+    int sample_splits;               // split points from a sample every cluster draws alike (no S2, two grid barriers fewer)
     unsigned int* cell_hist;         // Huffman: [bin_num + groups] cells per symbol, zeroed in S1
     unsigned long long* blk_tbits;   // Huffman: [grid][SKML_MAX_GROUPS] code bits per block and group
     unsigned int* tchunk_off;        // Huffman: [table chunks] bit offset of a chunk inside its owner's part of the stream
@@ -603,6 +604,64 @@ __device__ void stage_summary(const CP& p, Smem& s, const float* __restrict__ va
     }
 }
 
+// S1, sample form. Every thread-block cluster draws the SAME stratified sample of the values (one value
+// per stride of n / m positions, the offset a function of (seed, step, rank)), so every block ends up with
+// the same split points without a grid barrier and without S2. The two blocks of a cluster sort one half
+// of a 4096-value sample each and read the other half through distributed shared memory: split t is the
+// value of rank floor(m (t + 1) / q) in the union of the two sorted halves, found by a merge-path search
+// over the own half and a local copy of the other. Without clusters a block sorts 2048 values alone.
+// The rank error of a split is that of an m-value sample (standard deviation at most 0.8 % of n at
+// m = 4096), the same order as the k = 128 summary's; inputs of up to m values are summarised exactly.
+// Minimum and maximum of ALL values are taken by the count stage, which reads every value anyway.
+__device__ void stage_sample_splits(const CP& p, Smem& s, const float* __restrict__ vals, long long n) {
+    const unsigned int cs = cluster_nctarank(), cr = cluster_ctarank();
+    const int halves = cs >= 2 ? 2 : 1;
+    const long long M = (long long)TILE * halves;
+    const long long m = n < M ? n : M;   // sample size
+    const unsigned long long off = n > m ? skml_rand(p.seed, p.step, p.rank, 0x7300u) % (unsigned long long)n : 0ull;
+    const int mine = (int)((m - (long long)(cr % halves) + halves - 1) / halves);   // samples in this block's half
+    for (int t = threadIdx.x; t < TILE; t += blockDim.x) {
+        const long long j = (long long)t * halves + (cr % halves);
+        unsigned int key = 0xFFFFFFFFu;
+        if (j < m) {
+            const long long pos = n > m ? (long long)(((unsigned long long)j * (unsigned long long)n + off) / (unsigned long long)m) : j;
+            key = f2ord(__ldg(vals + pos));
+        }
+        s.qs.tile[t] = key;
+    }
+    __syncthreads();
+    block_sort_2048(s.qs.tile);
+    __syncthreads();
+    const int theirs = (int)(m - mine);
+    unsigned int* const their = s.qs.runs_all;   // local copy of the other block's sorted half
+    if (halves == 2) {
+        cluster_sync_all();   // both halves are sorted and visible in the cluster
+        const unsigned int other = dsmem_addr(s.qs.tile, (cr % halves) ^ 1u);
+        for (int t = threadIdx.x; t < theirs; t += blockDim.x) their[t] = ld_dsmem_u32(other + 4u * (unsigned int)t);
+        cluster_sync_all();   // nobody reads the other block's shared memory any more
+    }
+    __syncthreads();
+    const double inv_q = 1.0 / (double)p.q;
+    for (int t = threadIdx.x; t < p.q - 1; t += blockDim.x) {
+        long long k = (long long)((double)m * ((double)(t + 1) * inv_q));   // target rank in the sample
+        if (k > m - 1) k = m - 1;
+        // i = how many of the k values before the answer come from this block's half (ties: this half first)
+        int lo = (int)(k - theirs > 0 ? k - theirs : 0), hi = (int)(k < mine ? k : mine);
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            const long long j = k - mid;
+            const bool ok = j >= theirs || s.qs.tile[mid - 1] <= their[j];
+            if (ok) lo = mid;
+            else hi = mid - 1;
+        }
+        const long long j = k - lo;
+        const unsigned int a = lo < mine ? s.qs.tile[lo] : 0xFFFFFFFFu;
+        const unsigned int b = j < theirs ? their[j] : 0xFFFFFFFFu;
+        p.splits_raw[t] = a < b ? a : b;   // every block stores the same values
+    }
+    __syncthreads();
+}
+
 // ---------------------------------------------------------------------------
 // S2: weighted-rank query over all published runs -> splits_raw[q-1] (ordered keys)
 // ---------------------------------------------------------------------------
@@ -696,7 +755,9 @@ __device__ void stage_query(const CP& p, Smem& s, long long n) {
 // ---------------------------------------------------------------------------
 // S3 prelude: unique splits, zero bucket, group edges (every block, in shared memory)
 // ---------------------------------------------------------------------------
-__device__ void load_quantizer(const CP& p, Smem& s) {
+// minmax_ready = false: the minimum and maximum of the values are not known yet (sample form before the
+// count stage has run); the zero bucket does not need them (see below), refresh_minmax sets them later.
+__device__ void load_quantizer(const CP& p, Smem& s, bool minmax_ready = true) {
     const bool given = p.given_splits != nullptr;
     const int nraw = given ? p.n_given : p.q - 1;
     __shared__ int s_base;
@@ -727,21 +788,35 @@ __device__ void load_quantizer(const CP& p, Smem& s) {
         if (given) {
             q.minv = p.given_min;
             q.maxv = p.given_max;
-        } else {
+        } else if (minmax_ready) {
             q.minv = ord2f(~__ldcg(p.ctrl + 4));
             q.maxv = ord2f(__ldcg(p.ctrl + 5));
+        } else {
+            q.minv = q.maxv = 0.f;
         }
         // NaN or infinite gradient values cannot be bucketized (the reference's sketch throws on NaN)
         if (!isfinite(q.minv) || !isfinite(q.maxv)) skml_set_status(p.status, SKML_BAD_INPUT, 0x35u);
+        // With splits taken from the data, min > 0 means every split is positive and max < 0 that every split
+        // is negative, so the search below gives the first two cases' answers too; they stay for given splits.
         int z;
-        if (q.minv > 0.f) z = 0;
-        else if (q.maxv < 0.f) z = q.bin_num - 1;
+        if ((given || minmax_ready) && q.minv > 0.f) z = 0;
+        else if ((given || minmax_ready) && q.maxv < 0.f) z = q.bin_num - 1;
         else {
             z = 0;
             while (z < q.bin_num - 1 && s.splits[z] < 0.f) ++z;
         }
         q.zero_idx = z;
         skml_group_edges(z, q.bin_num, p.G, q.edges);
+    }
+    __syncthreads();
+}
+
+// Sample form, after the count stage and its grid barrier: minimum and maximum of all values.
+__device__ void refresh_minmax(const CP& p, Smem& s) {
+    if (threadIdx.x == 0) {
+        s.qi.minv = ord2f(~__ldcg(p.ctrl + 4));
+        s.qi.maxv = ord2f(__ldcg(p.ctrl + 5));
+        if (!isfinite(s.qi.minv) || !isfinite(s.qi.maxv)) skml_set_status(p.status, SKML_BAD_INPUT, 0x35u);
     }
     __syncthreads();
 }
@@ -771,8 +846,9 @@ __device__ __forceinline__ void build_group_lut(const CP& p, Smem& s) {
 }
 
 // S3: bucket of every value; keys of every group in every warp slice.
-__device__ void stage_count(const CP& p, Smem& s, long long n) {
+__device__ void stage_count(const CP& p, Smem& s, long long n, bool track_minmax) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned int kmin = 0xFFFFFFFFu, kmax = 0u;
     build_group_lut(p, s);
     const long long sub = vslice_size(n);
     const long long vb = (long long)blockIdx.x * SKML_WARPS + warp;
@@ -791,6 +867,9 @@ __device__ void stage_count(const CP& p, Smem& s, long long n) {
             const int bin = upper_bound_f(s.splits, s.qi.nsplits, val);
             p.bins[i] = (unsigned short)bin;
             g = s.grp_lut[bin];
+            const unsigned int k = f2ord(val);
+            kmin = min(kmin, k);
+            kmax = max(kmax, k);
         }
         const unsigned int peers = __match_any_sync(0xFFFFFFFFu, g);
         if (valid && (peers & lanemask_lt()) == 0) s.wcnt[warp][g] += (unsigned int)__popc(peers);  // one leader per group
@@ -801,6 +880,32 @@ __device__ void stage_count(const CP& p, Smem& s, long long n) {
     if (warp < p.G) {  // the block's totals: warp g adds up group g over the 32 slices
         const unsigned int tot = warp_sum(s.wcnt[lane][warp]);
         if (lane == 0) p.blk_cnt[(long long)blockIdx.x * SKML_MAX_GROUPS + warp] = tot;
+    }
+    if (track_minmax) {   // sample form: the extremes of all values (one pair of atomics per block)
+        __shared__ unsigned int c_mn[SKML_WARPS], c_mx[SKML_WARPS];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            kmin = min(kmin, __shfl_xor_sync(0xFFFFFFFFu, kmin, o));
+            kmax = max(kmax, __shfl_xor_sync(0xFFFFFFFFu, kmax, o));
+        }
+        if (lane == 0) {
+            c_mn[warp] = kmin;
+            c_mx[warp] = kmax;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            kmin = c_mn[lane];
+            kmax = c_mx[lane];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                kmin = min(kmin, __shfl_xor_sync(0xFFFFFFFFu, kmin, o));
+                kmax = max(kmax, __shfl_xor_sync(0xFFFFFFFFu, kmax, o));
+            }
+            if (lane == 0 && kmin <= kmax) {
+                atomicMax(&p.ctrl[4], ~kmin);
+                atomicMax(&p.ctrl[5], kmax);
+            }
+        }
     }
 }
 
@@ -2218,26 +2323,37 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_sparse_kernel(CP p, in
     }
     const bool given = p.given_splits != nullptr;
     if (FUSED) stage_stamp(p.ctrl, 0);
+    // sample form of the split search: S1 ends with the splits in every block, S2 and two grid barriers drop out
+    const bool sample = p.sample_splits != 0 && !given;
     if (FUSED || stage == 1) {
         stage_prepare(p, n);
         stage_stamp(p.ctrl, 8);
-        if (!given) stage_summary(p, s, p.vals, n);
+        if (sample) stage_sample_splits(p, s, p.vals, n);
+        else if (!given) stage_summary(p, s, p.vals, n);
         stage_stamp(p.ctrl, 9);
     }
-    STAGE_BARRIER(1)
-    if ((FUSED || stage == 2) && !given) stage_query(p, s, n);
-    STAGE_BARRIER(2)
+    if (sample) {
+        if (FUSED) {
+            stage_stamp(p.ctrl, 1);
+            stage_stamp(p.ctrl, 2);
+        }
+    } else {
+        STAGE_BARRIER(1)
+        if ((FUSED || stage == 2) && !given) stage_query(p, s, n);
+        STAGE_BARRIER(2)
+    }
     if (FUSED || stage == 3) {
-        load_quantizer(p, s);
+        load_quantizer(p, s, !sample);
         if (s.qi.bin_num > SKML_GPU_MAX_BINS) {
             if (threadIdx.x == 0) skml_set_status(p.status, SKML_BAD_INPUT, 0x32u);
             return;
         }
-        stage_count(p, s, n);
+        stage_count(p, s, n, sample);
     }
     STAGE_BARRIER(3)
     if (FUSED || stage == 4) {
         if (!FUSED) load_quantizer(p, s);
+        else if (sample) refresh_minmax(p, s);
         layout_from_counts(p, s);
         stage_scatter(p, s, n);
     }
@@ -2444,6 +2560,7 @@ static int fill_params(const SkmlCompressArgs* a, CP& p, int& grid) {
     p.key_hist = reinterpret_cast<unsigned int*>(ws + L.key_hist);
     p.key_encoder = (int)a->key_encoder;
     p.huffman = a->cell_bits == 0 ? 1 : 0;
+    p.sample_splits = a->quantile_summary == 1 ? 0 : 1;
     p.cell_hist = reinterpret_cast<unsigned int*>(ws + L.cell_hist);
     p.blk_tbits = reinterpret_cast<unsigned long long*>(ws + L.blk_tbits);
     p.tchunk_off = reinterpret_cast<unsigned int*>(ws + L.tchunk_off);

@@ -118,7 +118,8 @@ class GpuEngine:
             self.comp = GpuCompressor(dim, bound, conf.quant_bin_num, conf.sketch_group_num, conf.sketch_row_num,
                                       conf.sketch_col_ratio, conf.seed, self.device, grid=xsms,
                                       fused=bool(conf.extras.get("fused", True)), budget_s=conf.step_timeout_s,
-                                      key_encoder=conf.key_encoder, cell_bits=0 if conf.cell_bits == 0 else -1)
+                                      key_encoder=conf.key_encoder, cell_bits=0 if conf.cell_bits == 0 else -1,
+                                      quantile_summary=str(conf.extras.get("quantile_summary", "sample")))
             self.dec = GpuDecoder(dim, bound * comm.world, self.device, fused=bool(conf.extras.get("fused", True)), grid=3 * xsms,
                                   budget_s=conf.step_timeout_s, max_groups=conf.sketch_group_num,
                                   table_capacity=self._table_scratch_bytes(conf, bound, comm.world))

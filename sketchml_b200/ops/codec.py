@@ -47,7 +47,8 @@ class GpuCompressor:
 
     def __init__(self, dim: int, n_max: int, bin_num: int = 256, group_num: int = 8, row_num: int = 2,
                  col_ratio: float = 0.3, seed: int = 0, device="cuda", fused: bool = True, grid: int = 0,
-                 budget_s: float = 1.0, key_encoder: str = "delta_binary", cell_bits: int = -1):
+                 budget_s: float = 1.0, key_encoder: str = "delta_binary", cell_bits: int = -1,
+                 quantile_summary: str = "sample"):
         if bin_num > L.GPU_MAX_BINS:
             raise ValueError(f"the GPU compressor supports at most {L.GPU_MAX_BINS} buckets")
         self.lib = L.lib()
@@ -60,6 +61,10 @@ class GpuCompressor:
         if cell_bits not in (-1, 0, 8, 16):
             raise ValueError("cell_bits: -1 (8/16-bit codes by bucket count) or 0 (Huffman-coded tables)")
         self.cell_bits = 0 if cell_bits == 0 else -1
+        if quantile_summary not in ("sample", "sketch"):
+            raise ValueError("quantile_summary: 'sample' (split points from a shared 4096-value sample) or 'sketch' "
+                             "(mergeable k = 128 summaries)")
+        self.quantile_summary = 1 if quantile_summary == "sketch" else 0
         self.device = torch.device(device)
         ws_n = max(self.n_max, 1)
         self.ws_bytes = int(self.lib.skml_compress_workspace_bytes(ws_n, bin_num, group_num, row_num, self.col_ratio, 0))
@@ -92,6 +97,7 @@ class GpuCompressor:
             splits, mn, mx = given
             a.given_splits, a.n_given, a.given_min, a.given_max = L.ptr(splits), splits.numel(), float(mn), float(mx)
         a.fused, a.grid, a.key_encoder, a.cell_bits = int(self.fused), self.grid, self.key_encoder, self.cell_bits
+        a.quantile_summary = self.quantile_summary
         return a
 
     def make_args(self, *a, **k) -> L.CompressArgs:

@@ -35,7 +35,7 @@ class CompressArgs(C.Structure):
         ("payload", c_vp), ("slot_capacity", c_ll), ("peer_payload", c_vp * MAX_PEERS),
         ("peer_flag", c_vp * MAX_PEERS), ("workspace", c_vp), ("workspace_bytes", c_ll), ("status", c_vp),
         ("budget_cycles", c_ll), ("given_splits", c_vp), ("n_given", c_ll), ("given_min", c_d),
-        ("given_max", c_d), ("fused", c_ll), ("grid", c_ll), ("key_encoder", c_ll), ("cell_bits", c_ll),
+        ("given_max", c_d), ("fused", c_ll), ("grid", c_ll), ("key_encoder", c_ll), ("cell_bits", c_ll), ("quantile_summary", c_ll),
     ]
 
 
