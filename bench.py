@@ -374,6 +374,7 @@ def main():
             "segments": {"count": len(seg), "steps_each": args.steps, "ms_min": min(seg), "ms_median": statistics.median(seg),
                          "ms_max": max(seg)},
             "clocks": res["clocks"], "gpu_launches": res["launches"],
+            "compress_cluster_blocks": int(__import__("sketchml_b200.ops.lib", fromlist=["lib"]).lib().skml_compress_cluster_size()),
             "index_build_s": index_s, "index_bytes": index_bytes, **extra,
             "baselines": baselines,
             "payload": {"nnz_per_rank": nnz, "bytes_per_rank": pbytes,

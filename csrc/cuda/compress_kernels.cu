@@ -2589,6 +2589,8 @@ extern "C" long long skml_compress_splits_offset(long long n_max, long long bin_
 
 // Function attributes and the co-residency limit are looked up once per kernel (one process
 // drives one GPU), so a steady-state launch makes a single runtime call.
+static int g_last_cluster = 0;   // blocks per cluster of the most recent compress launch (0: none yet)
+
 struct LaunchCache {
     bool ready = false;
     int max_grid = 0;
@@ -2667,17 +2669,23 @@ static int launch_stages(K fused_kernel, K staged_kernel, LaunchCache& cache, CP
         if (e != cudaSuccess && cluster > 1) {
             // the device refuses cooperative clusters of this shape: plain blocks from now on
             cudaGetLastError();
-            cache.cluster = 1;
+            cache.cluster = cluster = 1;
             e = launch_ex(fused_kernel, grid, 1, true, p, -1, stream);
         }
+        g_last_cluster = cluster;
         return (int)e;
     }
+    g_last_cluster = cluster;
     for (int st = 1; st <= nstages; ++st) {
         e = launch_ex(staged_kernel, grid, st == 1 ? cluster : 1, false, p, st, stream);
         if (e != cudaSuccess) return (int)e;
     }
     return 0;
 }
+
+// Blocks per thread-block cluster of the most recent compress launch of this process (2 where the device
+// takes the whole grid as cooperative clusters of two, 1 for plain blocks, 0 before the first launch).
+extern "C" int skml_compress_cluster_size() { return g_last_cluster; }
 
 extern "C" int skml_compress_sparse(const SkmlCompressArgs* a, void* stream) {
     CP p;

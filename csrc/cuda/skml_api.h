@@ -51,6 +51,8 @@ long long skml_payload_capacity(long long n_max, long long dim, long long bin_nu
 long long skml_compress_splits_offset(long long n_max, long long bin_num, long long group_num, long long row_num,
                                       double col_ratio, long long grid);
 int skml_compress_sparse(const SkmlCompressArgs* args, void* stream);
+// Blocks per thread-block cluster of this process's most recent compress launch (2, 1, or 0 before the first).
+int skml_compress_cluster_size();
 int skml_compress_dense(const SkmlCompressArgs* args, void* stream);
 
 // Arguments of the fused decode + aggregate + update kernel.

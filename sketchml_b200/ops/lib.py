@@ -73,6 +73,7 @@ _SIGS = {
     "skml_payload_capacity": (c_ll, [c_ll, c_ll, c_ll, c_ll, c_ll, c_d]),
     "skml_compress_splits_offset": (c_ll, [c_ll, c_ll, c_ll, c_ll, c_d, c_ll]),
     "skml_compress_sparse": (c_int, [C.POINTER(CompressArgs), c_vp]),
+    "skml_compress_cluster_size": (c_int, []),
     "skml_compress_dense": (c_int, [C.POINTER(CompressArgs), c_vp]),
     "skml_decode_workspace_bytes": (c_ll, [c_ll, c_ll]),
     "skml_decode_update": (c_int, [C.POINTER(DecodeArgs), c_vp]),
