@@ -2457,12 +2457,20 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_dense_kernel(CP p, int
     if (p.meta[1] != SKML_KIND_DENSE) return;
     const long long n = p.dim;
     const bool given = p.given_splits != nullptr;
-    if ((FUSED || stage == 1) && !given) stage_summary(p, s, p.vals, n);
-    STAGE_BARRIER(1)
-    if ((FUSED || stage == 2) && !given) stage_query(p, s, n);
-    STAGE_BARRIER(2)
+    // sample form: the splits are in every block after S1; the extremes of the values (needed for the bucket
+    // values in the header only) are collected by the code pass, and the header is written after it
+    const bool sample = p.sample_splits != 0 && !given;
+    if (FUSED || stage == 1) {
+        if (sample) stage_sample_splits(p, s, p.vals, n);
+        else if (!given) stage_summary(p, s, p.vals, n);
+    }
+    if (!sample) {
+        STAGE_BARRIER(1)
+        if ((FUSED || stage == 2) && !given) stage_query(p, s, n);
+        STAGE_BARRIER(2)
+    }
     if (FUSED || stage == 3) {
-        load_quantizer(p, s);
+        load_quantizer(p, s, !sample);
         if (s.qi.bin_num > SKML_GPU_MAX_BINS) {
             if (threadIdx.x == 0) skml_set_status(p.status, SKML_BAD_INPUT, 0x33u);
             return;
@@ -2476,7 +2484,8 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_dense_kernel(CP p, int
             if (threadIdx.x == 0) skml_set_status(p.status, SKML_CAPACITY, 0x34u);
             return;
         }
-        write_header(p, s, n, SKML_KIND_DENSE);
+        if (!sample) write_header(p, s, n, SKML_KIND_DENSE);
+        unsigned int kmin = 0xFFFFFFFFu, kmax = 0u;
         const long long units = (n + per - 1) / per;
         const long long gsz = (long long)gridDim.x * blockDim.x, gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
         for (long long u = gid; u < units; u += gsz) {
@@ -2484,7 +2493,13 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_dense_kernel(CP p, int
             for (int t = 0; t < per; ++t) {
                 long long i = u * per + t;
                 unsigned int code = 0;
-                if (i < n) code = (unsigned int)upper_bound_f(s.splits, s.qi.nsplits, p.vals[i]);
+                if (i < n) {
+                    const float val = p.vals[i];
+                    code = (unsigned int)upper_bound_f(s.splits, s.qi.nsplits, val);
+                    const unsigned int k = f2ord(val);
+                    kmin = min(kmin, k);
+                    kmax = max(kmax, k);
+                }
                 if (cb == 8) words[t >> 2] |= (code & 0xFFu) << (8 * (t & 3));
                 else words[t >> 1] |= (code & 0xFFFFu) << (16 * (t & 1));
             }
@@ -2493,9 +2508,31 @@ __global__ void __launch_bounds__(SKML_BLOCK, 1) compress_dense_kernel(CP p, int
             for (unsigned int r = 0; r < p.world; ++r)
                 if (r != p.rank && p.peer_payload[r]) st_v4(reinterpret_cast<uint4*>(p.peer_payload[r] + off_codes) + u, v);
         }
+        if (sample) {   // one pair of atomics per warp
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                kmin = min(kmin, __shfl_xor_sync(0xFFFFFFFFu, kmin, o));
+                kmax = max(kmax, __shfl_xor_sync(0xFFFFFFFFu, kmax, o));
+            }
+            if ((threadIdx.x & 31) == 0 && kmin <= kmax) {
+                atomicMax(&p.ctrl[4], ~kmin);
+                atomicMax(&p.ctrl[5], kmax);
+            }
+        }
     }
     STAGE_BARRIER(3)
-    if (FUSED || stage == 4) finish_publish(p);
+    if (FUSED || stage == 4) {
+        if (sample) {
+            if (!FUSED) load_quantizer(p, s);   // staged launches: the extremes are complete now
+            else refresh_minmax(p, s);
+            if (!FUSED) {
+                if (threadIdx.x == 0) s.lay.overflow = 0;
+                __syncthreads();
+            }
+            write_header(p, s, n, SKML_KIND_DENSE);
+        }
+        finish_publish(p);
+    }
 }
 
 // ---------------------------------------------------------------------------

@@ -39,9 +39,9 @@ typedef struct SkmlCompressArgs {
     long long grid;                // 0 = one block per SM
     long long key_encoder;         // 0 = delta_binary (byte-aligned deltas), 1 = delta_adaptive (the reference's live encoder)
     long long cell_bits;           // sketch tables on the wire: -1 = 8/16-bit bucket codes, 0 = Huffman-coded (the reference's form)
-    long long quantile_summary;    // sparse kind: 0 = split points from a 4096-value sample that every thread-block cluster
+    long long quantile_summary;    // 0 = split points from a 4096-value sample that every thread-block cluster
                                    // draws alike (no grid barrier, no query stage), 1 = mergeable k = 128 sketch per block,
-                                   // merged per cluster and queried over all runs. The dense kind always takes the sketch.
+                                   // merged per cluster and queried over all runs.
 } SkmlCompressArgs;
 
 long long skml_compress_workspace_bytes(long long n_max, long long bin_num, long long group_num, long long row_num,
