@@ -959,7 +959,8 @@ colsum_kernel(const int* __restrict__ colptr, const int* __restrict__ rowidx, co
         const int t = b * 256 + threadIdx.x;
         if (t < n_short) {
             const int i = bins[t];
-            out[i] = colsum_range(rowidx, svals, coef, colptr[i], colptr[i + 1], 0, 1) + lambda * w[ucols[i]];
+            const float wv = __ldg(w + ucols[i]);   // issued first: this DRAM gather overlaps the coefficient chain
+            out[i] = colsum_range(rowidx, svals, coef, colptr[i], colptr[i + 1], 0, 1) + lambda * wv;
         }
         return;
     }
@@ -968,9 +969,10 @@ colsum_kernel(const int* __restrict__ colptr, const int* __restrict__ rowidx, co
         const int t = b * 8 + warp;
         if (t < n_medium) {
             const int i = bins[n_short + t];
+            const float wv = lane == 0 ? __ldg(w + ucols[i]) : 0.f;
             float v = colsum_range(rowidx, svals, coef, colptr[i], colptr[i + 1], lane, 32);
             v = warp_sum(v);
-            if (lane == 0) out[i] = v + lambda * w[ucols[i]];
+            if (lane == 0) out[i] = v + lambda * wv;
         }
         return;
     }
