@@ -141,61 +141,101 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
         }
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
+    // The work table: the non-empty (rank, group) lists moved to the front in (rank, group) order, each
+    // with the number of chunks and keys in front of it. Warp 0 does it 32 slots at a time (ballot for the
+    // positions, shuffle scans for the prefixes); thread 0 first looks at the per-rank header facts.
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
         int ni = 0, nhuf = 0;
         unsigned long long chunks = 0, keys = 0, tab_used = 0;
         int dense = 0, ref = 0;
         unsigned int ref_n = 0;
         double mx = 0.0;
-        for (int r = 0; r < p.world; ++r) {
-            const SkmlHeader& h = full[r];
-            s.rank_chunk_begin[r] = chunks;
-            s.rank_key_begin[r] = keys;
-            s.rank_item_begin[r] = ni;
-            if (h.kind == SKML_KIND_EMPTY) continue;
-            mx = fmax(mx, fmax(fabs(h.min_value), fabs(h.max_value)));
-            if (h.kind == SKML_KIND_DENSE) {
-                dense = 1;
-                continue;
-            }
-            if ((int)h.group_num > gcap) {
-                skml_set_status(p.status, SKML_BAD_HEADER, 0x300u | (unsigned int)r);
-                s.ok = 0;
-                break;
-            }
-            for (unsigned int g = 0; g < h.group_num; ++g) {
-                const int src = r * gcap + (int)g;
-                if (s.items[src].e.n == 0) continue;
-                if (s.items[src].chunk_prefix) {
-                    skml_set_status(p.status, SKML_BAD_HEADER, 0x100u | (unsigned int)r);
+        if (lane == 0) {
+            for (int r = 0; r < p.world; ++r) {
+                const SkmlHeader& h = full[r];
+                if (h.kind == SKML_KIND_EMPTY) continue;
+                mx = fmax(mx, fmax(fabs(h.min_value), fabs(h.max_value)));
+                if (h.kind == SKML_KIND_DENSE) dense = 1;
+                else if ((int)h.group_num > gcap) {
+                    skml_set_status(p.status, SKML_BAD_HEADER, 0x300u | (unsigned int)r);
                     s.ok = 0;
-                    break;
                 }
-                if (ni != src) s.items[ni] = s.items[src];  // ni <= src: compaction moves entries forward only
-                DecItem& it = s.items[ni];
-                it.chunk_prefix = chunks;
-                it.key_prefix = keys;
-                if (it.huffman) {
-                    const unsigned long long bytes = skml_align16((unsigned long long)it.rows * it.e.col_num * (it.cell_bits / 8));
-                    if (tab_used + bytes > (unsigned long long)p.tab_capacity) {
-                        skml_set_status(p.status, SKML_CAPACITY, 0x41u);
-                        s.ok = 0;
-                        break;
-                    }
-                    it.tab = p.tab_scratch + tab_used;
-                    tab_used += bytes;
-                    ++nhuf;
-                }
-                const unsigned int n_it = it.e.n;
-                chunks += (n_it + SKML_RESTART_INTERVAL - 1) / SKML_RESTART_INTERVAL;
-                keys += n_it;
-                if (n_it > ref_n) {   // the longest list (the first of equals) gives the apply its range bounds
-                    ref_n = n_it;
-                    ref = ni;
-                }
-                ++ni;
             }
-            if (!s.ok) break;
+        }
+        const int nslots = p.world * gcap;
+        for (int base = 0; base < nslots; base += 32) {
+            const int t = base + lane;
+            const bool in = t < nslots;
+            const int r = in ? t / gcap : 0, g = in ? t % gcap : 0;
+            const bool v = in && s.items[t].e.n != 0;
+            DecItem it;
+            if (v) it = s.items[t];
+            const unsigned int n = v ? it.e.n : 0u;
+            const bool failed = v && it.chunk_prefix != 0ull;
+            const bool huf = v && it.huffman != 0u;
+            unsigned long long c_inc = (n + SKML_RESTART_INTERVAL - 1) / SKML_RESTART_INTERVAL, k_inc = n;
+            unsigned long long b_inc = huf ? skml_align16((unsigned long long)it.rows * it.e.col_num * (it.cell_bits / 8)) : 0ull;
+            const unsigned long long c_own = c_inc, k_own = k_inc, b_own = b_inc;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long c2 = __shfl_up_sync(0xFFFFFFFFu, c_inc, o), k2 = __shfl_up_sync(0xFFFFFFFFu, k_inc, o),
+                                         b2 = __shfl_up_sync(0xFFFFFFFFu, b_inc, o);
+                if (lane >= o) {
+                    c_inc += c2;
+                    k_inc += k2;
+                    b_inc += b2;
+                }
+            }
+            const unsigned int vm = __ballot_sync(0xFFFFFFFFu, v);
+            const int pos = ni + __popc(vm & ((1u << lane) - 1u));
+            if (in && g == 0) {   // what lies in front of rank r's first slot
+                s.rank_chunk_begin[r] = chunks + c_inc - c_own;
+                s.rank_key_begin[r] = keys + k_inc - k_own;
+                s.rank_item_begin[r] = pos;
+            }
+            __syncwarp();   // every lane holds its entry in registers: entries may now move forward
+            if (v) {
+                it.chunk_prefix = chunks + c_inc - c_own;
+                it.key_prefix = keys + k_inc - k_own;
+                if (huf) it.tab = p.tab_scratch + tab_used + b_inc - b_own;
+                s.items[pos] = it;
+            }
+            const unsigned int fm = __ballot_sync(0xFFFFFFFFu, failed);
+            if (fm) {
+                const int r_bad = __shfl_sync(0xFFFFFFFFu, r, __ffs(fm) - 1);
+                if (lane == 0) {
+                    skml_set_status(p.status, SKML_BAD_HEADER, 0x100u | (unsigned int)r_bad);
+                    s.ok = 0;
+                }
+            }
+            // the longest list (the first of equals) gives the apply its range bounds
+            unsigned int best_n = n;
+            int best_pos = v ? pos : 0x7FFFFFFF;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const unsigned int on = __shfl_xor_sync(0xFFFFFFFFu, best_n, o);
+                const int op = __shfl_xor_sync(0xFFFFFFFFu, best_pos, o);
+                if (on > best_n || (on == best_n && op < best_pos)) {
+                    best_n = on;
+                    best_pos = op;
+                }
+            }
+            if (best_n > ref_n) {
+                ref_n = best_n;
+                ref = best_pos;
+            }
+            chunks += __shfl_sync(0xFFFFFFFFu, c_inc, 31);
+            keys += __shfl_sync(0xFFFFFFFFu, k_inc, 31);
+            tab_used += __shfl_sync(0xFFFFFFFFu, b_inc, 31);
+            ni += __popc(vm);
+            nhuf += __popc(__ballot_sync(0xFFFFFFFFu, huf));
+            __syncwarp();
+        }
+      if (lane == 0) {
+        if (tab_used > (unsigned long long)p.tab_capacity) {
+            skml_set_status(p.status, SKML_CAPACITY, 0x41u);
+            s.ok = 0;
         }
         if (keys > (unsigned long long)p.key_capacity) {
             skml_set_status(p.status, SKML_CAPACITY, 0x40u);
@@ -225,6 +265,7 @@ __device__ bool decode_prepare(const DP& p, DecSmem& s) {
         if (mx > 0.0 && isfinite(mx)) frexp(mx, &e);
         s.shift = 60 - e;
         s.inv_world = 1.0 / (double)p.world;
+      }
     }
     __syncthreads();
     return s.ok != 0;
