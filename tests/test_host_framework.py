@@ -320,3 +320,66 @@ def test_trainer_reports_auc_when_asked():
     t.train()
     v = t.validate(99)
     assert 0.5 < v["auc"] <= 1.0
+
+
+def test_batch_index_builders_describe_the_same_column_sums(monkeypatch):
+    """Both forms of the prepared batch index (per-column lists; row tiles with (tile, column) pairs and
+    16-bit local rows) are built with plain tensor ops, so their structure is checked here without a GPU:
+    walking either one reproduces the column sums of the batch."""
+    import types
+    import numpy as np
+    from sketchml_b200.ops import transposed as T
+    rng = np.random.default_rng(4)
+    rows, dim, lo, hi = 900, 400, 100, 800
+    counts = rng.integers(1, 12, rows)
+    rowptr = np.concatenate([[0], np.cumsum(counts)])
+    cols = np.concatenate([np.sort(rng.choice(dim, c, replace=False)) for c in counts]).astype(np.int32)
+    cols[rowptr[lo]:rowptr[lo] + 1] = 0
+    vals = rng.normal(size=len(cols)).astype(np.float32)
+    csr = types.SimpleNamespace(rowptr=torch.from_numpy(rowptr), cols=torch.from_numpy(cols), values=torch.from_numpy(vals))
+    coef = rng.normal(size=hi - lo)
+    e0, e1 = rowptr[lo], rowptr[hi]
+    want = np.zeros(dim)
+    r_of = np.repeat(np.arange(rows), counts)[e0:e1] - lo
+    np.add.at(want, cols[e0:e1], coef[r_of] * vals[e0:e1])
+    plain = T.build_batch_index(csr, lo, hi)
+    got = np.zeros(dim)
+    cp, ri, sv, uc = plain.colptr.numpy(), plain.rowidx.numpy(), plain.svals.numpy(), plain.ucols.numpy()
+    for i, c in enumerate(uc):
+        got[c] = np.sum(coef[ri[cp[i]:cp[i + 1]]] * sv[cp[i]:cp[i + 1]])
+    assert np.allclose(got, want) and np.all(np.diff(uc) > 0)
+    assert plain.n_short + plain.n_medium + len(np.unique(plain.long_col.numpy())) == plain.n_cols
+    monkeypatch.setattr(T, "TILE_ROWS_MAX", 96)
+    monkeypatch.setattr(T, "PAIR_SEGMENT", 4)
+    tiled = T.build_batch_index(csr, lo, hi, tiled=True)
+    tp = tiled.tiled
+    assert tp.n_tiles == -(-(hi - lo) // 96) and tp.tile_rows % 4 == 0 and tp.n_tiles * tp.tile_rows >= hi - lo
+    assert np.array_equal(tiled.ucols.numpy(), uc)
+    pair_ptr, lrow = tp.pair_ptr.numpy(), tp.lrow.numpy().astype(np.int64) & 0xFFFF
+    tptr, dst, cptr = tp.tile_pair_ptr.numpy(), tp.pair_dst.numpy(), tp.col_pair_ptr.numpy()
+    assert np.all(np.diff(pair_ptr) >= 1) and np.all(np.diff(pair_ptr) <= 4) and pair_ptr[-1] == e1 - e0
+    assert sorted(dst.tolist()) == list(range(tp.n_pairs)) and cptr[-1] == tp.n_pairs
+    partial = np.zeros(tp.n_pairs)
+    tv = tiled.svals.numpy()
+    for t in range(tp.n_tiles):
+        for p in range(tptr[t], tptr[t + 1]):
+            e = slice(pair_ptr[p], pair_ptr[p + 1])
+            assert np.all(lrow[e] < min(tp.tile_rows, hi - lo - t * tp.tile_rows))
+            partial[dst[p]] = np.sum(coef[t * tp.tile_rows + lrow[e]] * tv[e])
+    got2 = np.zeros(dim)
+    for i, c in enumerate(tiled.ucols.numpy()):
+        got2[c] = partial[cptr[i]:cptr[i + 1]].sum()
+    assert np.allclose(got2, want)
+
+
+def test_adam_moment_layouts_are_checked():
+    from sketchml_b200.ops.glm import moment_stride
+    quad = torch.zeros((10, 4))
+    assert moment_stride(None, None) == 1
+    assert moment_stride(torch.zeros(10), torch.zeros(10)) == 1
+    assert moment_stride(quad[:, 0], quad[:, 1]) == 4
+    with pytest.raises(ValueError):
+        moment_stride(quad[:, 0], quad[:, 2])
+    with pytest.raises(ValueError):
+        moment_stride(torch.zeros(10), quad[:, 1])
+
